@@ -1,0 +1,273 @@
+/* C restatement of the reference engine's MoE expert arithmetic.  TEST INFRASTRUCTURE ONLY:
+ * it is the checker for large parity cases and the timed CPU baseline; the shipped library
+ * never links or calls it.
+ *
+ * Decode formulas follow the reference kernels:
+ *   Q4_K / Q6_K      kogarashi kernels/native.cu:26-40, 52-82
+ *   NVFP4 linear     tsumuji kernels/include/decode.cuh:148-173, decode/gemv.cu:97-107,149-157
+ *   NVFP4 tiled      hayate cu/glm53/math.cuh:41-49, dense.cuh:26-37,61-73
+ *   block FP8        hayate cu/glm53/math.cuh:17-22,40, dense.cuh:38-41
+ * The work split (rows of all selected experts concatenated, claimed in chunks by a pool of
+ * threads; one dispatch for gate/up/SwiGLU and one for down) follows the reference CPU expert
+ * path, hayate crates/kernels/src/cpu/glm53.rs:760-967 and crates/models/src/glm53/
+ * cpu_experts.rs:142-393.  The reference has no CPU kernel for Q4_K / Q6_K or for the linear
+ * NVFP4 layout; for those formats this is a restatement of the GPU decode formulas.
+ * Parity of this file: pinned through tests/test_oracle_golden.py against oracle/formats.py,
+ * which in turn is pinned on the reference's known-answer vectors.
+ */
+#include <math.h>
+#include <omp.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+enum { FMT_F32 = 0, FMT_F16 = 1, FMT_Q4K = 12, FMT_Q6K = 14, FMT_BF16 = 30,
+       FMT_NVFP4_LINEAR = 100, FMT_NVFP4_TILED = 101, FMT_FP8_BLOCK = 102 };
+
+static float fp8_table[256];
+static int tables_ready = 0;
+static const float e2m1_table[16] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f,
+                                     -0.f, -.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f};
+
+static void init_tables(void) {
+  if (tables_ready) return;
+  for (int b = 0; b < 256; ++b) {
+    int e = (b >> 3) & 15, m = b & 7;
+    float v = (e == 15 && m == 7) ? NAN : e ? ldexpf(1.f + m / 8.f, e - 7) : ldexpf((float)m, -9);
+    fp8_table[b] = (b & 128) ? -v : v;
+  }
+  tables_ready = 1;
+}
+
+static inline float half_to_float(uint16_t h) {
+  uint32_t s = (uint32_t)(h >> 15) << 31, e = (h >> 10) & 31, m = h & 1023, u;
+  if (e == 0) {
+    if (!m) u = s;
+    else { int sh = 0; while (!(m & 1024)) { m <<= 1; ++sh; } u = s | ((uint32_t)(113 - sh) << 23) | ((m & 1023) << 13); }
+  } else if (e == 31) u = s | 0x7f800000u | (m << 13);
+  else u = s | ((e + 112) << 23) | (m << 13);
+  float f; memcpy(&f, &u, 4); return f;
+}
+static inline float bf16_to_float(uint16_t b) { uint32_t u = (uint32_t)b << 16; float f; memcpy(&f, &u, 4); return f; }
+static inline float bf16_round(float x) {
+  uint32_t u; memcpy(&u, &x, 4); u = (u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u; memcpy(&x, &u, 4); return x;
+}
+
+/* One matrix [n rows, k cols].  `w` is the payload, `aux` the scale area where the format keeps
+ * it apart (linear NVFP4: e4m3 [n][k/16]; block FP8: float [ceil(n/128)][ceil(k/128)]);
+ * `gscale` multiplies the row sum (linear NVFP4 global scale), `rounded` rounds each decoded
+ * weight to bf16 (Hayate FP8 / shared-expert path). */
+typedef struct { int fmt; const uint8_t* w; const uint8_t* aux; float gscale; int n, k; int rounded; } Mat;
+
+static void decode_row(const Mat* m, int r, float* out) {
+  const int k = m->k;
+  switch (m->fmt) {
+    case FMT_F32: memcpy(out, m->w + (size_t)r * k * 4, (size_t)k * 4); break;
+    case FMT_F16: { const uint16_t* p = (const uint16_t*)m->w + (size_t)r * k; for (int i = 0; i < k; ++i) out[i] = half_to_float(p[i]); } break;
+    case FMT_BF16: { const uint16_t* p = (const uint16_t*)m->w + (size_t)r * k; for (int i = 0; i < k; ++i) out[i] = bf16_to_float(p[i]); } break;
+    case FMT_Q4K: {
+      const uint8_t* row = m->w + (size_t)r * (k / 256) * 144;
+      for (int b = 0; b < k / 256; ++b) {
+        const uint8_t* bl = row + b * 144; const uint8_t* sc = bl + 4;
+        uint16_t hd, hm; memcpy(&hd, bl, 2); memcpy(&hm, bl + 2, 2);
+        const float d = half_to_float(hd), dm = half_to_float(hm);
+        for (int g = 0; g < 8; ++g) {
+          int scale = g < 4 ? (sc[g] & 63) : ((sc[g + 4] & 15) | ((sc[g - 4] >> 6) << 4));
+          int mi = g < 4 ? (sc[g + 4] & 63) : ((sc[g + 4] >> 4) | ((sc[g] >> 6) << 4));
+          const float ds = d * (float)scale, mm = dm * (float)mi;
+          const uint8_t* q = bl + 16 + (g / 2) * 32; const int sh = (g & 1) * 4;
+          float* o = out + b * 256 + g * 32;
+          for (int l = 0; l < 32; ++l) o[l] = ds * (float)((q[l] >> sh) & 15) - mm;
+        }
+      }
+    } break;
+    case FMT_Q6K: {
+      const uint8_t* row = m->w + (size_t)r * (k / 256) * 210;
+      for (int b = 0; b < k / 256; ++b) {
+        const uint8_t* bl = row + b * 210; const int8_t* sc = (const int8_t*)(bl + 192);
+        uint16_t hd; memcpy(&hd, bl + 208, 2); const float d = half_to_float(hd);
+        for (int n = 0; n < 2; ++n) for (int g = 0; g < 4; ++g) for (int l = 0; l < 32; ++l) {
+          int q = ((bl[n * 64 + l + (g & 1) * 32] >> ((g / 2) * 4)) & 15) | (((bl[128 + n * 32 + l] >> (g * 2)) & 3) << 4);
+          out[b * 256 + n * 128 + g * 32 + l] = (d * (float)sc[n * 8 + l / 16 + g * 2]) * (float)(q - 32);
+        }
+      }
+    } break;
+    case FMT_NVFP4_LINEAR: {
+      const uint8_t* c = m->w + (size_t)r * (k / 2); const uint8_t* s = m->aux + (size_t)r * (k / 16);
+      for (int i = 0; i < k; i += 2) {
+        const float sf = fp8_table[s[i / 16]];
+        out[i] = e2m1_table[c[i / 2] & 15] * sf; out[i + 1] = e2m1_table[c[i / 2] >> 4] * sf;
+      }
+    } break;
+    case FMT_NVFP4_TILED: {
+      const int n = m->n, cols = (k / 16 + 3) / 4 * 4;
+      const uint8_t* scales = m->w + (size_t)n * k / 2;
+      float global; memcpy(&global, scales + (size_t)((n + 127) / 128 * 128) * cols, 4);
+      const uint8_t* c = m->w + (size_t)r * (k / 2);
+      for (int sc = 0; sc < k / 16; ++sc) {
+        size_t at = ((size_t)(r / 128) * (cols / 4) + sc / 4) * 512 + (r % 32) * 16 + (r % 128 / 32) * 4 + sc % 4;
+        const float mult = fp8_table[scales[at]] * global;
+        for (int i = 0; i < 16; i += 2) {
+          float a = e2m1_table[c[sc * 8 + i / 2] & 15] * mult, b = e2m1_table[c[sc * 8 + i / 2] >> 4] * mult;
+          out[sc * 16 + i] = m->rounded ? bf16_round(a) : a; out[sc * 16 + i + 1] = m->rounded ? bf16_round(b) : b;
+        }
+      }
+    } break;
+    case FMT_FP8_BLOCK: {
+      const float* s = (const float*)m->aux + (size_t)(r / 128) * ((k + 127) / 128);
+      const uint8_t* p = m->w + (size_t)r * k;
+      for (int i = 0; i < k; ++i) { float v = fp8_table[p[i]] * s[i / 128]; out[i] = m->rounded ? bf16_round(v) : v; }
+    } break;
+    default: memset(out, 0, (size_t)k * 4);
+  }
+}
+
+/* dot of a decoded row with ntok activation rows; float partial sums in 16 lanes (vectorisable)
+ * or double when f64 is set. */
+static void row_dots(const float* w, const float* x, int k, int ntok, int ldx, double* out, int f64) {
+  for (int t = 0; t < ntok; ++t) {
+    const float* xt = x + (size_t)t * ldx;
+    if (f64) { double s = 0; for (int i = 0; i < k; ++i) s += (double)w[i] * (double)xt[i]; out[t] = s; }
+    else {
+      float acc[16] = {0};
+      for (int i = 0; i < k; i += 16) for (int j = 0; j < 16; ++j) acc[j] += w[i + j] * xt[i + j];
+      float s = 0; for (int j = 0; j < 16; ++j) s += acc[j];
+      out[t] = s;
+    }
+  }
+}
+
+/* y[t][r] = gscale * sum_k W[r][k] x[t][k]; rows are split over `threads` OpenMP threads. */
+void cpu_matvec(int fmt, const void* w, const void* aux, float gscale, int rounded, int n, int k,
+                const float* x, int ntok, float* y, int f64, int threads) {
+  init_tables();
+  Mat m = {fmt, (const uint8_t*)w, (const uint8_t*)aux, gscale, n, k, rounded};
+#pragma omp parallel num_threads(threads)
+  {
+    float* buf = (float*)malloc((size_t)k * 4);
+    double dots[64];
+#pragma omp for schedule(dynamic, 64)
+    for (int r = 0; r < n; ++r) {
+      decode_row(&m, r, buf);
+      for (int t0 = 0; t0 < ntok; t0 += 64) {
+        int nt = ntok - t0 < 64 ? ntok - t0 : 64;
+        row_dots(buf, x + (size_t)t0 * k, k, nt, k, dots, f64);
+        for (int t = 0; t < nt; ++t) y[(size_t)(t0 + t) * n + r] = (float)(dots[t] * (double)gscale);
+      }
+    }
+    free(buf);
+  }
+}
+
+void cpu_decode(int fmt, const void* w, const void* aux, int rounded, int n, int k, float* out) {
+  init_tables();
+  Mat m = {fmt, (const uint8_t*)w, (const uint8_t*)aux, 1.f, n, k, rounded};
+#pragma omp parallel for
+  for (int r = 0; r < n; ++r) decode_row(&m, r, out + (size_t)r * k);
+}
+
+/* ---- Kogarashi-shaped whole layer for `tokens` tokens (softmax top-k router, GGML weights,
+ * optional shared expert with a sigmoid gate), two dispatches like the reference CPU expert
+ * path: (1) gate/up/SwiGLU rows of every (token, slot) pair and of the shared expert,
+ * (2) down rows; then the combine.  Weights of an expert are decoded once per row and applied
+ * to every token that selected it. */
+typedef struct {
+  int hidden, inter, experts, topk, tokens;
+  const float* router;                       /* [E][H] */
+  const uint8_t *gate, *up, *down;           /* ggml [k, rows, E] */
+  int gate_ty, up_ty, down_ty;
+  const uint8_t *sh_gate, *sh_up, *sh_down;  /* nullable */
+  const float* sh_inp;                       /* [H] */
+  const float* n;                            /* [T][H] */
+  float* x;                                  /* [T][H] in/out */
+  float* logits; int* ids; float* prob;      /* [T][E], [T][k], [T][k] */
+} KogarashiCpu;
+
+static size_t row_bytes(int ty, int k) { return ty == FMT_Q4K ? (size_t)k / 256 * 144 : ty == FMT_Q6K ? (size_t)k / 256 * 210 : ty == FMT_F32 ? (size_t)k * 4 : (size_t)k * 2; }
+
+void cpu_route_softmax_topk(const float* logits, int tokens, int experts, int topk, int* ids, float* prob) {
+  for (int t = 0; t < tokens; ++t) {
+    float* v = (float*)malloc((size_t)experts * 4); memcpy(v, logits + (size_t)t * experts, (size_t)experts * 4);
+    for (int s = 0; s < topk; ++s) {
+      int best = 0; for (int e = 1; e < experts; ++e) if (v[e] > v[best]) best = e;
+      ids[t * topk + s] = best; prob[t * topk + s] = v[best]; v[best] = -INFINITY;
+    }
+    float mx = prob[t * topk], z = 0;
+    for (int s = 0; s < topk; ++s) z += expf(prob[t * topk + s] - mx);
+    for (int s = 0; s < topk; ++s) prob[t * topk + s] = expf(prob[t * topk + s] - mx) / z;
+    free(v);
+  }
+}
+
+int cpu_kogarashi_layer(const KogarashiCpu* L, int threads) {
+  init_tables();
+  const int H = L->hidden, F = L->inter, E = L->experts, K = L->topk, T = L->tokens;
+  const int shared = L->sh_gate != NULL;
+  cpu_matvec(FMT_F32, L->router, NULL, 1.f, 0, E, H, L->n, T, L->logits, 0, threads);
+  cpu_route_softmax_topk(L->logits, T, E, K, L->ids, L->prob);
+  /* expert -> list of (token, slot) */
+  int* count = (int*)calloc((size_t)E + 1, sizeof(int));
+  for (int a = 0; a < T * K; ++a) ++count[L->ids[a]];
+  int* start = (int*)malloc(((size_t)E + 1) * sizeof(int)); start[0] = 0;
+  for (int e = 0; e < E; ++e) start[e + 1] = start[e] + count[e];
+  int* fill = (int*)calloc((size_t)E, sizeof(int));
+  int* assign = (int*)malloc((size_t)T * K * sizeof(int));
+  for (int a = 0; a < T * K; ++a) { int e = L->ids[a]; assign[start[e] + fill[e]++] = a; }
+  int nact = 0; int* active = (int*)malloc((size_t)E * sizeof(int));
+  for (int e = 0; e < E; ++e) if (count[e]) active[nact++] = e;
+  const int slots = K + shared;
+  float* ff = (float*)malloc((size_t)T * slots * F * 4);      /* [T][slots][F] */
+  float* dn = (float*)malloc((size_t)T * slots * H * 4);      /* [T][slots][H] */
+  const size_t grow = row_bytes(L->gate_ty, H), urow = row_bytes(L->up_ty, H), drow = row_bytes(L->down_ty, F);
+  const int groups = nact + shared;
+  /* dispatch 1: gate/up/SwiGLU */
+#pragma omp parallel num_threads(threads)
+  {
+    float* wg = (float*)malloc((size_t)H * 4); float* wu = (float*)malloc((size_t)H * 4);
+#pragma omp for schedule(dynamic, 128) collapse(2)
+    for (int gi = 0; gi < groups; ++gi) for (int r = 0; r < F; ++r) {
+      const int is_sh = gi == nact; const int e = is_sh ? 0 : active[gi];
+      Mat mg = {L->gate_ty, is_sh ? L->sh_gate : L->gate + (size_t)e * F * grow, NULL, 1.f, F, H, 0};
+      Mat mu = {L->up_ty, is_sh ? L->sh_up : L->up + (size_t)e * F * urow, NULL, 1.f, F, H, 0};
+      decode_row(&mg, r, wg); decode_row(&mu, r, wu);
+      const int cnt = is_sh ? T : count[e];
+      for (int i = 0; i < cnt; ++i) {
+        const int a = is_sh ? -1 : assign[start[e] + i]; const int t = is_sh ? i : a / K, s = is_sh ? K : a % K;
+        double g, u; row_dots(wg, L->n + (size_t)t * H, H, 1, H, &g, 0); row_dots(wu, L->n + (size_t)t * H, H, 1, H, &u, 0);
+        const float gf = (float)g; ff[((size_t)t * slots + s) * F + r] = gf * (1.f / (1.f + expf(-gf))) * (float)u;
+      }
+    }
+    free(wg); free(wu);
+  }
+  /* dispatch 2: down */
+#pragma omp parallel num_threads(threads)
+  {
+    float* wd = (float*)malloc((size_t)F * 4);
+#pragma omp for schedule(dynamic, 128) collapse(2)
+    for (int gi = 0; gi < groups; ++gi) for (int r = 0; r < H; ++r) {
+      const int is_sh = gi == nact; const int e = is_sh ? 0 : active[gi];
+      Mat md = {L->down_ty, is_sh ? L->sh_down : L->down + (size_t)e * H * drow, NULL, 1.f, H, F, 0};
+      decode_row(&md, r, wd);
+      const int cnt = is_sh ? T : count[e];
+      for (int i = 0; i < cnt; ++i) {
+        const int a = is_sh ? -1 : assign[start[e] + i]; const int t = is_sh ? i : a / K, s = is_sh ? K : a % K;
+        double v; row_dots(wd, ff + ((size_t)t * slots + s) * F, F, 1, F, &v, 0);
+        dn[((size_t)t * slots + s) * H + r] = (float)v;
+      }
+    }
+    free(wd);
+  }
+  /* combine (native.cu:113-117) */
+  for (int t = 0; t < T; ++t) {
+    float sg = 0.f;
+    if (shared) { double d; row_dots(L->sh_inp, L->n + (size_t)t * H, H, 1, H, &d, 0); sg = 1.f / (1.f + expf(-(float)d)); }
+    for (int i = 0; i < H; ++i) {
+      float v = 0; for (int s = 0; s < K; ++s) v = fmaf(L->prob[t * K + s], dn[((size_t)t * slots + s) * H + i], v);
+      L->x[(size_t)t * H + i] += v + (shared ? sg * dn[((size_t)t * slots + K) * H + i] : 0.f);
+    }
+  }
+  free(count); free(start); free(fill); free(assign); free(active); free(ff); free(dn);
+  return 0;
+}
+
+int cpu_max_threads(void) { return omp_get_max_threads(); }
