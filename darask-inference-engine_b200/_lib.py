@@ -1,0 +1,70 @@
+"""ctypes binding of libdarask_moe_b200.so. There is no fallback: a missing library is an error."""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "libdarask_moe_b200.so"
+_lib = None
+
+c_void_p, c_int, c_float, c_size_t, c_uint, c_longlong = (ctypes.c_void_p, ctypes.c_int, ctypes.c_float,
+                                                           ctypes.c_size_t, ctypes.c_uint, ctypes.c_longlong)
+
+
+class KogarashiMoe(ctypes.Structure):
+    """Mirror of `KogarashiMoe` in include/darask_moe_b200.h."""
+    _fields_ = [
+        ("hidden", c_int), ("inter", c_int), ("experts", c_int), ("topk", c_int), ("tokens", c_int),
+        ("router_w", c_void_p), ("router_ty", c_int), ("router_bias", c_void_p),
+        ("gate_w", c_void_p), ("gate_ty", c_int),
+        ("up_w", c_void_p), ("up_ty", c_int),
+        ("down_w", c_void_p), ("down_ty", c_int),
+        ("sh_gate_w", c_void_p), ("sh_up_w", c_void_p), ("sh_down_w", c_void_p), ("sh_inp_w", c_void_p),
+        ("n", c_void_p), ("x", c_void_p), ("logits", c_void_p), ("ids", c_void_p), ("prob", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+    ]
+
+
+_SIGNATURES = {
+    "darask_route_topk": (c_int, [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p,
+                                  c_void_p, c_void_p]),
+    "darask_route_topk_hayate": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p,
+                                         c_void_p]),
+    "darask_moe_permute": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p]),
+    "darask_q6k_repacked_bytes": (c_size_t, [c_longlong, c_int]),
+    "darask_q6k_repack": (c_int, [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p]),
+    "kogarashi_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "kogarashi_moe_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),
+    "kogarashi_moe_layer": (c_int, [ctypes.POINTER(KogarashiMoe), c_void_p]),
+    "kogarashi_moe_status": (c_int, [c_void_p, ctypes.POINTER(c_uint), c_void_p]),
+}
+
+
+def exported_symbols():
+    return sorted(_SIGNATURES)
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the shared library (built by build.py). Raises if it is missing."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise RuntimeError(f"{LIB_PATH} is missing: run `python {HERE / 'build.py'}` (needs nvcc). "
+                               "There is no CPU fallback for the MoE kernels.")
+        handle = ctypes.CDLL(str(LIB_PATH))
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+class CudaError(RuntimeError):
+    pass
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise CudaError(f"{what} failed with cudaError {code}")

@@ -1,0 +1,206 @@
+// Kogarashi (Qwen3.5-MoE, GGUF Q4_K / Q6_K) MoE FFN layer for 1..N tokens as four launches:
+//   router projection + top-k + dispatch permutation   (reference: `gemv` on ffn_gate_inp, `route`)
+//   gate/up products with SwiGLU                        (`gemv` x2, `activate`, also the shared expert)
+//   down products                                       (`gemv`, also the shared expert)
+//   weighted combine into the residual stream           (`combine`)
+// Reference call site: kogarashi crates/kogarashi-engine/src/engine.rs:530-632; kernels
+// kogarashi kernels/native.cu:46-117. The reference runs 12 launches per layer for one token.
+#include "../../include/darask_moe_b200.h"
+#include "route_kernels.cuh"
+#include "stream_launch.cuh"
+
+namespace dmoe {
+
+// x[t][i] += sum_s fma(p[t][s], y[t*k+s][i]) + sigmoid(sg[t]) * y[T*k+t][i]   (native.cu:113-117)
+__global__ void __launch_bounds__(256) kogarashi_combine_kernel(float* x, const float* y, const float* prob,
+                                                                const float* sg, int hidden, int topk, int tokens,
+                                                                int has_shared) {
+  pdl_wait();
+  pdl_launch();
+  const int i = blockIdx.x * 256 + threadIdx.x, t = blockIdx.y;
+  if (i >= hidden) return;
+  float v = 0.f;
+  for (int s = 0; s < topk; ++s) v = fmaf(__ldcg(prob + t * topk + s), __ldcg(y + size_t(t * topk + s) * hidden + i), v);
+  if (has_shared) v += sigmoid_precise(__ldcg(sg + t)) * __ldcg(y + size_t(tokens * topk + t) * hidden + i);
+  const float out = x[size_t(t) * hidden + i] + v;
+  x[size_t(t) * hidden + i] = out;
+}
+
+// GGUF Q6_K rows (nblk x 210 bytes) <-> the row-aligned device layout read by q6k_block.
+__global__ void q6k_repack_kernel(const uint8_t* src, uint8_t* dst, long long rows, int nblk, int inverse) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int per_row = nblk * 105;                 // 16-bit units of payload per row
+  if (idx >= rows * per_row) return;
+  const long long r = idx / per_row;
+  const int u = int(idx % per_row), b = u / 105, o = (u % 105) * 2;   // byte o of block b
+  const int rbytes = nblk * 208 + ((2 * nblk + 15) / 16) * 16;
+  const uint8_t* g = src + (inverse ? 0 : r * (long long)nblk * 210 + b * 210 + o);
+  uint8_t* d = dst + (inverse ? r * (long long)nblk * 210 + b * 210 + o : 0);
+  const long long packed = r * rbytes + (o < 208 ? b * 208 + o : nblk * 208 + 2 * b);
+  if (inverse) {
+    d[0] = src[packed];
+    d[1] = src[packed + 1];
+  } else {
+    dst[packed] = g[0];
+    dst[packed + 1] = g[1];
+  }
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+struct KogarashiWs {
+  int* counters; unsigned* done; unsigned* status; int* active; unsigned* ranges; unsigned* assignments;
+  float* sg; float* h; float* y; size_t bytes;
+};
+static KogarashiWs carve(void* base, int hidden, int inter, int experts, int topk, int tokens) {
+  KogarashiWs w;
+  uint8_t* p = static_cast<uint8_t*>(base);
+  size_t off = 0;
+  auto take = [&](size_t bytes) { uint8_t* q = p ? p + off : nullptr; off = align_up(off + bytes, 256); return q; };
+  w.counters = reinterpret_cast<int*>(take(16));
+  w.done = reinterpret_cast<unsigned*>(take(4));
+  w.status = reinterpret_cast<unsigned*>(take(4));
+  w.active = reinterpret_cast<int*>(take(size_t(experts) * 4));
+  w.ranges = reinterpret_cast<unsigned*>(take(size_t(experts) * 8));
+  w.assignments = reinterpret_cast<unsigned*>(take(size_t(tokens) * topk * 4));
+  w.sg = reinterpret_cast<float*>(take(size_t(tokens) * 4));
+  const size_t rows = size_t(tokens) * topk + tokens;
+  w.h = reinterpret_cast<float*>(take(rows * inter * 4));
+  w.y = reinterpret_cast<float*>(take(rows * hidden * 4));
+  w.bytes = off;
+  return w;
+}
+
+static int q6k_r16_row_bytes(int k) { return k / 256 * 208 + ((2 * (k / 256) + 15) / 16) * 16; }
+static int row_bytes_of(int ty, int k) {
+  return ty == DARASK_GGML_Q4_K ? k / 256 * 144 : ty == DARASK_GGML_Q6_K ? q6k_r16_row_bytes(k) : 0;
+}
+
+template <int DUAL>
+static cudaError_t launch_ggml(int ty, const StreamArgs& a, int max_rows, cudaStream_t st) {
+  if (ty == DARASK_GGML_Q4_K) return launch_stream<kFmtQ4K, DUAL, kActSilu>(a, max_rows, st);
+  if (ty == DARASK_GGML_Q6_K) return launch_stream<kFmtQ6KR, DUAL, kActSilu>(a, max_rows, st);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace dmoe
+
+using namespace dmoe;
+
+extern "C" size_t kogarashi_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens) {
+  return carve(nullptr, hidden, inter, experts, topk, tokens).bytes;
+}
+
+extern "C" int kogarashi_moe_workspace_init(void* workspace, size_t bytes, cudaStream_t st) {
+  if (!workspace || !bytes) return cudaErrorInvalidValue;
+  return cudaMemsetAsync(workspace, 0, bytes < 4096 ? bytes : 4096, st);
+}
+
+extern "C" int kogarashi_moe_status(const void* workspace, unsigned* host_status, cudaStream_t st) {
+  if (!workspace || !host_status) return cudaErrorInvalidValue;
+  const KogarashiWs w = carve(const_cast<void*>(workspace), 256, 256, 1, 1, 1);
+  cudaError_t e = cudaMemcpyAsync(host_status, w.status, 4, cudaMemcpyDeviceToHost, st);
+  return e ? e : cudaStreamSynchronize(st);
+}
+
+extern "C" int darask_q6k_repack(void* dst, const void* src, long long rows, int k, int inverse, cudaStream_t st) {
+  if (!dst || !src || rows <= 0 || k <= 0 || k % 256) return cudaErrorInvalidValue;
+  const long long n = rows * (k / 256) * 105;
+  if (!inverse) {
+    cudaError_t e = cudaMemsetAsync(dst, 0, size_t(rows) * q6k_r16_row_bytes(k), st);
+    if (e) return e;
+  }
+  q6k_repack_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst),
+                                                             rows, k / 256, inverse);
+  return cudaGetLastError();
+}
+
+extern "C" size_t darask_q6k_repacked_bytes(long long rows, int k) { return size_t(rows) * q6k_r16_row_bytes(k); }
+
+extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
+  if (!d || !d->router_w || !d->gate_w || !d->up_w || !d->down_w || !d->n || !d->x || !d->logits || !d->ids ||
+      !d->prob || !d->workspace)
+    return cudaErrorInvalidValue;
+  const int H = d->hidden, F = d->inter, E = d->experts, K = d->topk, T = d->tokens;
+  if (H <= 0 || F <= 0 || H % 256 || F % 256 || E < K || E > 1024 || K < 1 || K > 32 || T < 1) return cudaErrorInvalidValue;
+  if (d->gate_ty != d->up_ty) return cudaErrorInvalidValue;
+  const bool shared = d->sh_gate_w != nullptr;
+  if (shared && (!d->sh_up_w || !d->sh_down_w || !d->sh_inp_w)) return cudaErrorInvalidValue;
+  if (d->workspace_bytes < kogarashi_moe_workspace_bytes(H, F, E, K, T)) return cudaErrorInvalidValue;
+  const KogarashiWs w = carve(d->workspace, H, F, E, K, T);
+
+  // 1. router projection, top-k, permutation
+  RouterArgs r = {};
+  r.w = d->router_w; r.extra = shared ? d->sh_inp_w : nullptr; r.x = d->n; r.row_bias = d->router_bias; r.logits = d->logits; r.extra_out = w.sg;
+  r.hidden = H; r.rows = E; r.ld = E; r.tokens = T;
+  r.route = RouteArgs{d->logits, E, E, K, T, nullptr, 1.f, d->ids, d->prob, nullptr};
+  r.perm = PermuteArgs{d->ids, T, K, E, w.assignments, w.ranges, w.active, w.counters, w.status};
+  r.done = w.done; r.fuse = 1;
+  const int rblocks = E + (shared ? 1 : 0);
+  const size_t hist = size_t(E + 1) * 4;
+  cudaError_t e;
+  if (d->router_ty == DARASK_GGML_F32) e = launch_pdl(router_kernel<float, float, kRouteKogarashi>, dim3(rblocks), dim3(128), hist, st, r);
+  else if (d->router_ty == DARASK_GGML_BF16) e = launch_pdl(router_kernel<__nv_bfloat16, float, kRouteKogarashi>, dim3(rblocks), dim3(128), hist, st, r);
+  else if (d->router_ty == DARASK_GGML_F16) e = launch_pdl(router_kernel<__half, float, kRouteKogarashi>, dim3(rblocks), dim3(128), hist, st, r);
+  else return cudaErrorInvalidValue;
+  if (e) return e;
+
+  // 2. gate/up + SwiGLU for every (token, slot) and the shared expert
+  StreamArgs a = {};
+  a.w[0] = static_cast<const uint8_t*>(d->gate_w); a.w[1] = static_cast<const uint8_t*>(d->up_w);
+  a.w_shared[0] = static_cast<const uint8_t*>(d->sh_gate_w); a.w_shared[1] = static_cast<const uint8_t*>(d->sh_up_w);
+  a.row_bytes = row_bytes_of(d->gate_ty, H);
+  a.expert_stride[0] = a.expert_stride[1] = (unsigned long long)a.row_bytes * F;
+  a.k = H; a.rows = F; a.nblk = H / 256;
+  a.x = d->n; a.x_by_assignment = 0;
+  a.counters = w.counters; a.active = w.active; a.ranges = w.ranges; a.assignments = w.assignments;
+  a.tokens = T; a.topk = K; a.has_shared = shared ? 1 : 0;
+  a.out = w.h; a.status = w.status;
+  if ((e = launch_ggml<1>(d->gate_ty, a, T, st))) return e;
+
+  // 3. down
+  StreamArgs b = a;
+  b.w[0] = static_cast<const uint8_t*>(d->down_w); b.w[1] = nullptr;
+  b.w_shared[0] = static_cast<const uint8_t*>(d->sh_down_w); b.w_shared[1] = nullptr;
+  b.row_bytes = row_bytes_of(d->down_ty, F);
+  b.expert_stride[0] = (unsigned long long)b.row_bytes * H; b.expert_stride[1] = 0;
+  b.k = F; b.rows = H; b.nblk = F / 256;
+  b.x = w.h; b.x_by_assignment = 1;
+  b.out = w.y;
+  if ((e = launch_ggml<0>(d->down_ty, b, T, st))) return e;
+
+  // 4. combine
+  return launch_pdl(kogarashi_combine_kernel, dim3((H + 255) / 256, T), dim3(256), 0, st, d->x, (const float*)w.y,
+                    (const float*)d->prob, (const float*)w.sg, H, K, T, shared ? 1 : 0);
+}
+
+// ---- stand-alone pieces (also used by the parity tests) ------------------------------------------
+
+extern "C" int darask_route_topk(int mode, const float* logits, int ld, int experts, int topk, int tokens,
+                                 const float* bias, float scale, int* ids, float* weights, float* shared_gate,
+                                 cudaStream_t st) {
+  if (!logits || !ids || !weights || experts < 1 || experts > 1024 || topk < 1 || topk > 32 || topk > experts ||
+      tokens < 1 || ld < experts)
+    return cudaErrorInvalidValue;
+  RouteArgs a{logits, ld, experts, topk, tokens, bias, scale, ids, weights, shared_gate};
+  const dim3 grid((tokens + 3) / 4), block(128);
+  if (mode == DARASK_ROUTE_KOGARASHI) return launch_pdl(route_topk_kernel<kRouteKogarashi>, grid, block, 0, st, a);
+  if (mode == DARASK_ROUTE_TSUMUJI) {
+    if (shared_gate && ld < experts + 1) return cudaErrorInvalidValue;
+    return launch_pdl(route_topk_kernel<kRouteTsumuji>, grid, block, 0, st, a);
+  }
+  if (mode == DARASK_ROUTE_HAYATE) {
+    if (!bias) return cudaErrorInvalidValue;
+    return darask_route_topk_hayate(logits, ld, experts, topk, tokens, bias, scale, ids, weights, st);
+  }
+  return cudaErrorInvalidValue;
+}
+
+extern "C" int darask_moe_permute(const int* ids, int tokens, int topk, int experts, unsigned* assignments,
+                                  unsigned* ranges, int* active, int* counters, unsigned* status, cudaStream_t st) {
+  if (!ids || !assignments || !ranges || !active || !counters || !status || tokens < 1 || topk < 1 || experts < 1 ||
+      experts > 1024)
+    return cudaErrorInvalidValue;
+  PermuteArgs p{ids, tokens, topk, experts, assignments, ranges, active, counters, status};
+  return launch_pdl(permute_kernel<0>, dim3(1), dim3(1024), size_t(experts + 1) * 4, st, p);
+}

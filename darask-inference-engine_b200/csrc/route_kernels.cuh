@@ -1,0 +1,116 @@
+// Kernels around route_impl.cuh: stand-alone top-k, the router projection (logits) fused with
+// top-k and the dispatch permutation through a "last block finishes" counter, and the
+// stand-alone permutation. Included by route.cu (precise math: Kogarashi, Tsumuji) and by
+// route_hayate.cu (fast math: Hayate).
+#pragma once
+#include "route_impl.cuh"
+
+namespace dmoe {
+
+template <int MODE>
+__global__ void __launch_bounds__(128) route_topk_kernel(RouteArgs a) {
+  pdl_wait();
+  pdl_launch();
+  const int token = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (token < a.tokens) route_token_any<MODE>(a, token, threadIdx.x & 31);
+}
+
+template <int UNUSED = 0>
+__global__ void __launch_bounds__(1024) permute_kernel(PermuteArgs p) {
+  extern __shared__ int hist[];
+  pdl_wait();
+  pdl_launch();
+  permute_block(p, hist);
+}
+
+// ---- router projection -----------------------------------------------------------------------
+// logits[t][row] = sum_k W[row][k] x[t][k], one block per row, the four warps split k.
+// Rows [0, experts) come from `w`; row `experts` (optional) from `extra` : the shared-expert gate
+// projection (kogarashi engine.rs:610-618 ffn_gate_inp_shexp; tsumuji keeps it as row E of the
+// router matrix, weights.rs:937-947).
+template <typename T> DEVI float to_f32(T v);
+template <> DEVI float to_f32<float>(float v) { return v; }
+template <> DEVI float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> DEVI float to_f32<__half>(__half v) { return __half2float(v); }
+
+struct RouterArgs {
+  const void* w;        // [rows][hidden]
+  const void* extra;    // [hidden] or null
+  const void* x;        // [T][hidden]
+  const float* row_bias; // [rows] added to the logits of rows < `rows` (null: none)
+  float* logits;        // [T][ld]
+  float* extra_out;     // [T] raw logit of the extra row when it is not stored in `logits`
+  int hidden, rows, ld, tokens;
+  RouteArgs route;      // routing of the finished logits (route.logits == logits)
+  PermuteArgs perm;
+  unsigned* done;       // counter, zero before the launch; reset to zero by the last block
+  int fuse;             // 1: last block routes and permutes
+};
+
+template <typename WT, typename XT, int MODE>
+__global__ void __launch_bounds__(128) router_kernel(RouterArgs a) {
+  extern __shared__ int hist[];
+  __shared__ float part[4][16];
+  __shared__ unsigned last;
+  constexpr int VEC = 16 / sizeof(WT);          // weights per 16-byte load
+  const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool is_extra = row >= a.rows;
+  const WT* wr = is_extra ? static_cast<const WT*>(a.extra) : static_cast<const WT*>(a.w) + size_t(row) * a.hidden;
+  // weights do not depend on earlier kernels: fetch them before the dependency wait
+  constexpr int MAXC = 8;                        // 16-byte chunks per thread kept in registers
+  uint4 wv[MAXC];
+  const int chunks = a.hidden / VEC;
+#pragma unroll
+  for (int i = 0; i < MAXC; ++i) {
+    const int c = tid + i * 128;
+    wv[i] = c < chunks ? __ldg(reinterpret_cast<const uint4*>(wr) + c) : make_uint4(0, 0, 0, 0);
+  }
+  pdl_wait();
+  pdl_launch();
+  for (int t0 = 0; t0 < a.tokens; t0 += 16) {
+    const int nt = min(16, a.tokens - t0);
+    for (int t = 0; t < nt; ++t) {
+      const XT* xt = static_cast<const XT*>(a.x) + size_t(t0 + t) * a.hidden;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < MAXC; ++i) {
+        const int c = tid + i * 128;
+        if (c < chunks) {
+          const WT* wp = reinterpret_cast<const WT*>(&wv[i]);
+#pragma unroll
+          for (int j = 0; j < VEC; ++j) acc = fmaf(to_f32(wp[j]), to_f32(xt[c * VEC + j]), acc);
+        }
+      }
+      for (int c = tid + MAXC * 128; c < chunks; c += 128) {   // rows longer than the register window
+        const uint4 q = __ldg(reinterpret_cast<const uint4*>(wr) + c);
+        const WT* wp = reinterpret_cast<const WT*>(&q);
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) acc = fmaf(to_f32(wp[j]), to_f32(xt[c * VEC + j]), acc);
+      }
+      acc = warp_sum(acc);
+      if (lane == 0) part[warp][t] = acc;
+    }
+    __syncthreads();
+    if (tid < nt) {
+      float v = (part[0][tid] + part[1][tid]) + (part[2][tid] + part[3][tid]);
+      if (!is_extra && a.row_bias) v += a.row_bias[row];
+      if (is_extra && a.extra_out) a.extra_out[t0 + tid] = v;
+      if (!is_extra || a.ld > a.rows) a.logits[size_t(t0 + tid) * a.ld + row] = v;
+    }
+    __syncthreads();
+  }
+  if (!a.fuse) return;
+  // Last block to finish routes every token and builds the permutation.
+  __threadfence();
+  if (tid == 0) last = atomicAdd(a.done, 1u) == gridDim.x - 1 ? 1u : 0u;
+  __syncthreads();
+  if (!last) return;
+  __threadfence();
+  for (int token = warp; token < a.tokens; token += 4) route_token_any<MODE>(a.route, token, lane);
+  __threadfence_block();
+  __syncthreads();
+  if (a.perm.assignments) permute_block(a.perm, hist);
+  if (tid == 0) *a.done = 0u;
+}
+
+}  // namespace dmoe

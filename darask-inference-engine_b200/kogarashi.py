@@ -1,0 +1,99 @@
+"""Host-side mirror of the Kogarashi MoE layer call.
+
+Reference: `Engine::record`, engines/kogarashi/crates/kogarashi-engine/src/engine.rs:530-632,
+with weights held as in `struct Weight {data, ty, k, rows, ne}` (engine.rs:13-19, upload at
+:73-107) and the activation buffers of engine.rs:128-139 ("n", "x", "router", "ids", "prob").
+The twelve launches of the reference become one call of `kogarashi_moe_layer`.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from .formats import GGML_Q6_K, ggml_tensor_bytes
+
+TENSORS = ("ffn_gate_inp.weight", "ffn_gate_exps.weight", "ffn_up_exps.weight", "ffn_down_exps.weight",
+           "ffn_gate_shexp.weight", "ffn_up_shexp.weight", "ffn_down_shexp.weight", "ffn_gate_inp_shexp.weight")
+
+
+@dataclass
+class Weight:
+    data: torch.Tensor      # uint8, device
+    ty: int
+    k: int
+    rows: int
+    ne: tuple
+
+
+class KogarashiMoeLayer:
+    """One layer's MoE FFN: weights resident on one GPU, buffers sized for `max_tokens`."""
+
+    def __init__(self, hidden: int, inter: int, experts: int, topk: int, max_tokens: int = 1, device="cuda"):
+        self.hidden, self.inter, self.experts, self.topk, self.max_tokens = hidden, inter, experts, topk, max_tokens
+        self.device = torch.device(device)
+        self.weights: dict[str, Weight] = {}
+        self.router_bias = None   # optional float32 [experts] logit offset (not in the reference model)
+        lib = _lib.lib()
+        nbytes = lib.kogarashi_moe_workspace_bytes(hidden, inter, experts, topk, max_tokens)
+        self.workspace = torch.empty(nbytes, dtype=torch.uint8, device=self.device)
+        _lib.check(lib.kogarashi_moe_workspace_init(self.workspace.data_ptr(), nbytes, self._stream()), "workspace_init")
+        self.logits = torch.empty(max_tokens, experts, dtype=torch.float32, device=self.device)
+        self.ids = torch.empty(max_tokens, topk, dtype=torch.int32, device=self.device)
+        self.prob = torch.empty(max_tokens, topk, dtype=torch.float32, device=self.device)
+
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def load(self, name: str, raw: torch.Tensor, ty: int, ne) -> None:
+        """Takes the bytes of a GGUF tensor (GGML order ne = [k, rows(, experts)]). Q6_K tensors are
+        regrouped once into the 16-byte aligned device layout (lossless)."""
+        if name not in TENSORS:
+            raise KeyError(name)
+        ne = tuple(int(d) for d in ne)
+        if raw.dtype != torch.uint8 or raw.numel() != ggml_tensor_bytes(ty, ne):
+            raise ValueError(f"{name}: expected {ggml_tensor_bytes(ty, ne)} bytes of GGML type {ty}")
+        raw = raw.to(self.device).contiguous()
+        k, rows = ne[0], ne[1] if len(ne) > 1 else 1
+        if ty == GGML_Q6_K:
+            lib = _lib.lib()
+            total_rows = raw.numel() // (k // 256 * 210)
+            packed = torch.empty(lib.darask_q6k_repacked_bytes(total_rows, k), dtype=torch.uint8, device=self.device)
+            _lib.check(lib.darask_q6k_repack(packed.data_ptr(), raw.data_ptr(), total_rows, k, 0, self._stream()), "q6k_repack")
+            raw = packed
+        self.weights[name] = Weight(raw, ty, k, rows, ne)
+
+    def _w(self, name):
+        w = self.weights.get(name)
+        return (w.data.data_ptr(), w.ty) if w is not None else (None, 0)
+
+    def forward(self, x: torch.Tensor, n: torch.Tensor) -> torch.Tensor:
+        """x [T,H] float32 residual stream (updated in place), n [T,H] float32 normalised input."""
+        t = n.shape[0]
+        if t > self.max_tokens or n.shape != x.shape or n.shape[1] != self.hidden:
+            raise ValueError("token count / shape")
+        if x.dtype != torch.float32 or n.dtype != torch.float32 or not x.is_contiguous() or not n.is_contiguous():
+            raise ValueError("x and n must be contiguous float32")
+        d = _lib.KogarashiMoe()
+        d.hidden, d.inter, d.experts, d.topk, d.tokens = self.hidden, self.inter, self.experts, self.topk, t
+        d.router_w, d.router_ty = self._w("ffn_gate_inp.weight")
+        d.router_bias = self.router_bias.data_ptr() if self.router_bias is not None else None
+        d.gate_w, d.gate_ty = self._w("ffn_gate_exps.weight")
+        d.up_w, d.up_ty = self._w("ffn_up_exps.weight")
+        d.down_w, d.down_ty = self._w("ffn_down_exps.weight")
+        d.sh_gate_w = self._w("ffn_gate_shexp.weight")[0]
+        d.sh_up_w = self._w("ffn_up_shexp.weight")[0]
+        d.sh_down_w = self._w("ffn_down_shexp.weight")[0]
+        d.sh_inp_w = self._w("ffn_gate_inp_shexp.weight")[0]
+        d.n, d.x = n.data_ptr(), x.data_ptr()
+        d.logits, d.ids, d.prob = self.logits.data_ptr(), self.ids.data_ptr(), self.prob.data_ptr()
+        d.workspace, d.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
+        _lib.check(_lib.lib().kogarashi_moe_layer(ctypes.byref(d), self._stream()), "kogarashi_moe_layer")
+        return x
+
+    def status(self) -> int:
+        out = ctypes.c_uint(0)
+        _lib.check(_lib.lib().kogarashi_moe_status(self.workspace.data_ptr(), ctypes.byref(out), self._stream()), "status")
+        return out.value

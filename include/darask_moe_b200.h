@@ -1,0 +1,91 @@
+/* C ABI of the B200 (sm_100a) MoE FFN library, libdarask_moe_b200.so.
+ *
+ * Conventions, the same as the reference engine's kernel launchers
+ * (engines/hayate/crates/kernels/src/cuda.rs:29-36): every call only enqueues work on the
+ * given stream, never allocates and never synchronizes (the two *_status calls, which copy one
+ * word back, are the exception); device pointers must stay valid until the stream has passed
+ * the launch; the return value is a cudaError_t as int, cudaErrorInvalidValue (1) for
+ * arguments that fail validation.  All pointers are device pointers unless a comment says
+ * "host".  `stream` is a cudaStream_t / CUstream.
+ */
+#ifndef DARASK_MOE_B200_H
+#define DARASK_MOE_B200_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* darask_stream_t;
+
+/* GGML tensor type ids as the reference reads them (engines/kogarashi/crates/kogarashi-engine/
+ * src/config.rs:86-105). */
+enum { DARASK_GGML_F32 = 0, DARASK_GGML_F16 = 1, DARASK_GGML_Q4_K = 12, DARASK_GGML_Q6_K = 14, DARASK_GGML_BF16 = 30 };
+enum { DARASK_ROUTE_KOGARASHI = 0, DARASK_ROUTE_TSUMUJI = 1, DARASK_ROUTE_HAYATE = 2 };
+/* bits of the status word kept in every workspace */
+enum { DARASK_STATUS_WAIT_TIMEOUT = 1, DARASK_STATUS_BAD_ROUTE = 2 };
+
+/* ---- routing ------------------------------------------------------------------------------
+ * Top-k and gate weights from float32 logits [tokens][ld], bit-exact in ids and order with
+ *   mode 0: kernel `route`        engines/kogarashi/kernels/native.cu:100-112
+ *   mode 1: kernel `router_topk`  engines/tsumuji/kernels/decode/ops.cu:148-200 (shared_gate = sigmoid(logits[t][experts]))
+ *   mode 2: `router_select`/`route` engines/hayate/crates/kernels/cu/glm53/decode.cu:23-31, ops.cu:100-114
+ * but for any experts <= 1024 and topk <= 32 (the reference kernels hard-code 256/8 and 288/8). */
+int darask_route_topk(int mode, const float* logits, int ld, int experts, int topk, int tokens,
+                      const float* bias, float scale, int* ids, float* weights, float* shared_gate,
+                      darask_stream_t stream);
+int darask_route_topk_hayate(const float* logits, int ld, int experts, int topk, int tokens, const float* bias,
+                             float scale, int* ids, float* weights, darask_stream_t stream);
+
+/* Dispatch permutation on the device: replaces the host function `groups`
+ * (engines/hayate/crates/models/src/glm53/prefill.rs:12-26) and `PackedMeta::push`
+ * (models/src/glm53/gpu.rs:29-80).  ids [tokens*topk] -> assignments [tokens*topk] (assignment
+ * index token*topk+slot, grouped by ascending expert id, ascending inside a group),
+ * ranges [experts][2] = {rows, offset}, active [experts] = ids with rows > 0, counters[0] = their
+ * number, counters[1] = total rows.  Ids out of range or repeated inside a token are dropped and
+ * set DARASK_STATUS_BAD_ROUTE in *status. */
+int darask_moe_permute(const int* ids, int tokens, int topk, int experts, unsigned* assignments, unsigned* ranges,
+                       int* active, int* counters, unsigned* status, darask_stream_t stream);
+
+/* ---- GGUF Q6_K device layout ------------------------------------------------------------------
+ * Lossless regrouping of Q6_K rows (k/256 blocks of 210 bytes, never 16-byte aligned) into
+ * rows of k/256 x 208 bytes [ql|qh|scales] followed by the k/256 f16 block scales, padded to
+ * 16 bytes, which the TMA engine can stream.  Done once after the upload that replaces
+ * engines/kogarashi/crates/kogarashi-engine/src/engine.rs:73-107.  inverse != 0 restores GGUF. */
+size_t darask_q6k_repacked_bytes(long long rows, int k);
+int darask_q6k_repack(void* dst, const void* src, long long rows, int k, int inverse, darask_stream_t stream);
+
+/* ---- Kogarashi MoE FFN layer -----------------------------------------------------------------
+ * One call replaces the 12 launches of engines/kogarashi/crates/kogarashi-engine/src/engine.rs:
+ * 530-632 (router `gemv`, `route`, expert `gemv` x3, `activate`, shared expert `gemv` x4,
+ * `activate`, `combine`; kernels engines/kogarashi/kernels/native.cu:46-117) for `tokens` >= 1.
+ * Weight tensors are the GGUF tensors of that call site in GGML order [k, rows, experts];
+ * Q4_K tensors as uploaded, Q6_K tensors after darask_q6k_repack. */
+typedef struct {
+  int hidden, inter, experts, topk, tokens;
+  const void* router_w; int router_ty;                 /* ffn_gate_inp        [hidden, experts]     */
+  const float* router_bias;                            /* [experts] added to the logits; NULL as in the reference */
+  const void* gate_w; int gate_ty;                     /* ffn_gate_exps       [hidden, inter, E]    */
+  const void* up_w; int up_ty;                         /* ffn_up_exps                               */
+  const void* down_w; int down_ty;                     /* ffn_down_exps       [inter, hidden, E]    */
+  const void* sh_gate_w; const void* sh_up_w;          /* ffn_{gate,up}_shexp, same types; NULL: no shared expert */
+  const void* sh_down_w;                               /* ffn_down_shexp                            */
+  const void* sh_inp_w;                                /* ffn_gate_inp_shexp  [hidden], type router_ty */
+  const float* n;                                      /* [tokens][hidden] normalised input (buffer "n") */
+  float* x;                                            /* [tokens][hidden] residual stream, updated in place ("x") */
+  float* logits;                                       /* [tokens][experts]   ("router")            */
+  int* ids;                                            /* [tokens][topk]      ("ids")               */
+  float* prob;                                         /* [tokens][topk]      ("prob")              */
+  void* workspace; size_t workspace_bytes;
+} KogarashiMoe;
+size_t kogarashi_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens);
+/* zeroes the control words once after allocation */
+int kogarashi_moe_workspace_init(void* workspace, size_t bytes, darask_stream_t stream);
+int kogarashi_moe_layer(const KogarashiMoe* desc /* host */, darask_stream_t stream);
+/* copies the status word to *host_status and synchronizes the stream */
+int kogarashi_moe_status(const void* workspace, unsigned* host_status /* host */, darask_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
