@@ -7,6 +7,7 @@ PyTorch is used for device memory and streams only.
 from . import _lib  # noqa: F401
 from .formats import (GGML_BF16, GGML_F16, GGML_F32, GGML_Q4_K, GGML_Q6_K, ggml_tensor_bytes,  # noqa: F401
                       nvfp4_tiled_bytes)
+from . import quantize  # noqa: F401
 from .kogarashi import KogarashiMoeLayer  # noqa: F401
 
 __all__ = ["KogarashiMoeLayer", "ggml_tensor_bytes", "nvfp4_tiled_bytes"]

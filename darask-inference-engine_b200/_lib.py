@@ -22,7 +22,7 @@ class KogarashiMoe(ctypes.Structure):
         ("down_w", c_void_p), ("down_ty", c_int),
         ("sh_gate_w", c_void_p), ("sh_up_w", c_void_p), ("sh_down_w", c_void_p), ("sh_inp_w", c_void_p),
         ("n", c_void_p), ("x", c_void_p), ("logits", c_void_p), ("ids", c_void_p), ("prob", c_void_p),
-        ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("stage_mask", c_int),
     ]
 
 
@@ -35,6 +35,12 @@ _SIGNATURES = {
                                    c_void_p]),
     "darask_q6k_repacked_bytes": (c_size_t, [c_longlong, c_int]),
     "darask_q6k_repack": (c_int, [c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p]),
+    "darask_quantize_ggml": (c_int, [c_void_p, c_void_p, c_int, c_longlong, c_void_p]),
+    "darask_quantize_nvfp4_linear": (c_int, [c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_int, c_void_p,
+                                             c_longlong, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "darask_quantize_nvfp4_tiled": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "darask_quantize_fp8_block": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "darask_quantize_fp8_act": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p]),
     "kogarashi_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "kogarashi_moe_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),
     "kogarashi_moe_layer": (c_int, [ctypes.POINTER(KogarashiMoe), c_void_p]),

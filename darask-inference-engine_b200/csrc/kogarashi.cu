@@ -138,8 +138,10 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
   r.done = w.done; r.fuse = 1;
   const int rblocks = E + (shared ? 1 : 0);
   const size_t hist = size_t(E + 1) * 4;
-  cudaError_t e;
-  if (d->router_ty == DARASK_GGML_F32) e = launch_pdl(router_kernel<float, float, kRouteKogarashi>, dim3(rblocks), dim3(128), hist, st, r);
+  const int mask = d->stage_mask ? d->stage_mask : 15;
+  cudaError_t e = cudaSuccess;
+  if (!(mask & 1)) {}
+  else if (d->router_ty == DARASK_GGML_F32) e = launch_pdl(router_kernel<float, float, kRouteKogarashi>, dim3(rblocks), dim3(128), hist, st, r);
   else if (d->router_ty == DARASK_GGML_BF16) e = launch_pdl(router_kernel<__nv_bfloat16, float, kRouteKogarashi>, dim3(rblocks), dim3(128), hist, st, r);
   else if (d->router_ty == DARASK_GGML_F16) e = launch_pdl(router_kernel<__half, float, kRouteKogarashi>, dim3(rblocks), dim3(128), hist, st, r);
   else return cudaErrorInvalidValue;
@@ -156,7 +158,7 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
   a.counters = w.counters; a.active = w.active; a.ranges = w.ranges; a.assignments = w.assignments;
   a.tokens = T; a.topk = K; a.has_shared = shared ? 1 : 0;
   a.out = w.h; a.status = w.status;
-  if ((e = launch_ggml<1>(d->gate_ty, a, T, st))) return e;
+  if ((mask & 2) && (e = launch_ggml<1>(d->gate_ty, a, T, st))) return e;
 
   // 3. down
   StreamArgs b = a;
@@ -167,9 +169,10 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
   b.k = F; b.rows = H; b.nblk = F / 256;
   b.x = w.h; b.x_by_assignment = 1;
   b.out = w.y;
-  if ((e = launch_ggml<0>(d->down_ty, b, T, st))) return e;
+  if ((mask & 4) && (e = launch_ggml<0>(d->down_ty, b, T, st))) return e;
 
   // 4. combine
+  if (!(mask & 8)) return cudaSuccess;
   return launch_pdl(kogarashi_combine_kernel, dim3((H + 255) / 256, T), dim3(256), 0, st, d->x, (const float*)w.y,
                     (const float*)d->prob, (const float*)w.sg, H, K, T, shared ? 1 : 0);
 }

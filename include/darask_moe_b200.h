@@ -55,6 +55,31 @@ int darask_moe_permute(const int* ids, int tokens, int topk, int experts, unsign
 size_t darask_q6k_repacked_bytes(long long rows, int k);
 int darask_q6k_repack(void* dst, const void* src, long long rows, int k, int inverse, darask_stream_t stream);
 
+/* ---- load-time quantizers ------------------------------------------------------------------------
+ * float32 source on the device -> the byte layouts the expert kernels read.
+ *   darask_quantize_nvfp4_linear  replaces kernels `nvfp4_amax` + `nvfp4_quant`
+ *       (engines/tsumuji/kernels/decode/quant.cu:77-114): `matrices` matrices of rows x cols, matrix m read
+ *       at src + m*src_stride (elements, rounded to bf16 first), codes written to dst + m*dst_stride +
+ *       codes_off, e4m3 scales to dst + m*dst_stride + scales_off, global scale to gs[m*gs_stride].
+ *   darask_quantize_nvfp4_tiled   one Hayate NVFP4 matrix image (codes | 128x4 tiled scales | f32), the
+ *       arithmetic of engines/hayate/python-tools/hayate_tools/quant.py:42-64.
+ *   darask_quantize_fp8_block     e4m3 payload [rows][cols] + float32 scale per 128x128 block
+ *       (format `Fp8Block`, engines/hayate/crates/kernels/src/cpu/glm53.rs:23-24).
+ *   darask_quantize_fp8_act       activations [rows][cols] (float32 or bf16) -> e4m3 codes + float32 scale per
+ *       row and 128 channels; no counterpart in the reference (its activations stay bf16 / float32).
+ *   darask_quantize_ggml          GGUF Q4_K (12) / Q6_K (14) blocks; the reference ships no quantizer for these
+ *       (it decodes them: engines/kogarashi/kernels/native.cu:26-40), this one is this library's own.
+ * amax_scratch: `matrices` (or 1) unsigned words of device scratch. */
+int darask_quantize_ggml(void* dst, const float* src, int ty, long long elements, darask_stream_t stream);
+int darask_quantize_nvfp4_linear(void* dst, long long dst_stride, long long codes_off, long long scales_off, float* gs,
+                                 int gs_stride, const float* src, long long src_stride, int matrices, int rows, int cols,
+                                 unsigned* amax_scratch, darask_stream_t stream);
+int darask_quantize_nvfp4_tiled(void* dst, const float* src, int rows, int cols, unsigned* amax_scratch,
+                                darask_stream_t stream);
+int darask_quantize_fp8_block(void* payload, float* scales, const float* src, int rows, int cols, darask_stream_t stream);
+int darask_quantize_fp8_act(void* codes, float* scales, const void* x, int x_is_bf16, long long rows, int cols,
+                            darask_stream_t stream);
+
 /* ---- Kogarashi MoE FFN layer -----------------------------------------------------------------
  * One call replaces the 12 launches of engines/kogarashi/crates/kogarashi-engine/src/engine.rs:
  * 530-632 (router `gemv`, `route`, expert `gemv` x3, `activate`, shared expert `gemv` x4,
@@ -77,6 +102,7 @@ typedef struct {
   int* ids;                                            /* [tokens][topk]      ("ids")               */
   float* prob;                                         /* [tokens][topk]      ("prob")              */
   void* workspace; size_t workspace_bytes;
+  int stage_mask;                                      /* 0: whole layer; else bits 1 router+top-k, 2 gate/up, 4 down, 8 combine */
 } KogarashiMoe;
 size_t kogarashi_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens);
 /* zeroes the control words once after allocation */

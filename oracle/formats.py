@@ -174,7 +174,7 @@ def q4k_quantize(w: np.ndarray) -> np.ndarray:
     lo = np.minimum(x.min(-1), 0.0)
     hi = np.maximum(x.max(-1), 0.0)
     sub_scale = (hi - lo) / 15.0
-    sub_min = -lo
+    sub_min = np.float32(0) - lo          # +0 for an all-zero sub-block
     d = (sub_scale.max(-1) / 63.0).astype(np.float16)
     dmin = (sub_min.max(-1) / 63.0).astype(np.float16)
     df, dmf = d.astype(np.float32)[:, None], dmin.astype(np.float32)[:, None]
