@@ -44,6 +44,8 @@ _SIGNATURES = {
     "kogarashi_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "kogarashi_moe_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),
     "kogarashi_moe_layer": (c_int, [ctypes.POINTER(KogarashiMoe), c_void_p]),
+    "kogarashi_moe_static_scratch_bytes": (c_size_t, []),
+    "kogarashi_moe_layer_static": (c_int, [ctypes.POINTER(KogarashiMoe), c_void_p]),
     "kogarashi_moe_status": (c_int, [c_void_p, ctypes.POINTER(c_uint), c_void_p]),
 }
 

@@ -8,6 +8,7 @@
 #include "../../include/darask_moe_b200.h"
 #include "route_kernels.cuh"
 #include "stream_launch.cuh"
+#include <cstdio>
 
 namespace dmoe {
 
@@ -206,4 +207,44 @@ extern "C" int darask_moe_permute(const int* ids, int tokens, int topk, int expe
     return cudaErrorInvalidValue;
   PermuteArgs p{ids, tokens, topk, experts, assignments, ranges, active, counters, status};
   return launch_pdl(permute_kernel<0>, dim3(1), dim3(1024), size_t(experts + 1) * 4, st, p);
+}
+
+// ---- entry point that needs no caller-provided workspace -----------------------------------------
+// Scratch of the layer lives in this fixed device array instead of `KogarashiMoe::workspace`.
+// Every GPU that loads the library holds these bytes until the process exits.
+#define KOGARASHI_STATIC_SCRATCH_BYTES (1u << 20)
+static __device__ __align__(256) unsigned char g_kogarashi_static_scratch[KOGARASHI_STATIC_SCRATCH_BYTES];
+
+extern "C" size_t kogarashi_moe_static_scratch_bytes(void) { return KOGARASHI_STATIC_SCRATCH_BYTES; }
+
+extern "C" int kogarashi_moe_layer_static(const KogarashiMoe* d, cudaStream_t st) {
+  if (!d) return cudaErrorInvalidValue;
+  const size_t need = kogarashi_moe_workspace_bytes(d->hidden, d->inter, d->experts, d->topk, d->tokens);
+  if (need > KOGARASHI_STATIC_SCRATCH_BYTES) {
+    fprintf(stderr,
+            "kogarashi_moe_layer_static: this shape needs %zu bytes of scratch, the built-in array holds %u; "
+            "use kogarashi_moe_layer with a caller-provided workspace\n",
+            need, KOGARASHI_STATIC_SCRATCH_BYTES);
+    return cudaErrorInvalidValue;
+  }
+  // The array's name is only a host-side handle: its device address is looked up once per device,
+  // with that device current, and kept.
+  static void* address[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (!address[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_kogarashi_static_scratch);
+    if (e != cudaSuccess) return e;
+    address[dev] = p;
+  }
+  // The array keeps whatever the previous call left: the control words must start at zero.
+  e = cudaMemsetAsync(address[dev], 0, 4096, st);
+  if (e != cudaSuccess) return e;
+  KogarashiMoe copy = *d;
+  copy.workspace = address[dev];
+  copy.workspace_bytes = KOGARASHI_STATIC_SCRATCH_BYTES;
+  return kogarashi_moe_layer(&copy, st);
 }

@@ -111,6 +111,20 @@ int kogarashi_moe_layer(const KogarashiMoe* desc /* host */, darask_stream_t str
 /* copies the status word to *host_status and synchronizes the stream */
 int kogarashi_moe_status(const void* workspace, unsigned* host_status /* host */, darask_stream_t stream);
 
+/* Same layer, for callers that cannot hand over a workspace.  No counterpart in the reference.
+ * Meant for hosts that have no device allocator at the call site: an FFI embedder that gave all
+ * device memory to its own arena at start-up, or plugin code running after the point where its
+ * engine forbids cudaMalloc.  The scratch is a fixed array inside the library
+ * (kogarashi_moe_static_scratch_bytes() = 1 MiB per GPU, held from library load to process exit);
+ * desc->workspace and desc->workspace_bytes are ignored.  Shapes whose scratch need
+ * (kogarashi_moe_workspace_bytes) exceeds the array are refused with cudaErrorInvalidValue and a
+ * message on stderr.  The call itself allocates nothing.  The first call on each device looks up
+ * the array's device address (with that device current); make that first call before any stream
+ * capture.  All calls on a device share the one array: calls whose kernels can overlap on the
+ * GPU (different streams) race; serialize them. */
+size_t kogarashi_moe_static_scratch_bytes(void);
+int kogarashi_moe_layer_static(const KogarashiMoe* desc /* host */, darask_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
