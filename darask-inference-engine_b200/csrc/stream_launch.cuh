@@ -19,12 +19,16 @@ constexpr int kComputeWarps = 12;
 
 // Chooses row groups / K split / ring depth so that the ring holds at least two stages and as
 // many compute warps as fit. Returns false when even one row group does not fit.
-inline bool plan_stream(StreamArgs& a, int tt, bool xsum, int* smem_bytes) {
-  a.pitch = a.row_bytes + (((a.row_bytes / 16) & 1) ? 0 : 16);
+inline bool plan_stream(StreamArgs& a, int fmt, int tt, int* smem_bytes) {
+  // Row-slot pitch chosen so that the lane pattern of the tile loads (8 rows x 4 lanes) is free of
+  // bank conflicts: 8-byte loads (Q4_K) want pitch % 128 in {32, 96}, 4-byte loads pitch % 32 == 16.
+  a.pitch = a.row_bytes;
+  if (fmt == kFmtQ4K) while (a.pitch % 128 != 32 && a.pitch % 128 != 96) a.pitch += 16;
+  else while (a.pitch % 32 != 16) a.pitch += 16;
   a.ks = a.nblk < kComputeWarps ? a.nblk : kComputeWarps;
   for (int rg = kComputeWarps / a.ks > 0 ? kComputeWarps / a.ks : 1; rg >= 1; --rg) {
     for (int stages = kMaxStages; stages >= 2; --stages) {
-      const StreamSmem s = stream_smem(rg, a.ks, stages, a.pitch, a.k, tt, xsum);
+      const StreamSmem s = stream_smem(fmt, rg, a.ks, stages, a.pitch, a.k, tt);
       if (s.total <= kSmemBudget && (stages >= 3 || rg == 1 || stages * s.stage_bytes >= 128 * 1024)) {
         a.rg = rg;
         a.stages = stages;
@@ -54,7 +58,7 @@ inline cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem,
 template <int FMT, int DUAL, int TT, int ACT>
 inline cudaError_t launch_stream_tt(StreamArgs a, cudaStream_t stream) {
   int smem = 0;
-  if (!plan_stream(a, TT, FMT == kFmtQ4K, &smem)) return cudaErrorInvalidConfiguration;
+  if (!plan_stream(a, FMT, TT, &smem)) return cudaErrorInvalidConfiguration;
   auto kernel = expert_stream_kernel<FMT, DUAL, TT, ACT>;
   static bool configured = false;       // one opt-in per instantiation (and process)
   if (!configured) {
