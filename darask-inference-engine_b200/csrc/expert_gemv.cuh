@@ -1,0 +1,369 @@
+// Decode-path expert products for small token counts (GGUF Q4_K / Q6_K weights).
+//
+// Every warp is independent: it owns an 8- or 16-row slab of one expert and a contiguous share of
+// the 256-element blocks of K, streams that share HBM -> its private shared-memory ring with
+// 16-byte cp.async copies (2-3 blocks in flight per warp, ~100 KB per SM), and multiplies on
+// fp16 tensor-core tiles (mma.sync m16n8k16, fp32 accumulate):
+//   * A operand = the weight codes as exact small fp16 integers (Q4_K: q * sc <= 945; Q6_K: q - 32),
+//     built from the packed bytes with two bit operations per pair, no int->float conversion;
+//   * B operand = the activations split as x = hi + lo (two fp16, error <= 2^-22 |x|), one column
+//     pair per token, so one tile serves up to four tokens of the same expert;
+//   * fp16 x fp16 products are exact in fp32, the f16/f32 scales are applied to the tile sums.
+// The warps that share a row slab (K split) add their partial sums through shared memory in a
+// fixed order. No CTA-wide barrier exists after the prologue.
+// Activation rows are read as "planes": per row k fp16 hi values then k fp16 lo values, each
+// aligned group of four stored as [x0, x2, x1, x3] (the order the tile fragments want).
+// Replaces kogarashi kernels/native.cu:46-88 (`gemv`) and :97-99 (`activate`).
+#pragma once
+#include "common.cuh"
+
+namespace dmoe {
+
+enum GemvFormat { kGemvQ4K = 0, kGemvQ6KR = 1 };
+
+struct GemvArgs {
+  const uint8_t* w[2];          // routed experts: matrix 0 (gate or down) and matrix 1 (up)
+  const uint8_t* w_shared[2];   // shared expert matrices (null when there is none)
+  unsigned long long expert_stride[2];   // bytes between consecutive experts
+  int row_bytes;                // bytes of one row in global memory (multiple of 16)
+  int k, rows, nblk;            // columns, rows per matrix, k / 256
+  int ks;                       // warps that split K for one row slab (divides nblk and the warps per CTA)
+  const __half* xplanes;        // [x rows][2][k] activation planes
+  const float* xsum32;          // [x rows][k/32] sums of x over 32 columns (Q4_K mins); null: use tiles
+  int x_by_assignment;          // 0: x row = token; 1: x row = assignment index
+  const int* counters;          // [0] = number of groups (active experts, plus the shared expert)
+  const int4* plan;             // per group {expert (-1: shared), rows, offset into assignments, 0}
+  const unsigned* assignments;  // [T*k]
+  int tokens, topk, max_groups;
+  __half* out_planes;           // DUAL: SwiGLU products as planes [T*k (+T)][2][rows]
+  float* out;                   // else: [T*k (+T)][rows]
+  unsigned* status;
+};
+
+constexpr int kGemvWarps = 24;
+
+DEVI void cp_async16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+DEVI void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> DEVI void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+DEVI uint4 lds128(uint32_t a) { uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v; }
+DEVI uint2 lds64(uint32_t a) { uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
+DEVI uint32_t lds32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+
+// D[16x8] += A[16x16] (f16, row) x B[16x8] (f16, col), fp32 accumulate. Thread (g = lane/4, j = lane%4):
+// a0/a1: rows g / g+8, k 2j,2j+1; a2/a3: same rows, k 2j+8,2j+9; b0: column g, k 2j,2j+1; b1: k 2j+8,2j+9;
+// c0,c1: row g, columns 2j,2j+1; c2,c3: row g+8.
+DEVI void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+DEVI uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+DEVI __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+// storage position of logical column e inside a plane
+DEVI int plane_pos(int e) { return (e & ~3) | ((e & 1) << 1) | ((e >> 1) & 1); }
+
+// ---- Q4_K -------------------------------------------------------------------------------------------
+// One 256-column block of 16 row slots staged at `slab` (row slot pitch PITCH: header 16 B, nibbles 128 B).
+// value = d*sc*q - dmin*m (kogarashi kernels/native.cu:26-34). `bcol`: this lane's B plane (column
+// g = lane/4 -> token g/2, hi or lo) at the block's first column, or null for an empty column.
+template <int PITCH, bool MINS_TILE>
+DEVI void q4k_block_f16(uint32_t slab, int lane, const __half* bcol, const float* xsum, float (&facc)[2]) {
+  const int g = lane >> 2, j = lane & 3;
+  const uint32_t r0 = slab + g * PITCH, r1 = slab + (g + 8) * PITCH;
+  const uint4 h0 = lds128(r0), h1 = lds128(r1);
+  // six-bit scales / mins of the eight sub-blocks, packed four per word
+  const uint32_t sc0[2] = {h0.y & 0x3F3F3F3Fu, (h0.w & 0x0F0F0F0Fu) | ((h0.y >> 2) & 0x30303030u)};
+  const uint32_t sc1[2] = {h1.y & 0x3F3F3F3Fu, (h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u)};
+  const uint32_t mn0[2] = {h0.z & 0x3F3F3F3Fu, ((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u)};
+  const uint32_t mn1[2] = {h1.z & 0x3F3F3F3Fu, ((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u)};
+  const __half2 k1024 = __float2half2_rn(1024.f);
+  float c[4] = {0.f, 0.f, 0.f, 0.f};      // sum over the block of sc * q * x   (rows g, g+8; columns 2j, 2j+1)
+  float cm[4] = {0.f, 0.f, 0.f, 0.f};     // sum over the block of m * x        (MINS_TILE only)
+#pragma unroll
+  for (int gp = 0; gp < 4; ++gp) {
+    // byte [sc, 0x64] pairs -> half2(1024 + sc) - 1024 = (sc, sc), exact
+    const int sel = (gp & 1) ? 0x4342 : 0x4140;        // bytes 2,3 or 0,1 of the scale word: [lo, 0x64, hi, 0x64]
+    const uint32_t w0s = sc0[gp >> 1], w1s = sc1[gp >> 1];
+    const __half2 p0 = __hsub2(u32_as_h2(__byte_perm(w0s, 0x64646464u, sel)), k1024);   // (sc[2gp], sc[2gp+1]) row g
+    const __half2 p1 = __hsub2(u32_as_h2(__byte_perm(w1s, 0x64646464u, sel)), k1024);   // row g+8
+    const __half2 sl0 = __low2half2(p0), sh0 = __high2half2(p0), sl1 = __low2half2(p1), sh1 = __high2half2(p1);
+    // low nibbles: (1024 + q) * sc - 1024 * sc; high nibbles: (1024 + 16 q) * sc/16 - 64 * sc
+    const __half2 bl0 = __hmul2(sl0, __float2half2_rn(-1024.f)), bl1 = __hmul2(sl1, __float2half2_rn(-1024.f));
+    const __half2 mh0 = __hmul2(sh0, __float2half2_rn(0.0625f)), mh1 = __hmul2(sh1, __float2half2_rn(0.0625f));
+    const __half2 bh0 = __hmul2(sh0, __float2half2_rn(-64.f)), bh1 = __hmul2(sh1, __float2half2_rn(-64.f));
+    const uint2 w0 = lds64(r0 + 16 + gp * 32 + 8 * j), w1 = lds64(r1 + 16 + gp * 32 + 8 * j);
+    uint4 blo = make_uint4(0, 0, 0, 0), bhi = make_uint4(0, 0, 0, 0);
+    if (bcol) {
+      blo = __ldg(reinterpret_cast<const uint4*>(bcol + gp * 64 + 8 * j));
+      bhi = __ldg(reinterpret_cast<const uint4*>(bcol + gp * 64 + 32 + 8 * j));
+    }
+    const uint32_t words0[2] = {w0.x, w0.y}, words1[2] = {w1.x, w1.y};
+    const uint32_t bl[4] = {blo.x, blo.y, blo.z, blo.w}, bh[4] = {bhi.x, bhi.y, bhi.z, bhi.w};
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {          // the two 16-column slabs of a 32-column sub-block
+      const uint32_t a = words0[s], b = words1[s];
+      // low nibbles -> sub-block 2gp
+      uint32_t a0 = h2_as_u32(__hfma2(u32_as_h2((a & 0x000F000Fu) | 0x64006400u), sl0, bl0));
+      uint32_t a2 = h2_as_u32(__hfma2(u32_as_h2(((a >> 8) & 0x000F000Fu) | 0x64006400u), sl0, bl0));
+      uint32_t a1 = h2_as_u32(__hfma2(u32_as_h2((b & 0x000F000Fu) | 0x64006400u), sl1, bl1));
+      uint32_t a3 = h2_as_u32(__hfma2(u32_as_h2(((b >> 8) & 0x000F000Fu) | 0x64006400u), sl1, bl1));
+      mma_f16(c, a0, a1, a2, a3, bl[2 * s], bl[2 * s + 1]);
+      // high nibbles -> sub-block 2gp + 1
+      a0 = h2_as_u32(__hfma2(u32_as_h2((a & 0x00F000F0u) | 0x64006400u), mh0, bh0));
+      a2 = h2_as_u32(__hfma2(u32_as_h2(((a >> 8) & 0x00F000F0u) | 0x64006400u), mh0, bh0));
+      a1 = h2_as_u32(__hfma2(u32_as_h2((b & 0x00F000F0u) | 0x64006400u), mh1, bh1));
+      a3 = h2_as_u32(__hfma2(u32_as_h2(((b >> 8) & 0x00F000F0u) | 0x64006400u), mh1, bh1));
+      mma_f16(c, a0, a1, a2, a3, bh[2 * s], bh[2 * s + 1]);
+      if (MINS_TILE) {
+        // the min of a sub-block as a constant row of the A operand: the tile sums m * x over the slab
+        const int msel = (gp & 1) ? 0x4342 : 0x4140;
+        const __half2 q0 = __hsub2(u32_as_h2(__byte_perm(mn0[gp >> 1], 0x64646464u, msel)), k1024);
+        const __half2 q1 = __hsub2(u32_as_h2(__byte_perm(mn1[gp >> 1], 0x64646464u, msel)), k1024);
+        const uint32_t ml0 = h2_as_u32(__low2half2(q0)), mh0u = h2_as_u32(__high2half2(q0));
+        const uint32_t ml1 = h2_as_u32(__low2half2(q1)), mh1u = h2_as_u32(__high2half2(q1));
+        mma_f16(cm, ml0, ml1, ml0, ml1, bl[2 * s], bl[2 * s + 1]);
+        mma_f16(cm, mh0u, mh1u, mh0u, mh1u, bh[2 * s], bh[2 * s + 1]);
+      }
+    }
+  }
+  const float d0 = half_lo(h0.x), dm0 = half_hi(h0.x), d1 = half_lo(h1.x), dm1 = half_hi(h1.x);
+  float m0 = 0.f, m1 = 0.f;
+  if (MINS_TILE) {
+    m0 = cm[0] + cm[1];
+    m1 = cm[2] + cm[3];
+  } else if (xsum) {
+    const float4 s0 = __ldg(reinterpret_cast<const float4*>(xsum)), s1 = __ldg(reinterpret_cast<const float4*>(xsum) + 1);
+    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const uint32_t wa = mn0[q >> 2], wb = mn1[q >> 2];
+      const float fa = (q & 3) == 0 ? byte_magic<0>(wa) : (q & 3) == 1 ? byte_magic<1>(wa) : (q & 3) == 2 ? byte_magic<2>(wa) : byte_magic<3>(wa);
+      const float fb = (q & 3) == 0 ? byte_magic<0>(wb) : (q & 3) == 1 ? byte_magic<1>(wb) : (q & 3) == 2 ? byte_magic<2>(wb) : byte_magic<3>(wb);
+      m0 = fmaf(fa - kMagic, sv[q], m0);
+      m1 = fmaf(fb - kMagic, sv[q], m1);
+    }
+  }
+  facc[0] += d0 * (c[0] + c[1]) - dm0 * m0;
+  facc[1] += d1 * (c[2] + c[3]) - dm1 * m1;
+}
+
+// ---- Q6_K (row-aligned device layout: per block ql 128 | qh 64 | int8 scales 16; d in a trailing chunk) --
+// value = d * scale * (q - 32) (kogarashi kernels/native.cu:35-40). Row slot: 208 data bytes, then the 16-byte
+// chunk of the row tail that holds this block's f16 d at byte `doff`.
+template <int PITCH>
+DEVI void q6k_block_f16(uint32_t slab, int lane, int doff, const __half* bcol, float (&facc)[2]) {
+  const int g = lane >> 2, j = lane & 3;
+  const uint32_t r0 = slab + g * PITCH, r1 = slab + (g + 8) * PITCH;
+  const uint4 s0v = lds128(r0 + 192), s1v = lds128(r1 + 192);
+  const uint32_t sw0[4] = {s0v.x ^ 0x80808080u, s0v.y ^ 0x80808080u, s0v.z ^ 0x80808080u, s0v.w ^ 0x80808080u};
+  const uint32_t sw1[4] = {s1v.x ^ 0x80808080u, s1v.y ^ 0x80808080u, s1v.z ^ 0x80808080u, s1v.w ^ 0x80808080u};
+  const uint32_t dw0 = lds32(r0 + 208 + (doff & ~3)), dw1 = lds32(r1 + 208 + (doff & ~3));
+  const float d0 = (doff & 2) ? half_hi(dw0) : half_lo(dw0), d1 = (doff & 2) ? half_hi(dw1) : half_lo(dw1);
+  const __half2 k1056 = __float2half2_rn(1056.f);      // 1024 (magic) + 32 (code offset)
+  float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+#pragma unroll
+    for (int lh = 0; lh < 2; ++lh) {
+      const uint32_t q0h = lds32(r0 + 128 + n * 32 + lh * 16 + 4 * j), q1h = lds32(r1 + 128 + n * 32 + lh * 16 + 4 * j);
+#pragma unroll
+      for (int gb = 0; gb < 2; ++gb) {
+        const uint32_t w0 = lds32(r0 + n * 64 + gb * 32 + lh * 16 + 4 * j), w1 = lds32(r1 + n * 64 + gb * 32 + lh * 16 + 4 * j);
+        const int col = n * 128 + gb * 32 + lh * 16 + 4 * j;       // columns of the low-nibble group; +64: high nibbles
+        uint2 blo = make_uint2(0, 0), bhi = make_uint2(0, 0);
+        if (bcol) {
+          blo = __ldg(reinterpret_cast<const uint2*>(bcol + col));
+          bhi = __ldg(reinterpret_cast<const uint2*>(bcol + col + 64));
+        }
+#pragma unroll
+        for (int hi = 0; hi < 2; ++hi) {
+          const uint32_t c0 = hi ? (((w0 >> 4) & 0x0F0F0F0Fu) | ((q0h >> (2 * gb)) & 0x30303030u))
+                                 : ((w0 & 0x0F0F0F0Fu) | ((q0h << (4 - 2 * gb)) & 0x30303030u));
+          const uint32_t c1 = hi ? (((w1 >> 4) & 0x0F0F0F0Fu) | ((q1h >> (2 * gb)) & 0x30303030u))
+                                 : ((w1 & 0x0F0F0F0Fu) | ((q1h << (4 - 2 * gb)) & 0x30303030u));
+          // bytes [b0, 0x64, b2, 0x64] = half2(1024 + b0, 1024 + b2); minus 1056 -> q - 32, exact
+          const uint32_t f0 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(c0, 0x64646464u, 0x4240)), k1056));
+          const uint32_t f2 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(c0, 0x64646464u, 0x4341)), k1056));
+          const uint32_t f1 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(c1, 0x64646464u, 0x4240)), k1056));
+          const uint32_t f3 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(c1, 0x64646464u, 0x4341)), k1056));
+          float c[4] = {0.f, 0.f, 0.f, 0.f};
+          mma_f16(c, f0, f1, f2, f3, hi ? bhi.x : blo.x, hi ? bhi.y : blo.y);
+          const int si = 8 * n + 2 * (gb + 2 * hi) + lh;            // scale index of this 16-column group
+          const uint32_t wa = sw0[si >> 2], wb = sw1[si >> 2];
+          const float fa = ((si & 3) == 0 ? byte_magic<0>(wa) : (si & 3) == 1 ? byte_magic<1>(wa) : (si & 3) == 2 ? byte_magic<2>(wa) : byte_magic<3>(wa)) - (kMagic + 128.f);
+          const float fb = ((si & 3) == 0 ? byte_magic<0>(wb) : (si & 3) == 1 ? byte_magic<1>(wb) : (si & 3) == 2 ? byte_magic<2>(wb) : byte_magic<3>(wb)) - (kMagic + 128.f);
+          a0 = fmaf(fa, c[0] + c[1], a0);
+          a1 = fmaf(fb, c[2] + c[3], a1);
+        }
+      }
+    }
+  }
+  facc[0] += d0 * a0;
+  facc[1] += d1 * a1;
+}
+
+template <int FMT> struct GemvLayout;
+template <> struct GemvLayout<kGemvQ4K> {
+  static constexpr int kBlockBytes = 144, kPitch = 160, kStages = 3, kChunks = 9;     // 16-byte chunks per row slot
+};
+template <> struct GemvLayout<kGemvQ6KR> {
+  static constexpr int kBlockBytes = 208, kPitch = 240, kStages = 2, kChunks = 14;    // 13 data chunks + the d chunk
+};
+
+__host__ __device__ inline int gemv_smem_bytes(int pitch, int stages, int ks) {
+  return kGemvWarps * stages * 16 * pitch + kGemvWarps * 4 * 16 * 4 + 16;
+}
+
+template <int FMT, int DUAL, bool MINS_TILE>
+__global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const GemvArgs a) {
+  using LY = GemvLayout<FMT>;
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t ring = smem_u32(smem) + warp * (LY::kStages * 16 * LY::kPitch);
+  float* red = reinterpret_cast<float*>(smem + kGemvWarps * LY::kStages * 16 * LY::kPitch);   // [warp][token 4][row 16]
+  pdl_wait();
+  pdl_launch();
+  constexpr int RPT = DUAL ? 8 : 16;                     // weight rows of matrix 0 per slab
+  const int tiles_per_group = (a.rows + RPT - 1) / RPT;
+  const int nb_per = a.nblk / a.ks;
+  const long long items = (long long)a.max_groups * tiles_per_group * a.ks;
+  const int groups = __ldcg(a.counters);
+  const int g4 = lane >> 2, j = lane & 3;
+  for (long long item = (long long)blockIdx.x * kGemvWarps + warp; item < items; item += (long long)gridDim.x * kGemvWarps) {
+    const int tile = int(item / a.ks), kpart = int(item % a.ks);
+    const int grp = tile / tiles_per_group, row0 = (tile % tiles_per_group) * RPT;
+    const bool live = grp < groups;          // uniform over the ks warps of a slab (they share `tile`)
+    int4 pl = make_int4(0, 0, 0, 0);
+    if (live) pl = __ldcg(a.plan + grp);
+    const int e = pl.x, count = live ? pl.y : 0, offset = pl.z;
+    const int valid = min(RPT, a.rows - row0);
+    const int b_first = kpart * nb_per;
+    // ---- weight stream: 16 row slots x one block per stage --------------------------------------------
+    auto issue = [&](int b, int stage) {
+      const uint32_t dst = ring + stage * (16 * LY::kPitch);
+      for (int c = lane; c < 16 * LY::kChunks; c += 32) {
+        const int slot = c / LY::kChunks, part = c % LY::kChunks;
+        const int m = DUAL ? (slot >> 3) : 0, r = DUAL ? (slot & 7) : slot;
+        if (r < valid) {
+          const uint8_t* base = (e < 0 ? a.w_shared[m] : a.w[m] + size_t(e) * a.expert_stride[m]) + size_t(row0 + r) * a.row_bytes;
+          const uint8_t* src;
+          if (FMT == kGemvQ4K) src = base + b * 144 + part * 16;
+          else src = part < 13 ? base + b * 208 + part * 16 : base + a.nblk * 208 + ((2 * b) & ~15);
+          cp_async16(dst + slot * LY::kPitch + part * 16, src);
+        }
+      }
+    };
+    if (count > 0) {
+#pragma unroll
+      for (int s = 0; s < LY::kStages - 1; ++s) {
+        if (s < nb_per) issue(b_first + s, s);
+        cp_async_commit();
+      }
+    }
+    for (int c0 = 0; c0 < count; c0 += 4) {               // up to four tokens of this group per pass
+      // this lane's B column g4 -> token g4/2 of the pass, hi (even) or lo (odd) plane
+      const int tcol = c0 + (g4 >> 1);
+      const __half* plane = nullptr;
+      const float* xs = nullptr;
+      if (tcol < count) {
+        const int as = e < 0 ? a.tokens * a.topk + tcol : int(__ldcg(a.assignments + offset + tcol));
+        const int xrow = a.x_by_assignment ? as : (e < 0 ? tcol : as / a.topk);
+        plane = a.xplanes + (size_t(xrow) * 2 + (g4 & 1)) * a.k;
+      }
+      // this lane's result column pair 2j,2j+1 -> token j of the pass
+      const int tres = c0 + j;
+      int ares = -1;
+      if (tres < count) {
+        ares = e < 0 ? a.tokens * a.topk + tres : int(__ldcg(a.assignments + offset + tres));
+        if (!MINS_TILE && a.xsum32) {
+          const int xrow = a.x_by_assignment ? ares : (e < 0 ? tres : ares / a.topk);
+          xs = a.xsum32 + size_t(xrow) * (a.k / 32);
+        }
+      }
+      if (c0 > 0) {                                       // later passes stream the blocks again (L2 hits)
+#pragma unroll
+        for (int s = 0; s < LY::kStages - 1; ++s) {
+          if (s < nb_per) issue(b_first + s, s);
+          cp_async_commit();
+        }
+      }
+      float facc[2] = {0.f, 0.f};
+      for (int i = 0; i < nb_per; ++i) {
+        const int nxt = i + LY::kStages - 1;
+        if (nxt < nb_per) issue(b_first + nxt, nxt % LY::kStages);
+        cp_async_commit();
+        cp_async_wait<LY::kStages - 1>();
+        __syncwarp();
+        const int b = b_first + i;
+        const uint32_t slab = ring + (i % LY::kStages) * (16 * LY::kPitch);
+        if (FMT == kGemvQ4K) q4k_block_f16<LY::kPitch, MINS_TILE>(slab, lane, plane ? plane + b * 256 : nullptr, xs ? xs + b * 8 : nullptr, facc);
+        else q6k_block_f16<LY::kPitch>(slab, lane, (2 * b) & 15, plane ? plane + b * 256 : nullptr, facc);
+        __syncwarp();
+      }
+      cp_async_wait<0>();
+      // ---- sum over the K split (fixed order) and store ------------------------------------------------
+      if (a.ks > 1) {
+        const int bar = 1 + warp / a.ks;                  // one named barrier per slab group (<= 12)
+        red[(warp * 4 + j) * 16 + g4] = facc[0];
+        red[(warp * 4 + j) * 16 + 8 + g4] = facc[1];
+        named_barrier(bar, a.ks * 32);
+        if (kpart == 0) {
+          facc[0] = 0.f;
+          facc[1] = 0.f;
+          for (int q = 0; q < a.ks; ++q) {
+            facc[0] += red[((warp + q) * 4 + j) * 16 + g4];
+            facc[1] += red[((warp + q) * 4 + j) * 16 + 8 + g4];
+          }
+        }
+        named_barrier(bar, a.ks * 32);                    // partials are consumed before the next pass overwrites them
+      }
+      if (kpart == 0 && ares >= 0) {
+        if (DUAL) {
+          if (g4 < valid) {
+            const float h = silu_mul(facc[0], facc[1]);
+            const __half hi = __float2half_rn(h);
+            const __half lo = __float2half_rn(h - __half2float(hi));
+            __half* dst = a.out_planes + size_t(ares) * 2 * a.rows + plane_pos(row0 + g4);
+            dst[0] = hi;
+            dst[a.rows] = lo;
+          }
+        } else {
+          if (g4 < valid) a.out[size_t(ares) * a.rows + row0 + g4] = facc[0];
+          if (g4 + 8 < valid) a.out[size_t(ares) * a.rows + row0 + g4 + 8] = facc[1];
+        }
+      }
+    }
+  }
+}
+
+// ---- activation rows -> planes (and per-32 sums) ------------------------------------------------------
+// One block per row. planes[row] = k fp16 hi values then k fp16 lo values, groups of four as [x0,x2,x1,x3].
+DEVI void act_planes_row(const float* x, int k, __half* planes, float* xsum32) {
+  for (int base = 0; base < k / 4; base += blockDim.x) {            // uniform trip count: shuffles below
+    const int i = base + threadIdx.x;
+    const float4 v = i < k / 4 ? __ldcg(reinterpret_cast<const float4*>(x) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    const float vals[4] = {v.x, v.z, v.y, v.w};                     // storage order
+    __half hi[4], lo[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      hi[q] = __float2half_rn(vals[q]);
+      lo[q] = __float2half_rn(vals[q] - __half2float(hi[q]));
+    }
+    if (i < k / 4) {
+      *reinterpret_cast<uint2*>(planes + 4 * i) = make_uint2(h2_as_u32(__halves2half2(hi[0], hi[1])), h2_as_u32(__halves2half2(hi[2], hi[3])));
+      *reinterpret_cast<uint2*>(planes + k + 4 * i) = make_uint2(h2_as_u32(__halves2half2(lo[0], lo[1])), h2_as_u32(__halves2half2(lo[2], lo[3])));
+    }
+    if (xsum32) {
+      float p = (v.x + v.y) + (v.z + v.w);
+      p += __shfl_xor_sync(0xffffffffu, p, 1);
+      p += __shfl_xor_sync(0xffffffffu, p, 2);
+      p += __shfl_xor_sync(0xffffffffu, p, 4);
+      if (i < k / 4 && (i & 7) == 0) xsum32[i >> 3] = p;
+    }
+  }
+}
+
+}  // namespace dmoe

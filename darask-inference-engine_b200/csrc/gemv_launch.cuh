@@ -1,0 +1,37 @@
+// Host side of expert_gemv.cuh: K split selection and launch.
+#pragma once
+#include "expert_gemv.cuh"
+#include "stream_launch.cuh"
+
+namespace dmoe {
+
+// Warps per row slab: the largest divisor of the block count (and of the warps per CTA) that still
+// lets every slab x split item start in the first wave of the persistent grid.
+inline int gemv_k_split(int nblk, long long slabs, int sms) {
+  const long long warps = (long long)sms * kGemvWarps;
+  int best = 1;
+  for (int ks = 1; ks <= nblk && ks <= 12; ++ks)
+    if (nblk % ks == 0 && kGemvWarps % ks == 0 && slabs * ks <= warps) best = ks;
+  return best;
+}
+
+template <int FMT, int DUAL, bool MINS_TILE>
+inline cudaError_t launch_gemv(GemvArgs a, cudaStream_t stream) {
+  using LY = GemvLayout<FMT>;
+  if (a.row_bytes % 16 || a.expert_stride[0] % 16 || a.expert_stride[1] % 16 || a.k % 256 || a.rows < 1 || a.max_groups < 1)
+    return cudaErrorInvalidValue;
+  constexpr int RPT = DUAL ? 8 : 16;
+  const long long slabs = (long long)a.max_groups * ((a.rows + RPT - 1) / RPT);
+  a.ks = gemv_k_split(a.nblk, slabs, sm_count());
+  const int smem = gemv_smem_bytes(LY::kPitch, LY::kStages, a.ks);
+  auto kernel = expert_gemv_kernel<FMT, DUAL, MINS_TILE>;
+  static bool configured = false;       // one opt-in per instantiation (and process)
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  return launch_pdl(kernel, dim3(sm_count()), dim3(kGemvWarps * 32), size_t(smem), stream, a);
+}
+
+}  // namespace dmoe

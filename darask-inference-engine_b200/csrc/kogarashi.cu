@@ -1,5 +1,5 @@
 // Kogarashi (Qwen3.5-MoE, GGUF Q4_K / Q6_K) MoE FFN layer for 1..N tokens as four launches:
-//   router projection + top-k + dispatch permutation   (reference: `gemv` on ffn_gate_inp, `route`)
+//   router projection + top-k + dispatch permutation + activation planes  (reference: `gemv` on ffn_gate_inp, `route`)
 //   gate/up products with SwiGLU                        (`gemv` x2, `activate`, also the shared expert)
 //   down products                                       (`gemv`, also the shared expert)
 //   weighted combine into the residual stream           (`combine`)
@@ -8,6 +8,7 @@
 #include "../../include/darask_moe_b200.h"
 #include "route_kernels.cuh"
 #include "stream_launch.cuh"
+#include "gemv_launch.cuh"
 #include <cstdio>
 
 namespace dmoe {
@@ -51,7 +52,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct KogarashiWs {
   int* counters; unsigned* done; unsigned* status; int* active; unsigned* ranges; unsigned* assignments;
-  float* sg; float* h; float* y; size_t bytes;
+  int4* plan; float* sg; __half* xplanes; float* xsum32; __half* hplanes; float* y; size_t bytes;
 };
 static KogarashiWs carve(void* base, int hidden, int inter, int experts, int topk, int tokens) {
   KogarashiWs w;
@@ -64,9 +65,12 @@ static KogarashiWs carve(void* base, int hidden, int inter, int experts, int top
   w.active = reinterpret_cast<int*>(take(size_t(experts) * 4));
   w.ranges = reinterpret_cast<unsigned*>(take(size_t(experts) * 8));
   w.assignments = reinterpret_cast<unsigned*>(take(size_t(tokens) * topk * 4));
+  w.plan = reinterpret_cast<int4*>(take(size_t(experts + 1) * 16));
   w.sg = reinterpret_cast<float*>(take(size_t(tokens) * 4));
+  w.xplanes = reinterpret_cast<__half*>(take(size_t(tokens) * 2 * hidden * 2));
+  w.xsum32 = reinterpret_cast<float*>(take(size_t(tokens) * (hidden / 32) * 4));
   const size_t rows = size_t(tokens) * topk + tokens;
-  w.h = reinterpret_cast<float*>(take(rows * inter * 4));
+  w.hplanes = reinterpret_cast<__half*>(take(rows * 2 * inter * 2));
   w.y = reinterpret_cast<float*>(take(rows * hidden * 4));
   w.bytes = off;
   return w;
@@ -78,9 +82,11 @@ static int row_bytes_of(int ty, int k) {
 }
 
 template <int DUAL>
-static cudaError_t launch_ggml(int ty, const StreamArgs& a, int max_rows, cudaStream_t st) {
-  if (ty == DARASK_GGML_Q4_K) return launch_stream<kFmtQ4K, DUAL, kActSilu>(a, max_rows, st);
-  if (ty == DARASK_GGML_Q6_K) return launch_stream<kFmtQ6KR, DUAL, kActSilu>(a, max_rows, st);
+static cudaError_t launch_gemv_ggml(int ty, const GemvArgs& a, cudaStream_t st) {
+  // gate/up read per-32 sums of x written with the planes; the down projection has no such sums and
+  // lets the tensor-core tiles form the Q4_K min term instead
+  if (ty == DARASK_GGML_Q4_K) return DUAL ? launch_gemv<kGemvQ4K, DUAL, false>(a, st) : launch_gemv<kGemvQ4K, DUAL, true>(a, st);
+  if (ty == DARASK_GGML_Q6_K) return launch_gemv<kGemvQ6KR, DUAL, false>(a, st);
   return cudaErrorInvalidValue;
 }
 
@@ -135,10 +141,11 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
   r.w = d->router_w; r.extra = shared ? d->sh_inp_w : nullptr; r.x = d->n; r.row_bias = d->router_bias; r.logits = d->logits; r.extra_out = w.sg;
   r.hidden = H; r.rows = E; r.ld = E; r.tokens = T;
   r.route = RouteArgs{d->logits, E, E, K, T, nullptr, 1.f, d->ids, d->prob, nullptr};
-  r.perm = PermuteArgs{d->ids, T, K, E, w.assignments, w.ranges, w.active, w.counters, w.status};
+  r.perm = PermuteArgs{d->ids, T, K, E, w.assignments, w.ranges, w.active, w.counters, w.status, w.plan, shared ? T : 0};
   r.done = w.done; r.fuse = 1;
-  const int rblocks = E + (shared ? 1 : 0);
-  const size_t hist = size_t(E + 1) * 4;
+  r.planes = w.xplanes; r.xsum32 = w.xsum32;
+  const int rblocks = E + (shared ? 1 : 0) + T;
+  const size_t hist = size_t(E + 1) * 4 + size_t(T * K <= kRouteIdCache ? T * K : 0) * 4;
   const int mask = d->stage_mask ? d->stage_mask : 15;
   cudaError_t e = cudaSuccess;
   if (!(mask & 1)) {}
@@ -149,28 +156,29 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
   if (e) return e;
 
   // 2. gate/up + SwiGLU for every (token, slot) and the shared expert
-  StreamArgs a = {};
+  const int max_groups = (T * K < E ? T * K : E) + (shared ? 1 : 0);
+  GemvArgs a = {};
   a.w[0] = static_cast<const uint8_t*>(d->gate_w); a.w[1] = static_cast<const uint8_t*>(d->up_w);
   a.w_shared[0] = static_cast<const uint8_t*>(d->sh_gate_w); a.w_shared[1] = static_cast<const uint8_t*>(d->sh_up_w);
   a.row_bytes = row_bytes_of(d->gate_ty, H);
   a.expert_stride[0] = a.expert_stride[1] = (unsigned long long)a.row_bytes * F;
   a.k = H; a.rows = F; a.nblk = H / 256;
-  a.x = d->n; a.x_by_assignment = 0;
-  a.counters = w.counters; a.active = w.active; a.ranges = w.ranges; a.assignments = w.assignments;
-  a.tokens = T; a.topk = K; a.has_shared = shared ? 1 : 0;
-  a.out = w.h; a.status = w.status;
-  if ((mask & 2) && (e = launch_ggml<1>(d->gate_ty, a, T, st))) return e;
+  a.xplanes = w.xplanes; a.xsum32 = w.xsum32; a.x_by_assignment = 0;
+  a.counters = w.counters + 2; a.plan = w.plan; a.assignments = w.assignments;
+  a.tokens = T; a.topk = K; a.max_groups = max_groups;
+  a.out_planes = w.hplanes; a.out = nullptr; a.status = w.status;
+  if ((mask & 2) && (e = launch_gemv_ggml<1>(d->gate_ty, a, st))) return e;
 
   // 3. down
-  StreamArgs b = a;
+  GemvArgs b = a;
   b.w[0] = static_cast<const uint8_t*>(d->down_w); b.w[1] = nullptr;
   b.w_shared[0] = static_cast<const uint8_t*>(d->sh_down_w); b.w_shared[1] = nullptr;
   b.row_bytes = row_bytes_of(d->down_ty, F);
   b.expert_stride[0] = (unsigned long long)b.row_bytes * H; b.expert_stride[1] = 0;
   b.k = F; b.rows = H; b.nblk = F / 256;
-  b.x = w.h; b.x_by_assignment = 1;
-  b.out = w.y;
-  if ((mask & 4) && (e = launch_ggml<0>(d->down_ty, b, T, st))) return e;
+  b.xplanes = w.hplanes; b.xsum32 = nullptr; b.x_by_assignment = 1;
+  b.out_planes = nullptr; b.out = w.y;
+  if ((mask & 4) && (e = launch_gemv_ggml<0>(d->down_ty, b, st))) return e;
 
   // 4. combine
   if (!(mask & 8)) return cudaSuccess;

@@ -136,21 +136,23 @@ struct PermuteArgs {
   unsigned* assignments;   // [T*k]
   unsigned* ranges;        // [E][2]
   int* active;             // [E]
-  int* counters;           // [4]: n_active, total rows, 0, 0
+  int* counters;           // [4]: n_active, total rows, number of plan entries, 0
   unsigned* status;
+  int4* plan;              // optional: per active expert {id, rows, offset, 0}, then (shared_rows > 0) {-1, shared_rows, 0, 0}
+  int shared_rows;
 };
 
 // Runs in one thread block (any size that is a multiple of 32, >= 64). `hist` : E + 1 ints of
-// shared memory.
-DEVI void permute_block(const PermuteArgs& p, int* hist) {
+// shared memory. `ids`: the routes, p.ids or a copy of them in shared memory.
+DEVI void permute_block(const PermuteArgs& p, int* hist, const int* ids) {
   const int tid = threadIdx.x, nthr = blockDim.x;
   const int n = p.tokens * p.topk, E = p.experts, K = p.topk;
   for (int e = tid; e <= E; e += nthr) hist[e] = 0;
   __syncthreads();
   for (int a = tid; a < n; a += nthr) {
-    const int e = p.ids[a];
+    const int e = ids[a];
     bool ok = e >= 0 && e < E;
-    for (int j = a - a % K; ok && j < a; ++j) ok = p.ids[j] != e;
+    for (int j = a - a % K; ok && j < a; ++j) ok = ids[j] != e;
     if (ok) atomicAdd(&hist[e], 1);
     else atomicOr(p.status, kStatusBadRoute);
   }
@@ -182,7 +184,10 @@ DEVI void permute_block(const PermuteArgs& p, int* hist) {
         const int c = hist[e];
         p.ranges[2 * e] = c;
         p.ranges[2 * e + 1] = off;
-        if (c) p.active[aoff++] = e;
+        if (c) {
+          if (p.plan) p.plan[aoff] = make_int4(e, c, off, 0);
+          p.active[aoff++] = e;
+        }
         hist[e] = off;          // becomes the write cursor
         off += c;
       }
@@ -190,14 +195,16 @@ DEVI void permute_block(const PermuteArgs& p, int* hist) {
     if (tid == 31) {
       p.counters[0] = arun;
       p.counters[1] = run;
+      p.counters[2] = arun + (p.shared_rows > 0 ? 1 : 0);
+      if (p.plan && p.shared_rows > 0) p.plan[arun] = make_int4(-1, p.shared_rows, 0, 0);
     }
     __syncwarp();
     // stable placement, 32 assignments per round
     for (int base = 0; base < n; base += 32) {
       const int a = base + tid;
-      int e = a < n ? p.ids[a] : -1;
+      int e = a < n ? ids[a] : -1;
       bool ok = e >= 0 && e < E;
-      for (int j = a - a % K; ok && j < a; ++j) ok = p.ids[j] != e;
+      for (int j = a - a % K; ok && j < a; ++j) ok = ids[j] != e;
       if (!ok) e = -1 - tid;    // unique key: never matches another lane
       const unsigned same = __match_any_sync(0xffffffffu, e);
       const int rank = __popc(same & ((1u << tid) - 1u));

@@ -4,6 +4,7 @@
 // route_hayate.cu (fast math: Hayate).
 #pragma once
 #include "route_impl.cuh"
+#include "expert_gemv.cuh"
 
 namespace dmoe {
 
@@ -20,7 +21,7 @@ __global__ void __launch_bounds__(1024) permute_kernel(PermuteArgs p) {
   extern __shared__ int hist[];
   pdl_wait();
   pdl_launch();
-  permute_block(p, hist);
+  permute_block(p, hist, p.ids);
 }
 
 // ---- router projection -----------------------------------------------------------------------
@@ -33,6 +34,8 @@ template <> DEVI float to_f32<float>(float v) { return v; }
 template <> DEVI float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> DEVI float to_f32<__half>(__half v) { return __half2float(v); }
 
+constexpr int kRouteIdCache = 2048;   // routes the fused kernel keeps in shared memory for the permutation
+
 struct RouterArgs {
   const void* w;        // [rows][hidden]
   const void* extra;    // [hidden] or null
@@ -44,6 +47,8 @@ struct RouterArgs {
   RouteArgs route;      // routing of the finished logits (route.logits == logits)
   PermuteArgs perm;
   unsigned* done;       // counter, zero before the launch; reset to zero by the last block
+  __half* planes;       // optional (float x only): blocks past the router rows write the activation planes
+  float* xsum32;        //   [T][2][hidden] and the per-32 sums [T][hidden/32] read by the expert kernels
   int fuse;             // 1: last block routes and permutes
 };
 
@@ -54,6 +59,17 @@ __global__ void __launch_bounds__(128) router_kernel(RouterArgs a) {
   __shared__ unsigned last;
   constexpr int VEC = 16 / sizeof(WT);          // weights per 16-byte load
   const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int router_rows = a.rows + (a.extra ? 1 : 0);
+  if (row >= router_rows) {          // activation planes of token row - router_rows
+    pdl_wait();
+    pdl_launch();
+    if (sizeof(XT) == 4 && a.planes) {
+      const int t = row - router_rows;
+      act_planes_row(static_cast<const float*>(a.x) + size_t(t) * a.hidden, a.hidden, a.planes + size_t(t) * 2 * a.hidden,
+                     a.xsum32 ? a.xsum32 + size_t(t) * (a.hidden / 32) : nullptr);
+    }
+    return;                            // not counted: only the router rows gate the routing below
+  }
   const bool is_extra = row >= a.rows;
   const WT* wr = is_extra ? static_cast<const WT*>(a.extra) : static_cast<const WT*>(a.w) + size_t(row) * a.hidden;
   // weights do not depend on earlier kernels: fetch them before the dependency wait
@@ -102,14 +118,25 @@ __global__ void __launch_bounds__(128) router_kernel(RouterArgs a) {
   if (!a.fuse) return;
   // Last block to finish routes every token and builds the permutation.
   __threadfence();
-  if (tid == 0) last = atomicAdd(a.done, 1u) == gridDim.x - 1 ? 1u : 0u;
+  if (tid == 0) last = atomicAdd(a.done, 1u) == unsigned(router_rows) - 1 ? 1u : 0u;
   __syncthreads();
   if (!last) return;
   __threadfence();
   for (int token = warp; token < a.tokens; token += 4) route_token_any<MODE>(a.route, token, lane);
   __threadfence_block();
   __syncthreads();
-  if (a.perm.assignments) permute_block(a.perm, hist);
+  if (a.perm.assignments) {
+    // the routes of this block, copied once into shared memory (after the E + 1 histogram words)
+    const int n = a.tokens * a.route.topk;
+    const int* ids = a.perm.ids;
+    if (n <= kRouteIdCache) {
+      int* cache = hist + a.route.experts + 1;
+      for (int i = tid; i < n; i += 128) cache[i] = __ldcg(a.perm.ids + i);
+      __syncthreads();
+      ids = cache;
+    }
+    permute_block(a.perm, hist, ids);
+  }
   if (tid == 0) *a.done = 0u;
 }
 
