@@ -26,6 +26,18 @@ class KogarashiMoe(ctypes.Structure):
     ]
 
 
+class TsumujiMoe(ctypes.Structure):
+    """Mirror of `TsumujiMoe` in include/darask_moe_b200.h."""
+    _fields_ = [
+        ("hidden", c_int), ("inter", c_int), ("experts", c_int), ("topk", c_int), ("tokens", c_int),
+        ("router_w", c_void_p), ("experts_w", c_void_p), ("gs", c_void_p),
+        ("shared_gu", c_void_p), ("shared_down", c_void_p),
+        ("x", c_void_p), ("out", c_void_p), ("rlogits", c_void_p), ("sel", c_void_p), ("rw", c_void_p),
+        ("shared_gate", c_void_p), ("accumulate", c_int),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+    ]
+
+
 _SIGNATURES = {
     "darask_route_topk": (c_int, [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p,
                                   c_void_p, c_void_p]),
@@ -41,6 +53,9 @@ _SIGNATURES = {
     "darask_quantize_nvfp4_tiled": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "darask_quantize_fp8_block": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "darask_quantize_fp8_act": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p]),
+    "tsumuji_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "tsumuji_moe_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),
+    "tsumuji_moe_layer": (c_int, [ctypes.POINTER(TsumujiMoe), c_void_p]),
     "kogarashi_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "kogarashi_moe_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),
     "kogarashi_moe_layer": (c_int, [ctypes.POINTER(KogarashiMoe), c_void_p]),

@@ -1,31 +1,50 @@
-// Decode-path expert products for small token counts (GGUF Q4_K / Q6_K weights).
+// Decode-path expert products for small token counts (GGUF Q4_K / Q6_K and NVFP4 weights).
 //
 // Every warp is independent: it owns an 8- or 16-row slab of one expert and a contiguous share of
 // the 256-element blocks of K, streams that share HBM -> its private shared-memory ring with
 // 16-byte cp.async copies (2-3 blocks in flight per warp, ~100 KB per SM), and multiplies on
 // fp16 tensor-core tiles (mma.sync m16n8k16, fp32 accumulate):
-//   * A operand = the weight codes as exact small fp16 integers (Q4_K: q * sc <= 945; Q6_K: q - 32),
-//     built from the packed bytes with two bit operations per pair, no int->float conversion;
+//   * A operand = the weight codes as exact fp16 values (Q4_K: q * sc <= 945; Q6_K: q - 32; NVFP4:
+//     e2m1 * e4m3, at most six significant bits), built from the packed bytes without int->float
+//     conversions;
 //   * B operand = the activations split as x = hi + lo (two fp16, error <= 2^-22 |x|), one column
 //     pair per token, so one tile serves up to four tokens of the same expert;
 //   * fp16 x fp16 products are exact in fp32, the f16/f32 scales are applied to the tile sums.
 // The warps that share a row slab (K split) add their partial sums through shared memory in a
 // fixed order. No CTA-wide barrier exists after the prologue.
-// Activation rows are read as "planes": per row k fp16 hi values then k fp16 lo values, each
-// aligned group of four stored as [x0, x2, x1, x3] (the order the tile fragments want).
-// Replaces kogarashi kernels/native.cu:46-88 (`gemv`) and :97-99 (`activate`).
+// Activation rows are read as "planes": per row k fp16 hi values then k fp16 lo values; for the GGUF
+// formats each aligned group of four is stored as [x0, x2, x1, x3] (the order their tile fragments
+// want), for NVFP4 in natural order.
+// Replaces kogarashi kernels/native.cu:46-88 (`gemv`) and :97-99 (`activate`), tsumuji kernels/decode/
+// gemv.cu:64-158 (`moe_gate_up`, `moe_down`) and hayate cu/glm53/decode.cu:37-54 (`gate_up`, `down`).
 #pragma once
 #include "common.cuh"
+#include <cuda_fp4.h>
+#include <cuda_fp8.h>
 
 namespace dmoe {
 
-enum GemvFormat { kGemvQ4K = 0, kGemvQ6KR = 1 };
+enum GemvFormat { kGemvQ4K = 0, kGemvQ6KR = 1, kGemvNvfp4Linear = 2, kGemvNvfp4Tiled = 3 };
+// what the epilogue writes
+enum GemvOut {
+  kOutSiluPlanes = 0,    // DUAL: silu(g) * u as fp16 hi/lo planes (Kogarashi, Tsumuji)
+  kOutFloat = 1,         // rows as float32
+  kOutHayateProduct = 2, // DUAL: Hayate SwiGLU (clamps, bf16 roundings) as bf16 rows and as planes
+  kOutBf16 = 3           // rows rounded to bf16
+};
 
 struct GemvArgs {
   const uint8_t* w[2];          // routed experts: matrix 0 (gate or down) and matrix 1 (up)
   const uint8_t* w_shared[2];   // shared expert matrices (null when there is none)
   unsigned long long expert_stride[2];   // bytes between consecutive experts
-  int row_bytes;                // bytes of one row in global memory (multiple of 16)
+  int row_bytes;                // bytes of one row (of codes, for NVFP4) in global memory (multiple of 16)
+  const void* const* w_table;   // optional: per group the base pointer of its expert image (replaces w[0] + e * stride)
+  unsigned long long matrix_stride;      // w_table / Hayate images: bytes between gate | up | down inside an image
+  unsigned long long scale_offset[2];    // NVFP4: byte offset of the scale area from the matrix base (per matrix)
+  const uint8_t* gscale;        // per-matrix float32 multiplier: gscale + e * gscale_estride + m * gscale_mstride (null: 1)
+  unsigned long long gscale_estride, gscale_mstride;
+  const uint8_t* gscale_shared[2];       // the same for the shared expert (null: 1)
+  unsigned long long gscale_in_matrix[2]; // non-zero: the multiplier is the float32 at this byte offset of the matrix itself
   int k, rows, nblk;            // columns, rows per matrix, k / 256
   int ks;                       // warps that split K for one row slab (divides nblk and the warps per CTA)
   const __half* xplanes;        // [x rows][2][k] activation planes
@@ -36,7 +55,9 @@ struct GemvArgs {
   const unsigned* assignments;  // [T*k]
   int tokens, topk, max_groups;
   __half* out_planes;           // DUAL: SwiGLU products as planes [T*k (+T)][2][rows]
-  float* out;                   // else: [T*k (+T)][rows]
+  float* out;                   // kOutFloat: [T*k (+T)][rows]
+  __nv_bfloat16* out_bf16;      // kOutHayateProduct / kOutBf16: [T*k (+T)][rows]
+  int out_shared_row;           // output row of the shared expert's token t is out_shared_row + t (default T*k)
   unsigned* status;
 };
 
@@ -48,9 +69,10 @@ DEVI void cp_async16(uint32_t dst, const void* src) {
 DEVI void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> DEVI void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-DEVI uint4 lds128(uint32_t a) { uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a)); return v; }
-DEVI uint2 lds64(uint32_t a) { uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a)); return v; }
-DEVI uint32_t lds32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a)); return v; }
+// volatile + memory clobber: the loads must stay behind the cp.async waits that make the data visible
+DEVI uint4 lds128(uint32_t a) { uint4 v; asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a) : "memory"); return v; }
+DEVI uint2 lds64(uint32_t a) { uint2 v; asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a) : "memory"); return v; }
+DEVI uint32_t lds32(uint32_t a) { uint32_t v; asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a) : "memory"); return v; }
 
 // D[16x8] += A[16x16] (f16, row) x B[16x8] (f16, col), fp32 accumulate. Thread (g = lane/4, j = lane%4):
 // a0/a1: rows g / g+8, k 2j,2j+1; a2/a3: same rows, k 2j+8,2j+9; b0: column g, k 2j,2j+1; b1: k 2j+8,2j+9;
@@ -205,54 +227,163 @@ DEVI void q6k_block_f16(uint32_t slab, int lane, int doff, const __half* bcol, f
   facc[1] += d1 * a1;
 }
 
-template <int FMT> struct GemvLayout;
-template <> struct GemvLayout<kGemvQ4K> {
-  static constexpr int kBlockBytes = 144, kPitch = 160, kStages = 3, kChunks = 9;     // 16-byte chunks per row slot
-};
-template <> struct GemvLayout<kGemvQ6KR> {
-  static constexpr int kBlockBytes = 208, kPitch = 240, kStages = 2, kChunks = 14;    // 13 data chunks + the d chunk
-};
 
-__host__ __device__ inline int gemv_smem_bytes(int pitch, int stages, int ks) {
-  return kGemvWarps * stages * 16 * pitch + kGemvWarps * 4 * 16 * 4 + 16;
+// ---- NVFP4 (e2m1 codes, one e4m3 scale per 16 columns) -------------------------------------------------
+// Row slot: 128 code bytes of the block (two columns per byte, even column in the low nibble). The scale
+// byte of row slot `slot` and 16-column group `c` of the block sits at sbase(slot) + c for the linear
+// layout (tsumuji weights.rs:10-12) and inside 16-byte pieces of the 128x4 scale tiles for the tiled one
+// (hayate math.cuh:41-49); SCALES tells which.
+DEVI uint32_t e2m1x2_to_h2(uint32_t byte) {                             // one code byte -> half2(even column, odd column)
+  const __half2_raw r = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>(byte & 0xffu), __NV_E2M1);
+  return uint32_t(r.x) | (uint32_t(r.y) << 16);
+}
+DEVI void e2m1x4_to_h2(uint32_t w16, uint32_t& lo, uint32_t& hi) {     // two code bytes -> 2 x half2
+  lo = e2m1x2_to_h2(w16);
+  hi = e2m1x2_to_h2(w16 >> 8);
+}
+DEVI __half2 e4m3_dup_h2(uint32_t byte) {                                // one scale byte -> half2(s, s)
+  uint32_t out;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(out) : "h"((unsigned short)(byte | (byte << 8))));
+  return u32_as_h2(out);
+}
+// Address of the 16 scale bytes region helpers. Linear: the slot carries its 16 scale bytes behind the codes.
+// Tiled: the stage carries, behind the 16 row slots, pieces[piece][16] where a piece holds the four bytes
+// (scale columns 4tc..4tc+3) of the four rows p, p+32, p+64, p+96 of a 128-row tile.
+template <int FMT, int DUAL, int PITCH>
+DEVI uint32_t nvfp4_scale_addr(uint32_t slab, int slot, int c) {
+  if (FMT == kGemvNvfp4Linear) return slab + slot * PITCH + 128 + c;
+  // tiled: slot -> (matrix m, local base row pl, quarter q)
+  const int s8 = DUAL ? (slot & 7) : slot;
+  const int m = DUAL ? (slot >> 3) : 0;
+  const int pl = DUAL ? (s8 & 1) : (s8 & 3), q = DUAL ? (s8 >> 1) : (s8 >> 2);
+  const int piece = (DUAL ? (m * 2 + pl) : pl) * 4 + (c >> 2);
+  return slab + 16 * PITCH + piece * 16 + q * 4 + (c & 3);
+}
+template <int FMT, int DUAL, int PITCH>
+DEVI void nvfp4_block_f16(uint32_t slab, int lane, const __half* bcol, float (&facc)[2]) {
+  const int g = lane >> 2, j = lane & 3;
+  const uint32_t r0 = slab + g * PITCH, r1 = slab + (g + 8) * PITCH;
+  float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {                      // 32 columns per step: this lane owns columns 8j..8j+7 of them
+    const uint32_t w0 = lds32(r0 + q * 16 + 4 * j), w1 = lds32(r1 + q * 16 + 4 * j);
+    const int sc = q * 2 + (j >> 1);
+    const uint32_t sa0 = nvfp4_scale_addr<FMT, DUAL, PITCH>(slab, g, sc), sa1 = nvfp4_scale_addr<FMT, DUAL, PITCH>(slab, g + 8, sc);
+    // byte loads through the aligned word that holds them
+    const uint32_t sw0 = lds32(sa0 & ~3u) >> (8 * (sa0 & 3u)), sw1 = lds32(sa1 & ~3u) >> (8 * (sa1 & 3u));
+    const __half2 s0 = e4m3_dup_h2(sw0 & 0xffu), s1 = e4m3_dup_h2(sw1 & 0xffu);
+    uint32_t a01, a23, a45, a67, b01, b23, b45, b67;
+    e2m1x4_to_h2(w0 & 0xffffu, a01, a23);
+    e2m1x4_to_h2(w0 >> 16, a45, a67);
+    e2m1x4_to_h2(w1 & 0xffffu, b01, b23);
+    e2m1x4_to_h2(w1 >> 16, b45, b67);
+    uint4 x = make_uint4(0, 0, 0, 0);
+    if (bcol) x = __ldg(reinterpret_cast<const uint4*>(bcol + q * 32 + 8 * j));
+    mma_f16(c, h2_as_u32(__hmul2(u32_as_h2(a01), s0)), h2_as_u32(__hmul2(u32_as_h2(b01), s1)),
+            h2_as_u32(__hmul2(u32_as_h2(a23), s0)), h2_as_u32(__hmul2(u32_as_h2(b23), s1)), x.x, x.y);
+    mma_f16(c, h2_as_u32(__hmul2(u32_as_h2(a45), s0)), h2_as_u32(__hmul2(u32_as_h2(b45), s1)),
+            h2_as_u32(__hmul2(u32_as_h2(a67), s0)), h2_as_u32(__hmul2(u32_as_h2(b67), s1)), x.z, x.w);
+  }
+  facc[0] += c[0] + c[1];
+  facc[1] += c[2] + c[3];
 }
 
-template <int FMT, int DUAL, bool MINS_TILE>
+template <int FMT> struct GemvLayout;
+// kPitch: bytes of a row slot; kChunks: 16-byte copies per row slot and block; kExtra: bytes per stage behind
+// the 16 row slots (scale tile pieces).
+template <> struct GemvLayout<kGemvQ4K> { static constexpr int kPitch = 160, kStages = 3, kChunks = 9, kExtra = 0; };
+template <> struct GemvLayout<kGemvQ6KR> { static constexpr int kPitch = 240, kStages = 2, kChunks = 14, kExtra = 0; };      // 13 data chunks + the d chunk
+template <> struct GemvLayout<kGemvNvfp4Linear> { static constexpr int kPitch = 144, kStages = 3, kChunks = 9, kExtra = 0; };  // 8 code chunks + 1 scale chunk
+template <> struct GemvLayout<kGemvNvfp4Tiled> { static constexpr int kPitch = 144, kStages = 3, kChunks = 8, kExtra = 256; };  // codes; 16 scale pieces per stage
+
+template <int FMT> __host__ __device__ constexpr int gemv_stage_bytes() { return 16 * GemvLayout<FMT>::kPitch + GemvLayout<FMT>::kExtra; }
+template <int FMT> __host__ __device__ constexpr int gemv_smem_bytes() {
+  return kGemvWarps * GemvLayout<FMT>::kStages * gemv_stage_bytes<FMT>() + kGemvWarps * 4 * 16 * 4 + 16;
+}
+
+// Weight row of matrix-0 row slot `s` of slab `u` (rows are slabs of RPT consecutive rows, except for the tiled
+// NVFP4 layout where a slab takes 16 / RPT... base rows of a 128-row tile in all four 32-row quarters, so that
+// the 16-byte pieces of the scale tiles are used completely).
+template <int FMT, int DUAL>
+DEVI int slab_row(int u, int s) {
+  constexpr int RPT = DUAL ? 8 : 16;
+  if (FMT != kGemvNvfp4Tiled) return u * RPT + s;
+  constexpr int per128 = 128 / RPT;                 // slabs per 128-row tile
+  const int t128 = u / per128, ul = u % per128;
+  const int pl = DUAL ? (s & 1) : (s & 3), q = DUAL ? (s >> 1) : (s >> 2);
+  return t128 * 128 + q * 32 + ul * (RPT / 4) + pl;
+}
+
+// Hayate SwiGLU: inputs rounded to bf16, gate <= 10, up in [-10, 10], bf16(bf16(g * sigmoid(g)) * u)
+// (hayate cu/glm53/math.cuh:31-34, decode.cu:46).
+DEVI float bf16_rn(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+DEVI float hayate_swiglu(float gate, float up) {
+  gate = fminf(bf16_rn(gate), 10.f);
+  up = fmaxf(-10.f, fminf(10.f, bf16_rn(up)));
+  return bf16_rn(bf16_rn(gate * sigmoid_precise(gate)) * up);
+}
+
+template <int FMT, int DUAL, bool MINS_TILE, int OUT>
 __global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const GemvArgs a) {
   using LY = GemvLayout<FMT>;
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t ring = smem_u32(smem) + warp * (LY::kStages * 16 * LY::kPitch);
-  float* red = reinterpret_cast<float*>(smem + kGemvWarps * LY::kStages * 16 * LY::kPitch);   // [warp][token 4][row 16]
+  constexpr int STAGE = gemv_stage_bytes<FMT>();
+  const uint32_t ring = smem_u32(smem) + warp * (LY::kStages * STAGE);
+  float* red = reinterpret_cast<float*>(smem + kGemvWarps * LY::kStages * STAGE);   // [warp][token 4][row 16]
   pdl_wait();
   pdl_launch();
   constexpr int RPT = DUAL ? 8 : 16;                     // weight rows of matrix 0 per slab
+  constexpr bool NV = FMT == kGemvNvfp4Linear || FMT == kGemvNvfp4Tiled;
   const int tiles_per_group = (a.rows + RPT - 1) / RPT;
   const int nb_per = a.nblk / a.ks;
   const long long items = (long long)a.max_groups * tiles_per_group * a.ks;
   const int groups = __ldcg(a.counters);
   const int g4 = lane >> 2, j = lane & 3;
+  const int shared_row0 = a.out_shared_row;
   for (long long item = (long long)blockIdx.x * kGemvWarps + warp; item < items; item += (long long)gridDim.x * kGemvWarps) {
     const int tile = int(item / a.ks), kpart = int(item % a.ks);
-    const int grp = tile / tiles_per_group, row0 = (tile % tiles_per_group) * RPT;
+    const int grp = tile / tiles_per_group, slab_u = tile % tiles_per_group;
     const bool live = grp < groups;          // uniform over the ks warps of a slab (they share `tile`)
     int4 pl = make_int4(0, 0, 0, 0);
     if (live) pl = __ldcg(a.plan + grp);
     const int e = pl.x, count = live ? pl.y : 0, offset = pl.z;
-    const int valid = min(RPT, a.rows - row0);
     const int b_first = kpart * nb_per;
+    // base of the two matrices of this group's expert
+    const uint8_t* mbase[2];
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+      if (e < 0) mbase[m] = a.w_shared[m];
+      else if (a.w_table) mbase[m] = reinterpret_cast<const uint8_t*>(__ldcg(reinterpret_cast<const unsigned long long*>(a.w_table) + grp)) + m * a.matrix_stride + (size_t)a.expert_stride[m];
+      else mbase[m] = a.w[m] ? a.w[m] + size_t(e) * a.expert_stride[m] : nullptr;
+    }
     // ---- weight stream: 16 row slots x one block per stage --------------------------------------------
     auto issue = [&](int b, int stage) {
-      const uint32_t dst = ring + stage * (16 * LY::kPitch);
+      const uint32_t dst = ring + stage * STAGE;
       for (int c = lane; c < 16 * LY::kChunks; c += 32) {
         const int slot = c / LY::kChunks, part = c % LY::kChunks;
-        const int m = DUAL ? (slot >> 3) : 0, r = DUAL ? (slot & 7) : slot;
-        if (r < valid) {
-          const uint8_t* base = (e < 0 ? a.w_shared[m] : a.w[m] + size_t(e) * a.expert_stride[m]) + size_t(row0 + r) * a.row_bytes;
+        const int m = DUAL ? (slot >> 3) : 0, s8 = DUAL ? (slot & 7) : slot;
+        const int r = slab_row<FMT, DUAL>(slab_u, s8);
+        if (r < a.rows) {
+          const uint8_t* base = mbase[m] + size_t(r) * a.row_bytes;
           const uint8_t* src;
           if (FMT == kGemvQ4K) src = base + b * 144 + part * 16;
-          else src = part < 13 ? base + b * 208 + part * 16 : base + a.nblk * 208 + ((2 * b) & ~15);
+          else if (FMT == kGemvQ6KR) src = part < 13 ? base + b * 208 + part * 16 : base + a.nblk * 208 + ((2 * b) & ~15);
+          else if (FMT == kGemvNvfp4Linear)
+            src = part < 8 ? base + b * 128 + part * 16 : mbase[m] + a.scale_offset[m] + size_t(r) * (a.k / 16) + b * 16;
+          else src = base + b * 128 + part * 16;
           cp_async16(dst + slot * LY::kPitch + part * 16, src);
+        }
+      }
+      if (FMT == kGemvNvfp4Tiled && lane < 16) {
+        // scale tile pieces: piece = (matrix, local base row) x 4 tile columns; 16 bytes each
+        const int piece = lane, tc = piece & 3, pm = piece >> 2;
+        const int m = DUAL ? (pm >> 1) : 0, pl_ = DUAL ? (pm & 1) : pm;
+        const int r = slab_row<FMT, DUAL>(slab_u, pl_);                 // quarter 0 row of this base row
+        if (r < a.rows) {
+          const int cols = (a.k / 16 + 3) / 4 * 4;
+          const uint8_t* src = mbase[m] + a.scale_offset[m] + (size_t(r / 128) * (cols / 4) + (b * 4 + tc)) * 512 + (r % 32) * 16;
+          cp_async16(dst + 16 * LY::kPitch + piece * 16, src);
         }
       }
     };
@@ -263,13 +394,27 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const G
         cp_async_commit();
       }
     }
+    // per-matrix float multipliers of this expert (global scales of NVFP4)
+    float gs0 = 1.f, gs1 = 1.f;
+    if (NV && live) {
+      if (a.gscale_in_matrix[0]) {
+        gs0 = __ldg(reinterpret_cast<const float*>(mbase[0] + a.gscale_in_matrix[0]));
+        if (DUAL) gs1 = __ldg(reinterpret_cast<const float*>(mbase[1] + a.gscale_in_matrix[1]));
+      } else if (e < 0) {
+        if (a.gscale_shared[0]) gs0 = __ldg(reinterpret_cast<const float*>(a.gscale_shared[0]));
+        if (DUAL && a.gscale_shared[1]) gs1 = __ldg(reinterpret_cast<const float*>(a.gscale_shared[1]));
+      } else if (a.gscale) {
+        gs0 = __ldg(reinterpret_cast<const float*>(a.gscale + size_t(e) * a.gscale_estride));
+        if (DUAL) gs1 = __ldg(reinterpret_cast<const float*>(a.gscale + size_t(e) * a.gscale_estride + a.gscale_mstride));
+      }
+    }
     for (int c0 = 0; c0 < count; c0 += 4) {               // up to four tokens of this group per pass
       // this lane's B column g4 -> token g4/2 of the pass, hi (even) or lo (odd) plane
       const int tcol = c0 + (g4 >> 1);
       const __half* plane = nullptr;
       const float* xs = nullptr;
       if (tcol < count) {
-        const int as = e < 0 ? a.tokens * a.topk + tcol : int(__ldcg(a.assignments + offset + tcol));
+        const int as = e < 0 ? shared_row0 + tcol : int(__ldcg(a.assignments + offset + tcol));
         const int xrow = a.x_by_assignment ? as : (e < 0 ? tcol : as / a.topk);
         plane = a.xplanes + (size_t(xrow) * 2 + (g4 & 1)) * a.k;
       }
@@ -277,8 +422,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const G
       const int tres = c0 + j;
       int ares = -1;
       if (tres < count) {
-        ares = e < 0 ? a.tokens * a.topk + tres : int(__ldcg(a.assignments + offset + tres));
-        if (!MINS_TILE && a.xsum32) {
+        ares = e < 0 ? shared_row0 + tres : int(__ldcg(a.assignments + offset + tres));
+        if (FMT == kGemvQ4K && !MINS_TILE && a.xsum32) {
           const int xrow = a.x_by_assignment ? ares : (e < 0 ? tres : ares / a.topk);
           xs = a.xsum32 + size_t(xrow) * (a.k / 32);
         }
@@ -298,9 +443,11 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const G
         cp_async_wait<LY::kStages - 1>();
         __syncwarp();
         const int b = b_first + i;
-        const uint32_t slab = ring + (i % LY::kStages) * (16 * LY::kPitch);
-        if (FMT == kGemvQ4K) q4k_block_f16<LY::kPitch, MINS_TILE>(slab, lane, plane ? plane + b * 256 : nullptr, xs ? xs + b * 8 : nullptr, facc);
-        else q6k_block_f16<LY::kPitch>(slab, lane, (2 * b) & 15, plane ? plane + b * 256 : nullptr, facc);
+        const uint32_t slab = ring + (i % LY::kStages) * STAGE;
+        const __half* bcol = plane ? plane + b * 256 : nullptr;
+        if (FMT == kGemvQ4K) q4k_block_f16<LY::kPitch, MINS_TILE>(slab, lane, bcol, xs ? xs + b * 8 : nullptr, facc);
+        else if (FMT == kGemvQ6KR) q6k_block_f16<LY::kPitch>(slab, lane, (2 * b) & 15, bcol, facc);
+        else nvfp4_block_f16<FMT, DUAL, LY::kPitch>(slab, lane, bcol, facc);
         __syncwarp();
       }
       cp_async_wait<0>();
@@ -322,17 +469,26 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const G
       }
       if (kpart == 0 && ares >= 0) {
         if (DUAL) {
-          if (g4 < valid) {
-            const float h = silu_mul(facc[0], facc[1]);
+          const int r = slab_row<FMT, DUAL>(slab_u, g4);
+          if (r < a.rows) {
+            const float gv = facc[0] * gs0, uv = facc[1] * gs1;
+            const float h = OUT == kOutHayateProduct ? hayate_swiglu(gv, uv) : silu_mul(gv, uv);
             const __half hi = __float2half_rn(h);
             const __half lo = __float2half_rn(h - __half2float(hi));
-            __half* dst = a.out_planes + size_t(ares) * 2 * a.rows + plane_pos(row0 + g4);
+            __half* dst = a.out_planes + size_t(ares) * 2 * a.rows + (NV ? r : plane_pos(r));
             dst[0] = hi;
             dst[a.rows] = lo;
+            if (OUT == kOutHayateProduct && a.out_bf16) a.out_bf16[size_t(ares) * a.rows + r] = __float2bfloat16_rn(h);
           }
         } else {
-          if (g4 < valid) a.out[size_t(ares) * a.rows + row0 + g4] = facc[0];
-          if (g4 + 8 < valid) a.out[size_t(ares) * a.rows + row0 + g4 + 8] = facc[1];
+          const int r0 = slab_row<FMT, DUAL>(slab_u, g4), r1 = slab_row<FMT, DUAL>(slab_u, g4 + 8);
+          if (OUT == kOutBf16) {
+            if (r0 < a.rows) a.out_bf16[size_t(ares) * a.rows + r0] = __float2bfloat16_rn(facc[0] * gs0);
+            if (r1 < a.rows) a.out_bf16[size_t(ares) * a.rows + r1] = __float2bfloat16_rn(facc[1] * gs0);
+          } else {
+            if (r0 < a.rows) a.out[size_t(ares) * a.rows + r0] = facc[0] * gs0;
+            if (r1 < a.rows) a.out[size_t(ares) * a.rows + r1] = facc[1] * gs0;
+          }
         }
       }
     }
@@ -340,12 +496,23 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const G
 }
 
 // ---- activation rows -> planes (and per-32 sums) ------------------------------------------------------
-// One block per row. planes[row] = k fp16 hi values then k fp16 lo values, groups of four as [x0,x2,x1,x3].
-DEVI void act_planes_row(const float* x, int k, __half* planes, float* xsum32) {
+// One block per row. planes[row] = k fp16 hi values then k fp16 lo values, groups of four as [x0,x2,x1,x3]
+// (or in natural order for the NVFP4 kernels).
+template <typename XT>
+DEVI void act_planes_row(const XT* x, int k, __half* planes, float* xsum32, bool natural) {
   for (int base = 0; base < k / 4; base += blockDim.x) {            // uniform trip count: shuffles below
     const int i = base + threadIdx.x;
-    const float4 v = i < k / 4 ? __ldcg(reinterpret_cast<const float4*>(x) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-    const float vals[4] = {v.x, v.z, v.y, v.w};                     // storage order
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < k / 4) {
+      if (sizeof(XT) == 4) v = __ldcg(reinterpret_cast<const float4*>(x) + i);
+      else {
+        const uint2 raw = __ldcg(reinterpret_cast<const uint2*>(x) + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 lo2 = __bfloat1622float2(h[0]), hi2 = __bfloat1622float2(h[1]);
+        v = make_float4(lo2.x, lo2.y, hi2.x, hi2.y);
+      }
+    }
+    const float vals[4] = {v.x, natural ? v.y : v.z, natural ? v.z : v.y, v.w};   // storage order
     __half hi[4], lo[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {

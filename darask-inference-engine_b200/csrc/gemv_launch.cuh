@@ -15,16 +15,17 @@ inline int gemv_k_split(int nblk, long long slabs, int sms) {
   return best;
 }
 
-template <int FMT, int DUAL, bool MINS_TILE>
+template <int FMT, int DUAL, bool MINS_TILE, int OUT>
 inline cudaError_t launch_gemv(GemvArgs a, cudaStream_t stream) {
-  using LY = GemvLayout<FMT>;
   if (a.row_bytes % 16 || a.expert_stride[0] % 16 || a.expert_stride[1] % 16 || a.k % 256 || a.rows < 1 || a.max_groups < 1)
     return cudaErrorInvalidValue;
   constexpr int RPT = DUAL ? 8 : 16;
   const long long slabs = (long long)a.max_groups * ((a.rows + RPT - 1) / RPT);
   a.ks = gemv_k_split(a.nblk, slabs, sm_count());
-  const int smem = gemv_smem_bytes(LY::kPitch, LY::kStages, a.ks);
-  auto kernel = expert_gemv_kernel<FMT, DUAL, MINS_TILE>;
+  if (a.out_shared_row == 0) a.out_shared_row = a.tokens * a.topk;
+  if (FMT == kGemvNvfp4Tiled && a.rows % 128) return cudaErrorInvalidValue;
+  const int smem = gemv_smem_bytes<FMT>();
+  auto kernel = expert_gemv_kernel<FMT, DUAL, MINS_TILE, OUT>;
   static bool configured = false;       // one opt-in per instantiation (and process)
   if (!configured) {
     const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);

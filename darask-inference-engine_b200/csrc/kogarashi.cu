@@ -85,8 +85,9 @@ template <int DUAL>
 static cudaError_t launch_gemv_ggml(int ty, const GemvArgs& a, cudaStream_t st) {
   // gate/up read per-32 sums of x written with the planes; the down projection has no such sums and
   // lets the tensor-core tiles form the Q4_K min term instead
-  if (ty == DARASK_GGML_Q4_K) return DUAL ? launch_gemv<kGemvQ4K, DUAL, false>(a, st) : launch_gemv<kGemvQ4K, DUAL, true>(a, st);
-  if (ty == DARASK_GGML_Q6_K) return launch_gemv<kGemvQ6KR, DUAL, false>(a, st);
+  constexpr int OUT = DUAL ? kOutSiluPlanes : kOutFloat;
+  if (ty == DARASK_GGML_Q4_K) return DUAL ? launch_gemv<kGemvQ4K, DUAL, false, OUT>(a, st) : launch_gemv<kGemvQ4K, DUAL, true, OUT>(a, st);
+  if (ty == DARASK_GGML_Q6_K) return launch_gemv<kGemvQ6KR, DUAL, false, OUT>(a, st);
   return cudaErrorInvalidValue;
 }
 

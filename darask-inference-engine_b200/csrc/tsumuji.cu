@@ -1,0 +1,153 @@
+// Tsumuji (Qwen-Next, NVFP4 routed experts + dense bf16 shared expert) MoE FFN for a window of N tokens.
+// Reference call site: tsumuji crates/tsumuji-engine/src/engine.rs:1586-1683 (`mlp_half`): router GEMV,
+// `router_topk`, `moe_gate_up`, `moe_down`, `moe_combine`; kernels tsumuji kernels/decode/ops.cu:148-230,
+// decode/gemv.cu:64-158. Expert block layout: tsumuji crates/tsumuji-engine/src/weights.rs:10-12.
+#include "../../include/darask_moe_b200.h"
+#include "dense_gemv.cuh"
+#include "gemv_launch.cuh"
+#include "route_kernels.cuh"
+
+namespace dmoe {
+
+// out[n][i] = sum_s fma(w[n][s], y[n*k+s][i]) then fma(shared_gate[n], y[N*k+n][i])   (ops.cu:217-223)
+__global__ void __launch_bounds__(256) tsumuji_combine_kernel(float* out, const float* y, const float* w, const float* sgate,
+                                                              int hidden, int topk, int tokens, int accumulate) {
+  pdl_wait();
+  pdl_launch();
+  const int i = blockIdx.x * 256 + threadIdx.x, n = blockIdx.y;
+  if (i >= hidden) return;
+  float o = 0.f;
+  for (int s = 0; s < topk; ++s) o = fmaf(__ldcg(w + n * topk + s), __ldcg(y + size_t(n * topk + s) * hidden + i), o);
+  o = fmaf(__ldcg(sgate + n), __ldcg(y + size_t(tokens * topk + n) * hidden + i), o);
+  out[size_t(n) * hidden + i] = accumulate ? out[size_t(n) * hidden + i] + o : o;
+}
+
+// stand-alone routing of given logits followed by the permutation, one block
+template <int MODE>
+__global__ void __launch_bounds__(128) route_permute_kernel(RouteArgs r, PermuteArgs p) {
+  extern __shared__ int hist[];
+  pdl_wait();
+  pdl_launch();
+  for (int token = threadIdx.x >> 5; token < r.tokens; token += 4) route_token_any<MODE>(r, token, threadIdx.x & 31);
+  __threadfence_block();
+  __syncthreads();
+  permute_block(p, hist, p.ids);
+}
+
+template <typename XT>
+__global__ void __launch_bounds__(128) act_planes_kernel(const XT* x, int k, __half* planes, float* xsum32, int natural) {
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.x;
+  act_planes_row(x + size_t(t) * k, k, planes + size_t(t) * 2 * k, xsum32 ? xsum32 + size_t(t) * (k / 32) : nullptr, natural != 0);
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+struct TsumujiWs {
+  int* counters; unsigned* done; unsigned* status; int* active; unsigned* ranges; unsigned* assignments; int4* plan;
+  __half* xplanes; __half* hplanes; float* y; size_t bytes;
+};
+static TsumujiWs carve(void* base, int hidden, int inter, int experts, int topk, int tokens) {
+  TsumujiWs w;
+  uint8_t* p = static_cast<uint8_t*>(base);
+  size_t off = 0;
+  auto take = [&](size_t bytes) { uint8_t* q = p ? p + off : nullptr; off = align_up(off + bytes, 256); return q; };
+  w.counters = reinterpret_cast<int*>(take(16));
+  w.done = reinterpret_cast<unsigned*>(take(4));
+  w.status = reinterpret_cast<unsigned*>(take(4));
+  w.active = reinterpret_cast<int*>(take(size_t(experts) * 4));
+  w.ranges = reinterpret_cast<unsigned*>(take(size_t(experts) * 8));
+  w.assignments = reinterpret_cast<unsigned*>(take(size_t(tokens) * topk * 4));
+  w.plan = reinterpret_cast<int4*>(take(size_t(experts + 1) * 16));
+  w.xplanes = reinterpret_cast<__half*>(take(size_t(tokens) * 2 * hidden * 2));
+  const size_t rows = size_t(tokens) * topk + tokens;
+  w.hplanes = reinterpret_cast<__half*>(take(rows * 2 * inter * 2));
+  w.y = reinterpret_cast<float*>(take(rows * hidden * 4));
+  w.bytes = off;
+  return w;
+}
+
+static int dense_k_split(int k, long long slabs) {
+  const long long warps = (long long)sm_count() * kGemvWarps;
+  int best = 1;
+  for (int ks = 1; ks <= 12; ++ks)
+    if (kGemvWarps % ks == 0 && k % (32 * ks) == 0 && slabs * ks <= warps) best = ks;
+  return best;
+}
+
+}  // namespace dmoe
+
+using namespace dmoe;
+
+extern "C" size_t tsumuji_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens) {
+  return carve(nullptr, hidden, inter, experts, topk, tokens).bytes;
+}
+
+extern "C" int tsumuji_moe_workspace_init(void* workspace, size_t bytes, cudaStream_t st) {
+  if (!workspace || !bytes) return cudaErrorInvalidValue;
+  return cudaMemsetAsync(workspace, 0, bytes < 4096 ? bytes : 4096, st);
+}
+
+extern "C" int tsumuji_moe_layer(const TsumujiMoe* d, cudaStream_t st) {
+  if (!d || !d->experts_w || !d->gs || !d->shared_gu || !d->shared_down || !d->x || !d->out || !d->rlogits || !d->sel ||
+      !d->rw || !d->shared_gate || !d->workspace)
+    return cudaErrorInvalidValue;
+  const int H = d->hidden, F = d->inter, E = d->experts, K = d->topk, N = d->tokens;
+  // the reference limits: E <= 1024, top-k <= 32, H and F multiples of 32 (tsumuji-engine/src/config.rs:185-195);
+  // the tiles here want multiples of 256
+  if (H <= 0 || F <= 0 || H % 256 || F % 256 || E < K || E > 1024 || K < 1 || K > 32 || N < 1) return cudaErrorInvalidValue;
+  if (d->workspace_bytes < tsumuji_moe_workspace_bytes(H, F, E, K, N)) return cudaErrorInvalidValue;
+  const TsumujiWs w = carve(d->workspace, H, F, E, K, N);
+  const RouteArgs route{d->rlogits, E + 1, E, K, N, nullptr, 1.f, d->sel, d->rw, d->shared_gate};
+  const PermuteArgs perm{d->sel, N, K, E, w.assignments, w.ranges, w.active, w.counters, w.status, w.plan, 0};
+  cudaError_t e;
+  if (d->router_w) {
+    // router projection (bf16 [E+1][H], row E = shared-expert gate), top-k, permutation, activation planes
+    RouterArgs r = {};
+    r.w = d->router_w; r.x = d->x; r.logits = d->rlogits; r.hidden = H; r.rows = E + 1; r.ld = E + 1; r.tokens = N;
+    r.route = route; r.perm = perm; r.done = w.done; r.fuse = 1;
+    r.planes = w.xplanes; r.xsum32 = nullptr; r.planes_natural = 1;
+    const size_t hist = size_t(E + 1) * 4 + size_t(N * K <= kRouteIdCache ? N * K : 0) * 4;
+    if ((e = launch_pdl(router_kernel<__nv_bfloat16, float, kRouteTsumuji>, dim3(E + 1 + N), dim3(128), hist, st, r))) return e;
+  } else {
+    // logits supplied by the caller (the reference computes them with its dense GEMV, engine.rs:1589)
+    if ((e = launch_pdl(route_permute_kernel<kRouteTsumuji>, dim3(1), dim3(128), size_t(E + 1) * 4, st, route, perm))) return e;
+    if ((e = launch_pdl(act_planes_kernel<float>, dim3(N), dim3(128), 0, st, d->x, H, w.xplanes, (float*)nullptr, 1))) return e;
+  }
+  const unsigned long long fh = (unsigned long long)F * H;
+  const uint8_t* base = static_cast<const uint8_t*>(d->experts_w);
+  // routed gate/up
+  GemvArgs a = {};
+  a.w[0] = base; a.w[1] = base + fh / 2;
+  a.expert_stride[0] = a.expert_stride[1] = fh * 27 / 16;
+  a.scale_offset[0] = fh * 3 / 2; a.scale_offset[1] = fh * 3 / 2 + fh / 16 - fh / 2;
+  a.row_bytes = H / 2; a.k = H; a.rows = F; a.nblk = H / 256;
+  a.gscale = reinterpret_cast<const uint8_t*>(d->gs); a.gscale_estride = 12; a.gscale_mstride = 4;
+  a.xplanes = w.xplanes; a.x_by_assignment = 0;
+  a.counters = w.counters + 2; a.plan = w.plan; a.assignments = w.assignments;
+  a.tokens = N; a.topk = K; a.max_groups = N * K < E ? N * K : E;
+  a.out_planes = w.hplanes; a.status = w.status;
+  if ((e = launch_gemv<kGemvNvfp4Linear, 1, false, kOutSiluPlanes>(a, st))) return e;
+  // shared gate/up (dense bf16 [2F][H])
+  DenseArgs s = {};
+  s.w[0] = static_cast<const __nv_bfloat16*>(d->shared_gu); s.w[1] = s.w[0] + size_t(F) * H;
+  s.k = H; s.rows = F; s.ks = dense_k_split(H, (F + 7) / 8);
+  s.xplanes = w.xplanes; s.x_row0 = 0; s.tokens = N; s.out_planes = w.hplanes; s.out_row0 = N * K;
+  if ((e = launch_pdl(dense_gemv_kernel<1>, dim3(sm_count()), dim3(kGemvWarps * 32), 0, st, s))) return e;
+  // routed down
+  GemvArgs b = a;
+  b.w[0] = base + fh; b.w[1] = nullptr;
+  b.scale_offset[0] = fh * 3 / 2 + fh / 8 - fh; b.scale_offset[1] = 0;
+  b.row_bytes = F / 2; b.k = F; b.rows = H; b.nblk = F / 256;
+  b.gscale = reinterpret_cast<const uint8_t*>(d->gs) + 8;
+  b.xplanes = w.hplanes; b.x_by_assignment = 1; b.out_planes = nullptr; b.out = w.y;
+  if ((e = launch_gemv<kGemvNvfp4Linear, 0, false, kOutFloat>(b, st))) return e;
+  // shared down (dense bf16 [H][F])
+  DenseArgs t = {};
+  t.w[0] = static_cast<const __nv_bfloat16*>(d->shared_down); t.w[1] = nullptr;
+  t.k = F; t.rows = H; t.ks = dense_k_split(F, (H + 15) / 16);
+  t.xplanes = w.hplanes; t.x_row0 = N * K; t.tokens = N; t.out = w.y; t.out_row0 = N * K;
+  if ((e = launch_pdl(dense_gemv_kernel<0>, dim3(sm_count()), dim3(kGemvWarps * 32), 0, st, t))) return e;
+  return launch_pdl(tsumuji_combine_kernel, dim3((H + 255) / 256, N), dim3(256), 0, st, d->out, (const float*)w.y,
+                    (const float*)d->rw, (const float*)d->shared_gate, H, K, N, d->accumulate);
+}

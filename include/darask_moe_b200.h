@@ -125,6 +125,35 @@ int kogarashi_moe_status(const void* workspace, unsigned* host_status /* host */
 size_t kogarashi_moe_static_scratch_bytes(void);
 int kogarashi_moe_layer_static(const KogarashiMoe* desc /* host */, darask_stream_t stream);
 
+/* ---- Tsumuji MoE FFN layer ----------------------------------------------------------------------------
+ * One call replaces `router_topk`, `moe_gate_up`, `moe_down` and the expert part of `moe_combine`
+ * (engines/tsumuji/crates/tsumuji-engine/src/engine.rs:1586-1683; kernels engines/tsumuji/kernels/decode/ops.cu:148-230,
+ * decode/gemv.cu:64-158) for a window of `tokens` tokens (the reference kernels stop at 8).
+ * experts_w: routed experts, per expert one block of 27/16*F*H bytes
+ *   [gate codes | up codes | down codes | gate sf | up sf | down sf] (engines/tsumuji/crates/tsumuji-engine/src/weights.rs:10-12),
+ * gs: float32 [experts][3] global scales; shared_gu bf16 [2F][H] (gate rows, then up rows), shared_down bf16 [H][F].
+ * router_w: bf16 [experts+1][H] (row `experts` = shared-expert gate) or NULL when rlogits already holds the
+ * logits.  out[n] = sum_s w_s y_s + shared_gate y_shared (accumulate != 0: added to out).  The write-back
+ * into the residual streams R and the sum-of-squares statistics of `moe_combine` stay with the caller. */
+typedef struct {
+  int hidden, inter, experts, topk, tokens;
+  const void* router_w;
+  const void* experts_w; const float* gs;
+  const void* shared_gu; const void* shared_down;
+  const float* x;                 /* [tokens][hidden] float32 ("inp")                          */
+  float* out;                     /* [tokens][hidden]                                          */
+  float* rlogits;                 /* [tokens][experts+1]                                       */
+  int* sel; float* rw;            /* [tokens][topk]                                            */
+  float* shared_gate;             /* [tokens]                                                  */
+  int accumulate;
+  void* workspace; size_t workspace_bytes;
+} TsumujiMoe;
+size_t tsumuji_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens);
+/* zeroes the control words once after allocation (same as kogarashi_moe_workspace_init) */
+int tsumuji_moe_workspace_init(void* workspace, size_t bytes, darask_stream_t stream);
+int tsumuji_moe_layer(const TsumujiMoe* desc /* host */, darask_stream_t stream);
+
+
 #ifdef __cplusplus
 }
 #endif

@@ -64,3 +64,25 @@ def check_output(got, ref, rel=1e-3, max_abs=2e-3):
     assert r <= rel, f"relative L2 {r:.3e} > {rel}"
     assert m <= bound, f"max abs {m:.3e} > {bound:.3e}"
     return r, m
+
+
+def tsumuji_layer(seed, hidden, inter, experts, topk, tokens, pool=8, uniform_logits=False):
+    """-> (oracle TsumujiLayer, dict(x, logits)). NVFP4 routed experts in the linear layout, dense bf16
+    shared expert, bf16 router with the shared-gate row. `uniform_logits`: logits drawn i.i.d. uniform
+    (near-balanced load) instead of coming from the router projection."""
+    rng = rng_for(seed)
+    x = F.bf16_round(normal(rng, (tokens, hidden), 1.0))
+    router = F.bf16_round(normal(rng, (experts + 1, hidden), 0.02))
+    pool = min(pool, experts)
+    blocks, gs = [], []
+    for _ in range(pool):
+        b, g = F.tsumuji_expert_block(normal(rng, (inter, hidden), 0.02), normal(rng, (inter, hidden), 0.02),
+                                      normal(rng, (hidden, inter), 0.02))
+        blocks.append(b)
+        gs.append(g)
+    idx = np.arange(experts) % pool
+    shared_gu = F.bf16_round(normal(rng, (2 * inter, hidden), 0.02))
+    shared_down = F.bf16_round(normal(rng, (hidden, inter), 0.02))
+    layer = L.TsumujiLayer(hidden, inter, experts, topk, router, np.stack(blocks)[idx], np.stack(gs)[idx], shared_gu, shared_down)
+    logits = rng.uniform(-1, 1, (tokens, experts + 1)).astype(np.float32) if uniform_logits else None
+    return layer, dict(x=x, logits=logits)
