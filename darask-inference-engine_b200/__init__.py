@@ -10,5 +10,6 @@ from .formats import (GGML_BF16, GGML_F16, GGML_F32, GGML_Q4_K, GGML_Q6_K, ggml_
 from . import quantize  # noqa: F401
 from .kogarashi import KogarashiMoeLayer  # noqa: F401
 from .tsumuji import TsumujiMoeLayer  # noqa: F401
+from .hayate import HayateMoeLayer  # noqa: F401
 
 __all__ = ["KogarashiMoeLayer", "ggml_tensor_bytes", "nvfp4_tiled_bytes"]

@@ -38,6 +38,20 @@ class TsumujiMoe(ctypes.Structure):
     ]
 
 
+class HayateDenseWeight(ctypes.Structure):
+    _fields_ = [("data", c_void_p), ("scale", c_void_p), ("format", c_uint)]
+
+
+class HayateMoe(ctypes.Structure):
+    """Mirror of `HayateMoe` in include/darask_moe_b200.h."""
+    _fields_ = [
+        ("hidden", c_int), ("inter", c_int), ("experts", c_int), ("topk", c_int), ("tokens", c_int), ("scale", c_float),
+        ("router_w", c_void_p), ("bias", c_void_p), ("images", c_void_p), ("stride", c_size_t), ("shared_image", c_void_p),
+        ("x", c_void_p), ("out", c_void_p), ("logits", c_void_p), ("ids", c_void_p), ("weights", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+    ]
+
+
 _SIGNATURES = {
     "darask_route_topk": (c_int, [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p,
                                   c_void_p, c_void_p]),
@@ -53,6 +67,19 @@ _SIGNATURES = {
     "darask_quantize_nvfp4_tiled": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "darask_quantize_fp8_block": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "darask_quantize_fp8_act": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p]),
+    "hayate_glm_moe_set_shape": (c_int, [c_uint, c_uint, c_uint, c_uint, c_float]),
+    "hayate_glm_moe_workspace_bytes": (c_size_t, [c_uint, c_uint, c_uint, c_uint, c_uint]),
+    "hayate_glm_moe_set_workspace": (c_int, [c_void_p, c_size_t, c_void_p]),
+    "hayate_glm_route_decode": (c_int, [c_void_p] * 6 + [c_void_p]),
+    "hayate_glm_route": (c_int, [c_void_p] * 6 + [c_uint, c_uint, c_uint, c_uint, c_void_p]),
+    "hayate_glm_route_batch": (c_int, [c_void_p] * 6 + [c_uint, c_void_p]),
+    "hayate_glm_moe_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, HayateDenseWeight, HayateDenseWeight, c_int,
+                                       c_int, c_size_t, c_void_p]),
+    "hayate_glm_moe_down": (c_int, [c_void_p, c_void_p, c_void_p, HayateDenseWeight, c_int, c_int, c_size_t, c_void_p]),
+    "hayate_glm_moe_reduce": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "hayate_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "hayate_moe_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),
+    "hayate_moe_layer": (c_int, [ctypes.POINTER(HayateMoe), c_void_p]),
     "tsumuji_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "tsumuji_moe_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),
     "tsumuji_moe_layer": (c_int, [ctypes.POINTER(TsumujiMoe), c_void_p]),

@@ -3,7 +3,7 @@
     python darask-inference-engine_b200/build.py [--force]
 
 Every translation unit under csrc/ is compiled with
-``-gencode arch=compute_100a,code=sm_100a -lineinfo``; ``route_hayate.cu`` additionally with
+``-gencode arch=compute_100a,code=sm_100a -lineinfo``; ``hayate.cu`` additionally with
 ``--use_fast_math`` (the reference builds its GLM kernels that way and the router selection
 has to round the same way).
 """
@@ -21,7 +21,7 @@ OBJ = HERE / "build"
 LIB = HERE / "libdarask_moe_b200.so"
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
-EXTRA = {"route_hayate.cu": ["--use_fast_math"]}
+EXTRA = {"hayate.cu": ["--use_fast_math"]}
 
 
 def _nvcc() -> str:

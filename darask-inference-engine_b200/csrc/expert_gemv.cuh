@@ -58,6 +58,8 @@ struct GemvArgs {
   float* out;                   // kOutFloat: [T*k (+T)][rows]
   __nv_bfloat16* out_bf16;      // kOutHayateProduct / kOutBf16: [T*k (+T)][rows]
   int out_shared_row;           // output row of the shared expert's token t is out_shared_row + t (default T*k)
+  int shared_x_row0;            // x row of the shared expert's token t when rows are per token (default 0: the token's own row)
+  int round_shared;             // NVFP4: the shared expert's weights are rounded to bf16 after scaling (Hayate)
   unsigned* status;
 };
 
@@ -259,8 +261,16 @@ DEVI uint32_t nvfp4_scale_addr(uint32_t slab, int slot, int c) {
   const int piece = (DUAL ? (m * 2 + pl) : pl) * 4 + (c >> 2);
   return slab + 16 * PITCH + piece * 16 + q * 4 + (c & 3);
 }
-template <int FMT, int DUAL, int PITCH>
-DEVI void nvfp4_block_f16(uint32_t slab, int lane, const __half* bcol, float (&facc)[2]) {
+// weight pair (code * scale, exact) -> fp16 of bf16(code * scale * global) * 2^s, with `rm` = global * 2^s: the
+// bf16-rounded weights of the reference's FP8 / shared-expert path (hayate cu/glm53/dense.cuh:61-73), kept inside
+// the fp16 range by the power of two (rounding to bf16 commutes with it).
+DEVI uint32_t round_bf16_pair(uint32_t v, float rm) {
+  const float2 f = __half22float2(u32_as_h2(v));
+  const float2 r = __bfloat1622float2(__floats2bfloat162_rn(f.x * rm, f.y * rm));
+  return h2_as_u32(__floats2half2_rn(r.x, r.y));
+}
+template <int FMT, int DUAL, int PITCH, bool ROUNDED>
+DEVI void nvfp4_block_f16(uint32_t slab, int lane, const __half* bcol, float rm0, float rm1, float (&facc)[2]) {
   const int g = lane >> 2, j = lane & 3;
   const uint32_t r0 = slab + g * PITCH, r1 = slab + (g + 8) * PITCH;
   float c[4] = {0.f, 0.f, 0.f, 0.f};
@@ -279,10 +289,16 @@ DEVI void nvfp4_block_f16(uint32_t slab, int lane, const __half* bcol, float (&f
     e2m1x4_to_h2(w1 >> 16, b45, b67);
     uint4 x = make_uint4(0, 0, 0, 0);
     if (bcol) x = __ldg(reinterpret_cast<const uint4*>(bcol + q * 32 + 8 * j));
-    mma_f16(c, h2_as_u32(__hmul2(u32_as_h2(a01), s0)), h2_as_u32(__hmul2(u32_as_h2(b01), s1)),
-            h2_as_u32(__hmul2(u32_as_h2(a23), s0)), h2_as_u32(__hmul2(u32_as_h2(b23), s1)), x.x, x.y);
-    mma_f16(c, h2_as_u32(__hmul2(u32_as_h2(a45), s0)), h2_as_u32(__hmul2(u32_as_h2(b45), s1)),
-            h2_as_u32(__hmul2(u32_as_h2(a67), s0)), h2_as_u32(__hmul2(u32_as_h2(b67), s1)), x.z, x.w);
+    a01 = h2_as_u32(__hmul2(u32_as_h2(a01), s0)); a23 = h2_as_u32(__hmul2(u32_as_h2(a23), s0));
+    a45 = h2_as_u32(__hmul2(u32_as_h2(a45), s0)); a67 = h2_as_u32(__hmul2(u32_as_h2(a67), s0));
+    b01 = h2_as_u32(__hmul2(u32_as_h2(b01), s1)); b23 = h2_as_u32(__hmul2(u32_as_h2(b23), s1));
+    b45 = h2_as_u32(__hmul2(u32_as_h2(b45), s1)); b67 = h2_as_u32(__hmul2(u32_as_h2(b67), s1));
+    if (ROUNDED) {
+      a01 = round_bf16_pair(a01, rm0); a23 = round_bf16_pair(a23, rm0); a45 = round_bf16_pair(a45, rm0); a67 = round_bf16_pair(a67, rm0);
+      b01 = round_bf16_pair(b01, rm1); b23 = round_bf16_pair(b23, rm1); b45 = round_bf16_pair(b45, rm1); b67 = round_bf16_pair(b67, rm1);
+    }
+    mma_f16(c, a01, b01, a23, b23, x.x, x.y);
+    mma_f16(c, a45, b45, a67, b67, x.z, x.w);
   }
   facc[0] += c[0] + c[1];
   facc[1] += c[2] + c[3];
@@ -408,6 +424,15 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const G
         if (DUAL) gs1 = __ldg(reinterpret_cast<const float*>(a.gscale + size_t(e) * a.gscale_estride + a.gscale_mstride));
       }
     }
+    // shared expert with bf16-rounded weights: A = bf16(code * scale * g) * 2^s, epilogue multiplier 2^-s
+    float rm0 = 0.f, rm1 = 0.f;
+    const bool rounded = NV && live && e < 0 && a.round_shared;
+    if (rounded) {
+      const int s0 = 14 - ilogbf(2688.f * gs0), s1 = 14 - ilogbf(2688.f * gs1);
+      rm0 = scalbnf(gs0, s0); gs0 = scalbnf(1.f, -s0);
+      rm1 = DUAL ? scalbnf(gs1, s1) : rm0;
+      if (DUAL) gs1 = scalbnf(1.f, -s1);
+    }
     for (int c0 = 0; c0 < count; c0 += 4) {               // up to four tokens of this group per pass
       // this lane's B column g4 -> token g4/2 of the pass, hi (even) or lo (odd) plane
       const int tcol = c0 + (g4 >> 1);
@@ -415,7 +440,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const G
       const float* xs = nullptr;
       if (tcol < count) {
         const int as = e < 0 ? shared_row0 + tcol : int(__ldcg(a.assignments + offset + tcol));
-        const int xrow = a.x_by_assignment ? as : (e < 0 ? tcol : as / a.topk);
+        const int xrow = a.x_by_assignment ? as : (e < 0 ? a.shared_x_row0 + tcol : as / a.topk);
         plane = a.xplanes + (size_t(xrow) * 2 + (g4 & 1)) * a.k;
       }
       // this lane's result column pair 2j,2j+1 -> token j of the pass
@@ -447,7 +472,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const G
         const __half* bcol = plane ? plane + b * 256 : nullptr;
         if (FMT == kGemvQ4K) q4k_block_f16<LY::kPitch, MINS_TILE>(slab, lane, bcol, xs ? xs + b * 8 : nullptr, facc);
         else if (FMT == kGemvQ6KR) q6k_block_f16<LY::kPitch>(slab, lane, (2 * b) & 15, bcol, facc);
-        else nvfp4_block_f16<FMT, DUAL, LY::kPitch>(slab, lane, bcol, facc);
+        else if (rounded) nvfp4_block_f16<FMT, DUAL, LY::kPitch, true>(slab, lane, bcol, rm0, rm1, facc);
+        else nvfp4_block_f16<FMT, DUAL, LY::kPitch, false>(slab, lane, bcol, 0.f, 0.f, facc);
         __syncwarp();
       }
       cp_async_wait<0>();

@@ -154,6 +154,52 @@ int tsumuji_moe_workspace_init(void* workspace, size_t bytes, darask_stream_t st
 int tsumuji_moe_layer(const TsumujiMoe* desc /* host */, darask_stream_t stream);
 
 
+/* ---- Hayate (GLM) ------------------------------------------------------------------------------------------
+ * Same names, argument order and error behaviour as the reference launchers
+ * (engines/hayate/crates/kernels/cu/glm53/decode.cu:69-88, ops.cu:308-311; Rust declarations
+ * engines/hayate/crates/kernels/src/glm53.rs:539-577, 847-860).  The reference hard-codes hidden 4096,
+ * intermediate 2048, 288 experts, top-8 and scale 2.5; here those are the defaults of a host-thread-local shape
+ * that hayate_glm_moe_set_shape changes (the reference already keeps one such thread-local knob,
+ * hayate_glm_grouped_packed_set_config, packed_grouped.cu:269,315-318).  The expert launchers need scratch for the
+ * fp16 activation planes and the routing plan: register it once per host thread with hayate_glm_moe_set_workspace
+ * (hayate_glm_moe_workspace_bytes(hidden, inter, experts, topk, 1) bytes); the router calls work without it.
+ * Only NVFP4 images (nv != 0, DenseWeight format 3) are implemented; block-FP8 images return cudaErrorInvalidValue. */
+typedef struct { const void* data; const void* scale; unsigned format; } HayateDenseWeight;
+int hayate_glm_moe_set_shape(unsigned hidden, unsigned inter, unsigned experts, unsigned topk, float scale);
+size_t hayate_glm_moe_workspace_bytes(unsigned hidden, unsigned inter, unsigned experts, unsigned topk, unsigned tokens);
+int hayate_glm_moe_set_workspace(void* workspace, size_t bytes, darask_stream_t stream);
+int hayate_glm_route_decode(void* logits, void* weights, void* ids, const void* x, const void* w, const void* bias, darask_stream_t stream);
+int hayate_glm_route(void* logits, void* weights, void* ids, const void* x, const void* w, const void* bias, unsigned tokens,
+                     unsigned hidden, unsigned experts, unsigned topk, darask_stream_t stream);
+int hayate_glm_route_batch(void* logits, void* weights, void* ids, const void* x, const void* w, const void* bias, unsigned m,
+                           darask_stream_t stream);
+/* images: device array of top-k image pointers in route order; a null pointer leaves a zero row (the reference's
+ * "computed on the CPU" slot).  out: bf16 [topk+1][inter], row topk = shared expert. */
+int hayate_glm_moe_gate_up(void* out, const void* x, const void* original, const void* images, HayateDenseWeight gate,
+                           HayateDenseWeight up, int nv, int down_fp8, size_t stride, darask_stream_t stream);
+int hayate_glm_moe_down(void* out, const void* x, const void* images, HayateDenseWeight shared, int nv, int down_fp8,
+                        size_t stride, darask_stream_t stream);
+int hayate_glm_moe_reduce(void* out, const void* x, const void* ids, const void* weights, darask_stream_t stream);
+
+/* Whole Hayate MoE layer for `tokens` tokens with every expert image resident in one slab (images + e * 3 * stride:
+ * gate | up | down at `stride`), replacing the route -> host lookup -> gate_up -> down -> reduce sequence of
+ * engines/hayate/crates/models/src/glm53/gpu.rs:1612-1757 including its device->host copy of the ids. */
+typedef struct {
+  int hidden, inter, experts, topk, tokens;
+  float scale;                          /* routed scaling factor (2.5 in the reference)           */
+  const void* router_w;                 /* bf16 [experts][hidden]                                 */
+  const float* bias;                    /* [experts], selection only                              */
+  const void* images; size_t stride;    /* NVFP4 expert images                                    */
+  const void* shared_image;             /* gate | up | down of the shared expert at `stride`      */
+  const void* x;                        /* bf16 [tokens][hidden]                                  */
+  void* out;                            /* bf16 [tokens][hidden]                                  */
+  float* logits; int* ids; float* weights;
+  void* workspace; size_t workspace_bytes;
+} HayateMoe;
+size_t hayate_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens);
+int hayate_moe_workspace_init(void* workspace, size_t bytes, darask_stream_t stream);
+int hayate_moe_layer(const HayateMoe* desc /* host */, darask_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,129 @@
+"""Parity of the CUDA Hayate layer and of the reference-named one-token launchers with the oracle."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import formats as F
+from oracle import layers as L
+from oracle import routing as R
+from tests import workloads as W
+
+pytestmark = pytest.mark.gpu
+
+
+def bf16_tensor(a):
+    return torch.from_numpy(np.ascontiguousarray(a, np.float32)).bfloat16()
+
+
+def check_ids(ids, ref_ids, keys):
+    """ids equal, except that experts whose selection keys are closer than 1e-6 may swap (approximate sigmoid)."""
+    for t in np.nonzero((ids != ref_ids).any(1))[0]:
+        a, b = keys[t, ids[t]], keys[t, ref_ids[t]]
+        assert np.all(np.abs(a - b) <= 1e-6), (t, ids[t], ref_ids[t])
+    return np.array_equal(ids, ref_ids)
+
+
+def run_layer(layer, acts):
+    import darask_inference_engine_b200 as D
+    t = acts["x"].shape[0]
+    m = D.HayateMoeLayer(layer.hidden, layer.inter, layer.experts, layer.topk, layer.scale, t)
+    m.load(bf16_tensor(layer.router), torch.from_numpy(layer.bias), torch.from_numpy(layer.images.reshape(-1)),
+           torch.from_numpy(layer.shared))
+    out = m.forward(bf16_tensor(acts["x"]).cuda())
+    torch.cuda.synchronize()
+    return m, out.float().cpu().numpy()
+
+
+def check_layer(layer, acts):
+    m, out = run_layer(layer, acts)
+    t = acts["x"].shape[0]
+    logits = m.logits[:t].cpu().numpy()
+    assert np.allclose(logits, L.hayate_logits(layer, acts["x"]), rtol=1e-4, atol=1e-4)
+    ref = L.hayate_forward(layer, acts["x"], logits=logits)
+    keys = R.selection_keys(R.HAYATE, logits, layer.experts, layer.bias)
+    if not check_ids(m.ids[:t].cpu().numpy(), ref["ids"], keys):
+        pytest.skip("near-equal selection keys resolved differently; outputs not comparable")
+    assert np.allclose(m.weights[:t].cpu().numpy(), ref["weights"], rtol=1e-4)
+    # outputs are bf16: one rounding flip is 2^-8 of the value, so the max-abs bar is one bf16 step of max|ref|
+    return W.check_output(out, ref["out"], rel=1e-3, max_abs=2.0 ** -8)
+
+
+@pytest.mark.parametrize("tokens", [1, 3])
+def test_small_layer(tokens):
+    layer, acts = W.hayate_layer(41, hidden=512, inter=256, experts=16, topk=4, tokens=tokens, scale=2.5, pool=16)
+    check_layer(layer, acts)
+
+
+@pytest.mark.parametrize("tokens", [1, 8])
+def test_config3_glm_decode(tokens):
+    # hidden 2048, 64 experts, sigmoid + bias, top-4, scale 1.8, intermediate 1536, NVFP4, one shared expert, seed 2
+    layer, acts = W.hayate_layer(2, 2048, 1536, 64, 4, tokens, scale=1.8, pool=8)
+    check_layer(layer, acts)
+
+
+def test_reference_named_decode_launchers():
+    """route_decode -> gate_up -> down -> reduce with the reference's signatures, at a non-default shape."""
+    import darask_inference_engine_b200 as D
+    lib = D._lib.lib()
+    H, Fi, E, K, scale = 1024, 512, 32, 4, 1.8
+    layer, acts = W.hayate_layer(43, H, Fi, E, K, 1, scale=scale, pool=8)
+    dev = torch.device("cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.hayate_glm_moe_set_shape(H, Fi, E, K, scale) == 0
+    ws = torch.zeros(lib.hayate_glm_moe_workspace_bytes(H, Fi, E, K, 1), dtype=torch.uint8, device=dev)
+    assert lib.hayate_glm_moe_set_workspace(ws.data_ptr(), ws.numel(), st) == 0
+    x = bf16_tensor(acts["x"]).to(dev)
+    router = bf16_tensor(layer.router).to(dev)
+    bias = torch.from_numpy(layer.bias).to(dev)
+    images = torch.from_numpy(layer.images).to(dev)
+    shared = torch.from_numpy(layer.shared).to(dev)
+    logits = torch.zeros(E, device=dev)
+    weights = torch.zeros(K, device=dev)
+    ids = torch.zeros(K, dtype=torch.int32, device=dev)
+    assert lib.hayate_glm_route_decode(logits.data_ptr(), weights.data_ptr(), ids.data_ptr(), x.data_ptr(), router.data_ptr(),
+                                       bias.data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    ref = L.hayate_forward(layer, acts["x"], logits=logits.cpu().numpy()[None])
+    keys = R.selection_keys(R.HAYATE, logits.cpu().numpy()[None], E, layer.bias)
+    if not check_ids(ids.cpu().numpy()[None], ref["ids"], keys):
+        pytest.skip("near-equal selection keys")
+    # the host looks the images up (all resident): device array of top-k pointers in route order
+    table = torch.tensor([images.data_ptr() + int(e) * images.shape[1] for e in ids.cpu().numpy()], dtype=torch.int64, device=dev)
+    stride = layer.stride
+    dw = lambda part: D._lib.HayateDenseWeight(shared.data_ptr() + part * stride, None, 3)
+    product = torch.zeros(K + 1, Fi, dtype=torch.bfloat16, device=dev)
+    expert = torch.zeros(K + 1, H, dtype=torch.bfloat16, device=dev)
+    out = torch.zeros(H, dtype=torch.bfloat16, device=dev)
+    assert lib.hayate_glm_moe_gate_up(product.data_ptr(), x.data_ptr(), x.data_ptr(), table.data_ptr(), dw(0), dw(1), 1, 0, stride, st) == 0
+    assert lib.hayate_glm_moe_down(expert.data_ptr(), product.data_ptr(), table.data_ptr(), dw(2), 1, 0, stride, st) == 0
+    assert lib.hayate_glm_moe_reduce(out.data_ptr(), expert.data_ptr(), ids.data_ptr(), weights.data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    W.check_output(out.float().cpu().numpy()[None], ref["out"], rel=1e-3, max_abs=2.0 ** -8)
+    # validation failures return cudaErrorInvalidValue like the reference launchers
+    assert lib.hayate_glm_moe_reduce(None, expert.data_ptr(), ids.data_ptr(), weights.data_ptr(), st) == 1
+    assert lib.hayate_glm_moe_set_shape(4096, 2048, 288, 8, 2.5) == 0
+    assert lib.hayate_glm_moe_set_workspace(None, 0, st) == 0
+
+
+def test_reduction_order_golden():
+    # reference test engines/hayate/crates/kernels/src/glm53.rs:1702: ids [287,0,17,42,8,256,3,4] are added in the
+    # order [1,6,7,4,2,3,5,0]; with bf16 rounding after every add the order is visible in the result
+    import darask_inference_engine_b200 as D
+    lib = D._lib.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.hayate_glm_moe_set_shape(4096, 2048, 288, 8, 2.5) == 0
+    ids = np.array([287, 0, 17, 42, 8, 256, 3, 4], np.int32)
+    rng = np.random.default_rng(9)
+    y = F.bf16_round(rng.standard_normal((9, 4096)).astype(np.float32) * np.float32(3))
+    w = rng.uniform(0.1, 0.9, 8).astype(np.float32)
+    acc = np.zeros(4096, np.float32)
+    for s in R.route_order(ids):
+        acc = F.bf16_round(acc + F.bf16_round((y[s] * w[s]).astype(np.float32)))
+    expect = F.bf16_round(acc + y[8])
+    out = torch.zeros(4096, dtype=torch.bfloat16, device="cuda")
+    assert lib.hayate_glm_moe_reduce(out.data_ptr(), bf16_tensor(y).cuda().data_ptr(), torch.from_numpy(ids).cuda().data_ptr(),
+                                     torch.from_numpy(w).cuda().data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(out.float().cpu().numpy(), expect)

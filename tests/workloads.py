@@ -86,3 +86,20 @@ def tsumuji_layer(seed, hidden, inter, experts, topk, tokens, pool=8, uniform_lo
     layer = L.TsumujiLayer(hidden, inter, experts, topk, router, np.stack(blocks)[idx], np.stack(gs)[idx], shared_gu, shared_down)
     logits = rng.uniform(-1, 1, (tokens, experts + 1)).astype(np.float32) if uniform_logits else None
     return layer, dict(x=x, logits=logits)
+
+
+def hayate_layer(seed, hidden, inter, experts, topk, tokens, scale=2.5, pool=8):
+    """-> (oracle HayateLayer, dict(x)). bf16 activations and router, float32 bias ~N(0, 0.1), NVFP4 images
+    in the tiled-scale layout (gate | up | down at the 256-byte aligned stride), one shared expert image."""
+    rng = rng_for(seed)
+    x = F.bf16_round(normal(rng, (tokens, hidden), 1.0))
+    router = F.bf16_round(normal(rng, (experts, hidden), 0.02))
+    bias = normal(rng, (experts,), 0.1)
+    pool = min(pool, experts)
+    imgs = [F.hayate_expert_image(normal(rng, (inter, hidden), 0.02), normal(rng, (inter, hidden), 0.02),
+                                  normal(rng, (hidden, inter), 0.02)) for _ in range(pool)]
+    shared = F.hayate_expert_image(normal(rng, (inter, hidden), 0.02), normal(rng, (inter, hidden), 0.02),
+                                   normal(rng, (hidden, inter), 0.02))
+    stride = F.hayate_expert_stride(hidden, inter)
+    layer = L.HayateLayer(hidden, inter, experts, topk, scale, router, bias, np.stack(imgs)[np.arange(experts) % pool], stride, shared)
+    return layer, dict(x=x)
