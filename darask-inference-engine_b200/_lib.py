@@ -52,6 +52,16 @@ class HayateMoe(ctypes.Structure):
     ]
 
 
+class DaraskFp8Moe(ctypes.Structure):
+    """Mirror of `DaraskFp8Moe` in include/darask_moe_b200.h."""
+    _fields_ = [
+        ("hidden", c_int), ("inter", c_int), ("experts", c_int), ("topk", c_int), ("tokens", c_int),
+        ("x", c_void_p), ("logits", c_void_p), ("gate_w", c_void_p), ("up_w", c_void_p), ("down_w", c_void_p),
+        ("gate_s", c_void_p), ("up_s", c_void_p), ("down_s", c_void_p), ("out", c_void_p), ("ids", c_void_p), ("prob", c_void_p),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+    ]
+
+
 _SIGNATURES = {
     "darask_route_topk": (c_int, [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p,
                                   c_void_p, c_void_p]),
@@ -67,6 +77,11 @@ _SIGNATURES = {
     "darask_quantize_nvfp4_tiled": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "darask_quantize_fp8_block": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "darask_quantize_fp8_act": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p]),
+    "darask_fp8_grouped_gemm": (c_int, [c_void_p, c_void_p, ctypes.c_ulonglong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                        c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "darask_fp8_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "darask_fp8_moe_layer": (c_int, [ctypes.POINTER(DaraskFp8Moe), c_void_p]),
+    "darask_fp8_moe_status": (c_int, [c_void_p, ctypes.POINTER(c_uint), c_void_p]),
     "hayate_glm_moe_set_shape": (c_int, [c_uint, c_uint, c_uint, c_uint, c_float]),
     "hayate_glm_moe_workspace_bytes": (c_size_t, [c_uint, c_uint, c_uint, c_uint, c_uint]),
     "hayate_glm_moe_set_workspace": (c_int, [c_void_p, c_size_t, c_void_p]),

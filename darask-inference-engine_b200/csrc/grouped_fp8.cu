@@ -1,0 +1,186 @@
+// FP8 prefill MoE layer: routing -> activation quantization -> dispatch gather -> grouped FP8 GEMM (gate/up with
+// SwiGLU) -> quantization of the products -> grouped FP8 GEMM (down) -> weighted combine.
+// The grouped GEMM kernel is in grouped_fp8.cuh. Reference orchestration: hayate crates/models/src/glm53/gpu.rs:
+// 2068-2566 (`prefill_experts`: route, host-side `group_routes`, gather, grouped GEMMs, scatter).
+#include "../../include/darask_moe_b200.h"
+#include "grouped_fp8.cuh"
+#include "route_kernels.cuh"
+#include "stream_launch.cuh"
+
+namespace dmoe {
+
+// rows in dispatch order: out row i = token assignments[i] / topk; also the inverse map position[a] = i
+__global__ void __launch_bounds__(256) gather_fp8_kernel(const uint8_t* codes, const float* scales, const unsigned* assignments,
+                                                         const int* counters, int topk, int k, uint8_t* out_codes,
+                                                         float* out_scales, unsigned* position) {
+  pdl_wait();
+  pdl_launch();
+  const int i = blockIdx.x;
+  if (i >= __ldcg(counters + 1)) return;
+  const unsigned asg = __ldcg(assignments + i);
+  const size_t src = size_t(asg / topk), dst = size_t(i);
+  if (threadIdx.x == 0) position[asg] = i;
+  for (int c = threadIdx.x; c < k / 16; c += 256)
+    reinterpret_cast<uint4*>(out_codes + dst * k)[c] = __ldg(reinterpret_cast<const uint4*>(codes + src * k) + c);
+  for (int c = threadIdx.x; c < k / 128; c += 256) out_scales[dst * (k / 128) + c] = __ldg(scales + src * (k / 128) + c);
+}
+
+// bf16 rows -> e4m3 codes + float32 scale per row and 128 columns (same arithmetic as darask_quantize_fp8_act)
+__global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* x, const int* counters, int k, uint8_t* q, float* scales) {
+  pdl_wait();
+  pdl_launch();
+  const long long rows = __ldcg(counters + 1);
+  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31, groups = k / 128;
+  if (w >= rows * groups) return;
+  const long long r = w / groups;
+  const int g = int(w % groups);
+  const __nv_bfloat16* p = x + r * k + g * 128 + lane * 4;
+  float v[4], amax = 0.f;
+  for (int i = 0; i < 4; ++i) { v[i] = __bfloat162float(p[i]); amax = fmaxf(amax, fabsf(v[i])); }
+  amax = warp_max(amax);
+  const float scale = amax == 0.f ? 1.f : amax / 448.f;
+  if (lane == 0) scales[r * groups + g] = scale;
+  uint32_t out = 0;
+  for (int i = 0; i < 4; ++i)
+    out |= uint32_t((uint8_t)__nv_cvt_float_to_fp8(fminf(fmaxf(v[i] / scale, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3)) << (8 * i);
+  *reinterpret_cast<uint32_t*>(q + r * k + g * 128 + lane * 4) = out;
+}
+
+// out[t][i] = sum_s prob[t][s] * y[position[t*k+s]][i]  (fp32 fma in slot order), stored as float32
+__global__ void __launch_bounds__(256) combine_rows_kernel(float* out, const float* y, const float* prob, const unsigned* position,
+                                                           int hidden, int topk) {
+  pdl_wait();
+  pdl_launch();
+  const int i = blockIdx.x * 256 + threadIdx.x, t = blockIdx.y;
+  if (i >= hidden) return;
+  float v = 0.f;
+  for (int s = 0; s < topk; ++s) v = fmaf(__ldg(prob + t * topk + s), __ldg(y + size_t(__ldg(position + t * topk + s)) * hidden + i), v);
+  out[size_t(t) * hidden + i] = v;
+}
+
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiled encode_tiled() {
+  static EncodeTiled fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiled>(p);
+  }
+  return fn;
+}
+// 2D byte tensor [rows][k], box [box_rows][128], 128-byte swizzle
+static bool make_map(CUtensorMap* m, const void* base, unsigned long long rows, unsigned long long k, unsigned box_rows) {
+  EncodeTiled enc = encode_tiled();
+  if (!enc) return false;
+  const cuuint64_t dims[2] = {k, rows}, strides[1] = {k};
+  const cuuint32_t box[2] = {128, box_rows}, estr[2] = {1, 1};
+  return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static cudaError_t launch_grouped(const void* a_codes, const float* a_scales, unsigned long long a_rows, const void* w0,
+                                  const void* w1, const float* sw0, const float* sw1, int experts, int n, int k, int gate_up,
+                                  const unsigned* ranges, __nv_bfloat16* out_bf16, float* out_f32, unsigned* status, cudaStream_t st) {
+  CUtensorMap ma, mw0, mw1;
+  if (!make_map(&ma, a_codes, a_rows, k, 128)) return cudaErrorInvalidValue;
+  if (!make_map(&mw0, w0, (unsigned long long)experts * n, k, gate_up ? 64 : 128)) return cudaErrorInvalidValue;
+  if (!make_map(&mw1, gate_up ? w1 : w0, (unsigned long long)experts * n, k, gate_up ? 64 : 128)) return cudaErrorInvalidValue;
+  G8Args g = {};
+  g.sa = a_scales; g.sw[0] = sw0; g.sw[1] = sw1;
+  g.sw_expert_stride = (unsigned long long)((n + 127) / 128) * (k / 128);
+  g.ranges = ranges; g.experts = experts; g.n = n; g.k = k; g.gate_up = gate_up;
+  g.out_bf16 = out_bf16; g.out_f32 = out_f32; g.status = status;
+  const size_t smem = size_t(kG8Stages) * kG8StageBytes + 1024;
+  static bool configured = false;
+  if (!configured) {
+    const cudaError_t e = cudaFuncSetAttribute(grouped_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  return launch_pdl(grouped_fp8_kernel, dim3(sm_count()), dim3(kG8Threads), smem, st, ma, mw0, mw1, g);
+}
+
+static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+struct Fp8Ws {
+  int* counters; unsigned* status; int* active; unsigned* ranges; unsigned* assignments; unsigned* position;
+  uint8_t* xq; float* xs; uint8_t* aq; float* as; __nv_bfloat16* p; uint8_t* pq; float* ps; float* y; size_t bytes;
+};
+static Fp8Ws carve(void* base, int hidden, int inter, int experts, int topk, int tokens) {
+  Fp8Ws w;
+  uint8_t* p = static_cast<uint8_t*>(base);
+  size_t off = 0;
+  auto take = [&](size_t bytes) { uint8_t* q = p ? p + off : nullptr; off = align_up(off + bytes, 1024); return q; };
+  const size_t rows = size_t(tokens) * topk + 128;          // + one tile of slack for the last tile's tail loads
+  w.counters = reinterpret_cast<int*>(take(16));
+  w.status = reinterpret_cast<unsigned*>(take(4));
+  w.active = reinterpret_cast<int*>(take(size_t(experts) * 4));
+  w.ranges = reinterpret_cast<unsigned*>(take(size_t(experts) * 8));
+  w.assignments = reinterpret_cast<unsigned*>(take(size_t(tokens) * topk * 4));
+  w.position = reinterpret_cast<unsigned*>(take(size_t(tokens) * topk * 4));
+  w.xq = take(size_t(tokens) * hidden);
+  w.xs = reinterpret_cast<float*>(take(size_t(tokens) * (hidden / 128) * 4));
+  w.aq = take(rows * hidden);
+  w.as = reinterpret_cast<float*>(take(rows * (hidden / 128) * 4));
+  w.p = reinterpret_cast<__nv_bfloat16*>(take(rows * inter * 2));
+  w.pq = take(rows * inter);
+  w.ps = reinterpret_cast<float*>(take(rows * (inter / 128) * 4));
+  w.y = reinterpret_cast<float*>(take(rows * hidden * 4));
+  w.bytes = off;
+  return w;
+}
+
+}  // namespace dmoe
+
+using namespace dmoe;
+
+extern "C" int darask_fp8_grouped_gemm(const void* a_codes, const float* a_scales, unsigned long long a_rows, const void* w0,
+                                       const void* w1, const float* sw0, const float* sw1, int experts, int n, int k, int gate_up,
+                                       const unsigned* ranges, void* out, unsigned* status, cudaStream_t st) {
+  if (!a_codes || !a_scales || !w0 || !sw0 || !ranges || !out || !status || experts < 1 || experts > 1024 || n < 128 || n % 128 ||
+      k < 128 || k % 128 || (gate_up && (!w1 || !sw1)))
+    return cudaErrorInvalidValue;
+  return launch_grouped(a_codes, a_scales, a_rows, w0, w1, sw0, sw1, experts, n, k, gate_up, ranges,
+                        gate_up ? static_cast<__nv_bfloat16*>(out) : nullptr, gate_up ? nullptr : static_cast<float*>(out), status, st);
+}
+
+extern "C" size_t darask_fp8_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens) {
+  return carve(nullptr, hidden, inter, experts, topk, tokens).bytes;
+}
+
+extern "C" int darask_fp8_moe_layer(const DaraskFp8Moe* d, cudaStream_t st) {
+  if (!d || !d->x || !d->logits || !d->gate_w || !d->up_w || !d->down_w || !d->gate_s || !d->up_s || !d->down_s || !d->out ||
+      !d->ids || !d->prob || !d->workspace)
+    return cudaErrorInvalidValue;
+  const int H = d->hidden, F = d->inter, E = d->experts, K = d->topk, T = d->tokens;
+  if (H < 128 || F < 128 || H % 128 || F % 128 || E < K || E > 1024 || K < 1 || K > 32 || T < 1) return cudaErrorInvalidValue;
+  if (d->workspace_bytes < darask_fp8_moe_workspace_bytes(H, F, E, K, T)) return cudaErrorInvalidValue;
+  const Fp8Ws w = carve(d->workspace, H, F, E, K, T);
+  cudaError_t e;
+  if ((e = cudaMemsetAsync(w.counters, 0, 2048, st))) return e;       // counters and the status word
+  const RouteArgs route{d->logits, E, E, K, T, nullptr, 1.f, d->ids, d->prob, nullptr};
+  const PermuteArgs perm{d->ids, T, K, E, w.assignments, w.ranges, w.active, w.counters, w.status, nullptr, 0};
+  if ((e = launch_pdl(route_topk_kernel<kRouteKogarashi>, dim3((T + 3) / 4), dim3(128), 0, st, route))) return e;
+  if ((e = launch_pdl(permute_kernel<0>, dim3(1), dim3(1024), size_t(E + 1) * 4, st, perm))) return e;
+  if ((e = (cudaError_t)darask_quantize_fp8_act(w.xq, w.xs, d->x, 1, T, H, st))) return e;
+  if ((e = launch_pdl(gather_fp8_kernel, dim3(T * K), dim3(256), 0, st, (const uint8_t*)w.xq, (const float*)w.xs,
+                      (const unsigned*)w.assignments, (const int*)w.counters, K, H, w.aq, w.as, w.position))) return e;
+  const unsigned long long rows = (unsigned long long)T * K + 128;
+  if ((e = launch_grouped(w.aq, w.as, rows, d->gate_w, d->up_w, d->gate_s, d->up_s, E, F, H, 1, w.ranges, w.p, nullptr, w.status, st))) return e;
+  const long long warps = (long long)T * K * (F / 128);
+  if ((e = launch_pdl(quant_rows_kernel, dim3(unsigned((warps + 7) / 8)), dim3(256), 0, st, (const __nv_bfloat16*)w.p,
+                      (const int*)w.counters, F, w.pq, w.ps))) return e;
+  if ((e = launch_grouped(w.pq, w.ps, rows, d->down_w, nullptr, d->down_s, nullptr, E, H, F, 0, w.ranges, nullptr, w.y, w.status, st))) return e;
+  return launch_pdl(combine_rows_kernel, dim3((H + 255) / 256, T), dim3(256), 0, st, d->out, (const float*)w.y, (const float*)d->prob,
+                    (const unsigned*)w.position, H, K);
+}
+
+extern "C" int darask_fp8_moe_status(const void* workspace, unsigned* host_status, cudaStream_t st) {
+  if (!workspace || !host_status) return cudaErrorInvalidValue;
+  const Fp8Ws w = carve(const_cast<void*>(workspace), 128, 128, 1, 1, 1);
+  cudaError_t e = cudaMemcpyAsync(host_status, w.status, 4, cudaMemcpyDeviceToHost, st);
+  return e ? e : cudaStreamSynchronize(st);
+}

@@ -200,6 +200,35 @@ size_t hayate_moe_workspace_bytes(int hidden, int inter, int experts, int topk, 
 int hayate_moe_workspace_init(void* workspace, size_t bytes, darask_stream_t stream);
 int hayate_moe_layer(const HayateMoe* desc /* host */, darask_stream_t stream);
 
+/* ---- FP8 prefill path -----------------------------------------------------------------------------------------
+ * Ragged grouped GEMM on tcgen05 tensor cores over block-scaled e4m3 operands.  Replaces hayate_glm_grouped /
+ * hayate_glm_grouped_nvfp4 (engines/hayate/crates/kernels/cu/glm53/grouped.cu:59-124: CUTLASS Sm80 grouped GEMM on
+ * weights restored to bf16) and hayate_glm_grouped_packed_{gate_up,down} (packed_grouped.cu:177-318) for the
+ * FP8 format: a_codes e4m3 [a_rows][k] with a_scales float32 [a_rows][k/128] (rows in dispatch order; the buffer
+ * must reach one 128-row tile past the last expert's rows), w e4m3 [experts][n][k] with sw float32
+ * [experts][n/128][k/128], ranges [experts][2] = {rows, offset}.  gate_up != 0: out = silu(a.w0^T) * (a.w1^T) as
+ * bf16 [a_rows][n]; else out = a.w0^T as float32 [a_rows][n].  n and k multiples of 128. */
+int darask_fp8_grouped_gemm(const void* a_codes, const float* a_scales, unsigned long long a_rows, const void* w0,
+                            const void* w1, const float* sw0, const float* sw1, int experts, int n, int k, int gate_up,
+                            const unsigned* ranges, void* out, unsigned* status, darask_stream_t stream);
+/* Whole FP8 MoE layer for a prefill batch: softmax top-k (renormalised) on the given logits, activations
+ * quantized to e4m3 per token and 128 channels, dispatch gather, grouped gate/up GEMM with SwiGLU, products
+ * quantized the same way, grouped down GEMM, combine.  Mirrors `prefill_experts`
+ * (engines/hayate/crates/models/src/glm53/gpu.rs:2068-2566) without its device->host copy of the routes. */
+typedef struct {
+  int hidden, inter, experts, topk, tokens;
+  const void* x;                        /* bf16 [tokens][hidden]                                         */
+  const float* logits;                  /* [tokens][experts]                                             */
+  const void* gate_w; const void* up_w; const void* down_w;     /* e4m3 [E][inter][hidden] x2, [E][hidden][inter] */
+  const float* gate_s; const float* up_s; const float* down_s;  /* float32 per 128x128 block              */
+  float* out;                           /* float32 [tokens][hidden]                                      */
+  int* ids; float* prob;                /* [tokens][topk]                                                */
+  void* workspace; size_t workspace_bytes;
+} DaraskFp8Moe;
+size_t darask_fp8_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens);
+int darask_fp8_moe_layer(const DaraskFp8Moe* desc /* host */, darask_stream_t stream);
+int darask_fp8_moe_status(const void* workspace, unsigned* host_status /* host */, darask_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

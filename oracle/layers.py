@@ -229,8 +229,9 @@ def fp8_dequant_gemm(aq, a_scale, wq, w_scale):
 
 def fp8_forward(layer: Fp8Layer, x: np.ndarray, logits: np.ndarray):
     """x bf16-valued float32 [T,H], logits float32 [T,E] (softmax top-k, renormalised, as
-    Kogarashi). Activations and the SwiGLU product are quantized to e4m3 with one float32
-    scale per token and 128 channels. -> dict(ids, prob, out float32 [T,H])."""
+    Kogarashi). Activations and the SwiGLU product (stored as bf16 between the two grouped
+    products) are quantized to e4m3 with one float32 scale per token and 128 channels.
+    -> dict(ids, prob, out float32 [T,H])."""
     ids, prob = R.route_kogarashi(logits, layer.topk)
     xq, xs = F.fp8_act_quantize(x)
     out = np.zeros((x.shape[0], layer.hidden), np.float64)
@@ -242,7 +243,7 @@ def fp8_forward(layer: Fp8Layer, x: np.ndarray, logits: np.ndarray):
         tok = a // layer.topk
         g = fp8_dequant_gemm(xq[tok], xs[tok], *layer.gate[e])
         u = fp8_dequant_gemm(xq[tok], xs[tok], *layer.up[e])
-        hq, hs = F.fp8_act_quantize((_silu64(g) * u).astype(np.float32))
+        hq, hs = F.fp8_act_quantize(F.bf16_round((_silu64(g) * u).astype(np.float32)))
         y = fp8_dequant_gemm(hq, hs, *layer.down[e]).astype(np.float32)
         np.add.at(out, tok, y.astype(np.float64) * prob.reshape(-1)[a].astype(np.float64)[:, None])
     return dict(ids=ids, prob=prob, out=out.astype(np.float32))

@@ -103,3 +103,22 @@ def hayate_layer(seed, hidden, inter, experts, topk, tokens, scale=2.5, pool=8):
     stride = F.hayate_expert_stride(hidden, inter)
     layer = L.HayateLayer(hidden, inter, experts, topk, scale, router, bias, np.stack(imgs)[np.arange(experts) % pool], stride, shared)
     return layer, dict(x=x)
+
+
+def fp8_layer(seed, hidden, inter, experts, topk, tokens, pool=4, zipf=None):
+    """Block-FP8 experts (a pool of distinct experts repeated), bf16-valued activations, router logits."""
+    rng = rng_for(seed)
+    pool = min(pool, experts)
+    mats = []
+    for _ in range(pool):
+        mats.append(tuple(F.fp8_block_quantize(normal(rng, shp, std)) for shp, std in
+                          (((inter, hidden), hidden ** -0.5), ((inter, hidden), hidden ** -0.5), ((hidden, inter), inter ** -0.5))))
+    layer = L.Fp8Layer(hidden, inter, experts, topk)
+    for e in range(experts):
+        g, u, d = mats[e % pool]
+        layer.gate.append(g), layer.up.append(u), layer.down.append(d)
+    x = F.bf16_round(normal(rng, (tokens, hidden), 1.0))
+    logits = normal(rng, (tokens, experts), 1.0)
+    if zipf:
+        logits = (logits + zipf_bias(rng, experts, zipf)[None, :]).astype(np.float32)
+    return layer, dict(x=x, logits=logits)
