@@ -77,6 +77,9 @@ _SIGNATURES = {
     "darask_quantize_nvfp4_tiled": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "darask_quantize_fp8_block": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "darask_quantize_fp8_act": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p]),
+    "darask_moe_permute_scratch_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "darask_moe_permute_large": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                         c_size_t, c_void_p]),
     "darask_fp8_grouped_gemm": (c_int, [c_void_p, c_void_p, ctypes.c_ulonglong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                         c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "darask_fp8_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),

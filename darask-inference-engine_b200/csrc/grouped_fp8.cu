@@ -5,6 +5,7 @@
 #include "../../include/darask_moe_b200.h"
 #include "grouped_fp8.cuh"
 #include "route_kernels.cuh"
+#include "permute_large.cuh"
 #include "stream_launch.cuh"
 
 namespace dmoe {
@@ -106,7 +107,7 @@ static cudaError_t launch_grouped(const void* a_codes, const float* a_scales, un
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 struct Fp8Ws {
-  int* counters; unsigned* status; int* active; unsigned* ranges; unsigned* assignments; unsigned* position;
+  int* counters; unsigned* status; int* active; unsigned* ranges; unsigned* assignments; unsigned* position; int* perm_scratch;
   uint8_t* xq; float* xs; uint8_t* aq; float* as; __nv_bfloat16* p; uint8_t* pq; float* ps; float* y; size_t bytes;
 };
 static Fp8Ws carve(void* base, int hidden, int inter, int experts, int topk, int tokens) {
@@ -121,6 +122,7 @@ static Fp8Ws carve(void* base, int hidden, int inter, int experts, int topk, int
   w.ranges = reinterpret_cast<unsigned*>(take(size_t(experts) * 8));
   w.assignments = reinterpret_cast<unsigned*>(take(size_t(tokens) * topk * 4));
   w.position = reinterpret_cast<unsigned*>(take(size_t(tokens) * topk * 4));
+  w.perm_scratch = reinterpret_cast<int*>(take(permute_scratch_bytes(tokens, topk, experts)));
   w.xq = take(size_t(tokens) * hidden);
   w.xs = reinterpret_cast<float*>(take(size_t(tokens) * (hidden / 128) * 4));
   w.aq = take(rows * hidden);
@@ -147,6 +149,20 @@ extern "C" int darask_fp8_grouped_gemm(const void* a_codes, const float* a_scale
                         gate_up ? static_cast<__nv_bfloat16*>(out) : nullptr, gate_up ? nullptr : static_cast<float*>(out), status, st);
 }
 
+extern "C" size_t darask_moe_permute_scratch_bytes(int tokens, int topk, int experts) {
+  return tokens < 1 || topk < 1 || experts < 1 ? 0 : permute_scratch_bytes(tokens, topk, experts);
+}
+
+extern "C" int darask_moe_permute_large(const int* ids, int tokens, int topk, int experts, unsigned* assignments, unsigned* ranges,
+                                        int* active, int* counters, unsigned* status, void* scratch, size_t scratch_bytes,
+                                        cudaStream_t st) {
+  if (!ids || !assignments || !ranges || !active || !counters || !status || !scratch || tokens < 1 || topk < 1 || experts < 1 ||
+      experts > 1024 || scratch_bytes < permute_scratch_bytes(tokens, topk, experts))
+    return cudaErrorInvalidValue;
+  const PermuteArgs p{ids, tokens, topk, experts, assignments, ranges, active, counters, status, nullptr, 0};
+  return launch_permute_large(p, scratch, st);
+}
+
 extern "C" size_t darask_fp8_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens) {
   return carve(nullptr, hidden, inter, experts, topk, tokens).bytes;
 }
@@ -164,7 +180,9 @@ extern "C" int darask_fp8_moe_layer(const DaraskFp8Moe* d, cudaStream_t st) {
   const RouteArgs route{d->logits, E, E, K, T, nullptr, 1.f, d->ids, d->prob, nullptr};
   const PermuteArgs perm{d->ids, T, K, E, w.assignments, w.ranges, w.active, w.counters, w.status, nullptr, 0};
   if ((e = launch_pdl(route_topk_kernel<kRouteKogarashi>, dim3((T + 3) / 4), dim3(128), 0, st, route))) return e;
-  if ((e = launch_pdl(permute_kernel<0>, dim3(1), dim3(1024), size_t(E + 1) * 4, st, perm))) return e;
+  if (T * K > 2048) {
+    if ((e = launch_permute_large(perm, w.perm_scratch, st))) return e;
+  } else if ((e = launch_pdl(permute_kernel<0>, dim3(1), dim3(1024), size_t(E + 1) * 4, st, perm))) return e;
   if ((e = (cudaError_t)darask_quantize_fp8_act(w.xq, w.xs, d->x, 1, T, H, st))) return e;
   if ((e = launch_pdl(gather_fp8_kernel, dim3(T * K), dim3(256), 0, st, (const uint8_t*)w.xq, (const float*)w.xs,
                       (const unsigned*)w.assignments, (const int*)w.counters, K, H, w.aq, w.as, w.position))) return e;

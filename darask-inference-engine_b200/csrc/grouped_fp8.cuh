@@ -5,12 +5,13 @@
 // columns; W: e4m3 with one float32 scale per 128x128 block (hayate `Fp8Block`, cpu/glm53.rs:23-24).
 // One CTA computes a 128-row x 128-column output tile of one expert:
 //   warp 0    TMA producer: cp.async.bulk.tensor 2D loads (128B swizzle) of the A and W tiles of one 128-wide
-//             K block per stage into a 4-stage shared-memory ring (mbarrier full/empty)
-//   warp 1    issues tcgen05.mma kind::f8f6f4 (M128 N128 K32, four per K block) into one of two TMEM
+//             K block per stage into a 6-stage shared-memory ring (mbarrier full/empty)
+//   warp 1    issues tcgen05.mma kind::f8f6f4 (M128 N128 K32, four per K block) into one of four TMEM
 //             accumulator buffers and commits to the ring / accumulator barriers
-//   warps 2-5 epilogue: tcgen05.ld the K block's partial tile (one TMEM lane = one row per thread), multiply by
-//             the block scales and add into float32 registers; after the last K block apply SwiGLU (gate/up
-//             mode: columns 0-63 are gate rows, 64-127 the matching up rows) and store
+//   warps 2-9 epilogue: two warps per TMEM lane quarter, 64 columns each; tcgen05.ld the K block's partial tile
+//             (one TMEM lane = one row per thread), multiply by the block scales and add into float32 registers
+//             (packed f32x2 fma); after the last K block apply SwiGLU (gate/up mode: columns 0-63 are gate rows,
+//             64-127 the matching up rows; a warp owns 32 gate columns and their 32 up columns) and store
 // Every wait is bounded; a timeout sets a status bit, the CTA drains, frees its TMEM and returns.
 // Replaces hayate cu/glm53/grouped.cu:59-124 (CUTLASS Sm80 grouped GEMM on restored bf16 weights) and
 // packed_grouped.cu:177-266 (mma.sync grouped GEMM); the FP8 activation path has no reference counterpart.
@@ -20,10 +21,11 @@
 
 namespace dmoe {
 
-constexpr int kG8Stages = 4;
+constexpr int kG8Stages = 6;
 constexpr int kG8TileM = 128, kG8TileN = 128, kG8TileK = 128;
 constexpr int kG8StageBytes = kG8TileM * kG8TileK + kG8TileN * kG8TileK;     // A tile + W tile, one byte per element
-constexpr int kG8Threads = 192;
+constexpr int kG8Threads = 320;          // TMA warp, MMA warp, 8 epilogue warps
+constexpr int kG8AccBufs = 4;            // TMEM accumulator buffers of 128 columns
 
 struct G8Args {
   const float* sa;             // [rows_total][K/128]
@@ -58,8 +60,7 @@ DEVI void umma_commit(uint64_t* bar) {
 }
 DEVI void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 DEVI void tmem_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-DEVI void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
+DEVI void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -68,10 +69,8 @@ DEVI void tmem_ld32(uint32_t taddr, float (&v)[32]) {
         "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+DEVI void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // tile index -> (expert, first row of the tile inside the expert, first output column)
 struct G8Tile { int expert, m0, n0, rows, offset; };
@@ -81,7 +80,7 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                    const __grid_constant__ CUtensorMap map_w1, const G8Args a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t full[kG8Stages], empty[kG8Stages], tfull[2], tempty[2];
+  __shared__ uint64_t full[kG8Stages], empty[kG8Stages], tfull[kG8AccBufs], tempty[kG8AccBufs];
   __shared__ uint32_t tmem_base_slot;
   __shared__ int ends[1025];
   __shared__ volatile int abort_flag;
@@ -90,11 +89,11 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   if (threadIdx.x == 0) {
     abort_flag = 0;
     for (int s = 0; s < kG8Stages; ++s) { mbar_init(full + s, 1); mbar_init(empty + s, 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull + b, 1); mbar_init(tempty + b, 128); }
+    for (int b = 0; b < kG8AccBufs; ++b) { mbar_init(tfull + b, 1); mbar_init(tempty + b, 256); }
     mbar_fence_init();
   }
-  if (warp == 1) {       // TMEM: two accumulator buffers of 128 columns
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(256u) : "memory");
+  if (warp == 1) {       // TMEM: all 512 columns = four accumulator buffers
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512u) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   pdl_wait();
@@ -155,8 +154,8 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       int it = 0, acc_it = 0;
       for (int tile = blockIdx.x; tile < total && !abort_flag; tile += gridDim.x) {
         for (int kb = 0; kb < kblocks; ++kb, ++it, ++acc_it) {
-          const int s = it % kG8Stages, buf = acc_it & 1;
-          if (acc_it >= 2 && !mbar_wait(tempty + buf, ((acc_it >> 1) & 1) ^ 1, a.status)) { abort_flag = 1; break; }
+          const int s = it % kG8Stages, buf = acc_it & (kG8AccBufs - 1);
+          if (acc_it >= kG8AccBufs && !mbar_wait(tempty + buf, ((acc_it / kG8AccBufs) & 1) ^ 1, a.status)) { abort_flag = 1; break; }
           if (!mbar_wait(full + s, (it / kG8Stages) & 1, a.status)) { abort_flag = 1; break; }
           tmem_fence_after();
           const uint32_t sa = smem_u32(smem + s * kG8StageBytes), sb = sa + kG8TileM * kG8TileK;
@@ -170,9 +169,11 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       }
     }
   } else {
-    // ---- epilogue: thread = one row of the tile -------------------------------------------------------------
+    // ---- epilogue: thread = one row of the tile, 64 of its 128 columns -----------------------------------------
     const int quarter = warp & 3;                       // TMEM lanes 32*quarter .. +31 belong to this warp
+    const int half = (warp - 2) >> 2;
     const int row_in_tile = quarter * 32 + lane;
+    const int col0 = a.gate_up ? 32 * half : 64 * half, col1 = a.gate_up ? 64 + 32 * half : 64 * half + 32;
     int acc_it = 0;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
       const G8Tile t = locate(tile);
@@ -181,41 +182,49 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       const float* sa_row = a.sa + size_t(grow) * kblocks;
       const float* sw0 = a.sw[0] + size_t(t.expert) * a.sw_expert_stride + size_t(t.n0 / 128) * kblocks;
       const float* sw1 = a.gate_up ? a.sw[1] + size_t(t.expert) * a.sw_expert_stride + size_t(t.n0 / 128) * kblocks : sw0;
-      float acc[128];
+      float2 acc[32];
 #pragma unroll
-      for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+      for (int i = 0; i < 32; ++i) acc[i] = make_float2(0.f, 0.f);
       bool ok = true;
       for (int kb = 0; kb < kblocks; ++kb, ++acc_it) {
-        const int buf = acc_it & 1;
-        if (ok && !mbar_wait(tfull + buf, (acc_it >> 1) & 1, a.status)) { abort_flag = 1; ok = false; }
-        if (!ok) continue;
-        tmem_fence_after();
+        const int buf = acc_it & (kG8AccBufs - 1);
         const float s_row = valid ? __ldg(sa_row + kb) : 0.f;
         const float f0 = s_row * __ldg(sw0 + kb), f1 = s_row * __ldg(sw1 + kb);
+        if (ok && !mbar_wait(tfull + buf, (acc_it / kG8AccBufs) & 1, a.status)) { abort_flag = 1; ok = false; }
+        if (!ok) continue;
+        tmem_fence_after();
         const uint32_t taddr = tmem_base + buf * 128 + (uint32_t(quarter * 32) << 16);
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          float v[32];
-          tmem_ld32(taddr + c * 32, v);
-          const float f = (a.gate_up && c >= 2) ? f1 : f0;
-#pragma unroll
-          for (int i = 0; i < 32; ++i) acc[c * 32 + i] = fmaf(v[i], f, acc[c * 32 + i]);
-        }
+        uint32_t v0[32], v1[32];
+        tmem_ld32_issue(taddr + col0, v0);
+        tmem_ld32_issue(taddr + col1, v1);
+        tmem_ld_wait();
         tmem_fence_before();
-        mbar_arrive(tempty + buf);
+        mbar_arrive(tempty + buf);                      // the values are in registers: the buffer may be overwritten
+        const float2 p0 = make_float2(f0, f0), p1 = make_float2(f1, f1);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          acc[i] = __ffma2_rn(make_float2(__uint_as_float(v0[2 * i]), __uint_as_float(v0[2 * i + 1])), p0, acc[i]);
+          acc[16 + i] = __ffma2_rn(make_float2(__uint_as_float(v1[2 * i]), __uint_as_float(v1[2 * i + 1])), p1, acc[16 + i]);
+        }
       }
       if (ok && valid) {
         if (a.gate_up) {
-          __nv_bfloat16* dst = a.out_bf16 + size_t(grow) * a.n + t.n0;
+          __nv_bfloat16* dst = a.out_bf16 + size_t(grow) * a.n + t.n0 + 32 * half;
 #pragma unroll
-          for (int i = 0; i < 64; i += 2) {
-            const float h0 = silu_mul(acc[i], acc[64 + i]), h1 = silu_mul(acc[i + 1], acc[64 + i + 1]);
-            *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(h0, h1);
+          for (int i = 0; i < 16; i += 4) {
+            uint4 o;
+            uint32_t* w = &o.x;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const __nv_bfloat162 h = __floats2bfloat162_rn(silu_mul(acc[i + j].x, acc[16 + i + j].x), silu_mul(acc[i + j].y, acc[16 + i + j].y));
+              w[j] = *reinterpret_cast<const uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(dst + 2 * i) = o;
           }
         } else {
-          float* dst = a.out_f32 + size_t(grow) * a.n + t.n0;
+          float* dst = a.out_f32 + size_t(grow) * a.n + t.n0 + 64 * half;
 #pragma unroll
-          for (int i = 0; i < 128; i += 4) *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+          for (int i = 0; i < 32; i += 2) *reinterpret_cast<float4*>(dst + 2 * i) = make_float4(acc[i].x, acc[i].y, acc[i + 1].x, acc[i + 1].y);
         }
       }
       if (!ok) break;
@@ -223,7 +232,7 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   }
   tmem_fence_before();
   __syncthreads();
-  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(256u) : "memory");
+  if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
 }
 
 }  // namespace dmoe

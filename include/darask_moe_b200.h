@@ -46,6 +46,12 @@ int darask_route_topk_hayate(const float* logits, int ld, int experts, int topk,
  * set DARASK_STATUS_BAD_ROUTE in *status. */
 int darask_moe_permute(const int* ids, int tokens, int topk, int experts, unsigned* assignments, unsigned* ranges,
                        int* active, int* counters, unsigned* status, darask_stream_t stream);
+/* The same permutation for prefill-sized batches, spread over many thread blocks (three launches);
+ * `scratch`: darask_moe_permute_scratch_bytes(tokens, topk, experts) bytes of device memory. */
+size_t darask_moe_permute_scratch_bytes(int tokens, int topk, int experts);
+int darask_moe_permute_large(const int* ids, int tokens, int topk, int experts, unsigned* assignments, unsigned* ranges,
+                             int* active, int* counters, unsigned* status, void* scratch, size_t scratch_bytes,
+                             darask_stream_t stream);
 
 /* ---- GGUF Q6_K device layout ------------------------------------------------------------------
  * Lossless regrouping of Q6_K rows (k/256 blocks of 210 bytes, never 16-byte aligned) into

@@ -83,7 +83,7 @@ def test_hayate_router(experts, topk, scale):
         assert ids.tolist() == [[1, 3], [1, 3]] and np.allclose(w, 1.25, rtol=1e-6)
 
 
-def gpu_permute(ids, experts, topk):
+def gpu_permute(ids, experts, topk, large=False):
     import darask_inference_engine_b200 as D
     lib = D._lib.lib()
     t = ids.size // topk
@@ -93,8 +93,14 @@ def gpu_permute(ids, experts, topk):
     active = torch.full((experts,), -1, dtype=torch.int32, device="cuda")
     counters = torch.zeros(4, dtype=torch.int32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    rc = lib.darask_moe_permute(d.data_ptr(), t, topk, experts, asg.data_ptr(), ranges.data_ptr(), active.data_ptr(),
-                                counters.data_ptr(), status.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    if large:
+        scratch = torch.empty(lib.darask_moe_permute_scratch_bytes(t, topk, experts), dtype=torch.uint8, device="cuda")
+        rc = lib.darask_moe_permute_large(d.data_ptr(), t, topk, experts, asg.data_ptr(), ranges.data_ptr(), active.data_ptr(),
+                                          counters.data_ptr(), status.data_ptr(), scratch.data_ptr(), scratch.numel(),
+                                          torch.cuda.current_stream().cuda_stream)
+    else:
+        rc = lib.darask_moe_permute(d.data_ptr(), t, topk, experts, asg.data_ptr(), ranges.data_ptr(), active.data_ptr(),
+                                    counters.data_ptr(), status.data_ptr(), torch.cuda.current_stream().cuda_stream)
     assert rc == 0
     torch.cuda.synchronize()
     return (asg.cpu().numpy().view(np.uint32), ranges.cpu().numpy().reshape(experts, 2), active.cpu().numpy(),
@@ -118,6 +124,23 @@ def test_permutation_golden_and_random():
         assert status == 0 and np.array_equal(asg, ra) and np.array_equal(ranges[:, 0], rc)
         assert np.array_equal(ranges[:, 1], ro)
         assert np.array_equal(active[:counters[0]], np.nonzero(rc)[0])
+
+
+def test_permutation_large_batches():
+    """The multi-block permutation equals the host loop on prefill-sized and ragged batches, skewed and uniform."""
+    rng = np.random.default_rng(1)
+    for t, e, k, skew in [(4096, 256, 8, True), (4096, 256, 8, False), (1, 8, 2, False), (129, 1024, 5, False),
+                          (1025, 64, 4, True), (8192, 512, 10, False)]:
+        p = 1.0 / np.arange(1, e + 1) ** 1.1 if skew else np.ones(e)
+        p = p / p.sum()
+        ids = np.stack([rng.choice(e, size=k, replace=False, p=p) for _ in range(t)])
+        asg, ranges, active, counters, status = gpu_permute(ids, e, k, large=True)
+        ra, rc, ro = R.permutation(ids, e, k)
+        assert status == 0 and np.array_equal(asg, ra)
+        assert np.array_equal(ranges[:, 0], rc) and np.array_equal(ranges[:, 1], ro)
+        assert np.array_equal(active[:counters[0]], np.nonzero(rc)[0]) and counters[1] == t * k
+    _, _, _, counters, status = gpu_permute(np.array([2, 2, 3, 4, 5, 6, 1, 0] * 300), 288, 8, large=True)
+    assert status & 2 and counters[1] == 7 * 300
 
 
 def test_permutation_flags_bad_routes():
