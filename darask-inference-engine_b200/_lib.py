@@ -81,7 +81,7 @@ _SIGNATURES = {
     "darask_moe_permute_large": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                          c_size_t, c_void_p]),
     "darask_fp8_grouped_gemm": (c_int, [c_void_p, c_void_p, ctypes.c_ulonglong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                                        c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+                                        c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "darask_fp8_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "darask_fp8_moe_layer": (c_int, [ctypes.POINTER(DaraskFp8Moe), c_void_p]),
     "darask_fp8_moe_status": (c_int, [c_void_p, ctypes.POINTER(c_uint), c_void_p]),

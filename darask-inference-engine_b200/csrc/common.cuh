@@ -34,6 +34,8 @@ DEVI float warp_max(float v) {
 }
 DEVI float sigmoid_precise(float x) { return 1.f / (1.f + expf(-x)); }
 DEVI float silu_mul(float g, float u) { return g * (1.f / (1.f + expf(-g))) * u; }
+// hardware exp2 / reciprocal approximations (about 2 ulp each): for products that are rounded to bf16 right after
+DEVI float silu_mul_fast(float g, float u) { return __fdividef(g * u, 1.f + __expf(-g)); }
 
 DEVI uint64_t global_timer_ns() {
   uint64_t t;
@@ -79,6 +81,31 @@ DEVI bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned* status) {
     if ((spin & 63u) == 0) {
       __nanosleep(64);
       if (global_timer_ns() - start > kWaitLimitNs) {
+        atomicOr(status, kStatusWaitTimeout);
+        return false;
+      }
+    }
+  }
+}
+// Same contract, but each probe lets the hardware suspend the thread until the phase completes or a short
+// time limit passes, so that many waiting warps do not fill the issue slots with polling.
+DEVI bool mbar_wait_suspend(uint64_t* bar, uint32_t parity, unsigned* status) {
+  const uint32_t addr = smem_u32(bar);
+  uint64_t start = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity), "r"(20000u)
+        : "memory");
+    if (ok) return true;
+    if ((spin & 15u) == 0) {
+      const uint64_t now = global_timer_ns();
+      if (spin == 0) start = now;
+      else if (now - start > kWaitLimitNs) {
         atomicOr(status, kStatusWaitTimeout);
         return false;
       }

@@ -26,28 +26,6 @@ __global__ void __launch_bounds__(256) gather_fp8_kernel(const uint8_t* codes, c
   for (int c = threadIdx.x; c < k / 128; c += 256) out_scales[dst * (k / 128) + c] = __ldg(scales + src * (k / 128) + c);
 }
 
-// bf16 rows -> e4m3 codes + float32 scale per row and 128 columns (same arithmetic as darask_quantize_fp8_act)
-__global__ void __launch_bounds__(256) quant_rows_kernel(const __nv_bfloat16* x, const int* counters, int k, uint8_t* q, float* scales) {
-  pdl_wait();
-  pdl_launch();
-  const long long rows = __ldcg(counters + 1);
-  const long long w = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31, groups = k / 128;
-  if (w >= rows * groups) return;
-  const long long r = w / groups;
-  const int g = int(w % groups);
-  const __nv_bfloat16* p = x + r * k + g * 128 + lane * 4;
-  float v[4], amax = 0.f;
-  for (int i = 0; i < 4; ++i) { v[i] = __bfloat162float(p[i]); amax = fmaxf(amax, fabsf(v[i])); }
-  amax = warp_max(amax);
-  const float scale = amax == 0.f ? 1.f : amax / 448.f;
-  if (lane == 0) scales[r * groups + g] = scale;
-  uint32_t out = 0;
-  for (int i = 0; i < 4; ++i)
-    out |= uint32_t((uint8_t)__nv_cvt_float_to_fp8(fminf(fmaxf(v[i] / scale, -448.f), 448.f), __NV_SATFINITE, __NV_E4M3)) << (8 * i);
-  *reinterpret_cast<uint32_t*>(q + r * k + g * 128 + lane * 4) = out;
-}
-
 // out[t][i] = sum_s prob[t][s] * y[position[t*k+s]][i]  (fp32 fma in slot order), stored as float32
 __global__ void __launch_bounds__(256) combine_rows_kernel(float* out, const float* y, const float* prob, const unsigned* position,
                                                            int hidden, int topk) {
@@ -83,32 +61,53 @@ static bool make_map(CUtensorMap* m, const void* base, unsigned long long rows, 
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+#ifdef DMOE_G8_TRACE
+#include <cstdlib>
+static long long* g_g8_trace = nullptr;
+extern "C" void darask_g8_set_trace(long long* p) { g_g8_trace = p; }
+#endif
+
 static cudaError_t launch_grouped(const void* a_codes, const float* a_scales, unsigned long long a_rows, const void* w0,
-                                  const void* w1, const float* sw0, const float* sw1, int experts, int n, int k, int gate_up,
-                                  const unsigned* ranges, __nv_bfloat16* out_bf16, float* out_f32, unsigned* status, cudaStream_t st) {
+                                  const void* w1, const float* sw0, const float* sw1, int experts, int n, int k, int mode,
+                                  const unsigned* ranges, void* out, float* out_scales, const unsigned* out_row_map,
+                                  unsigned* status, cudaStream_t st) {
   CUtensorMap ma, mw0, mw1;
+  const bool gate_up = mode != kG8Plain;
   if (!make_map(&ma, a_codes, a_rows, k, 128)) return cudaErrorInvalidValue;
-  if (!make_map(&mw0, w0, (unsigned long long)experts * n, k, gate_up ? 64 : 128)) return cudaErrorInvalidValue;
-  if (!make_map(&mw1, gate_up ? w1 : w0, (unsigned long long)experts * n, k, gate_up ? 64 : 128)) return cudaErrorInvalidValue;
+  if (!make_map(&mw0, w0, (unsigned long long)experts * n, k, 128)) return cudaErrorInvalidValue;
+  if (!make_map(&mw1, gate_up ? w1 : w0, (unsigned long long)experts * n, k, 128)) return cudaErrorInvalidValue;
   G8Args g = {};
   g.sa = a_scales; g.sw[0] = sw0; g.sw[1] = sw1;
-  g.sw_expert_stride = (unsigned long long)((n + 127) / 128) * (k / 128);
-  g.ranges = ranges; g.experts = experts; g.n = n; g.k = k; g.gate_up = gate_up;
-  g.out_bf16 = out_bf16; g.out_f32 = out_f32; g.status = status;
-  const size_t smem = size_t(kG8Stages) * kG8StageBytes + 1024;
+  g.sw_expert_stride = (unsigned long long)(n / 128) * (k / 128);
+  g.ranges = ranges; g.experts = experts; g.n = n; g.k = k; g.mode = mode;
+  g.out_f32 = mode == kG8Plain ? static_cast<float*>(out) : nullptr;
+  g.out_bf16 = mode == kG8GateUpBf16 ? static_cast<__nv_bfloat16*>(out) : nullptr;
+  g.out_codes = mode == kG8GateUpFp8 ? static_cast<uint8_t*>(out) : nullptr;
+  g.out_scales = out_scales; g.out_row_map = out_row_map; g.status = status;
+#ifdef DMOE_G8_TRACE
+  g.trace = g_g8_trace;
+  { const char* dbg = getenv("DMOE_G8_DEBUG"); g.debug = dbg ? atoi(dbg) : 0; }
+#endif
+  const size_t smem = size_t(kG8FixedSmem) + size_t(experts + 1) * sizeof(int);
   static bool configured = false;
   if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(grouped_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    const int most = int(size_t(kG8FixedSmem) + size_t(kG8MaxExperts + 1) * sizeof(int));
+    cudaError_t e = cudaFuncSetAttribute(grouped_fp8_kernel<kG8Plain>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    if (!e) e = cudaFuncSetAttribute(grouped_fp8_kernel<kG8GateUpBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
+    if (!e) e = cudaFuncSetAttribute(grouped_fp8_kernel<kG8GateUpFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (e != cudaSuccess) return e;
     configured = true;
   }
-  return launch_pdl(grouped_fp8_kernel, dim3(sm_count()), dim3(kG8Threads), smem, st, ma, mw0, mw1, g);
+  const dim3 grid(sm_count()), block(kG8Threads);
+  if (mode == kG8Plain) return launch_pdl(grouped_fp8_kernel<kG8Plain>, grid, block, smem, st, ma, mw0, mw1, g);
+  if (mode == kG8GateUpBf16) return launch_pdl(grouped_fp8_kernel<kG8GateUpBf16>, grid, block, smem, st, ma, mw0, mw1, g);
+  return launch_pdl(grouped_fp8_kernel<kG8GateUpFp8>, grid, block, smem, st, ma, mw0, mw1, g);
 }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 struct Fp8Ws {
   int* counters; unsigned* status; int* active; unsigned* ranges; unsigned* assignments; unsigned* position; int* perm_scratch;
-  uint8_t* xq; float* xs; uint8_t* aq; float* as; __nv_bfloat16* p; uint8_t* pq; float* ps; float* y; size_t bytes;
+  uint8_t* xq; float* xs; uint8_t* aq; float* as; uint8_t* pq; float* ps; float* y; size_t bytes;
 };
 static Fp8Ws carve(void* base, int hidden, int inter, int experts, int topk, int tokens) {
   Fp8Ws w;
@@ -127,7 +126,6 @@ static Fp8Ws carve(void* base, int hidden, int inter, int experts, int topk, int
   w.xs = reinterpret_cast<float*>(take(size_t(tokens) * (hidden / 128) * 4));
   w.aq = take(rows * hidden);
   w.as = reinterpret_cast<float*>(take(rows * (hidden / 128) * 4));
-  w.p = reinterpret_cast<__nv_bfloat16*>(take(rows * inter * 2));
   w.pq = take(rows * inter);
   w.ps = reinterpret_cast<float*>(take(rows * (inter / 128) * 4));
   w.y = reinterpret_cast<float*>(take(rows * hidden * 4));
@@ -140,13 +138,14 @@ static Fp8Ws carve(void* base, int hidden, int inter, int experts, int topk, int
 using namespace dmoe;
 
 extern "C" int darask_fp8_grouped_gemm(const void* a_codes, const float* a_scales, unsigned long long a_rows, const void* w0,
-                                       const void* w1, const float* sw0, const float* sw1, int experts, int n, int k, int gate_up,
-                                       const unsigned* ranges, void* out, unsigned* status, cudaStream_t st) {
-  if (!a_codes || !a_scales || !w0 || !sw0 || !ranges || !out || !status || experts < 1 || experts > 1024 || n < 128 || n % 128 ||
-      k < 128 || k % 128 || (gate_up && (!w1 || !sw1)))
+                                       const void* w1, const float* sw0, const float* sw1, int experts, int n, int k, int mode,
+                                       const unsigned* ranges, void* out, float* out_scales, const unsigned* out_row_map,
+                                       unsigned* status, cudaStream_t st) {
+  if (!a_codes || !a_scales || !w0 || !sw0 || !ranges || !out || !status || experts < 1 || experts > kG8MaxExperts || n < 128 ||
+      n % 128 || k < 128 || k % 128 || mode < kG8Plain || mode > kG8GateUpFp8 || (mode != kG8Plain && (!w1 || !sw1 || out_row_map)) ||
+      (mode == kG8GateUpFp8 && !out_scales))
     return cudaErrorInvalidValue;
-  return launch_grouped(a_codes, a_scales, a_rows, w0, w1, sw0, sw1, experts, n, k, gate_up, ranges,
-                        gate_up ? static_cast<__nv_bfloat16*>(out) : nullptr, gate_up ? nullptr : static_cast<float*>(out), status, st);
+  return launch_grouped(a_codes, a_scales, a_rows, w0, w1, sw0, sw1, experts, n, k, mode, ranges, out, out_scales, out_row_map, status, st);
 }
 
 extern "C" size_t darask_moe_permute_scratch_bytes(int tokens, int topk, int experts) {
@@ -187,11 +186,10 @@ extern "C" int darask_fp8_moe_layer(const DaraskFp8Moe* d, cudaStream_t st) {
   if ((e = launch_pdl(gather_fp8_kernel, dim3(T * K), dim3(256), 0, st, (const uint8_t*)w.xq, (const float*)w.xs,
                       (const unsigned*)w.assignments, (const int*)w.counters, K, H, w.aq, w.as, w.position))) return e;
   const unsigned long long rows = (unsigned long long)T * K + 128;
-  if ((e = launch_grouped(w.aq, w.as, rows, d->gate_w, d->up_w, d->gate_s, d->up_s, E, F, H, 1, w.ranges, w.p, nullptr, w.status, st))) return e;
-  const long long warps = (long long)T * K * (F / 128);
-  if ((e = launch_pdl(quant_rows_kernel, dim3(unsigned((warps + 7) / 8)), dim3(256), 0, st, (const __nv_bfloat16*)w.p,
-                      (const int*)w.counters, F, w.pq, w.ps))) return e;
-  if ((e = launch_grouped(w.pq, w.ps, rows, d->down_w, nullptr, d->down_s, nullptr, E, H, F, 0, w.ranges, nullptr, w.y, w.status, st))) return e;
+  if ((e = launch_grouped(w.aq, w.as, rows, d->gate_w, d->up_w, d->gate_s, d->up_s, E, F, H, kG8GateUpFp8, w.ranges, w.pq, w.ps, nullptr,
+                          w.status, st))) return e;
+  if ((e = launch_grouped(w.pq, w.ps, rows, d->down_w, nullptr, d->down_s, nullptr, E, H, F, kG8Plain, w.ranges, w.y, nullptr, nullptr,
+                          w.status, st))) return e;
   return launch_pdl(combine_rows_kernel, dim3((H + 255) / 256, T), dim3(256), 0, st, d->out, (const float*)w.y, (const float*)d->prob,
                     (const unsigned*)w.position, H, K);
 }

@@ -193,7 +193,8 @@ __global__ void __launch_bounds__(256) fp8_block_quant_kernel(const float* __res
   }
 }
 
-// Activations: one warp per (row, 128-channel group): e4m3 codes + float32 scale = absmax / 448.
+// Activations: one warp per (row, 128-channel group): e4m3 codes + float32 scale = absmax / 448 (1 for zeros);
+// code = e4m3(x * (1 / scale)) with the reciprocal rounded to float32 once per group.
 template <typename T>
 __global__ void __launch_bounds__(256) fp8_act_quant_kernel(const T* __restrict__ x, long long rows, int k,
                                                             uint8_t* __restrict__ q, float* __restrict__ scales) {
@@ -214,7 +215,8 @@ __global__ void __launch_bounds__(256) fp8_act_quant_kernel(const T* __restrict_
   const float scale = a == 0.f ? 1.f : a / 448.f;
   if (lane == 0) scales[r * groups + g] = scale;
   uint32_t out = 0;
-  for (int i = 0; i < 4; ++i) out |= uint32_t(e4m3_rn(fminf(fmaxf(v[i] / scale, -448.f), 448.f))) << (8 * i);
+  const float inv = 1.f / scale;      // codes = e4m3(x * (1 / scale)): one division per group
+  for (int i = 0; i < 4; ++i) out |= uint32_t(e4m3_rn(fminf(fmaxf(v[i] * inv, -448.f), 448.f))) << (8 * i);
   *reinterpret_cast<uint32_t*>(q + r * k + g * 128 + lane * 4) = out;
 }
 

@@ -14,24 +14,27 @@ import torch
 from . import _lib
 
 
-def grouped_gemm(a_codes, a_scales, ranges, w0, sw0, w1=None, sw1=None):
+def grouped_gemm(a_codes, a_scales, ranges, w0, sw0, w1=None, sw1=None, quantize=False, row_map=None):
     """Ragged grouped product. a_codes uint8 [rows(+pad), k], a_scales float32 [rows(+pad), k/128], ranges uint32
-    [E, 2] = {rows, offset}, w uint8 [E, n, k], sw float32 [E, n/128, k/128].  With w1: bf16 silu(a w0^T) * (a w1^T),
-    else float32 a w0^T.  Rows outside every range are left untouched."""
+    [E, 2] = {rows, offset}, w uint8 [E, n, k], sw float32 [E, n/128, k/128].  Without w1: float32 a w0^T (dispatch
+    row i written to row row_map[i] when a map is given).  With w1: bf16 silu(a w0^T) * (a w1^T), or with `quantize`
+    its e4m3 codes and float32 scales per row and 128 columns.  Rows outside every range are left untouched."""
     experts, n, k = w0.shape
     rows = a_codes.shape[0]
     dev = a_codes.device
-    gate_up = w1 is not None
-    out = torch.zeros(rows, n, dtype=torch.bfloat16 if gate_up else torch.float32, device=dev)
+    mode = 0 if w1 is None else (2 if quantize else 1)
+    out = torch.zeros(rows, n, dtype=(torch.float32, torch.bfloat16, torch.uint8)[mode], device=dev)
+    scales = torch.zeros(rows, n // 128, dtype=torch.float32, device=dev) if mode == 2 else None
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     st = torch.cuda.current_stream(dev).cuda_stream
     _lib.check(_lib.lib().darask_fp8_grouped_gemm(
-        a_codes.data_ptr(), a_scales.data_ptr(), rows, w0.data_ptr(), w1.data_ptr() if gate_up else None, sw0.data_ptr(),
-        sw1.data_ptr() if gate_up else None, experts, n, k, int(gate_up), ranges.data_ptr(), out.data_ptr(), status.data_ptr(), st),
+        a_codes.data_ptr(), a_scales.data_ptr(), rows, w0.data_ptr(), w1.data_ptr() if mode else None, sw0.data_ptr(),
+        sw1.data_ptr() if mode else None, experts, n, k, mode, ranges.data_ptr(), out.data_ptr(),
+        scales.data_ptr() if mode == 2 else None, row_map.data_ptr() if row_map is not None else None, status.data_ptr(), st),
         "darask_fp8_grouped_gemm")
     if int(status.item()):
         raise RuntimeError(f"darask_fp8_grouped_gemm: device status {int(status.item()):#x}")
-    return out
+    return (out, scales) if mode == 2 else out
 
 
 class Fp8MoeLayer:

@@ -212,11 +212,15 @@ int hayate_moe_layer(const HayateMoe* desc /* host */, darask_stream_t stream);
  * weights restored to bf16) and hayate_glm_grouped_packed_{gate_up,down} (packed_grouped.cu:177-318) for the
  * FP8 format: a_codes e4m3 [a_rows][k] with a_scales float32 [a_rows][k/128] (rows in dispatch order; the buffer
  * must reach one 128-row tile past the last expert's rows), w e4m3 [experts][n][k] with sw float32
- * [experts][n/128][k/128], ranges [experts][2] = {rows, offset}.  gate_up != 0: out = silu(a.w0^T) * (a.w1^T) as
- * bf16 [a_rows][n]; else out = a.w0^T as float32 [a_rows][n].  n and k multiples of 128. */
+ * [experts][n/128][k/128], ranges [experts][2] = {rows, offset}.  n and k multiples of 128.
+ *   mode 0: out = a.w0^T as float32 [a_rows][n]; with out_row_map, dispatch row i is written to row out_row_map[i]
+ *   mode 1: out = silu(a.w0^T) * (a.w1^T) as bf16 [a_rows][n]
+ *   mode 2: the same product rounded to bf16, then quantized: out = e4m3 codes [a_rows][n], out_scales float32
+ *           [a_rows][n/128] = absmax/448 of each 128 columns (1 where they are all zero) */
 int darask_fp8_grouped_gemm(const void* a_codes, const float* a_scales, unsigned long long a_rows, const void* w0,
-                            const void* w1, const float* sw0, const float* sw1, int experts, int n, int k, int gate_up,
-                            const unsigned* ranges, void* out, unsigned* status, darask_stream_t stream);
+                            const void* w1, const float* sw0, const float* sw1, int experts, int n, int k, int mode,
+                            const unsigned* ranges, void* out, float* out_scales, const unsigned* out_row_map,
+                            unsigned* status, darask_stream_t stream);
 /* Whole FP8 MoE layer for a prefill batch: softmax top-k (renormalised) on the given logits, activations
  * quantized to e4m3 per token and 128 channels, dispatch gather, grouped gate/up GEMM with SwiGLU, products
  * quantized the same way, grouped down GEMM, combine.  Mirrors `prefill_experts`

@@ -430,11 +430,13 @@ def fp8_block_decode(payload: np.ndarray, scale: np.ndarray, rounded: bool = Tru
 
 def fp8_act_quantize(x: np.ndarray):
     """Activations -> (e4m3 codes [T,H], float32 scales [T,H/128]), scale = absmax/448 of each
-    128-channel group of a token (1 where the group is zero)."""
+    128-channel group of a token (1 where the group is zero); code = e4m3(x * (1/scale)) with the
+    reciprocal rounded to float32 (one division per group, a multiplication per element)."""
     x = np.asarray(x, np.float32)
     t, h = x.shape
     g = x.reshape(t, h // 128, 128)
     amax = np.abs(g).max(-1).astype(np.float32)
     scale = np.where(amax == 0, np.float32(1), (amax / np.float32(448.0)).astype(np.float32)).astype(np.float32)
-    q = (g / scale[:, :, None]).astype(np.float32).clip(-448, 448)
+    inv = (np.float32(1.0) / scale).astype(np.float32)
+    q = (g * inv[:, :, None]).astype(np.float32).clip(-448, 448)
     return e4m3_encode(q).reshape(t, h), scale
