@@ -90,20 +90,16 @@ DEVI void umma_commit(uint64_t* bar) {
 }
 DEVI void tmem_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 DEVI void tmem_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-DEVI void tmem_ld16_issue(uint32_t taddr, uint32_t (&r)[16]) {
+// 16 columns of this warp's 32 TMEM lanes -> registers, complete on return (load and wait in one statement, so
+// that no use of the registers can be scheduled between them and the compiler needs no copies to keep them apart)
+DEVI void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
         "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
 }
-// Waits for this thread's tcgen05.ld's. The loaded registers are passed through the statement so that no use of
-// them can be scheduled ahead of the wait.
-#define DMOE_R8(v, o) "+r"(v[o]), "+r"(v[o + 1]), "+r"(v[o + 2]), "+r"(v[o + 3]), "+r"(v[o + 4]), "+r"(v[o + 5]), "+r"(v[o + 6]), "+r"(v[o + 7])
-DEVI void tmem_ld_wait(uint32_t (&a)[16]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" : DMOE_R8(a, 0), DMOE_R8(a, 8)::"memory");
-}
-#undef DMOE_R8
 
 struct G8Tile { int expert, m0, n0, rows, offset; };
 
@@ -239,7 +235,7 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     bool ok = true;
     long long w_tfull = 0, w_close = 0, t_all = G8_CLK();
     uint32_t va[16];
-    auto issue_first = [&](int step) {
+    auto await_step = [&](int step) {                   // the MMAs of this step have written their TMEM buffer
       const int buf = step & (kG8AccBufs - 1);
       // one lane watches the barrier (many threads probing one barrier word serialise in shared memory)
       int got = 1;
@@ -249,7 +245,6 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       G8_ADD(w_tfull, c0);
       if (!got) { abort_flag = 1; ok = false; return; }
       tmem_fence_after();
-      tmem_ld16_issue(tlane + buf * 256 + colA, va);
     };
     int tile = blockIdx.x, kb = 0, tile_it = 0;
     G8Tile t = {};
@@ -398,7 +393,7 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       fetch_row4(t, 0);
       fetch_sw(t);
       open_tile();
-      issue_first(0);
+      await_step(0);
       for (int step = 0; step < steps && ok; ++step) {
         const uint32_t tbuf = tlane + (step & (kG8AccBufs - 1)) * 256;
         if ((kb & 3) == 0) {
@@ -418,16 +413,15 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         // covers a load's latency with its adds
 #pragma unroll
         for (int j = 0; j < 7; ++j) {
-          tmem_ld_wait(va);
+          tmem_ld16(tbuf + (j < 4 ? colA + 16 * j : colB + 16 * (j - 4)), va);
           fma16(j < 4 ? fA : fB, 8 * j);
-          tmem_ld16_issue(tbuf + (j + 1 < 4 ? colA + 16 * (j + 1) : colB + 16 * (j + 1 - 4)), va);
         }
-        tmem_ld_wait(va);
+        tmem_ld16(tbuf + colB + 48, va);
         tmem_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty + (step & (kG8AccBufs - 1)));   // the values are in registers: the buffer may be overwritten
         fma16(fB, 56);
-        if (step + 1 < steps) issue_first(step + 1);
+        if (step + 1 < steps) await_step(step + 1);
         if (++kb == kblocks) {
           const long long c0 = G8_CLK();
           close_tile();
@@ -438,7 +432,6 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
           if (tile < total) { t = locate(tile); open_tile(); }
         }
       }
-      if (!ok) tmem_ld_wait(va);                        // drain a load that may still be in flight
     }
     if (warp == 4 && lane == 0) {
       G8_OUT(6, G8_CLK() - t_all);
