@@ -38,6 +38,61 @@ __global__ void __launch_bounds__(256) combine_rows_kernel(float* out, const flo
   out[size_t(t) * hidden + i] = v;
 }
 
+// ---- expert-parallel regrouping ----------------------------------------------------------------------------------
+// Rows received from `ranks` peers arrive grouped by source rank and, inside a source, by ascending local expert.
+// plan: per local expert the range {rows, offset} of the regrouped order (expert-major, then source rank, then
+// arrival order) and per (source, expert) segment its first received row and its first regrouped row.
+__global__ void __launch_bounds__(1024) ep_plan_kernel(const int* counts, int ranks, int local, unsigned* ranges, int* seg_src, int* seg_dst) {
+  __shared__ int expert_off[1025];
+  __shared__ int rank_off[65];
+  pdl_wait();
+  pdl_launch();
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    int run = 0;
+    for (int e = 0; e < local; ++e) {
+      int rows = 0;
+      for (int r = 0; r < ranks; ++r) rows += counts[r * local + e];
+      ranges[2 * e] = rows;
+      ranges[2 * e + 1] = run;
+      expert_off[e] = run;
+      run += rows;
+    }
+  }
+  if (tid == 32) {
+    int run = 0;
+    for (int r = 0; r < ranks; ++r) {
+      rank_off[r] = run;
+      for (int e = 0; e < local; ++e) run += counts[r * local + e];
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < local; e += 1024) {
+    int dst = expert_off[e];
+    for (int r = 0; r < ranks; ++r) { seg_dst[r * local + e] = dst; dst += counts[r * local + e]; }
+  }
+  for (int r = tid; r < ranks; r += 1024) {
+    int src = rank_off[r];
+    for (int e = 0; e < local; ++e) { seg_src[r * local + e] = src; src += counts[r * local + e]; }
+  }
+}
+// row_map[regrouped row] = received row
+__global__ void __launch_bounds__(128) ep_row_map_kernel(const int* counts, const int* seg_src, const int* seg_dst, unsigned* row_map) {
+  pdl_wait();
+  pdl_launch();
+  const int seg = blockIdx.x, n = counts[seg], src = seg_src[seg], dst = seg_dst[seg];
+  for (int i = threadIdx.x; i < n; i += 128) row_map[dst + i] = src + i;
+}
+__global__ void __launch_bounds__(256) ep_regroup_rows_kernel(const uint8_t* in_codes, const float* in_scales, const unsigned* row_map,
+                                                              int k, uint8_t* codes, float* scales) {
+  pdl_wait();
+  pdl_launch();
+  const size_t dst = blockIdx.x, src = __ldcg(row_map + dst);
+  for (int c = threadIdx.x; c < k / 16; c += 256)
+    reinterpret_cast<uint4*>(codes + dst * k)[c] = __ldg(reinterpret_cast<const uint4*>(in_codes + src * k) + c);
+  for (int c = threadIdx.x; c < k / 128; c += 256) scales[dst * (k / 128) + c] = __ldg(in_scales + src * (k / 128) + c);
+}
+
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -192,6 +247,85 @@ extern "C" int darask_fp8_moe_layer(const DaraskFp8Moe* d, cudaStream_t st) {
                           w.status, st))) return e;
   return launch_pdl(combine_rows_kernel, dim3((H + 255) / 256, T), dim3(256), 0, st, d->out, (const float*)w.y, (const float*)d->prob,
                     (const unsigned*)w.position, H, K);
+}
+
+// ---- expert-parallel entry points ------------------------------------------------------------------------------
+extern "C" size_t darask_fp8_ep_dispatch_scratch_bytes(int hidden, int experts, int topk, int tokens) {
+  if (hidden < 128 || experts < 1 || topk < 1 || tokens < 1) return 0;
+  return 4096 + align_up(size_t(experts) * 4, 1024) + align_up(size_t(tokens) * topk * 4, 1024) +
+         align_up(permute_scratch_bytes(tokens, topk, experts), 1024) + align_up(size_t(tokens) * hidden, 1024) +
+         align_up(size_t(tokens) * (hidden / 128) * 4, 1024);
+}
+
+extern "C" int darask_fp8_ep_dispatch(const void* x, const float* logits, int hidden, int experts, int topk, int tokens, int* ids,
+                                      float* prob, void* send_codes, float* send_scales, unsigned* ranges, unsigned* position,
+                                      void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  if (!x || !logits || !ids || !prob || !send_codes || !send_scales || !ranges || !position || !scratch || hidden < 128 ||
+      hidden % 128 || experts < topk || experts > 1024 || topk < 1 || topk > 32 || tokens < 1 ||
+      scratch_bytes < darask_fp8_ep_dispatch_scratch_bytes(hidden, experts, topk, tokens))
+    return cudaErrorInvalidValue;
+  uint8_t* p = static_cast<uint8_t*>(scratch);
+  size_t off = 0;
+  auto take = [&](size_t bytes) { uint8_t* q = p + off; off = align_up(off + bytes, 1024); return q; };
+  int* counters = reinterpret_cast<int*>(take(2048));
+  unsigned* status = reinterpret_cast<unsigned*>(take(2048));
+  int* active = reinterpret_cast<int*>(take(size_t(experts) * 4));
+  unsigned* assignments = reinterpret_cast<unsigned*>(take(size_t(tokens) * topk * 4));
+  int* perm_scratch = reinterpret_cast<int*>(take(permute_scratch_bytes(tokens, topk, experts)));
+  uint8_t* xq = take(size_t(tokens) * hidden);
+  float* xs = reinterpret_cast<float*>(take(size_t(tokens) * (hidden / 128) * 4));
+  cudaError_t e;
+  if ((e = cudaMemsetAsync(counters, 0, 4096, st))) return e;
+  const RouteArgs route{logits, experts, experts, topk, tokens, nullptr, 1.f, ids, prob, nullptr};
+  const PermuteArgs perm{ids, tokens, topk, experts, assignments, ranges, active, counters, status, nullptr, 0};
+  if ((e = launch_pdl(route_topk_kernel<kRouteKogarashi>, dim3((tokens + 3) / 4), dim3(128), 0, st, route))) return e;
+  if (tokens * topk > 2048) {
+    if ((e = launch_permute_large(perm, perm_scratch, st))) return e;
+  } else if ((e = launch_pdl(permute_kernel<0>, dim3(1), dim3(1024), size_t(experts + 1) * 4, st, perm))) return e;
+  if ((e = (cudaError_t)darask_quantize_fp8_act(xq, xs, x, 1, tokens, hidden, st))) return e;
+  return launch_pdl(gather_fp8_kernel, dim3(tokens * topk), dim3(256), 0, st, (const uint8_t*)xq, (const float*)xs,
+                    (const unsigned*)assignments, (const int*)counters, topk, hidden, static_cast<uint8_t*>(send_codes), send_scales,
+                    position);
+}
+
+extern "C" int darask_fp8_ep_regroup(const int* recv_counts, int ranks, int local_experts, const void* recv_codes,
+                                     const float* recv_scales, int hidden, long long recv_rows, void* codes, float* scales,
+                                     unsigned* ranges, unsigned* row_map, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  if (!recv_counts || !codes || !scales || !ranges || !row_map || !scratch || ranks < 1 || ranks > 64 || local_experts < 1 ||
+      local_experts > 1024 || hidden < 128 || hidden % 128 || recv_rows < 0 || (recv_rows > 0 && (!recv_codes || !recv_scales)) ||
+      scratch_bytes < size_t(ranks) * local_experts * 8)
+    return cudaErrorInvalidValue;
+  int* seg_src = static_cast<int*>(scratch);
+  int* seg_dst = seg_src + size_t(ranks) * local_experts;
+  cudaError_t e;
+  if ((e = launch_pdl(ep_plan_kernel, dim3(1), dim3(1024), 0, st, recv_counts, ranks, local_experts, ranges, seg_src, seg_dst))) return e;
+  if (recv_rows == 0) return cudaSuccess;
+  if ((e = launch_pdl(ep_row_map_kernel, dim3(ranks * local_experts), dim3(128), 0, st, recv_counts, (const int*)seg_src,
+                      (const int*)seg_dst, row_map))) return e;
+  return launch_pdl(ep_regroup_rows_kernel, dim3((unsigned)recv_rows), dim3(256), 0, st, static_cast<const uint8_t*>(recv_codes),
+                    recv_scales, (const unsigned*)row_map, hidden, static_cast<uint8_t*>(codes), scales);
+}
+
+extern "C" int darask_fp8_ep_experts(const void* codes, const float* scales, unsigned long long rows_alloc, const unsigned* ranges,
+                                     int local_experts, int hidden, int inter, const void* gate_w, const void* up_w,
+                                     const void* down_w, const float* gate_s, const float* up_s, const float* down_s,
+                                     const unsigned* row_map, float* y, void* prod_codes, float* prod_scales, unsigned* status,
+                                     cudaStream_t st) {
+  if (!codes || !scales || !ranges || !gate_w || !up_w || !down_w || !gate_s || !up_s || !down_s || !y || !prod_codes ||
+      !prod_scales || !status || local_experts < 1 || local_experts > kG8MaxExperts || hidden < 128 || hidden % 128 || inter < 128 ||
+      inter % 128 || rows_alloc < 128)
+    return cudaErrorInvalidValue;
+  cudaError_t e;
+  if ((e = launch_grouped(codes, scales, rows_alloc, gate_w, up_w, gate_s, up_s, local_experts, inter, hidden, kG8GateUpFp8, ranges,
+                          prod_codes, prod_scales, nullptr, status, st))) return e;
+  return launch_grouped(prod_codes, prod_scales, rows_alloc, down_w, nullptr, down_s, nullptr, local_experts, hidden, inter, kG8Plain,
+                        ranges, y, nullptr, row_map, status, st);
+}
+
+extern "C" int darask_fp8_ep_combine(float* out, const float* y, const float* prob, const unsigned* position, int tokens, int hidden,
+                                     int topk, cudaStream_t st) {
+  if (!out || !y || !prob || !position || tokens < 1 || hidden < 1 || topk < 1) return cudaErrorInvalidValue;
+  return launch_pdl(combine_rows_kernel, dim3((hidden + 255) / 256, tokens), dim3(256), 0, st, out, y, prob, position, hidden, topk);
 }
 
 extern "C" int darask_fp8_moe_status(const void* workspace, unsigned* host_status, cudaStream_t st) {

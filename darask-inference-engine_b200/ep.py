@@ -1,0 +1,172 @@
+"""Expert-parallel FP8 prefill MoE layer: one process per GPU, experts sharded in contiguous blocks, tokens
+data-parallel, two all-to-all-v exchanges per layer over `torch.distributed` (NCCL on GPUs).
+
+Rank g of G holds experts [g*E/G, (g+1)*E/G).  Every rank routes its own tokens, sorts the routed rows by expert (which
+also groups them by destination rank), exchanges the per-expert row counts, sends the FP8 rows and their scales,
+runs the grouped products over what it received, sends the float32 rows back and combines them with the routing
+weights.  The reference engines have no multi-GPU path; their single-GPU orchestration is `prefill_experts`,
+engines/hayate/crates/models/src/glm53/gpu.rs:2068-2566.
+
+`ep_forward` is the device-agnostic orchestration (split sizes, exchanges); the kernels sit behind a backend object.
+`CudaFp8Backend` is the product backend (C ABI calls); the tests drive `ep_forward` with a CPU backend under gloo.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+
+def exchange_counts(counts: torch.Tensor, group=None):
+    """counts int32 [G, E/G] (rows this rank sends to each rank's experts) -> (recv_counts [G, E/G], send_splits,
+    recv_splits).  One all-to-all of G*E/G integers and one device->host copy."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        recv = counts.clone()
+    else:
+        recv = torch.empty_like(counts)
+        dist.all_to_all_single(recv, counts.contiguous(), group=group)
+    both = torch.stack([counts.sum(1), recv.sum(1)]).cpu()
+    return recv, [int(v) for v in both[0]], [int(v) for v in both[1]]
+
+
+def all_to_all_rows(send: torch.Tensor, send_splits, recv_splits, group=None, pad_rows: int = 0) -> torch.Tensor:
+    """Rows of `send` (first sum(send_splits) rows) to the ranks as split; returns sum(recv_splits) (+ pad_rows) rows."""
+    n_recv = sum(recv_splits)
+    out = torch.zeros((n_recv + pad_rows,) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    n_send = sum(send_splits)
+    if world == 1:
+        out[:n_recv] = send[:n_send]
+    else:
+        dist.all_to_all_single(out[:n_recv], send[:n_send].contiguous(), recv_splits, send_splits, group=group)
+    return out
+
+
+def ep_forward(backend, x, logits, group=None):
+    """One expert-parallel layer call on this rank's tokens; returns (out, info)."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    d = backend.dispatch(x, logits)                                   # rows in ascending expert order
+    counts = d["ranges"][:, 0].to(torch.int32).reshape(world, -1)
+    recv_counts, send_splits, recv_splits = exchange_counts(counts, group)
+    recv_codes = all_to_all_rows(d["codes"], send_splits, recv_splits, group, pad_rows=backend.pad_rows)
+    recv_scales = all_to_all_rows(d["scales"], send_splits, recv_splits, group, pad_rows=backend.pad_rows)
+    n_recv = sum(recv_splits)
+    y_recv = backend.run_experts(recv_counts, recv_codes, recv_scales, n_recv)      # [n_recv, H] in received order
+    y_home = all_to_all_rows(y_recv, recv_splits, send_splits, group)
+    out = backend.combine(y_home, d)
+    return out, dict(ids=d["ids"], prob=d["prob"], send_rows=sum(send_splits), recv_rows=n_recv,
+                     cross_rows=sum(send_splits) - send_splits[dist.get_rank(group) if world > 1 else 0])
+
+
+class CudaFp8Backend:
+    """Kernels of one rank: block-FP8 weights of its E/G experts resident on the GPU."""
+    pad_rows = 128          # the grouped GEMM loads whole 128-row tiles
+
+    def __init__(self, hidden, inter, experts, topk, world, max_tokens, device="cuda"):
+        if experts % world:
+            raise ValueError("experts must divide evenly over the ranks")
+        self.hidden, self.inter, self.experts, self.topk, self.world = hidden, inter, experts, topk, world
+        self.local = experts // world
+        self.max_tokens, self.device = max_tokens, torch.device(device)
+        lib = _lib.lib()
+        self.scratch = torch.zeros(lib.darask_fp8_ep_dispatch_scratch_bytes(hidden, experts, topk, max_tokens), dtype=torch.uint8,
+                                   device=self.device)
+        rows = max_tokens * topk + self.pad_rows
+        self.send_codes = torch.zeros(rows, hidden, dtype=torch.uint8, device=self.device)
+        self.send_scales = torch.zeros(rows, hidden // 128, dtype=torch.float32, device=self.device)
+        self.ranges = torch.zeros(experts, 2, dtype=torch.int32, device=self.device)
+        self.position = torch.zeros(max_tokens * topk, dtype=torch.int32, device=self.device)
+        self.ids = torch.zeros(max_tokens, topk, dtype=torch.int32, device=self.device)
+        self.prob = torch.zeros(max_tokens, topk, dtype=torch.float32, device=self.device)
+        self.seg = torch.zeros(world * self.local * 2, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.w = {}
+
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def load(self, name: str, payload: torch.Tensor, scales: torch.Tensor) -> None:
+        """This rank's experts: payload uint8 [E/G, n, k], scales float32 [E/G, n/128, k/128]; name in gate|up|down."""
+        n, k = (self.hidden, self.inter) if name == "down" else (self.inter, self.hidden)
+        if tuple(payload.shape) != (self.local, n, k) or tuple(scales.shape) != (self.local, n // 128, k // 128):
+            raise ValueError(f"{name}: expected payload [{self.local},{n},{k}] and scales [{self.local},{n // 128},{k // 128}]")
+        self.w[name] = (payload.to(self.device, torch.uint8).contiguous(), scales.to(self.device, torch.float32).contiguous())
+
+    def dispatch(self, x, logits):
+        t = x.shape[0]
+        if t > self.max_tokens or x.dtype != torch.bfloat16 or logits.dtype != torch.float32 or not x.is_contiguous() or not logits.is_contiguous():
+            raise ValueError("x must be contiguous bf16 [T<=max_tokens,H], logits contiguous float32 [T,E]")
+        _lib.check(_lib.lib().darask_fp8_ep_dispatch(
+            x.data_ptr(), logits.data_ptr(), self.hidden, self.experts, self.topk, t, self.ids.data_ptr(), self.prob.data_ptr(),
+            self.send_codes.data_ptr(), self.send_scales.data_ptr(), self.ranges.data_ptr(), self.position.data_ptr(),
+            self.scratch.data_ptr(), self.scratch.numel(), self._stream()), "darask_fp8_ep_dispatch")
+        return dict(codes=self.send_codes, scales=self.send_scales, ranges=self.ranges, position=self.position, ids=self.ids[:t],
+                    prob=self.prob[:t], tokens=t)
+
+    def run_experts(self, recv_counts, recv_codes, recv_scales, n_recv):
+        lib, dev = _lib.lib(), self.device
+        rows = n_recv + self.pad_rows
+        y = torch.empty(max(n_recv, 1), self.hidden, dtype=torch.float32, device=dev)
+        if n_recv == 0:
+            return y[:0]
+        (gw, gs), (uw, us), (dw, ds) = self.w["gate"], self.w["up"], self.w["down"]
+        ranges = torch.empty(self.local, 2, dtype=torch.int32, device=dev)
+        row_map = torch.empty(n_recv, dtype=torch.int32, device=dev)
+        prod = torch.empty(rows, self.inter, dtype=torch.uint8, device=dev)
+        prod_s = torch.empty(rows, self.inter // 128, dtype=torch.float32, device=dev)
+        if self.world == 1:
+            # one rank: the received order already is the expert order
+            codes, scales = recv_codes, recv_scales
+            ranges.copy_(self._ranges_from_counts(recv_counts))
+            row_map_ptr = None
+        else:
+            codes = torch.empty(rows, self.hidden, dtype=torch.uint8, device=dev)
+            scales = torch.empty(rows, self.hidden // 128, dtype=torch.float32, device=dev)
+            _lib.check(lib.darask_fp8_ep_regroup(
+                recv_counts.data_ptr(), self.world, self.local, recv_codes.data_ptr(), recv_scales.data_ptr(), self.hidden, n_recv,
+                codes.data_ptr(), scales.data_ptr(), ranges.data_ptr(), row_map.data_ptr(), self.seg.data_ptr(), self.seg.numel() * 4,
+                self._stream()), "darask_fp8_ep_regroup")
+            row_map_ptr = row_map.data_ptr()
+        _lib.check(lib.darask_fp8_ep_experts(
+            codes.data_ptr(), scales.data_ptr(), rows, ranges.data_ptr(), self.local, self.hidden, self.inter, gw.data_ptr(),
+            uw.data_ptr(), dw.data_ptr(), gs.data_ptr(), us.data_ptr(), ds.data_ptr(), row_map_ptr, y.data_ptr(), prod.data_ptr(),
+            prod_s.data_ptr(), self.status.data_ptr(), self._stream()), "darask_fp8_ep_experts")
+        return y
+
+    @staticmethod
+    def _ranges_from_counts(counts):
+        c = counts.reshape(-1).to(torch.int32)
+        off = torch.cumsum(c, 0, dtype=torch.int32) - c
+        return torch.stack([c, off], 1)
+
+    def combine(self, y_home, d):
+        t = d["tokens"]
+        out = torch.empty(t, self.hidden, dtype=torch.float32, device=self.device)
+        _lib.check(_lib.lib().darask_fp8_ep_combine(out.data_ptr(), y_home.data_ptr(), d["prob"].data_ptr(), d["position"].data_ptr(), t,
+                                                    self.hidden, self.topk, self._stream()), "darask_fp8_ep_combine")
+        return out
+
+    def device_status(self) -> int:
+        return int(self.status.item())
+
+
+class Fp8ExpertParallelMoe:
+    """The call a user makes: `forward(x, logits)` on every rank with that rank's tokens."""
+
+    def __init__(self, hidden, inter, experts, topk, max_tokens, group=None, device="cuda"):
+        self.group = group
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.backend = CudaFp8Backend(hidden, inter, experts, topk, world, max_tokens, device)
+        self.first_expert = self.rank * self.backend.local
+
+    def load(self, name, payload, scales):
+        self.backend.load(name, payload, scales)
+
+    def forward(self, x, logits):
+        out, self.info = ep_forward(self.backend, x, logits, self.group)
+        return out

@@ -239,6 +239,39 @@ size_t darask_fp8_moe_workspace_bytes(int hidden, int inter, int experts, int to
 int darask_fp8_moe_layer(const DaraskFp8Moe* desc /* host */, darask_stream_t stream);
 int darask_fp8_moe_status(const void* workspace, unsigned* host_status /* host */, darask_stream_t stream);
 
+/* ---- expert-parallel FP8 prefill: the same layer cut at its two exchange steps ---------------------------------
+ * Rank g of G holds experts [g*E/G, (g+1)*E/G) and its own tokens.  Per layer and rank:
+ *   1. darask_fp8_ep_dispatch   route (softmax top-k, renormalised), permutation over all E experts, activation
+ *                               quantization, gather: send_codes / send_scales hold the token rows in ascending
+ *                               expert order (so already grouped by destination rank), ranges [E][2] their
+ *                               {rows, offset}, position[a] the dispatch row of assignment a = token*topk+slot.
+ *   2. host: all-to-all of the per-expert counts, then all-to-all-v of rows and scales (NCCL).
+ *   3. darask_fp8_ep_regroup    received rows (by source rank, then local expert) -> local expert order;
+ *                               ranges [E/G][2], row_map[regrouped row] = received row.
+ *   4. darask_fp8_ep_experts    grouped gate/up GEMM + SwiGLU + quantization, grouped down GEMM; y float32
+ *                               [received rows][hidden] written back in RECEIVED order through row_map.
+ *   5. host: all-to-all-v of y back (splits swapped): rows return in the sender's dispatch order.
+ *   6. darask_fp8_ep_combine    out[t] = sum_s prob[t][s] * y[position[t*topk+s]]  (slot order, fp32 fma).
+ * These replace the host-side `group_routes` + gather/scatter of `prefill_experts`
+ * (engines/hayate/crates/models/src/glm53/gpu.rs:2068-2566); the reference has no multi-GPU path.
+ * Buffers holding rows that feed a grouped GEMM (send_codes at G = 1, codes, prod_codes and their scales) must reach
+ * 128 rows past the last used row.  recv_counts: int32 [G][E/G], row r = the counts rank r sends here. */
+size_t darask_fp8_ep_dispatch_scratch_bytes(int hidden, int experts, int topk, int tokens);
+int darask_fp8_ep_dispatch(const void* x /* bf16 [tokens][hidden] */, const float* logits, int hidden, int experts, int topk,
+                           int tokens, int* ids, float* prob, void* send_codes, float* send_scales, unsigned* ranges,
+                           unsigned* position, void* scratch, size_t scratch_bytes, darask_stream_t stream);
+int darask_fp8_ep_regroup(const int* recv_counts, int ranks, int local_experts, const void* recv_codes,
+                          const float* recv_scales, int hidden, long long recv_rows, void* codes, float* scales,
+                          unsigned* ranges, unsigned* row_map, void* scratch /* ranks*local_experts*8 bytes */,
+                          size_t scratch_bytes, darask_stream_t stream);
+int darask_fp8_ep_experts(const void* codes, const float* scales, unsigned long long rows_alloc, const unsigned* ranges,
+                          int local_experts, int hidden, int inter, const void* gate_w, const void* up_w, const void* down_w,
+                          const float* gate_s, const float* up_s, const float* down_s, const unsigned* row_map, float* y,
+                          void* prod_codes /* [rows_alloc][inter] */, float* prod_scales /* [rows_alloc][inter/128] */,
+                          unsigned* status, darask_stream_t stream);
+int darask_fp8_ep_combine(float* out, const float* y, const float* prob, const unsigned* position, int tokens, int hidden,
+                          int topk, darask_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,83 @@
+"""Expert-parallel FP8 layer on GPUs: one rank against the fused single-GPU entry point, two virtual ranks on one
+GPU (regroup / row-map kernels, exchanges emulated by slicing), and real NCCL ranks where the box has several GPUs."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import layers as L
+from tests import workloads as W
+from tests.test_ep_host import run_workers
+
+pytestmark = pytest.mark.gpu
+
+
+def load_rank(m, layer, rank, local):
+    for name in ("gate", "up", "down"):
+        mats = getattr(layer, name)[rank * local:(rank + 1) * local]
+        m.load(name, torch.from_numpy(np.stack([p for p, _ in mats])), torch.from_numpy(np.stack([s for _, s in mats])))
+
+
+def test_single_rank_matches_fused_layer():
+    import darask_inference_engine_b200 as D
+    layer, acts = W.fp8_layer(31, 512, 256, 16, 4, 200, zipf=1.1)
+    x, logits = torch.from_numpy(acts["x"]).bfloat16().cuda(), torch.from_numpy(acts["logits"]).cuda()
+    ep = D.Fp8ExpertParallelMoe(512, 256, 16, 4, 200)
+    load_rank(ep, layer, 0, 16)
+    out = ep.forward(x, logits)
+    fused = D.Fp8MoeLayer(512, 256, 16, 4, 200)
+    load_rank(fused, layer, 0, 16)
+    ref = fused.forward(x, logits)
+    torch.cuda.synchronize()
+    assert ep.backend.device_status() == 0 and torch.equal(out, ref)
+    W.check_output(out.cpu().numpy(), L.fp8_forward(layer, acts["x"], acts["logits"])["out"])
+
+
+@pytest.mark.parametrize("world,tokens", [(2, 96), (4, 33)])
+def test_virtual_ranks_on_one_gpu(world, tokens):
+    """All ranks' kernels run on one GPU one after the other; the two all-to-all-v steps are done by slicing."""
+    import darask_inference_engine_b200 as D
+    hidden, inter, experts, topk = 256, 128, 8, 2
+    local = experts // world
+    layer, acts = W.fp8_layer(5 + world, hidden, inter, experts, topk, tokens * world, pool=experts, zipf=1.1)
+    backends, sent = [], []
+    for r in range(world):
+        b = D.ep.CudaFp8Backend(hidden, inter, experts, topk, world, tokens)
+        load_rank(b, layer, r, local)
+        x = torch.from_numpy(acts["x"][r * tokens:(r + 1) * tokens]).bfloat16().cuda()
+        lg = torch.from_numpy(acts["logits"][r * tokens:(r + 1) * tokens]).cuda()
+        d = b.dispatch(x, lg)
+        counts = d["ranges"][:, 0].reshape(world, local).cpu().numpy()
+        offs = d["ranges"][:, 1].reshape(world, local).cpu().numpy()
+        backends.append(b)
+        sent.append((d, counts, offs))
+    y_home = [torch.zeros(tokens * topk, hidden, device="cuda") for _ in range(world)]
+    for dst in range(world):                                   # what rank dst receives, in source-rank order
+        recv_counts = np.stack([sent[src][1][dst] for src in range(world)]).astype(np.int32)
+        pieces_c, pieces_s, origin = [], [], []
+        for src in range(world):
+            d, counts, offs = sent[src]
+            lo, n = int(offs[dst, 0]), int(counts[dst].sum())
+            pieces_c.append(d["codes"][lo:lo + n]); pieces_s.append(d["scales"][lo:lo + n]); origin.append((src, lo, n))
+        n_recv = int(recv_counts.sum())
+        pad_c = torch.zeros(128, hidden, dtype=torch.uint8, device="cuda")
+        pad_s = torch.zeros(128, hidden // 128, device="cuda")
+        y = backends[dst].run_experts(torch.from_numpy(recv_counts).cuda(), torch.cat(pieces_c + [pad_c]).contiguous(),
+                                  torch.cat(pieces_s + [pad_s]).contiguous(), n_recv)
+        row = 0
+        for src, lo, n in origin:                              # rows go back to where they came from
+            y_home[src][lo:lo + n] = y[row:row + n]
+            row += n
+        assert backends[dst].device_status() == 0
+    for r in range(world):
+        out = backends[r].combine(y_home[r], sent[r][0]).cpu().numpy()
+        ref = L.fp8_forward(layer, acts["x"][r * tokens:(r + 1) * tokens], acts["logits"][r * tokens:(r + 1) * tokens])
+        assert np.array_equal(sent[r][0]["ids"].cpu().numpy(), ref["ids"])
+        W.check_output(out, ref["out"])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_ep_forward_nccl(tmp_path):
+    world = min(4, torch.cuda.device_count())
+    world = 2 if world == 3 else world
+    rows = run_workers("cuda", world, tmp_path, 29631)
+    assert sum(r[0] for r in rows) == sum(r[1] for r in rows) and any(r[2] > 0 for r in rows)
