@@ -82,6 +82,14 @@ _SIGNATURES = {
                                          c_size_t, c_void_p]),
     "darask_fp8_grouped_gemm": (c_int, [c_void_p, c_void_p, ctypes.c_ulonglong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                         c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "hayate_glm_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_uint, c_void_p, c_void_p]),
+    "hayate_glm_grouped_nvfp4": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_uint, c_void_p, c_void_p,
+                                         c_uint, c_void_p]),
+    "hayate_glm_nvfp4_restore": (c_int, [c_void_p, c_void_p, c_uint, c_uint, c_void_p]),
+    "hayate_glm_nvfp4_restore_unscaled": (c_int, [c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_void_p]),
+    "hayate_glm_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_void_p]),
+    "hayate_glm_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_void_p]),
+    "hayate_glm_copy": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "darask_fp8_ep_dispatch_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "darask_fp8_ep_dispatch": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_size_t, c_void_p]),

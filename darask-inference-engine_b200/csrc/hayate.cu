@@ -137,6 +137,8 @@ extern "C" int hayate_glm_moe_set_shape(unsigned hidden, unsigned inter, unsigne
   return cudaSuccess;
 }
 
+namespace dmoe { int hayate_shape_topk() { return g_shape.topk; } }
+
 extern "C" size_t hayate_glm_moe_workspace_bytes(unsigned hidden, unsigned inter, unsigned experts, unsigned topk, unsigned tokens) {
   return carve(nullptr, int(hidden), int(inter), int(experts), int(topk), int(tokens)).bytes;
 }

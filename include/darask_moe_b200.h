@@ -206,6 +206,22 @@ size_t hayate_moe_workspace_bytes(int hidden, int inter, int experts, int topk, 
 int hayate_moe_workspace_init(void* workspace, size_t bytes, darask_stream_t stream);
 int hayate_moe_layer(const HayateMoe* desc /* host */, darask_stream_t stream);
 
+/* Hayate prefill launchers, the reference's names and signatures (engines/hayate/crates/kernels/src/glm53.rs:588-650,
+ * bodies cu/glm53/grouped.cu:28-124).  x / out / w are bf16; ranges u32 [groups][2] = {rows, offset}; assignments
+ * index [token][topk] routes (topk from hayate_glm_moe_set_shape, 8 by default as in the reference).  The grouped
+ * GEMM accepts any n % 128 == 0, k % 64 == 0 and up to 1024 groups (the reference: two fixed shapes, 8 groups) and
+ * ignores `metadata`.  hayate_glm_grouped_nvfp4: accumulator = float32 x.w^T, out = bf16(accumulator * scales[g]). */
+int hayate_glm_grouped(void* out, const void* x, const void* w, const void* ranges, unsigned groups, unsigned n, unsigned k,
+                       void* metadata, darask_stream_t stream);
+int hayate_glm_grouped_nvfp4(void* out, void* accumulator, const void* x, const void* w, const void* ranges, unsigned groups,
+                             unsigned n, unsigned k, void* metadata, const void* scales, unsigned max_rows, darask_stream_t stream);
+int hayate_glm_nvfp4_restore(void* out, const void* image, unsigned n, unsigned k, darask_stream_t stream);
+int hayate_glm_nvfp4_restore_unscaled(void* out, void* scale, const void* image, unsigned n, unsigned k, darask_stream_t stream);
+int hayate_glm_gather(void* out, const void* x, const void* assignments, unsigned rows, unsigned hidden, darask_stream_t stream);
+int hayate_glm_scatter(void* out, const void* x, const void* weights, const void* assignments, unsigned rows, unsigned hidden,
+                       darask_stream_t stream);
+int hayate_glm_copy(void* out, const void* x, size_t bytes, darask_stream_t stream);
+
 /* ---- FP8 prefill path -----------------------------------------------------------------------------------------
  * Ragged grouped GEMM on tcgen05 tensor cores over block-scaled e4m3 operands.  Replaces hayate_glm_grouped /
  * hayate_glm_grouped_nvfp4 (engines/hayate/crates/kernels/cu/glm53/grouped.cu:59-124: CUTLASS Sm80 grouped GEMM on
