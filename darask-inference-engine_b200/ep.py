@@ -33,16 +33,21 @@ def exchange_counts(counts: torch.Tensor, group=None):
     return recv, [int(v) for v in both[0]], [int(v) for v in both[1]]
 
 
-def all_to_all_rows(send: torch.Tensor, send_splits, recv_splits, group=None, pad_rows: int = 0) -> torch.Tensor:
-    """Rows of `send` (first sum(send_splits) rows) to the ranks as split; returns sum(recv_splits) (+ pad_rows) rows."""
+def all_to_all_rows(send: torch.Tensor, send_splits, recv_splits, group=None, pad_rows: int = 0, out=None) -> torch.Tensor:
+    """Rows of `send` (first sum(send_splits) rows) to the ranks as split; returns sum(recv_splits) (+ pad_rows) rows
+    (the pad rows are uninitialised: the grouped GEMM loads them as part of its last tile and discards the result).
+    `out`: optional preallocated buffer with at least that many rows."""
     n_recv = sum(recv_splits)
-    out = torch.zeros((n_recv + pad_rows,) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+    if out is None or out.shape[0] < n_recv + pad_rows:
+        out = torch.empty((n_recv + pad_rows,) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+    else:
+        out = out[:n_recv + pad_rows]
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     n_send = sum(send_splits)
     if world == 1:
         out[:n_recv] = send[:n_send]
     else:
-        dist.all_to_all_single(out[:n_recv], send[:n_send].contiguous(), recv_splits, send_splits, group=group)
+        dist.all_to_all_single(out[:n_recv], send[:n_send], recv_splits, send_splits, group=group)
     return out
 
 
@@ -52,11 +57,12 @@ def ep_forward(backend, x, logits, group=None):
     d = backend.dispatch(x, logits)                                   # rows in ascending expert order
     counts = d["ranges"][:, 0].to(torch.int32).reshape(world, -1)
     recv_counts, send_splits, recv_splits = exchange_counts(counts, group)
-    recv_codes = all_to_all_rows(d["codes"], send_splits, recv_splits, group, pad_rows=backend.pad_rows)
-    recv_scales = all_to_all_rows(d["scales"], send_splits, recv_splits, group, pad_rows=backend.pad_rows)
+    bufs = getattr(backend, "buffers", {})
+    recv_codes = all_to_all_rows(d["codes"], send_splits, recv_splits, group, pad_rows=backend.pad_rows, out=bufs.get("recv_codes"))
+    recv_scales = all_to_all_rows(d["scales"], send_splits, recv_splits, group, pad_rows=backend.pad_rows, out=bufs.get("recv_scales"))
     n_recv = sum(recv_splits)
     y_recv = backend.run_experts(recv_counts, recv_codes, recv_scales, n_recv)      # [n_recv, H] in received order
-    y_home = all_to_all_rows(y_recv, recv_splits, send_splits, group)
+    y_home = all_to_all_rows(y_recv, recv_splits, send_splits, group, out=bufs.get("y_home"))
     out = backend.combine(y_home, d)
     return out, dict(ids=d["ids"], prob=d["prob"], send_rows=sum(send_splits), recv_rows=n_recv,
                      cross_rows=sum(send_splits) - send_splits[dist.get_rank(group) if world > 1 else 0])
@@ -85,6 +91,26 @@ class CudaFp8Backend:
         self.seg = torch.zeros(world * self.local * 2, dtype=torch.int32, device=self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.w = {}
+        # receive-side buffers, kept between calls; `capacity` rows (default: twice the mean load) grow on demand
+        self.capacity = 0
+        self.buffers = {}
+        self._reserve(2 * max_tokens * topk)
+        self.buffers["y_home"] = torch.empty(max_tokens * topk, hidden, dtype=torch.float32, device=self.device)
+
+    def _reserve(self, rows):
+        if rows <= self.capacity:
+            return
+        dev, alloc = self.device, rows + self.pad_rows
+        self.capacity = rows
+        self.buffers["recv_codes"] = torch.empty(alloc, self.hidden, dtype=torch.uint8, device=dev)
+        self.buffers["recv_scales"] = torch.empty(alloc, self.hidden // 128, dtype=torch.float32, device=dev)
+        self.codes = torch.empty(alloc, self.hidden, dtype=torch.uint8, device=dev)
+        self.scales = torch.empty(alloc, self.hidden // 128, dtype=torch.float32, device=dev)
+        self.prod = torch.empty(alloc, self.inter, dtype=torch.uint8, device=dev)
+        self.prod_s = torch.empty(alloc, self.inter // 128, dtype=torch.float32, device=dev)
+        self.y = torch.empty(rows, self.hidden, dtype=torch.float32, device=dev)
+        self.row_map = torch.empty(rows, dtype=torch.int32, device=dev)
+        self.local_ranges = torch.empty(self.local, 2, dtype=torch.int32, device=dev)
 
     def _stream(self):
         return torch.cuda.current_stream(self.device).cuda_stream
@@ -108,33 +134,29 @@ class CudaFp8Backend:
                     prob=self.prob[:t], tokens=t)
 
     def run_experts(self, recv_counts, recv_codes, recv_scales, n_recv):
-        lib, dev = _lib.lib(), self.device
-        rows = n_recv + self.pad_rows
-        y = torch.empty(max(n_recv, 1), self.hidden, dtype=torch.float32, device=dev)
+        lib = _lib.lib()
         if n_recv == 0:
-            return y[:0]
+            return self.y[:0]
+        self._reserve(n_recv)            # no-op unless this call received more rows than any before
+        rows = n_recv + self.pad_rows
         (gw, gs), (uw, us), (dw, ds) = self.w["gate"], self.w["up"], self.w["down"]
-        ranges = torch.empty(self.local, 2, dtype=torch.int32, device=dev)
-        row_map = torch.empty(n_recv, dtype=torch.int32, device=dev)
-        prod = torch.empty(rows, self.inter, dtype=torch.uint8, device=dev)
-        prod_s = torch.empty(rows, self.inter // 128, dtype=torch.float32, device=dev)
+        ranges, y = self.local_ranges, self.y[:n_recv]
         if self.world == 1:
             # one rank: the received order already is the expert order
             codes, scales = recv_codes, recv_scales
             ranges.copy_(self._ranges_from_counts(recv_counts))
             row_map_ptr = None
         else:
-            codes = torch.empty(rows, self.hidden, dtype=torch.uint8, device=dev)
-            scales = torch.empty(rows, self.hidden // 128, dtype=torch.float32, device=dev)
+            codes, scales = self.codes, self.scales
             _lib.check(lib.darask_fp8_ep_regroup(
                 recv_counts.data_ptr(), self.world, self.local, recv_codes.data_ptr(), recv_scales.data_ptr(), self.hidden, n_recv,
-                codes.data_ptr(), scales.data_ptr(), ranges.data_ptr(), row_map.data_ptr(), self.seg.data_ptr(), self.seg.numel() * 4,
+                codes.data_ptr(), scales.data_ptr(), ranges.data_ptr(), self.row_map.data_ptr(), self.seg.data_ptr(), self.seg.numel() * 4,
                 self._stream()), "darask_fp8_ep_regroup")
-            row_map_ptr = row_map.data_ptr()
+            row_map_ptr = self.row_map.data_ptr()
         _lib.check(lib.darask_fp8_ep_experts(
             codes.data_ptr(), scales.data_ptr(), rows, ranges.data_ptr(), self.local, self.hidden, self.inter, gw.data_ptr(),
-            uw.data_ptr(), dw.data_ptr(), gs.data_ptr(), us.data_ptr(), ds.data_ptr(), row_map_ptr, y.data_ptr(), prod.data_ptr(),
-            prod_s.data_ptr(), self.status.data_ptr(), self._stream()), "darask_fp8_ep_experts")
+            uw.data_ptr(), dw.data_ptr(), gs.data_ptr(), us.data_ptr(), ds.data_ptr(), row_map_ptr, y.data_ptr(), self.prod.data_ptr(),
+            self.prod_s.data_ptr(), self.status.data_ptr(), self._stream()), "darask_fp8_ep_experts")
         return y
 
     @staticmethod
