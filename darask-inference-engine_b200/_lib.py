@@ -82,6 +82,11 @@ _SIGNATURES = {
                                          c_size_t, c_void_p]),
     "darask_fp8_grouped_gemm": (c_int, [c_void_p, c_void_p, ctypes.c_ulonglong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                         c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "tsumuji_ep_dispatch": (c_int, [ctypes.POINTER(TsumujiMoe), c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "tsumuji_ep_experts_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "tsumuji_ep_experts": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_size_t,
+                                   c_void_p]),
+    "tsumuji_ep_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "hayate_glm_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_uint, c_void_p, c_void_p]),
     "hayate_glm_grouped_nvfp4": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_uint, c_void_p, c_void_p,
                                          c_uint, c_void_p]),

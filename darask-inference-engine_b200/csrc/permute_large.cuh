@@ -2,6 +2,7 @@
 // many thread blocks.  Assignments are cut into chunks of 1024; (1) every chunk counts its rows per expert,
 // (2) one block turns the counts into per-expert ranges and per-(chunk, expert) start offsets, (3) every chunk
 // places its assignments: rank inside the chunk = rows of the same expert in earlier warps + earlier lanes.
+// (The kernels are templates only so that several translation units may include this file.)
 // Replaces the host loop `groups` (hayate models/src/glm53/prefill.rs:12-26) for batches where one block is slow.
 #pragma once
 #include "route_impl.cuh"
@@ -20,6 +21,7 @@ DEVI bool route_ok(const int* ids, int a, int n, int E, int K, int& e) {
 }
 
 // chunk_counts [chunks][E]
+template <int UNUSED = 0>
 __global__ void __launch_bounds__(kPermChunk) permute_count_kernel(PermuteArgs p, int* chunk_counts) {
   extern __shared__ int hist[];
   pdl_wait();
@@ -36,6 +38,7 @@ __global__ void __launch_bounds__(kPermChunk) permute_count_kernel(PermuteArgs p
 }
 
 // chunk_counts -> in place: rows of the expert in earlier chunks; ranges / active / plan / counters as permute_block
+template <int UNUSED = 0>
 __global__ void __launch_bounds__(1024) permute_scan_kernel(PermuteArgs p, int* chunk_counts, int chunks) {
   extern __shared__ int hist[];
   pdl_wait();
@@ -87,6 +90,7 @@ __global__ void __launch_bounds__(1024) permute_scan_kernel(PermuteArgs p, int* 
   }
 }
 
+template <int UNUSED = 0>
 __global__ void __launch_bounds__(kPermChunk) permute_place_kernel(PermuteArgs p, const int* chunk_base) {
   extern __shared__ unsigned short warp_rows[];        // [32 warps][E]
   pdl_wait();
@@ -125,14 +129,14 @@ inline cudaError_t launch_permute_large(const PermuteArgs& p, void* scratch, cud
   const size_t place_smem = size_t(32) * p.experts * sizeof(unsigned short);
   static bool configured = false;
   if (!configured) {
-    const cudaError_t e = cudaFuncSetAttribute(permute_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024 * 2);
+    const cudaError_t e = cudaFuncSetAttribute(permute_place_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024 * 2);
     if (e != cudaSuccess) return e;
     configured = true;
   }
   cudaError_t e;
-  if ((e = launch_pdl(permute_count_kernel, dim3(chunks), dim3(kPermChunk), size_t(p.experts) * 4, st, p, counts))) return e;
-  if ((e = launch_pdl(permute_scan_kernel, dim3(1), dim3(1024), size_t(p.experts) * 4, st, p, counts, chunks))) return e;
-  return launch_pdl(permute_place_kernel, dim3(chunks), dim3(kPermChunk), place_smem, st, p, (const int*)counts);
+  if ((e = launch_pdl(permute_count_kernel<0>, dim3(chunks), dim3(kPermChunk), size_t(p.experts) * 4, st, p, counts))) return e;
+  if ((e = launch_pdl(permute_scan_kernel<0>, dim3(1), dim3(1024), size_t(p.experts) * 4, st, p, counts, chunks))) return e;
+  return launch_pdl(permute_place_kernel<0>, dim3(chunks), dim3(kPermChunk), place_smem, st, p, (const int*)counts);
 }
 
 }  // namespace dmoe

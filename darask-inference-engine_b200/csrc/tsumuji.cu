@@ -6,6 +6,7 @@
 #include "dense_gemv.cuh"
 #include "gemv_launch.cuh"
 #include "route_kernels.cuh"
+#include "permute_large.cuh"
 
 namespace dmoe {
 
@@ -40,6 +41,49 @@ __global__ void __launch_bounds__(128) act_planes_kernel(const XT* x, int k, __h
   pdl_launch();
   const int t = blockIdx.x;
   act_planes_row(x + size_t(t) * k, k, planes + size_t(t) * 2 * k, xsum32 ? xsum32 + size_t(t) * (k / 32) : nullptr, natural != 0);
+}
+
+// ---- expert-parallel pieces ---------------------------------------------------------------------------------------
+// send rows in dispatch order: row i = x[assignments[i] / topk]; position[a] = i
+__global__ void __launch_bounds__(256) tsumuji_gather_kernel(const float* x, const unsigned* assignments, const int* counters, int topk,
+                                                             int hidden, float* send, unsigned* position) {
+  pdl_wait();
+  pdl_launch();
+  const int i = blockIdx.x;
+  if (i >= __ldcg(counters + 1)) return;
+  const unsigned a = __ldcg(assignments + i);
+  if (threadIdx.x == 0) position[a] = i;
+  const float4* src = reinterpret_cast<const float4*>(x + size_t(a / topk) * hidden);
+  float4* dst = reinterpret_cast<float4*>(send + size_t(i) * hidden);
+  for (int c = threadIdx.x; c < hidden / 4; c += 256) dst[c] = __ldg(src + c);
+}
+// received rows come grouped by source rank, then by ascending local expert: ids[row] = that expert
+__global__ void __launch_bounds__(128) ep_row_experts_kernel(const int* counts, int ranks, int local, int* ids) {
+  pdl_wait();
+  pdl_launch();
+  __shared__ int start;
+  const int seg = blockIdx.x;                 // = rank * local + expert
+  if (threadIdx.x == 0) {
+    int s = 0;
+    for (int i = 0; i < seg; ++i) s += counts[i];
+    start = s;
+  }
+  __syncthreads();
+  const int n = counts[seg];
+  for (int i = threadIdx.x; i < n; i += 128) ids[start + i] = seg % local;
+}
+// out[n][i] = sum_s fma(w[n][s], y[position[n*k+s]][i]) then fma(shared_gate[n], y_shared[n][i])
+__global__ void __launch_bounds__(256) tsumuji_ep_combine_kernel(float* out, const float* y, const float* w, const unsigned* position,
+                                                                 const float* sgate, const float* y_shared, int hidden, int topk,
+                                                                 int accumulate) {
+  pdl_wait();
+  pdl_launch();
+  const int i = blockIdx.x * 256 + threadIdx.x, n = blockIdx.y;
+  if (i >= hidden) return;
+  float o = 0.f;
+  for (int s = 0; s < topk; ++s) o = fmaf(__ldcg(w + n * topk + s), __ldcg(y + size_t(__ldcg(position + n * topk + s)) * hidden + i), o);
+  o = fmaf(__ldcg(sgate + n), __ldcg(y_shared + size_t(n) * hidden + i), o);
+  out[size_t(n) * hidden + i] = accumulate ? out[size_t(n) * hidden + i] + o : o;
 }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -150,4 +194,98 @@ extern "C" int tsumuji_moe_layer(const TsumujiMoe* d, cudaStream_t st) {
   if ((e = launch_pdl(dense_gemv_kernel<0>, dim3(sm_count()), dim3(kGemvWarps * 32), 0, st, t))) return e;
   return launch_pdl(tsumuji_combine_kernel, dim3((H + 255) / 256, N), dim3(256), 0, st, d->out, (const float*)w.y,
                     (const float*)d->rw, (const float*)d->shared_gate, H, K, N, d->accumulate);
+}
+
+// ---- expert-parallel entry points (rank g holds experts [g*E/G, (g+1)*E/G) and its own tokens) ---------------------------
+static void routed_args(GemvArgs& a, GemvArgs& b, const void* experts_w, const float* gs, int H, int F) {
+  const unsigned long long fh = (unsigned long long)F * H;
+  const uint8_t* base = static_cast<const uint8_t*>(experts_w);
+  a = GemvArgs{};
+  a.w[0] = base; a.w[1] = base + fh / 2;
+  a.expert_stride[0] = a.expert_stride[1] = fh * 27 / 16;
+  a.scale_offset[0] = fh * 3 / 2; a.scale_offset[1] = fh * 3 / 2 + fh / 16 - fh / 2;
+  a.row_bytes = H / 2; a.k = H; a.rows = F; a.nblk = H / 256;
+  a.gscale = reinterpret_cast<const uint8_t*>(gs); a.gscale_estride = 12; a.gscale_mstride = 4;
+  b = a;
+  b.w[0] = base + fh; b.w[1] = nullptr;
+  b.scale_offset[0] = fh * 3 / 2 + fh / 8 - fh; b.scale_offset[1] = 0;
+  b.row_bytes = F / 2; b.k = F; b.rows = H; b.nblk = F / 256;
+  b.gscale = reinterpret_cast<const uint8_t*>(gs) + 8;
+}
+
+extern "C" int tsumuji_ep_dispatch(const TsumujiMoe* d, float* send_x, unsigned* ranges, unsigned* position, float* y_shared,
+                                   cudaStream_t st) {
+  if (!d || !d->router_w || !d->shared_gu || !d->shared_down || !d->x || !d->rlogits || !d->sel || !d->rw || !d->shared_gate ||
+      !d->workspace || !send_x || !ranges || !position || !y_shared)
+    return cudaErrorInvalidValue;
+  const int H = d->hidden, F = d->inter, E = d->experts, K = d->topk, N = d->tokens;
+  if (H <= 0 || F <= 0 || H % 256 || F % 256 || E < K || E > 1024 || K < 1 || K > 32 || N < 1) return cudaErrorInvalidValue;
+  if (d->workspace_bytes < tsumuji_moe_workspace_bytes(H, F, E, K, N)) return cudaErrorInvalidValue;
+  const TsumujiWs w = carve(d->workspace, H, F, E, K, N);
+  cudaError_t e;
+  RouterArgs r = {};
+  r.w = d->router_w; r.x = d->x; r.logits = d->rlogits; r.hidden = H; r.rows = E + 1; r.ld = E + 1; r.tokens = N;
+  r.route = RouteArgs{d->rlogits, E + 1, E, K, N, nullptr, 1.f, d->sel, d->rw, d->shared_gate};
+  r.perm = PermuteArgs{d->sel, N, K, E, w.assignments, ranges, w.active, w.counters, w.status, w.plan, 0};
+  r.done = w.done; r.fuse = 1;
+  r.planes = w.xplanes; r.xsum32 = nullptr; r.planes_natural = 1;
+  const size_t hist = size_t(E + 1) * 4 + size_t(N * K <= kRouteIdCache ? N * K : 0) * 4;
+  if ((e = launch_pdl(router_kernel<__nv_bfloat16, float, kRouteTsumuji>, dim3(E + 1 + N), dim3(128), hist, st, r))) return e;
+  if ((e = launch_pdl(tsumuji_gather_kernel, dim3(N * K), dim3(256), 0, st, d->x, (const unsigned*)w.assignments, (const int*)w.counters, K,
+                      H, send_x, position))) return e;
+  // the shared expert stays on the home rank (dense bf16), its rows go straight to y_shared
+  DenseArgs s = {};
+  s.w[0] = static_cast<const __nv_bfloat16*>(d->shared_gu); s.w[1] = s.w[0] + size_t(F) * H;
+  s.k = H; s.rows = F; s.ks = dense_k_split(H, (F + 7) / 8);
+  s.xplanes = w.xplanes; s.x_row0 = 0; s.tokens = N; s.out_planes = w.hplanes; s.out_row0 = 0;
+  if ((e = launch_pdl(dense_gemv_kernel<1>, dim3(sm_count()), dim3(kGemvWarps * 32), 0, st, s))) return e;
+  DenseArgs t = {};
+  t.w[0] = static_cast<const __nv_bfloat16*>(d->shared_down); t.w[1] = nullptr;
+  t.k = F; t.rows = H; t.ks = dense_k_split(F, (H + 15) / 16);
+  t.xplanes = w.hplanes; t.x_row0 = 0; t.tokens = N; t.out = y_shared; t.out_row0 = 0;
+  return launch_pdl(dense_gemv_kernel<0>, dim3(sm_count()), dim3(kGemvWarps * 32), 0, st, t);
+}
+
+extern "C" size_t tsumuji_ep_experts_workspace_bytes(int hidden, int inter, int local_experts, int rows) {
+  if (hidden < 1 || inter < 1 || local_experts < 1 || rows < 1) return 0;
+  return carve(nullptr, hidden, inter, local_experts, 1, rows).bytes + align_up(size_t(rows) * 4, 256) +
+         align_up(permute_scratch_bytes(rows, 1, local_experts), 256);
+}
+
+extern "C" int tsumuji_ep_experts(const void* experts_w, const float* gs, int hidden, int inter, int local_experts, int ranks,
+                                  const int* recv_counts, const float* x_rows, int rows, float* y_rows, void* workspace,
+                                  size_t workspace_bytes, cudaStream_t st) {
+  if (!experts_w || !gs || !recv_counts || !x_rows || !y_rows || !workspace || hidden <= 0 || inter <= 0 || hidden % 256 ||
+      inter % 256 || local_experts < 1 || local_experts > 1024 || ranks < 1 || rows < 1 ||
+      workspace_bytes < tsumuji_ep_experts_workspace_bytes(hidden, inter, local_experts, rows))
+    return cudaErrorInvalidValue;
+  const TsumujiWs w = carve(workspace, hidden, inter, local_experts, 1, rows);
+  int* ids = reinterpret_cast<int*>(static_cast<uint8_t*>(workspace) + w.bytes);
+  void* perm_scratch = reinterpret_cast<uint8_t*>(ids) + align_up(size_t(rows) * 4, 256);
+  cudaError_t e;
+  if ((e = cudaMemsetAsync(w.counters, 0, 16, st))) return e;
+  if ((e = launch_pdl(ep_row_experts_kernel, dim3(ranks * local_experts), dim3(128), 0, st, recv_counts, ranks, local_experts, ids))) return e;
+  const PermuteArgs perm{ids, rows, 1, local_experts, w.assignments, w.ranges, w.active, w.counters, w.status, w.plan, 0};
+  if (rows > 2048) {
+    if ((e = launch_permute_large(perm, perm_scratch, st))) return e;
+  } else if ((e = launch_pdl(permute_kernel<0>, dim3(1), dim3(1024), size_t(local_experts + 1) * 4, st, perm))) return e;
+  if ((e = launch_pdl(act_planes_kernel<float>, dim3(rows), dim3(128), 0, st, x_rows, hidden, w.xplanes, (float*)nullptr, 1))) return e;
+  GemvArgs a, b;
+  routed_args(a, b, experts_w, gs, hidden, inter);
+  a.xplanes = w.xplanes; a.x_by_assignment = 0;
+  a.counters = w.counters + 2; a.plan = w.plan; a.assignments = w.assignments;
+  a.tokens = rows; a.topk = 1; a.max_groups = rows < local_experts ? rows : local_experts;
+  a.out_planes = w.hplanes; a.status = w.status;
+  if ((e = launch_gemv<kGemvNvfp4Linear, 1, false, kOutSiluPlanes>(a, st))) return e;
+  b.counters = a.counters; b.plan = a.plan; b.assignments = a.assignments; b.tokens = rows; b.topk = 1; b.max_groups = a.max_groups;
+  b.status = w.status;
+  b.xplanes = w.hplanes; b.x_by_assignment = 1; b.out_planes = nullptr; b.out = y_rows;
+  return launch_gemv<kGemvNvfp4Linear, 0, false, kOutFloat>(b, st);
+}
+
+extern "C" int tsumuji_ep_combine(float* out, const float* y_home, const float* rw, const unsigned* position, const float* shared_gate,
+                                  const float* y_shared, int tokens, int hidden, int topk, int accumulate, cudaStream_t st) {
+  if (!out || !y_home || !rw || !position || !shared_gate || !y_shared || tokens < 1 || hidden < 1 || topk < 1) return cudaErrorInvalidValue;
+  return launch_pdl(tsumuji_ep_combine_kernel, dim3((hidden + 255) / 256, tokens), dim3(256), 0, st, out, y_home, rw, position, shared_gate,
+                    y_shared, hidden, topk, accumulate);
 }

@@ -51,17 +51,21 @@ def all_to_all_rows(send: torch.Tensor, send_splits, recv_splits, group=None, pa
     return out
 
 
-def ep_forward(backend, x, logits, group=None):
-    """One expert-parallel layer call on this rank's tokens; returns (out, info)."""
+def ep_forward(backend, *inputs, group=None):
+    """One expert-parallel layer call on this rank's tokens; returns (out, info).
+
+    backend.dispatch(*inputs) -> dict with `send` (list of row tensors in ascending expert order), `ranges` [E, 2];
+    backend.run_experts(recv_counts, received list, n_recv) -> rows [n_recv, H] in received order;
+    backend.combine(rows back in dispatch order, dispatch dict) -> out."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
-    d = backend.dispatch(x, logits)                                   # rows in ascending expert order
+    d = backend.dispatch(*inputs)                                     # rows in ascending expert order
     counts = d["ranges"][:, 0].to(torch.int32).reshape(world, -1)
     recv_counts, send_splits, recv_splits = exchange_counts(counts, group)
     bufs = getattr(backend, "buffers", {})
-    recv_codes = all_to_all_rows(d["codes"], send_splits, recv_splits, group, pad_rows=backend.pad_rows, out=bufs.get("recv_codes"))
-    recv_scales = all_to_all_rows(d["scales"], send_splits, recv_splits, group, pad_rows=backend.pad_rows, out=bufs.get("recv_scales"))
+    received = [all_to_all_rows(t, send_splits, recv_splits, group, pad_rows=backend.pad_rows, out=bufs.get(f"recv{i}"))
+                for i, t in enumerate(d["send"])]
     n_recv = sum(recv_splits)
-    y_recv = backend.run_experts(recv_counts, recv_codes, recv_scales, n_recv)      # [n_recv, H] in received order
+    y_recv = backend.run_experts(recv_counts, received, n_recv)       # [n_recv, H] in received order
     y_home = all_to_all_rows(y_recv, recv_splits, send_splits, group, out=bufs.get("y_home"))
     out = backend.combine(y_home, d)
     return out, dict(ids=d["ids"], prob=d["prob"], send_rows=sum(send_splits), recv_rows=n_recv,
@@ -102,8 +106,8 @@ class CudaFp8Backend:
             return
         dev, alloc = self.device, rows + self.pad_rows
         self.capacity = rows
-        self.buffers["recv_codes"] = torch.empty(alloc, self.hidden, dtype=torch.uint8, device=dev)
-        self.buffers["recv_scales"] = torch.empty(alloc, self.hidden // 128, dtype=torch.float32, device=dev)
+        self.buffers["recv0"] = torch.empty(alloc, self.hidden, dtype=torch.uint8, device=dev)
+        self.buffers["recv1"] = torch.empty(alloc, self.hidden // 128, dtype=torch.float32, device=dev)
         self.codes = torch.empty(alloc, self.hidden, dtype=torch.uint8, device=dev)
         self.scales = torch.empty(alloc, self.hidden // 128, dtype=torch.float32, device=dev)
         self.prod = torch.empty(alloc, self.inter, dtype=torch.uint8, device=dev)
@@ -130,10 +134,11 @@ class CudaFp8Backend:
             x.data_ptr(), logits.data_ptr(), self.hidden, self.experts, self.topk, t, self.ids.data_ptr(), self.prob.data_ptr(),
             self.send_codes.data_ptr(), self.send_scales.data_ptr(), self.ranges.data_ptr(), self.position.data_ptr(),
             self.scratch.data_ptr(), self.scratch.numel(), self._stream()), "darask_fp8_ep_dispatch")
-        return dict(codes=self.send_codes, scales=self.send_scales, ranges=self.ranges, position=self.position, ids=self.ids[:t],
+        return dict(send=[self.send_codes, self.send_scales], ranges=self.ranges, position=self.position, ids=self.ids[:t],
                     prob=self.prob[:t], tokens=t)
 
-    def run_experts(self, recv_counts, recv_codes, recv_scales, n_recv):
+    def run_experts(self, recv_counts, received, n_recv):
+        recv_codes, recv_scales = received
         lib = _lib.lib()
         if n_recv == 0:
             return self.y[:0]
@@ -190,5 +195,103 @@ class Fp8ExpertParallelMoe:
         self.backend.load(name, payload, scales)
 
     def forward(self, x, logits):
-        out, self.info = ep_forward(self.backend, x, logits, self.group)
+        out, self.info = ep_forward(self.backend, x, logits, group=self.group)
+        return out
+
+
+class CudaTsumujiBackend:
+    """Kernels of one rank of the Tsumuji (NVFP4, Qwen-Next-shaped) layer: its E/G packed expert blocks, the router and
+    the shared expert replicated.  Reference single-GPU call site: tsumuji-engine/src/engine.rs:1586-1683."""
+    pad_rows = 0
+
+    def __init__(self, hidden, inter, experts, topk, world, max_tokens, device="cuda"):
+        if experts % world:
+            raise ValueError("experts must divide evenly over the ranks")
+        self.hidden, self.inter, self.experts, self.topk, self.world = hidden, inter, experts, topk, world
+        self.local, self.max_tokens, self.device = experts // world, max_tokens, torch.device(device)
+        lib, dev = _lib.lib(), self.device
+        self.workspace = torch.zeros(lib.tsumuji_moe_workspace_bytes(hidden, inter, experts, topk, max_tokens), dtype=torch.uint8, device=dev)
+        self.rlogits = torch.zeros(max_tokens, experts + 1, dtype=torch.float32, device=dev)
+        self.sel = torch.zeros(max_tokens, topk, dtype=torch.int32, device=dev)
+        self.rw = torch.zeros(max_tokens, topk, dtype=torch.float32, device=dev)
+        self.sgate = torch.zeros(max_tokens, dtype=torch.float32, device=dev)
+        self.send_x = torch.empty(max_tokens * topk, hidden, dtype=torch.float32, device=dev)
+        self.ranges = torch.zeros(experts, 2, dtype=torch.int32, device=dev)
+        self.position = torch.zeros(max_tokens * topk, dtype=torch.int32, device=dev)
+        self.y_shared = torch.empty(max_tokens, hidden, dtype=torch.float32, device=dev)
+        self.buffers = {"y_home": torch.empty(max_tokens * topk, hidden, dtype=torch.float32, device=dev)}
+        self.capacity = 0
+        self._reserve(2 * max_tokens * topk)
+
+    def _reserve(self, rows):
+        if rows <= self.capacity:
+            return
+        self.capacity = rows
+        self.buffers["recv0"] = torch.empty(rows, self.hidden, dtype=torch.float32, device=self.device)
+        self.y = torch.empty(rows, self.hidden, dtype=torch.float32, device=self.device)
+        nbytes = _lib.lib().tsumuji_ep_experts_workspace_bytes(self.hidden, self.inter, self.local, rows)
+        self.expert_ws = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
+
+    def _stream(self):
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def load(self, router, blocks, gs, shared_gu, shared_down):
+        """router bf16 [E+1,H] (replicated), blocks uint8 [E/G * 27/16 F H] and gs float32 [E/G,3] (this rank's experts),
+        shared_gu bf16 [2F,H], shared_down bf16 [H,F] (replicated)."""
+        dev = self.device
+        self.router = router.to(dev, torch.bfloat16).contiguous()
+        self.blocks = blocks.to(dev, torch.uint8).contiguous()
+        self.gs = gs.to(dev, torch.float32).contiguous()
+        self.shared_gu = shared_gu.to(dev, torch.bfloat16).contiguous()
+        self.shared_down = shared_down.to(dev, torch.bfloat16).contiguous()
+        if self.blocks.numel() != self.local * self.hidden * self.inter * 27 // 16 or tuple(self.gs.shape) != (self.local, 3):
+            raise ValueError("blocks / gs: expected this rank's E/G experts")
+
+    def dispatch(self, x):
+        n = x.shape[0]
+        if n > self.max_tokens or x.dtype != torch.float32 or not x.is_contiguous():
+            raise ValueError("x must be contiguous float32 [N<=max_tokens,H]")
+        d = _lib.TsumujiMoe()
+        d.hidden, d.inter, d.experts, d.topk, d.tokens = self.hidden, self.inter, self.experts, self.topk, n
+        d.router_w, d.shared_gu, d.shared_down = self.router.data_ptr(), self.shared_gu.data_ptr(), self.shared_down.data_ptr()
+        d.x, d.rlogits, d.sel, d.rw, d.shared_gate = x.data_ptr(), self.rlogits.data_ptr(), self.sel.data_ptr(), self.rw.data_ptr(), self.sgate.data_ptr()
+        d.workspace, d.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
+        _lib.check(_lib.lib().tsumuji_ep_dispatch(ctypes.byref(d), self.send_x.data_ptr(), self.ranges.data_ptr(), self.position.data_ptr(),
+                                                  self.y_shared.data_ptr(), self._stream()), "tsumuji_ep_dispatch")
+        return dict(send=[self.send_x], ranges=self.ranges, position=self.position, ids=self.sel[:n], prob=self.rw[:n], tokens=n)
+
+    def run_experts(self, recv_counts, received, n_recv):
+        if n_recv == 0:
+            return self.y[:0]
+        self._reserve(n_recv)
+        x_rows, y = received[0], self.y[:n_recv]
+        _lib.check(_lib.lib().tsumuji_ep_experts(
+            self.blocks.data_ptr(), self.gs.data_ptr(), self.hidden, self.inter, self.local, self.world, recv_counts.data_ptr(),
+            x_rows.data_ptr(), n_recv, y.data_ptr(), self.expert_ws.data_ptr(), self.expert_ws.numel(), self._stream()),
+            "tsumuji_ep_experts")
+        return y
+
+    def combine(self, y_home, d):
+        n = d["tokens"]
+        out = torch.empty(n, self.hidden, dtype=torch.float32, device=self.device)
+        _lib.check(_lib.lib().tsumuji_ep_combine(out.data_ptr(), y_home.data_ptr(), self.rw.data_ptr(), self.position.data_ptr(),
+                                                 self.sgate.data_ptr(), self.y_shared.data_ptr(), n, self.hidden, self.topk, 0,
+                                                 self._stream()), "tsumuji_ep_combine")
+        return out
+
+
+class TsumujiExpertParallelMoe:
+    """`forward(x)` on every rank with that rank's float32 token rows."""
+
+    def __init__(self, hidden, inter, experts, topk, max_tokens, group=None, device="cuda"):
+        self.group = group
+        world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.backend = CudaTsumujiBackend(hidden, inter, experts, topk, world, max_tokens, device)
+
+    def load(self, *weights):
+        self.backend.load(*weights)
+
+    def forward(self, x):
+        out, self.info = ep_forward(self.backend, x, group=self.group)
         return out

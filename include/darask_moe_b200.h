@@ -158,6 +158,21 @@ size_t tsumuji_moe_workspace_bytes(int hidden, int inter, int experts, int topk,
 /* zeroes the control words once after allocation (same as kogarashi_moe_workspace_init) */
 int tsumuji_moe_workspace_init(void* workspace, size_t bytes, darask_stream_t stream);
 int tsumuji_moe_layer(const TsumujiMoe* desc /* host */, darask_stream_t stream);
+/* The same layer cut at the two exchange steps of expert parallelism (rank g holds experts [g*E/G, (g+1)*E/G) and its
+ * own tokens; the reference has no multi-GPU path).  Home rank: tsumuji_ep_dispatch = router projection, router_topk,
+ * permutation over all E experts, the token rows gathered in ascending expert order (send_x float32
+ * [tokens*topk][hidden], ranges [E][2], position[a] = dispatch row of assignment a) and the shared expert
+ * (y_shared [tokens][hidden]).  Expert rank: tsumuji_ep_experts = gate/up + SwiGLU + down over the received rows
+ * (grouped by source rank, then local expert; recv_counts int32 [ranks][local_experts]) -> y_rows in received order.
+ * Home rank: tsumuji_ep_combine = sum_s rw*y[position] in slot order, then the gated shared expert (ops.cu:217-223). */
+int tsumuji_ep_dispatch(const TsumujiMoe* desc /* host; out unused */, float* send_x, unsigned* ranges, unsigned* position,
+                        float* y_shared, darask_stream_t stream);
+size_t tsumuji_ep_experts_workspace_bytes(int hidden, int inter, int local_experts, int rows);
+int tsumuji_ep_experts(const void* experts_w, const float* gs, int hidden, int inter, int local_experts, int ranks,
+                       const int* recv_counts, const float* x_rows, int rows, float* y_rows, void* workspace,
+                       size_t workspace_bytes, darask_stream_t stream);
+int tsumuji_ep_combine(float* out, const float* y_home, const float* rw, const unsigned* position, const float* shared_gate,
+                       const float* y_shared, int tokens, int hidden, int topk, int accumulate, darask_stream_t stream);
 
 
 /* ---- Hayate (GLM) ------------------------------------------------------------------------------------------

@@ -39,13 +39,13 @@ class OracleBackend:
         tok = assign.astype(np.int64) // self.layer.topk
         position = np.empty(assign.size, np.int32)
         position[assign.astype(np.int64)] = np.arange(assign.size, dtype=np.int32)
-        return dict(codes=torch.from_numpy(xq[tok]), scales=torch.from_numpy(xs[tok]),
+        return dict(send=[torch.from_numpy(xq[tok]), torch.from_numpy(xs[tok])],
                     ranges=torch.from_numpy(np.stack([counts, offsets], 1).astype(np.int32)), position=position, ids=ids, prob=prob,
                     tokens=x.shape[0])
 
-    def run_experts(self, recv_counts, recv_codes, recv_scales, n_recv):
+    def run_experts(self, recv_counts, received, n_recv):
         counts = recv_counts.numpy().reshape(self.world, self.local)
-        codes, scales = recv_codes.numpy(), recv_scales.numpy()
+        codes, scales = received[0].numpy(), received[1].numpy()
         y = np.zeros((n_recv, self.layer.hidden), np.float32)
         row = 0
         for r in range(self.world):
@@ -72,7 +72,7 @@ class OracleBackend:
 def main():
     mode, out_dir = sys.argv[1], sys.argv[2]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
-    if mode == "cuda":
+    if mode.startswith("cuda"):
         torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
         dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
     else:
@@ -82,6 +82,25 @@ def main():
     x, logits = acts["x"][lo:hi], acts["logits"][lo:hi]
     ref = L.fp8_forward(layer, x, logits)
     import darask_inference_engine_b200 as D
+    if mode == "cuda_tsumuji":
+        tl, ta = W.tsumuji_layer(78, 512, 256, 16, 4, TOKENS_PER_RANK * world, pool=16)
+        tx = ta["x"][lo:hi]
+        local = 16 // world
+        m = D.TsumujiExpertParallelMoe(512, 256, 16, 4, TOKENS_PER_RANK)
+        t = torch.from_numpy
+        m.load(t(tl.router), t(tl.blocks[rank * local:(rank + 1) * local].reshape(-1)), t(tl.gs[rank * local:(rank + 1) * local]),
+               t(tl.shared_gu), t(tl.shared_down))
+        out = m.forward(t(tx).cuda())
+        torch.cuda.synchronize()
+        tref = L.tsumuji_forward(tl, tx, logits=m.backend.rlogits[:TOKENS_PER_RANK].cpu().numpy())
+        assert np.array_equal(m.info["ids"].cpu().numpy(), tref["ids"]), "routes differ"
+        W.check_output(out.cpu().numpy(), tref["out"])
+        info = m.info
+        dist.barrier()
+        with open(os.path.join(out_dir, f"ok.{rank}"), "w") as f:
+            f.write(f"{info['send_rows']} {info['recv_rows']} {info['cross_rows']}\n")
+        dist.destroy_process_group()
+        return
     if mode == "cuda":
         m = D.Fp8ExpertParallelMoe(HIDDEN, INTER, EXPERTS, TOPK, TOKENS_PER_RANK)
         local = EXPERTS // world
