@@ -23,6 +23,46 @@ __global__ void __launch_bounds__(256) tsumuji_combine_kernel(float* out, const 
   out[size_t(n) * hidden + i] = accumulate ? out[size_t(n) * hidden + i] + o : o;
 }
 
+// Router projection for token windows (N > 16): logits[t][row] = W[row] . x[t]. A block keeps four bf16 router rows in
+// shared memory; each of its 8 warps takes every 8th token, reads the token's float32 row once and forms the four
+// dot products. (The one-block-per-row kernel re-reads all N token rows in every block.)
+constexpr int kRouterBatchRows = 4;
+__global__ void __launch_bounds__(256) router_batch_kernel(const __nv_bfloat16* w, const float* x, float* logits, int rows, int hidden,
+                                                           int ld, int tokens) {
+  extern __shared__ __align__(16) uint8_t rb_smem[];
+  __nv_bfloat16* ws = reinterpret_cast<__nv_bfloat16*>(rb_smem);      // [4][hidden]
+  const int row0 = blockIdx.x * kRouterBatchRows, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < kRouterBatchRows * hidden / 8; i += 256) {
+    const int r = i / (hidden / 8), c = i % (hidden / 8);
+    reinterpret_cast<uint4*>(ws)[i] = row0 + r < rows ? __ldg(reinterpret_cast<const uint4*>(w + size_t(row0 + r) * hidden) + c)
+                                                      : make_uint4(0, 0, 0, 0);
+  }
+  pdl_wait();
+  pdl_launch();
+  __syncthreads();
+  for (int t = warp; t < tokens; t += 8) {
+    const float4* xr = reinterpret_cast<const float4*>(x + size_t(t) * hidden);
+    float acc[kRouterBatchRows] = {0.f, 0.f, 0.f, 0.f};
+    for (int c = lane; c < hidden / 4; c += 32) {
+      const float4 v = __ldg(xr + c);
+#pragma unroll
+      for (int r = 0; r < kRouterBatchRows; ++r) {
+        const uint2 q = *reinterpret_cast<const uint2*>(ws + size_t(r) * hidden + c * 4);
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&q.x), b = *reinterpret_cast<const __nv_bfloat162*>(&q.y);
+        acc[r] = fmaf(__low2float(a), v.x, acc[r]);
+        acc[r] = fmaf(__high2float(a), v.y, acc[r]);
+        acc[r] = fmaf(__low2float(b), v.z, acc[r]);
+        acc[r] = fmaf(__high2float(b), v.w, acc[r]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kRouterBatchRows; ++r) {
+      const float v = warp_sum(acc[r]);
+      if (lane == 0 && row0 + r < rows) logits[size_t(t) * ld + row0 + r] = v;
+    }
+  }
+}
+
 // stand-alone routing of given logits followed by the permutation, one block
 template <int MODE>
 __global__ void __launch_bounds__(128) route_permute_kernel(RouteArgs r, PermuteArgs p) {
@@ -89,7 +129,7 @@ __global__ void __launch_bounds__(256) tsumuji_ep_combine_kernel(float* out, con
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 struct TsumujiWs {
   int* counters; unsigned* done; unsigned* status; int* active; unsigned* ranges; unsigned* assignments; int4* plan;
-  __half* xplanes; __half* hplanes; float* y; size_t bytes;
+  __half* xplanes; __half* hplanes; float* y; int* perm_scratch; size_t bytes;
 };
 static TsumujiWs carve(void* base, int hidden, int inter, int experts, int topk, int tokens) {
   TsumujiWs w;
@@ -107,8 +147,28 @@ static TsumujiWs carve(void* base, int hidden, int inter, int experts, int topk,
   const size_t rows = size_t(tokens) * topk + tokens;
   w.hplanes = reinterpret_cast<__half*>(take(rows * 2 * inter * 2));
   w.y = reinterpret_cast<float*>(take(rows * hidden * 4));
+  w.perm_scratch = reinterpret_cast<int*>(take(permute_scratch_bytes(tokens, topk, experts)));
   w.bytes = off;
   return w;
+}
+
+// token windows: projection, routing, permutation and planes as separate launches that scale with N
+static cudaError_t route_window(const void* router_w, const float* x, const RouteArgs& route, const PermuteArgs& perm, const TsumujiWs& w,
+                                int H, int E, int N, cudaStream_t st) {
+  cudaError_t e;
+  if (router_w) {
+    static bool configured = false;
+    const size_t smem = size_t(kRouterBatchRows) * H * 2;
+    if (!configured && smem > 48 * 1024) {
+      if ((e = cudaFuncSetAttribute(router_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)))) return e;
+      configured = true;
+    }
+    if ((e = launch_pdl(router_batch_kernel, dim3((E + 1 + kRouterBatchRows - 1) / kRouterBatchRows), dim3(256), smem, st,
+                        static_cast<const __nv_bfloat16*>(router_w), x, const_cast<float*>(route.logits), E + 1, H, E + 1, N))) return e;
+  }
+  if ((e = launch_pdl(route_topk_kernel<kRouteTsumuji>, dim3((N + 3) / 4), dim3(128), 0, st, route))) return e;
+  if ((e = launch_permute_large(perm, w.perm_scratch, st))) return e;
+  return launch_pdl(act_planes_kernel<float>, dim3(N), dim3(128), 0, st, x, H, w.xplanes, (float*)nullptr, 1);
 }
 
 static int dense_k_split(int k, long long slabs) {
@@ -145,7 +205,10 @@ extern "C" int tsumuji_moe_layer(const TsumujiMoe* d, cudaStream_t st) {
   const RouteArgs route{d->rlogits, E + 1, E, K, N, nullptr, 1.f, d->sel, d->rw, d->shared_gate};
   const PermuteArgs perm{d->sel, N, K, E, w.assignments, w.ranges, w.active, w.counters, w.status, w.plan, 0};
   cudaError_t e;
-  if (d->router_w) {
+  if (N > 16) {
+    if ((e = cudaMemsetAsync(w.counters, 0, 16, st))) return e;
+    if ((e = route_window(d->router_w, d->x, route, perm, w, H, E, N, st))) return e;
+  } else if (d->router_w) {
     // router projection (bf16 [E+1][H], row E = shared-expert gate), top-k, permutation, activation planes
     RouterArgs r = {};
     r.w = d->router_w; r.x = d->x; r.logits = d->rlogits; r.hidden = H; r.rows = E + 1; r.ld = E + 1; r.tokens = N;
@@ -223,14 +286,20 @@ extern "C" int tsumuji_ep_dispatch(const TsumujiMoe* d, float* send_x, unsigned*
   if (d->workspace_bytes < tsumuji_moe_workspace_bytes(H, F, E, K, N)) return cudaErrorInvalidValue;
   const TsumujiWs w = carve(d->workspace, H, F, E, K, N);
   cudaError_t e;
-  RouterArgs r = {};
-  r.w = d->router_w; r.x = d->x; r.logits = d->rlogits; r.hidden = H; r.rows = E + 1; r.ld = E + 1; r.tokens = N;
-  r.route = RouteArgs{d->rlogits, E + 1, E, K, N, nullptr, 1.f, d->sel, d->rw, d->shared_gate};
-  r.perm = PermuteArgs{d->sel, N, K, E, w.assignments, ranges, w.active, w.counters, w.status, w.plan, 0};
-  r.done = w.done; r.fuse = 1;
-  r.planes = w.xplanes; r.xsum32 = nullptr; r.planes_natural = 1;
-  const size_t hist = size_t(E + 1) * 4 + size_t(N * K <= kRouteIdCache ? N * K : 0) * 4;
-  if ((e = launch_pdl(router_kernel<__nv_bfloat16, float, kRouteTsumuji>, dim3(E + 1 + N), dim3(128), hist, st, r))) return e;
+  const RouteArgs route{d->rlogits, E + 1, E, K, N, nullptr, 1.f, d->sel, d->rw, d->shared_gate};
+  const PermuteArgs perm{d->sel, N, K, E, w.assignments, ranges, w.active, w.counters, w.status, w.plan, 0};
+  if (N > 16) {
+    if ((e = cudaMemsetAsync(w.counters, 0, 16, st))) return e;
+    if ((e = route_window(d->router_w, d->x, route, perm, w, H, E, N, st))) return e;
+  } else {
+    RouterArgs r = {};
+    r.w = d->router_w; r.x = d->x; r.logits = d->rlogits; r.hidden = H; r.rows = E + 1; r.ld = E + 1; r.tokens = N;
+    r.route = route; r.perm = perm;
+    r.done = w.done; r.fuse = 1;
+    r.planes = w.xplanes; r.xsum32 = nullptr; r.planes_natural = 1;
+    const size_t hist = size_t(E + 1) * 4 + size_t(N * K <= kRouteIdCache ? N * K : 0) * 4;
+    if ((e = launch_pdl(router_kernel<__nv_bfloat16, float, kRouteTsumuji>, dim3(E + 1 + N), dim3(128), hist, st, r))) return e;
+  }
   if ((e = launch_pdl(tsumuji_gather_kernel, dim3(N * K), dim3(256), 0, st, d->x, (const unsigned*)w.assignments, (const int*)w.counters, K,
                       H, send_x, position))) return e;
   // the shared expert stays on the home rank (dense bf16), its rows go straight to y_shared
