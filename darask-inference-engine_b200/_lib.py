@@ -90,6 +90,7 @@ _SIGNATURES = {
     "hayate_glm_grouped": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_uint, c_void_p, c_void_p]),
     "hayate_glm_grouped_nvfp4": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_uint, c_void_p, c_void_p,
                                          c_uint, c_void_p]),
+    "hayate_glm_restore": (c_int, [c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_void_p]),
     "hayate_glm_nvfp4_restore": (c_int, [c_void_p, c_void_p, c_uint, c_uint, c_void_p]),
     "hayate_glm_nvfp4_restore_unscaled": (c_int, [c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_void_p]),
     "hayate_glm_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_void_p]),

@@ -37,6 +37,11 @@ __global__ void __launch_bounds__(256) restore_nvfp4_kernel(__nv_bfloat16* out, 
   const size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
   if (i < size_t(n) * k) out[i] = __float2bfloat16_rn(nvfp4_element(image, unsigned(i / k), unsigned(i % k), n, k, scaled));
 }
+// block-FP8 matrix -> bf16: out = bf16(e4m3(w) * scale[row/128][col/128])   (reference `restore`, cu/glm53/ops.cu:13-16)
+__global__ void __launch_bounds__(256) restore_fp8_kernel(__nv_bfloat16* out, const uint8_t* w, const float* scale, unsigned n, unsigned k) {
+  const size_t i = size_t(blockIdx.x) * 256 + threadIdx.x;
+  if (i < size_t(n) * k) out[i] = __float2bfloat16_rn(e4m3_value(w[i]) * scale[(i / k / 128) * ((k + 127) / 128) + (i % k) / 128]);
+}
 // out row i = x row assignments[i] / topk, 16 bytes per thread
 __global__ void __launch_bounds__(256) gather_rows_kernel(uint4* out, const uint4* x, const unsigned* assignments, unsigned rows,
                                                           unsigned chunks, unsigned topk) {
@@ -135,6 +140,13 @@ extern "C" int hayate_glm_nvfp4_restore_unscaled(void* out, void* scale, const v
   restore_nvfp4_kernel<<<unsigned((size_t(n) * k + 255) / 256), 256, 0, st>>>(static_cast<__nv_bfloat16*>(out),
                                                                              static_cast<const uint8_t*>(image), n, k, false,
                                                                              static_cast<float*>(scale));
+  return cudaGetLastError();
+}
+
+extern "C" int hayate_glm_restore(void* out, const void* w, const void* scale, unsigned n, unsigned k, cudaStream_t st) {
+  if (!out || !w || !scale || !n || !k) return cudaErrorInvalidValue;
+  restore_fp8_kernel<<<unsigned((size_t(n) * k + 255) / 256), 256, 0, st>>>(static_cast<__nv_bfloat16*>(out), static_cast<const uint8_t*>(w),
+                                                                           static_cast<const float*>(scale), n, k);
   return cudaGetLastError();
 }
 

@@ -230,6 +230,8 @@ int hayate_glm_grouped(void* out, const void* x, const void* w, const void* rang
                        void* metadata, darask_stream_t stream);
 int hayate_glm_grouped_nvfp4(void* out, void* accumulator, const void* x, const void* w, const void* ranges, unsigned groups,
                              unsigned n, unsigned k, void* metadata, const void* scales, unsigned max_rows, darask_stream_t stream);
+/* block-FP8 matrix (e4m3 payload, float32 scale per 128x128) -> bf16 (glm53.rs:746-753) */
+int hayate_glm_restore(void* out, const void* w, const void* scale, unsigned n, unsigned k, darask_stream_t stream);
 int hayate_glm_nvfp4_restore(void* out, const void* image, unsigned n, unsigned k, darask_stream_t stream);
 int hayate_glm_nvfp4_restore_unscaled(void* out, void* scale, const void* image, unsigned n, unsigned k, darask_stream_t stream);
 int hayate_glm_gather(void* out, const void* x, const void* assignments, unsigned rows, unsigned hidden, darask_stream_t stream);

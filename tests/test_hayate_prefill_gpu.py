@@ -46,6 +46,17 @@ def test_nvfp4_restore(n, k):
     assert l.hayate_glm_nvfp4_restore(out.data_ptr(), d.data_ptr(), n, 24, stream()) != 0      # k % 16 as in the reference
 
 
+@pytest.mark.parametrize("n,k", [(256, 384), (130, 200)])
+def test_fp8_restore(n, k):
+    l, check = lib()
+    rng = W.rng_for(6)
+    payload, scale = F.fp8_block_quantize(W.normal(rng, (n, k), 0.02))
+    p_d, s_d = torch.from_numpy(payload).cuda(), torch.from_numpy(scale).cuda()
+    out = torch.empty(n, k, dtype=torch.bfloat16, device="cuda")
+    check(l.hayate_glm_restore(out.data_ptr(), p_d.data_ptr(), s_d.data_ptr(), n, k, stream()), "restore")
+    assert np.array_equal(out.float().cpu().numpy(), F.fp8_block_decode(payload, scale, rounded=True))
+
+
 def test_gather_scatter_copy():
     l, check = lib()
     rng = W.rng_for(4)
