@@ -25,6 +25,8 @@
 
 namespace dmoe {
 
+// Optional instrumentation (-DDMOE_G8_TRACE): per-role cycle counters written to G8Args::trace and switches that
+// disable the MMAs or the TMA loads; compiled out of the product build.
 #ifdef DMOE_G8_TRACE
 #define G8_CLK() clock64()
 #define G8_ADD(var, t0) var += clock64() - (t0)
@@ -170,13 +172,13 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     if (warp == 0 && lane == 0) {
       // ---- TMA producer ------------------------------------------------------------------------------------
       int it = 0;
-      long long w_empty = 0, t_all = G8_CLK();
+      [[maybe_unused]] long long w_empty = 0, t_all = G8_CLK();
       for (int tile = blockIdx.x; tile < total && !abort_flag; tile += gridDim.x) {
         const G8Tile t = locate(tile);
         const int wrow = t.expert * a.n + t.n0;                              // row of the weight tensor [E*N][K]
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % kG8Stages;
-          const long long c0 = G8_CLK();
+          [[maybe_unused]] const long long c0 = G8_CLK();
           if (it >= kG8Stages && !mbar_wait_suspend(empty + s, ((it / kG8Stages) & 1) ^ 1, a.status)) { abort_flag = 1; break; }
           G8_ADD(w_empty, c0);
           const uint32_t dst = smem_u32(smem + s * kG8StageBytes);
@@ -194,14 +196,14 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     } else if (warp == 1 && lane == 0) {
       // ---- MMA issuer ----------------------------------------------------------------------------------------
       int it = 0;
-      long long w_tempty = 0, w_full = 0, t_all = G8_CLK();
+      [[maybe_unused]] long long w_tempty = 0, w_full = 0, t_all = G8_CLK();
       for (int tile = blockIdx.x; tile < total && !abort_flag; tile += gridDim.x) {
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const int s = it % kG8Stages, buf = it & (kG8AccBufs - 1);
-          const long long c0 = G8_CLK();
+          [[maybe_unused]] const long long c0 = G8_CLK();
           if (it >= kG8AccBufs && !mbar_wait_suspend(tempty + buf, ((it / kG8AccBufs) & 1) ^ 1, a.status)) { abort_flag = 1; break; }
           G8_ADD(w_tempty, c0);
-          const long long c1 = G8_CLK();
+          [[maybe_unused]] const long long c1 = G8_CLK();
           if (!mbar_wait_suspend(full + s, (it / kG8Stages) & 1, a.status)) { abort_flag = 1; break; }
           G8_ADD(w_full, c1);
           tmem_fence_after();
@@ -233,13 +235,13 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const int steps = my_tiles * kblocks;
     const uint32_t tlane = tmem_base + (uint32_t(quarter * 32) << 16);
     bool ok = true;
-    long long w_tfull = 0, w_close = 0, t_all = G8_CLK();
+    [[maybe_unused]] long long w_tfull = 0, w_close = 0, t_all = G8_CLK();
     uint32_t va[16];
     auto await_step = [&](int step) {                   // the MMAs of this step have written their TMEM buffer
       const int buf = step & (kG8AccBufs - 1);
       // one lane watches the barrier (many threads probing one barrier word serialise in shared memory)
       int got = 1;
-      const long long c0 = G8_CLK();
+      [[maybe_unused]] const long long c0 = G8_CLK();
       if (lane == 0) got = mbar_wait_suspend(tfull + buf, (step / kG8AccBufs) & 1, a.status) ? 1 : 0;
       got = __shfl_sync(0xffffffffu, got, 0);
       G8_ADD(w_tfull, c0);
@@ -423,7 +425,7 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         fma16(fB, 56);
         if (step + 1 < steps) await_step(step + 1);
         if (++kb == kblocks) {
-          const long long c0 = G8_CLK();
+          [[maybe_unused]] const long long c0 = G8_CLK();
           close_tile();
           G8_ADD(w_close, c0);
           kb = 0;

@@ -123,7 +123,7 @@ def test_reduction_order_golden():
         acc = F.bf16_round(acc + F.bf16_round((y[s] * w[s]).astype(np.float32)))
     expect = F.bf16_round(acc + y[8])
     out = torch.zeros(4096, dtype=torch.bfloat16, device="cuda")
-    assert lib.hayate_glm_moe_reduce(out.data_ptr(), bf16_tensor(y).cuda().data_ptr(), torch.from_numpy(ids).cuda().data_ptr(),
-                                     torch.from_numpy(w).cuda().data_ptr(), st) == 0
+    y_d, ids_d, w_d = bf16_tensor(y).cuda(), torch.from_numpy(ids).cuda(), torch.from_numpy(w).cuda()
+    assert lib.hayate_glm_moe_reduce(out.data_ptr(), y_d.data_ptr(), ids_d.data_ptr(), w_d.data_ptr(), st) == 0
     torch.cuda.synchronize()
     assert np.array_equal(out.float().cpu().numpy(), expect)
