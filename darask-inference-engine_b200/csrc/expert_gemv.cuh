@@ -339,16 +339,15 @@ DEVI float hayate_swiglu(float gate, float up) {
   return bf16_rn(bf16_rn(gate * sigmoid_precise(gate)) * up);
 }
 
+// All items of one launch for this CTA (blockDim = kGemvWarps * 32, `smem` = gemv_smem_bytes<FMT>() bytes, 128-byte
+// aligned). Also called phase by phase from the single-launch decode layer.
 template <int FMT, int DUAL, bool MINS_TILE, int OUT>
-__global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const GemvArgs a) {
+DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
   using LY = GemvLayout<FMT>;
-  extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int STAGE = gemv_stage_bytes<FMT>();
   const uint32_t ring = smem_u32(smem) + warp * (LY::kStages * STAGE);
   float* red = reinterpret_cast<float*>(smem + kGemvWarps * LY::kStages * STAGE);   // [warp][token 4][row 16]
-  pdl_wait();
-  pdl_launch();
   constexpr int RPT = DUAL ? 8 : 16;                     // weight rows of matrix 0 per slab
   constexpr bool NV = FMT == kGemvNvfp4Linear || FMT == kGemvNvfp4Tiled;
   const int tiles_per_group = (a.rows + RPT - 1) / RPT;
@@ -519,6 +518,14 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const G
       }
     }
   }
+}
+
+template <int FMT, int DUAL, bool MINS_TILE, int OUT>
+__global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const GemvArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  pdl_wait();
+  pdl_launch();
+  gemv_items<FMT, DUAL, MINS_TILE, OUT>(a, smem);
 }
 
 // ---- activation rows -> planes (and per-32 sums) ------------------------------------------------------
