@@ -24,7 +24,7 @@
 
 namespace dmoe {
 
-enum GemvFormat { kGemvQ4K = 0, kGemvQ6KR = 1, kGemvNvfp4Linear = 2, kGemvNvfp4Tiled = 3 };
+enum GemvFormat { kGemvQ4K = 0, kGemvQ6KR = 1, kGemvNvfp4Linear = 2, kGemvNvfp4Tiled = 3, kGemvFp8Block = 4 };
 // what the epilogue writes
 enum GemvOut {
   kOutSiluPlanes = 0,    // DUAL: silu(g) * u as fp16 hi/lo planes (Kogarashi, Tsumuji)
@@ -40,7 +40,8 @@ struct GemvArgs {
   int row_bytes;                // bytes of one row (of codes, for NVFP4) in global memory (multiple of 16)
   const void* const* w_table;   // optional: per group the base pointer of its expert image (replaces w[0] + e * stride)
   unsigned long long matrix_stride;      // w_table / Hayate images: bytes between gate | up | down inside an image
-  unsigned long long scale_offset[2];    // NVFP4: byte offset of the scale area from the matrix base (per matrix)
+  unsigned long long scale_offset[2];    // NVFP4 / block-FP8: byte offset of the scale area from the matrix base (per matrix)
+  const float* scale_shared[2];          // block-FP8: the shared expert's scale arrays when they are not behind its payload (null: scale_offset)
   const uint8_t* gscale;        // per-matrix float32 multiplier: gscale + e * gscale_estride + m * gscale_mstride (null: 1)
   unsigned long long gscale_estride, gscale_mstride;
   const uint8_t* gscale_shared[2];       // the same for the shared expert (null: 1)
@@ -304,12 +305,50 @@ DEVI void nvfp4_block_f16(uint32_t slab, int lane, const __half* bcol, float rm0
   facc[1] += c[2] + c[3];
 }
 
+// ---- block-FP8 (e4m3 payload [rows][k], float32 scale per 128 x 128; hayate `Fp8Block`) ---------------------------
+// weight = bf16(e4m3 * scale) (hayate cu/glm53/math.cuh:40 `scaled_fp8`): formed per pair in float32, rounded to
+// bf16, kept in fp16 as bf16(..) * 2^s with s chosen per scale so that the values stay normal. One 256-column block =
+// two 128-column halves with their own scale. sc0 / sc1: the two scales of rows g / g + 8 for this block.
+DEVI uint32_t e4m3x2_to_h2(uint32_t two_bytes) {
+  uint32_t out;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(out) : "h"((unsigned short)two_bytes));
+  return out;
+}
+template <int PITCH>
+DEVI void fp8_block_f16(uint32_t slab, int lane, const __half* bcol, const float* sc0, const float* sc1, float (&facc)[2]) {
+  const int g = lane >> 2, j = lane & 3;
+  const uint32_t r0 = slab + g * PITCH, r1 = slab + (g + 8) * PITCH;
+#pragma unroll
+  for (int hb = 0; hb < 2; ++hb) {                   // 128-column halves
+    const float s0 = __ldg(sc0 + hb), s1 = __ldg(sc1 + hb);
+    const int e0 = 14 - ilogbf(448.f * s0), e1 = 14 - ilogbf(448.f * s1);
+    const float rm0 = scalbnf(s0, e0), rm1 = scalbnf(s1, e1);
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {                    // 32 columns per step: this lane owns columns 8j..8j+7 of them
+      const int col = hb * 128 + q * 32 + 8 * j;
+      const uint2 w0 = lds64(r0 + col), w1 = lds64(r1 + col);
+      uint4 x = make_uint4(0, 0, 0, 0);
+      if (bcol) x = __ldg(reinterpret_cast<const uint4*>(bcol + col));
+      const uint32_t a01 = round_bf16_pair(e4m3x2_to_h2(w0.x & 0xffffu), rm0), a23 = round_bf16_pair(e4m3x2_to_h2(w0.x >> 16), rm0);
+      const uint32_t a45 = round_bf16_pair(e4m3x2_to_h2(w0.y & 0xffffu), rm0), a67 = round_bf16_pair(e4m3x2_to_h2(w0.y >> 16), rm0);
+      const uint32_t b01 = round_bf16_pair(e4m3x2_to_h2(w1.x & 0xffffu), rm1), b23 = round_bf16_pair(e4m3x2_to_h2(w1.x >> 16), rm1);
+      const uint32_t b45 = round_bf16_pair(e4m3x2_to_h2(w1.y & 0xffffu), rm1), b67 = round_bf16_pair(e4m3x2_to_h2(w1.y >> 16), rm1);
+      mma_f16(c, a01, b01, a23, b23, x.x, x.y);
+      mma_f16(c, a45, b45, a67, b67, x.z, x.w);
+    }
+    facc[0] += scalbnf(c[0] + c[1], -e0);
+    facc[1] += scalbnf(c[2] + c[3], -e1);
+  }
+}
+
 template <int FMT> struct GemvLayout;
 // kPitch: bytes of a row slot; kChunks: 16-byte copies per row slot and block; kExtra: bytes per stage behind
 // the 16 row slots (scale tile pieces).
 template <> struct GemvLayout<kGemvQ4K> { static constexpr int kPitch = 160, kStages = 3, kChunks = 9, kExtra = 0; };
 template <> struct GemvLayout<kGemvQ6KR> { static constexpr int kPitch = 240, kStages = 2, kChunks = 14, kExtra = 0; };      // 13 data chunks + the d chunk
 template <> struct GemvLayout<kGemvNvfp4Linear> { static constexpr int kPitch = 144, kStages = 3, kChunks = 9, kExtra = 0; };  // 8 code chunks + 1 scale chunk
+template <> struct GemvLayout<kGemvFp8Block> { static constexpr int kPitch = 272, kStages = 2, kChunks = 16, kExtra = 0; };       // 256 payload bytes per row slot
 template <> struct GemvLayout<kGemvNvfp4Tiled> { static constexpr int kPitch = 144, kStages = 3, kChunks = 8, kExtra = 256; };  // codes; 16 scale pieces per stage
 
 template <int FMT> __host__ __device__ constexpr int gemv_stage_bytes() { return 16 * GemvLayout<FMT>::kPitch + GemvLayout<FMT>::kExtra; }
@@ -350,6 +389,7 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
   float* red = reinterpret_cast<float*>(smem + kGemvWarps * LY::kStages * STAGE);   // [warp][token 4][row 16]
   constexpr int RPT = DUAL ? 8 : 16;                     // weight rows of matrix 0 per slab
   constexpr bool NV = FMT == kGemvNvfp4Linear || FMT == kGemvNvfp4Tiled;
+  constexpr bool NATURAL = NV || FMT == kGemvFp8Block;    // activation planes in natural column order
   const int tiles_per_group = (a.rows + RPT - 1) / RPT;
   const int nb_per = a.nblk / a.ks;
   const long long items = (long long)a.max_groups * tiles_per_group * a.ks;
@@ -386,6 +426,7 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
           else if (FMT == kGemvQ6KR) src = part < 13 ? base + b * 208 + part * 16 : base + a.nblk * 208 + ((2 * b) & ~15);
           else if (FMT == kGemvNvfp4Linear)
             src = part < 8 ? base + b * 128 + part * 16 : mbase[m] + a.scale_offset[m] + size_t(r) * (a.k / 16) + b * 16;
+          else if (FMT == kGemvFp8Block) src = base + b * 256 + part * 16;
           else src = base + b * 128 + part * 16;
           cp_async16(dst + slot * LY::kPitch + part * 16, src);
         }
@@ -422,6 +463,17 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
         gs0 = __ldg(reinterpret_cast<const float*>(a.gscale + size_t(e) * a.gscale_estride));
         if (DUAL) gs1 = __ldg(reinterpret_cast<const float*>(a.gscale + size_t(e) * a.gscale_estride + a.gscale_mstride));
       }
+    }
+    // block-FP8: the scale rows of this lane's two weight rows (rows g and g + 8 of the slab)
+    const float *fsc0 = nullptr, *fsc1 = nullptr;
+    if (FMT == kGemvFp8Block && live) {
+      const int kb128 = a.k / 128;
+      const int ra = slab_row<FMT, DUAL>(slab_u, DUAL ? g4 : g4), rb = slab_row<FMT, DUAL>(slab_u, DUAL ? g4 : g4 + 8);
+      const int ma = 0, mb = DUAL ? 1 : 0;
+      const float* base_a = (e < 0 && a.scale_shared[ma]) ? a.scale_shared[ma] : reinterpret_cast<const float*>(mbase[ma] + a.scale_offset[ma]);
+      const float* base_b = (e < 0 && a.scale_shared[mb]) ? a.scale_shared[mb] : reinterpret_cast<const float*>(mbase[mb] + a.scale_offset[mb]);
+      fsc0 = base_a + size_t((ra < a.rows ? ra : 0) / 128) * kb128;
+      fsc1 = base_b + size_t((rb < a.rows ? rb : 0) / 128) * kb128;
     }
     // shared expert with bf16-rounded weights: A = bf16(code * scale * g) * 2^s, epilogue multiplier 2^-s
     float rm0 = 0.f, rm1 = 0.f;
@@ -471,6 +523,7 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
         const __half* bcol = plane ? plane + b * 256 : nullptr;
         if (FMT == kGemvQ4K) q4k_block_f16<LY::kPitch, MINS_TILE>(slab, lane, bcol, xs ? xs + b * 8 : nullptr, facc);
         else if (FMT == kGemvQ6KR) q6k_block_f16<LY::kPitch>(slab, lane, (2 * b) & 15, bcol, facc);
+        else if (FMT == kGemvFp8Block) fp8_block_f16<LY::kPitch>(slab, lane, bcol, fsc0 + 2 * b, fsc1 + 2 * b, facc);
         else if (rounded) nvfp4_block_f16<FMT, DUAL, LY::kPitch, true>(slab, lane, bcol, rm0, rm1, facc);
         else nvfp4_block_f16<FMT, DUAL, LY::kPitch, false>(slab, lane, bcol, 0.f, 0.f, facc);
         __syncwarp();
@@ -500,7 +553,7 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
             const float h = OUT == kOutHayateProduct ? hayate_swiglu(gv, uv) : silu_mul(gv, uv);
             const __half hi = __float2half_rn(h);
             const __half lo = __float2half_rn(h - __half2float(hi));
-            __half* dst = a.out_planes + size_t(ares) * 2 * a.rows + (NV ? r : plane_pos(r));
+            __half* dst = a.out_planes + size_t(ares) * 2 * a.rows + (NATURAL ? r : plane_pos(r));
             dst[0] = hi;
             dst[a.rows] = lo;
             if (OUT == kOutHayateProduct && a.out_bf16) a.out_bf16[size_t(ares) * a.rows + r] = __float2bfloat16_rn(h);

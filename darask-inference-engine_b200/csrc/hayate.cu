@@ -115,6 +115,14 @@ static cudaError_t launch_hayate_gemv(bool dual, GemvArgs a, int n, int k, cudaS
   return dual ? launch_gemv<kGemvNvfp4Tiled, 1, false, kOutHayateProduct>(a, st) : launch_gemv<kGemvNvfp4Tiled, 0, false, kOutBf16>(a, st);
 }
 
+// the same over block-FP8 images: payload [n][k] e4m3, float32 scales [n/128][k/128] right behind it
+// (decode.cu:32-36 `routed`: scale = w + n*k); the shared expert's scales come with its DenseWeight
+static cudaError_t launch_hayate_gemv_fp8(bool dual, GemvArgs a, int n, int k, cudaStream_t st) {
+  a.row_bytes = k; a.k = k; a.rows = n; a.nblk = k / 256;
+  a.scale_offset[0] = a.scale_offset[1] = (unsigned long long)n * k;
+  return dual ? launch_gemv<kGemvFp8Block, 1, false, kOutHayateProduct>(a, st) : launch_gemv<kGemvFp8Block, 0, false, kOutBf16>(a, st);
+}
+
 }  // namespace dmoe
 
 using namespace dmoe;
@@ -199,7 +207,9 @@ extern "C" int hayate_glm_moe_gate_up(void* out, const void* x, const void* orig
                                       HayateDenseWeight gate, HayateDenseWeight up, int nv, int down_fp8, size_t stride,
                                       cudaStream_t st) {
   if (!out || !x || !original || !images || !gate.data || !up.data || !stride || !g_shape.ws) return cudaErrorInvalidValue;
-  if (!nv || gate.format != 3 || up.format != 3) return cudaErrorInvalidValue;      // only NVFP4 images are built here
+  // routed and shared expert in one launch: both NVFP4 (nv, format 3) or both block-FP8 (!nv, format 1 with scales)
+  const bool fp8 = !nv;
+  if (fp8 ? (gate.format != 1 || up.format != 1 || !gate.scale || !up.scale) : (gate.format != 3 || up.format != 3)) return cudaErrorInvalidValue;
   (void)down_fp8;
   const int H = g_shape.hidden, F = g_shape.inter, K = g_shape.topk;
   const HayateWs ws = carve(g_shape.ws, H, F, g_shape.experts, K, 1);
@@ -215,13 +225,18 @@ extern "C" int hayate_glm_moe_gate_up(void* out, const void* x, const void* orig
   a.counters = ws.counters + 2; a.plan = ws.plan; a.assignments = ws.assignments;
   a.tokens = 1; a.topk = K; a.max_groups = K + 1;
   a.out_planes = ws.hplanes; a.out_bf16 = (__nv_bfloat16*)out; a.status = ws.status;
+  if (fp8) {
+    a.scale_shared[0] = static_cast<const float*>(gate.scale); a.scale_shared[1] = static_cast<const float*>(up.scale);
+    return launch_hayate_gemv_fp8(true, a, F, H, st);
+  }
   return launch_hayate_gemv(true, a, F, H, st);
 }
 
 extern "C" int hayate_glm_moe_down(void* out, const void* x, const void* images, HayateDenseWeight shared, int nv, int down_fp8,
                                    size_t stride, cudaStream_t st) {
   if (!out || !x || !images || !shared.data || !stride || !g_shape.ws) return cudaErrorInvalidValue;
-  if (!nv || down_fp8 || shared.format != 3) return cudaErrorInvalidValue;
+  const bool fp8 = !nv || down_fp8;     // the down matrices are block-FP8 (decode.cu:32-36)
+  if (fp8 ? (shared.format != 1 || !shared.scale) : shared.format != 3) return cudaErrorInvalidValue;
   const int H = g_shape.hidden, F = g_shape.inter, K = g_shape.topk;
   const HayateWs ws = carve(g_shape.ws, H, F, g_shape.experts, K, 1);
   cudaError_t e;
@@ -237,6 +252,10 @@ extern "C" int hayate_glm_moe_down(void* out, const void* x, const void* images,
   a.counters = ws.counters + 2; a.plan = ws.plan; a.assignments = ws.assignments;
   a.tokens = 1; a.topk = K; a.max_groups = K + 1;
   a.out_bf16 = (__nv_bfloat16*)out; a.status = ws.status;
+  if (fp8) {
+    a.scale_shared[0] = static_cast<const float*>(shared.scale);
+    return launch_hayate_gemv_fp8(false, a, H, F, st);
+  }
   return launch_hayate_gemv(false, a, H, F, st);
 }
 

@@ -196,6 +196,9 @@ int hayate_glm_route_batch(void* logits, void* weights, void* ids, const void* x
                            darask_stream_t stream);
 /* images: device array of top-k image pointers in route order; a null pointer leaves a zero row (the reference's
  * "computed on the CPU" slot).  out: bf16 [topk+1][inter], row topk = shared expert. */
+/* Image formats of the expert launchers: nv != 0: NVFP4 tiled images with the shared expert's DenseWeight.format == 3;
+ * nv == 0 (gate/up and down) or down_fp8 != 0 (down only): block-FP8 images (payload [n][k], float32 scales [n/128][k/128]
+ * right behind it, decode.cu:32-36) with the shared expert as format 1 {data, scale}.  Other combinations: cudaErrorInvalidValue. */
 int hayate_glm_moe_gate_up(void* out, const void* x, const void* original, const void* images, HayateDenseWeight gate,
                            HayateDenseWeight up, int nv, int down_fp8, size_t stride, darask_stream_t stream);
 int hayate_glm_moe_down(void* out, const void* x, const void* images, HayateDenseWeight shared, int nv, int down_fp8,

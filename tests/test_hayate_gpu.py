@@ -127,3 +127,87 @@ def test_reduction_order_golden():
     assert lib.hayate_glm_moe_reduce(out.data_ptr(), y_d.data_ptr(), ids_d.data_ptr(), w_d.data_ptr(), st) == 0
     torch.cuda.synchronize()
     assert np.array_equal(out.float().cpu().numpy(), expect)
+
+
+def fp8_image(rng, n, k):
+    """Block-FP8 matrix image as the reference lays it out (decode.cu:32-36): payload [n][k], then the float32 scales."""
+    payload, scale = F.fp8_block_quantize(W.normal(rng, (n, k), 0.02))
+    return payload, scale, np.concatenate([payload.reshape(-1), scale.reshape(-1).view(np.uint8)])
+
+
+@pytest.mark.parametrize("nv", [0, 1])
+def test_block_fp8_images(nv):
+    """nv = 0: gate, up and down of the routed and the shared expert are block-FP8; nv = 1 with down_fp8: NVFP4 gate/up,
+    block-FP8 down.  Weights are bf16(e4m3 * scale) as the reference's `scaled_fp8` forms them."""
+    import darask_inference_engine_b200 as D
+    lib = D._lib.lib()
+    H, Fi, E, K, scale = 1024, 512, 32, 4, 1.8
+    rng = W.rng_for(77 + nv)
+    dev, st = torch.device("cuda"), torch.cuda.current_stream().cuda_stream
+    assert lib.hayate_glm_moe_set_shape(H, Fi, E, K, scale) == 0
+    ws = torch.zeros(lib.hayate_glm_moe_workspace_bytes(H, Fi, E, K, 1), dtype=torch.uint8, device=dev)
+    assert lib.hayate_glm_moe_set_workspace(ws.data_ptr(), ws.numel(), st) == 0
+    stride = max(F.hayate_expert_stride(H, Fi), (H * Fi + (H // 128) * (Fi // 128) * 4 + 255) // 256 * 256)
+
+    def expert():
+        """-> (image bytes [3*stride], dense (gate, up, down) float64 as the kernels must see them)"""
+        img = np.zeros(3 * stride, np.uint8)
+        dense = []
+        for part, (n, k) in enumerate(((Fi, H), (Fi, H), (H, Fi))):
+            if nv and part < 2:
+                m = F.nvfp4_tiled_quantize(W.normal(rng, (n, k), 0.02))
+                dense.append(("nv", m, n, k))
+            else:
+                p, s, m = fp8_image(rng, n, k)
+                dense.append(("f8", (p, s), n, k))
+            img[part * stride:part * stride + m.size] = m
+        return img, dense
+
+    def mats(dense, rounded_nv):
+        out = []
+        for kind, m, n, k in dense:
+            out.append((F.nvfp4_tiled_decode(m, n, k, rounded=rounded_nv) if kind == "nv" else F.fp8_block_decode(m[0], m[1], rounded=True)).astype(np.float64))
+        return out
+
+    ids = rng.permutation(E)[:K].astype(np.int32)
+    weights = (rng.random(K, dtype=np.float32) + 0.1).astype(np.float32)
+    images = [expert() for _ in range(K)]
+    shared_img, shared_dense = expert()
+    x = F.bf16_round(W.normal(rng, (H,), 1.0))
+    # oracle (decode.cu:37-59)
+    xt = x.astype(np.float64)
+    ys = []
+    for img, dense in images + [(shared_img, shared_dense)]:
+        g, u, d = mats(dense, rounded_nv=dense is shared_dense)
+        p = L.hayate_swiglu(F.bf16_round((g @ xt).astype(np.float32)), F.bf16_round((u @ xt).astype(np.float32)))
+        ys.append(F.bf16_round((d @ p.astype(np.float64)).astype(np.float32)))
+    acc = np.zeros(H, np.float32)
+    for a in R.route_order(ids):
+        acc = F.bf16_round(acc + F.bf16_round((ys[a] * weights[a]).astype(np.float32)))
+    ref = F.bf16_round((acc + ys[K]).astype(np.float32))
+    # device
+    imgs_d = [torch.from_numpy(img).to(dev) for img, _ in images]
+    shared_d = torch.from_numpy(shared_img).to(dev)
+    table = torch.tensor([t.data_ptr() for t in imgs_d], dtype=torch.int64, device=dev)
+    DW = D._lib.HayateDenseWeight
+
+    def dw(part):
+        kind, m, n, k = shared_dense[part]
+        base = shared_d.data_ptr() + part * stride
+        return DW(base, None, 3) if kind == "nv" else DW(base, base + n * k, 1)
+
+    x_d = bf16_tensor(x[None]).to(dev)
+    product = torch.zeros(K + 1, Fi, dtype=torch.bfloat16, device=dev)
+    expert_out = torch.zeros(K + 1, H, dtype=torch.bfloat16, device=dev)
+    out = torch.zeros(H, dtype=torch.bfloat16, device=dev)
+    ids_d, w_d = torch.from_numpy(ids).to(dev), torch.from_numpy(weights).to(dev)
+    assert lib.hayate_glm_moe_gate_up(product.data_ptr(), x_d.data_ptr(), x_d.data_ptr(), table.data_ptr(), dw(0), dw(1), nv, 1 if nv else 0, stride, st) == 0
+    assert lib.hayate_glm_moe_down(expert_out.data_ptr(), product.data_ptr(), table.data_ptr(), dw(2), nv, 1 if nv else 0, stride, st) == 0
+    assert lib.hayate_glm_moe_reduce(out.data_ptr(), expert_out.data_ptr(), ids_d.data_ptr(), w_d.data_ptr(), st) == 0
+    torch.cuda.synchronize()
+    W.check_output(expert_out.float().cpu().numpy(), np.stack(ys), rel=4e-3, max_abs=2.0 ** -7)
+    W.check_output(out.float().cpu().numpy()[None], ref[None], rel=4e-3, max_abs=2.0 ** -7)
+    # formats that are not built answer like the reference answers bad arguments
+    assert lib.hayate_glm_moe_down(expert_out.data_ptr(), product.data_ptr(), table.data_ptr(), DW(shared_d.data_ptr(), None, 0), nv, 1, stride, st) == 1
+    assert lib.hayate_glm_moe_set_shape(4096, 2048, 288, 8, 2.5) == 0
+    assert lib.hayate_glm_moe_set_workspace(None, 0, st) == 0
