@@ -400,8 +400,10 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
     const int tile = int(item / a.ks), kpart = int(item % a.ks);
     const int grp = tile / tiles_per_group, slab_u = tile % tiles_per_group;
     const bool live = grp < groups;          // uniform over the ks warps of a slab (they share `tile`)
-    int4 pl = make_int4(0, 0, 0, 0);
-    if (live) pl = __ldcg(a.plan + grp);
+    // the plan array holds max_groups entries: the entry is fetched without waiting for the group count (two
+    // dependent L2 round trips less before the first weight request), stale entries are masked by `live`
+    int4 pl = __ldcg(a.plan + grp);
+    if (!live) pl = make_int4(0, 0, 0, 0);
     const int e = pl.x, count = live ? pl.y : 0, offset = pl.z;
     const int b_first = kpart * nb_per;
     // base of the two matrices of this group's expert
