@@ -62,6 +62,10 @@ struct GemvArgs {
   int shared_x_row0;            // x row of the shared expert's token t when rows are per token (default 0: the token's own row)
   int round_shared;             // NVFP4: the shared expert's weights are rounded to bf16 after scaling (Hayate)
   unsigned* status;
+  // 1: counters / plan / assignments were written by a kernel BEFORE the immediate predecessor in the stream (which
+  // itself waited for it), only the activation planes come from the predecessor: the dependency wait is then taken after
+  // the first weight requests are in flight instead of at kernel entry.
+  int late_wait;
 };
 
 constexpr int kGemvWarps = 24;
@@ -396,6 +400,7 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
   const int groups = __ldcg(a.counters);
   const int g4 = lane >> 2, j = lane & 3;
   const int shared_row0 = a.out_shared_row;
+  bool waited = !a.late_wait;
   for (long long item = (long long)blockIdx.x * kGemvWarps + warp; item < items; item += (long long)gridDim.x * kGemvWarps) {
     const int tile = int(item / a.ks), kpart = int(item % a.ks);
     const int grp = tile / tiles_per_group, slab_u = tile % tiles_per_group;
@@ -485,6 +490,10 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
       rm0 = scalbnf(gs0, s0); gs0 = scalbnf(1.f, -s0);
       rm1 = DUAL ? scalbnf(gs1, s1) : rm0;
       if (DUAL) gs1 = scalbnf(1.f, -s1);
+    }
+    if (!waited) {                                        // the activation planes of the predecessor are read from here on
+      pdl_wait();
+      waited = true;
     }
     for (int c0 = 0; c0 < count; c0 += 4) {               // up to four tokens of this group per pass
       // this lane's B column g4 -> token g4/2 of the pass, hi (even) or lo (odd) plane
@@ -578,9 +587,10 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
 template <int FMT, int DUAL, bool MINS_TILE, int OUT>
 __global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const GemvArgs a) {
   extern __shared__ __align__(128) uint8_t smem[];
-  pdl_wait();
+  if (!a.late_wait) pdl_wait();
   pdl_launch();
   gemv_items<FMT, DUAL, MINS_TILE, OUT>(a, smem);
+  if (a.late_wait) pdl_wait();       // warps without items: the grid must not finish before its predecessor
 }
 
 // ---- activation rows -> planes (and per-32 sums) ------------------------------------------------------

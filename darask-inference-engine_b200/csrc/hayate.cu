@@ -302,6 +302,7 @@ extern "C" int hayate_moe_layer(const HayateMoe* d, cudaStream_t st) {
   b.w[0] = images + 2 * d->stride; b.w[1] = nullptr;
   b.w_shared[0] = shared + 2 * d->stride; b.w_shared[1] = nullptr;
   b.xplanes = w.hplanes; b.x_by_assignment = 1; b.out_planes = nullptr; b.out_bf16 = w.y;
+  b.late_wait = 1;           // the plan is the router's (two launches back); only the products come from gate/up
   if ((e = launch_hayate_gemv(false, b, H, F, st))) return e;
   return launch_pdl(hayate_reduce_kernel, dim3((H + 255) / 256, T), dim3(256), 0, st, static_cast<__nv_bfloat16*>(d->out),
                     (const __nv_bfloat16*)w.y, (const int*)d->ids, (const float*)d->weights, H, K, T, T * K);

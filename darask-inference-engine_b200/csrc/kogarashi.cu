@@ -179,6 +179,7 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
   b.k = F; b.rows = H; b.nblk = F / 256;
   b.xplanes = w.hplanes; b.xsum32 = nullptr; b.x_by_assignment = 1;
   b.out_planes = nullptr; b.out = w.y;
+  b.late_wait = (mask & 2) ? 1 : 0;      // the plan is the router's, two launches back; only the products come from gate/up
   if ((mask & 4) && (e = launch_gemv_ggml<0>(d->down_ty, b, st))) return e;
 
   // 4. combine

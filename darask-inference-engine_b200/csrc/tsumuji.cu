@@ -248,6 +248,7 @@ extern "C" int tsumuji_moe_layer(const TsumujiMoe* d, cudaStream_t st) {
   b.row_bytes = F / 2; b.k = F; b.rows = H; b.nblk = F / 256;
   b.gscale = reinterpret_cast<const uint8_t*>(d->gs) + 8;
   b.xplanes = w.hplanes; b.x_by_assignment = 1; b.out_planes = nullptr; b.out = w.y;
+  b.late_wait = 1;           // the plan is the router's; the predecessor (shared gate/up) only adds product rows
   if ((e = launch_gemv<kGemvNvfp4Linear, 0, false, kOutFloat>(b, st))) return e;
   // shared down (dense bf16 [H][F])
   DenseArgs t = {};
