@@ -79,7 +79,8 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-static cudaError_t launch_grouped_bf16(void* out, float* acc, const void* x, const void* w, const void* ranges, unsigned groups,
+// also used by the Tsumuji token-window path (tsumuji.cu)
+cudaError_t launch_grouped_bf16(void* out, float* acc, const void* x, const void* w, const void* ranges, unsigned groups,
                                        unsigned n, unsigned k, const float* scales, cudaStream_t st) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return cudaErrorInvalidValue;

@@ -126,10 +126,53 @@ __global__ void __launch_bounds__(256) tsumuji_ep_combine_kernel(float* out, con
   out[size_t(n) * hidden + i] = accumulate ? out[size_t(n) * hidden + i] + o : o;
 }
 
+// ---- shared expert of a token window on the tensor cores ---------------------------------------------------------
+// hayate_prefill.cu: ragged grouped bf16 GEMM (tcgen05), float32 accumulator output
+cudaError_t launch_grouped_bf16(void* out, float* acc, const void* x, const void* w, const void* ranges, unsigned groups,
+                                unsigned n, unsigned k, const float* scales, cudaStream_t st);
+// float32 rows -> bf16 "hi" rows [0, N) and bf16 "lo" rows [N, 2N) with x = hi + lo up to 2^-17 |x|; one group of 2N rows
+__global__ void __launch_bounds__(256) split_rows_kernel(const float* x, int rows, int k, __nv_bfloat16* hl, unsigned* ranges) {
+  pdl_wait();
+  pdl_launch();
+  if (blockIdx.x == 0 && threadIdx.x == 0) { ranges[0] = 2u * unsigned(rows); ranges[1] = 0u; }
+  const size_t i = size_t(blockIdx.x) * 256 + threadIdx.x, total = size_t(rows) * k;
+  if (i >= total) return;
+  const float v = x[i];
+  const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+  hl[i] = hi;
+  hl[total + i] = __float2bfloat16_rn(v - __bfloat162float(hi));
+}
+// acc [2N][2F] (hi rows then lo rows; gate columns then up columns) -> h = silu(g) * u as bf16 hi/lo rows [2N][F]
+__global__ void __launch_bounds__(256) shared_swiglu_kernel(const float* acc, int rows, int inter, __nv_bfloat16* hl) {
+  pdl_wait();
+  pdl_launch();
+  const size_t i = size_t(blockIdx.x) * 256 + threadIdx.x, total = size_t(rows) * inter;
+  if (i >= total) return;
+  const size_t t = i / inter, c = i % inter;
+  const float* a0 = acc + t * 2 * inter;
+  const float* a1 = acc + (t + rows) * 2 * inter;
+  const float g = a0[c] + a1[c], u = a0[inter + c] + a1[inter + c];
+  const float h = silu_mul(g, u);
+  const __nv_bfloat16 hi = __float2bfloat16_rn(h);
+  hl[i] = hi;
+  hl[total + i] = __float2bfloat16_rn(h - __bfloat162float(hi));
+}
+// y[t] = acc[t] + acc[N + t]
+__global__ void __launch_bounds__(256) add_halves_kernel(const float* acc, int rows, int hidden, float* y) {
+  pdl_wait();
+  pdl_launch();
+  const size_t i = size_t(blockIdx.x) * 256 + threadIdx.x, total = size_t(rows) * hidden;
+  if (i < total) y[i] = acc[i] + acc[total + i];
+}
+
+constexpr int kWindowTokens = 16;      // more tokens than this: the batched front end and the tensor-core shared expert
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 struct TsumujiWs {
   int* counters; unsigned* done; unsigned* status; int* active; unsigned* ranges; unsigned* assignments; int4* plan;
-  __half* xplanes; __half* hplanes; float* y; int* perm_scratch; size_t bytes;
+  __half* xplanes; __half* hplanes; float* y; int* perm_scratch;
+  // token windows: operands of the shared expert's tensor-core products
+  unsigned* sh_ranges; __nv_bfloat16* sh_x; float* sh_acc; __nv_bfloat16* sh_out; __nv_bfloat16* sh_h;
+  size_t bytes;
 };
 static TsumujiWs carve(void* base, int hidden, int inter, int experts, int topk, int tokens) {
   TsumujiWs w;
@@ -148,6 +191,12 @@ static TsumujiWs carve(void* base, int hidden, int inter, int experts, int topk,
   w.hplanes = reinterpret_cast<__half*>(take(rows * 2 * inter * 2));
   w.y = reinterpret_cast<float*>(take(rows * hidden * 4));
   w.perm_scratch = reinterpret_cast<int*>(take(permute_scratch_bytes(tokens, topk, experts)));
+  const size_t wide = size_t(hidden > 2 * inter ? hidden : 2 * inter), win = tokens > kWindowTokens ? size_t(tokens) : 0;
+  w.sh_ranges = reinterpret_cast<unsigned*>(take(8));
+  w.sh_x = reinterpret_cast<__nv_bfloat16*>(take(2 * win * hidden * 2));
+  w.sh_acc = reinterpret_cast<float*>(take(2 * win * wide * 4));
+  w.sh_out = reinterpret_cast<__nv_bfloat16*>(take(2 * win * wide * 2));
+  w.sh_h = reinterpret_cast<__nv_bfloat16*>(take(2 * win * inter * 2));
   w.bytes = off;
   return w;
 }
@@ -169,6 +218,18 @@ static cudaError_t route_window(const void* router_w, const float* x, const Rout
   if ((e = launch_pdl(route_topk_kernel<kRouteTsumuji>, dim3((N + 3) / 4), dim3(128), 0, st, route))) return e;
   if ((e = launch_permute_large(perm, w.perm_scratch, st))) return e;
   return launch_pdl(act_planes_kernel<float>, dim3(N), dim3(128), 0, st, x, H, w.xplanes, (float*)nullptr, 1);
+}
+
+// shared expert of a window: y_out[t] = W_down . silu(W_gate . x[t]) * (W_up . x[t]), two tcgen05 bf16 GEMMs over the
+// hi / lo split of the float32 operands (exact bf16 weights, float32 accumulation)
+static cudaError_t shared_expert_window(const TsumujiMoe* d, const TsumujiWs& w, int N, int H, int F, float* y_out, cudaStream_t st) {
+  cudaError_t e;
+  const unsigned blocks_x = unsigned((size_t(N) * H + 255) / 256), blocks_h = unsigned((size_t(N) * F + 255) / 256);
+  if ((e = launch_pdl(split_rows_kernel, dim3(blocks_x), dim3(256), 0, st, d->x, N, H, w.sh_x, w.sh_ranges))) return e;
+  if ((e = launch_grouped_bf16(w.sh_out, w.sh_acc, w.sh_x, d->shared_gu, w.sh_ranges, 1, unsigned(2 * F), unsigned(H), nullptr, st))) return e;
+  if ((e = launch_pdl(shared_swiglu_kernel, dim3(blocks_h), dim3(256), 0, st, (const float*)w.sh_acc, N, F, w.sh_h))) return e;
+  if ((e = launch_grouped_bf16(w.sh_out, w.sh_acc, w.sh_h, d->shared_down, w.sh_ranges, 1, unsigned(H), unsigned(F), nullptr, st))) return e;
+  return launch_pdl(add_halves_kernel, dim3(blocks_x), dim3(256), 0, st, (const float*)w.sh_acc, N, H, y_out);
 }
 
 static int dense_k_split(int k, long long slabs) {
@@ -205,7 +266,7 @@ extern "C" int tsumuji_moe_layer(const TsumujiMoe* d, cudaStream_t st) {
   const RouteArgs route{d->rlogits, E + 1, E, K, N, nullptr, 1.f, d->sel, d->rw, d->shared_gate};
   const PermuteArgs perm{d->sel, N, K, E, w.assignments, w.ranges, w.active, w.counters, w.status, w.plan, 0};
   cudaError_t e;
-  if (N > 16) {
+  if (N > kWindowTokens) {
     if ((e = cudaMemsetAsync(w.counters, 0, 16, st))) return e;
     if ((e = route_window(d->router_w, d->x, route, perm, w, H, E, N, st))) return e;
   } else if (d->router_w) {
@@ -235,12 +296,17 @@ extern "C" int tsumuji_moe_layer(const TsumujiMoe* d, cudaStream_t st) {
   a.tokens = N; a.topk = K; a.max_groups = N * K < E ? N * K : E;
   a.out_planes = w.hplanes; a.status = w.status;
   if ((e = launch_gemv<kGemvNvfp4Linear, 1, false, kOutSiluPlanes>(a, st))) return e;
-  // shared gate/up (dense bf16 [2F][H])
-  DenseArgs s = {};
-  s.w[0] = static_cast<const __nv_bfloat16*>(d->shared_gu); s.w[1] = s.w[0] + size_t(F) * H;
-  s.k = H; s.rows = F; s.ks = dense_k_split(H, (F + 7) / 8);
-  s.xplanes = w.xplanes; s.x_row0 = 0; s.tokens = N; s.out_planes = w.hplanes; s.out_row0 = N * K;
-  if ((e = launch_pdl(dense_gemv_kernel<1>, dim3(sm_count()), dim3(kGemvWarps * 32), 0, st, s))) return e;
+  const bool window = N > kWindowTokens && H % 64 == 0 && F % 64 == 0;
+  if (window) {
+    if ((e = shared_expert_window(d, w, N, H, F, w.y + size_t(N) * K * H, st))) return e;
+  } else {
+    // shared gate/up (dense bf16 [2F][H])
+    DenseArgs s = {};
+    s.w[0] = static_cast<const __nv_bfloat16*>(d->shared_gu); s.w[1] = s.w[0] + size_t(F) * H;
+    s.k = H; s.rows = F; s.ks = dense_k_split(H, (F + 7) / 8);
+    s.xplanes = w.xplanes; s.x_row0 = 0; s.tokens = N; s.out_planes = w.hplanes; s.out_row0 = N * K;
+    if ((e = launch_pdl(dense_gemv_kernel<1>, dim3(sm_count()), dim3(kGemvWarps * 32), 0, st, s))) return e;
+  }
   // routed down
   GemvArgs b = a;
   b.w[0] = base + fh; b.w[1] = nullptr;
@@ -250,12 +316,14 @@ extern "C" int tsumuji_moe_layer(const TsumujiMoe* d, cudaStream_t st) {
   b.xplanes = w.hplanes; b.x_by_assignment = 1; b.out_planes = nullptr; b.out = w.y;
   b.late_wait = 1;           // the plan is the router's; the predecessor (shared gate/up) only adds product rows
   if ((e = launch_gemv<kGemvNvfp4Linear, 0, false, kOutFloat>(b, st))) return e;
-  // shared down (dense bf16 [H][F])
-  DenseArgs t = {};
-  t.w[0] = static_cast<const __nv_bfloat16*>(d->shared_down); t.w[1] = nullptr;
-  t.k = F; t.rows = H; t.ks = dense_k_split(F, (H + 15) / 16);
-  t.xplanes = w.hplanes; t.x_row0 = N * K; t.tokens = N; t.out = w.y; t.out_row0 = N * K;
-  if ((e = launch_pdl(dense_gemv_kernel<0>, dim3(sm_count()), dim3(kGemvWarps * 32), 0, st, t))) return e;
+  if (!window) {
+    // shared down (dense bf16 [H][F])
+    DenseArgs t = {};
+    t.w[0] = static_cast<const __nv_bfloat16*>(d->shared_down); t.w[1] = nullptr;
+    t.k = F; t.rows = H; t.ks = dense_k_split(F, (H + 15) / 16);
+    t.xplanes = w.hplanes; t.x_row0 = N * K; t.tokens = N; t.out = w.y; t.out_row0 = N * K;
+    if ((e = launch_pdl(dense_gemv_kernel<0>, dim3(sm_count()), dim3(kGemvWarps * 32), 0, st, t))) return e;
+  }
   return launch_pdl(tsumuji_combine_kernel, dim3((H + 255) / 256, N), dim3(256), 0, st, d->out, (const float*)w.y,
                     (const float*)d->rw, (const float*)d->shared_gate, H, K, N, d->accumulate);
 }
@@ -289,7 +357,7 @@ extern "C" int tsumuji_ep_dispatch(const TsumujiMoe* d, float* send_x, unsigned*
   cudaError_t e;
   const RouteArgs route{d->rlogits, E + 1, E, K, N, nullptr, 1.f, d->sel, d->rw, d->shared_gate};
   const PermuteArgs perm{d->sel, N, K, E, w.assignments, ranges, w.active, w.counters, w.status, w.plan, 0};
-  if (N > 16) {
+  if (N > kWindowTokens) {
     if ((e = cudaMemsetAsync(w.counters, 0, 16, st))) return e;
     if ((e = route_window(d->router_w, d->x, route, perm, w, H, E, N, st))) return e;
   } else {
@@ -304,6 +372,7 @@ extern "C" int tsumuji_ep_dispatch(const TsumujiMoe* d, float* send_x, unsigned*
   if ((e = launch_pdl(tsumuji_gather_kernel, dim3(N * K), dim3(256), 0, st, d->x, (const unsigned*)w.assignments, (const int*)w.counters, K,
                       H, send_x, position))) return e;
   // the shared expert stays on the home rank (dense bf16), its rows go straight to y_shared
+  if (N > kWindowTokens && H % 64 == 0 && F % 64 == 0) return shared_expert_window(d, w, N, H, F, y_shared, st);
   DenseArgs s = {};
   s.w[0] = static_cast<const __nv_bfloat16*>(d->shared_gu); s.w[1] = s.w[0] + size_t(F) * H;
   s.k = H; s.rows = F; s.ks = dense_k_split(H, (F + 7) / 8);
