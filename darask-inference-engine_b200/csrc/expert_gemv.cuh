@@ -49,7 +49,7 @@ struct GemvArgs {
   int k, rows, nblk;            // columns, rows per matrix, k / 256
   int ks;                       // warps that split K for one row slab (divides nblk and the warps per CTA)
   const __half* xplanes;        // [x rows][2][k] activation planes
-  const float* xsum32;          // [x rows][k/32] sums of x over 32 columns (Q4_K mins); null: use tiles
+  const __half* xsum_planes;    // [x rows][2][k/32] sums of x over 32 columns as fp16 hi / lo planes (Q4_K mins); null: use tiles
   int x_by_assignment;          // 0: x row = token; 1: x row = assignment index
   const int* counters;          // [0] = number of groups (active experts, plus the shared expert)
   const int4* plan;             // per group {expert (-1: shared), rows, offset into assignments, 0}
@@ -68,7 +68,10 @@ struct GemvArgs {
   int late_wait;
 };
 
-constexpr int kGemvWarps = 24;
+#ifndef DMOE_GEMV_WARPS
+#define DMOE_GEMV_WARPS 24
+#endif
+constexpr int kGemvWarps = DMOE_GEMV_WARPS;
 
 DEVI void cp_async16(uint32_t dst, const void* src) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -99,7 +102,7 @@ DEVI int plane_pos(int e) { return (e & ~3) | ((e & 1) << 1) | ((e >> 1) & 1); }
 // value = d*sc*q - dmin*m (kogarashi kernels/native.cu:26-34). `bcol`: this lane's B plane (column
 // g = lane/4 -> token g/2, hi or lo) at the block's first column, or null for an empty column.
 template <int PITCH, bool MINS_TILE>
-DEVI void q4k_block_f16(uint32_t slab, int lane, const __half* bcol, const float* xsum, float (&facc)[2]) {
+DEVI void q4k_block_f16(uint32_t slab, int lane, const __half* bcol, const __half* xsum, float (&facc)[2]) {
   const int g = lane >> 2, j = lane & 3;
   const uint32_t r0 = slab + g * PITCH, r1 = slab + (g + 8) * PITCH;
   const uint4 h0 = lds128(r0), h1 = lds128(r1);
@@ -163,17 +166,16 @@ DEVI void q4k_block_f16(uint32_t slab, int lane, const __half* bcol, const float
   if (MINS_TILE) {
     m0 = cm[0] + cm[1];
     m1 = cm[2] + cm[3];
-  } else if (xsum) {
-    const float4 s0 = __ldg(reinterpret_cast<const float4*>(xsum)), s1 = __ldg(reinterpret_cast<const float4*>(xsum) + 1);
-    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      const uint32_t wa = mn0[q >> 2], wb = mn1[q >> 2];
-      const float fa = (q & 3) == 0 ? byte_magic<0>(wa) : (q & 3) == 1 ? byte_magic<1>(wa) : (q & 3) == 2 ? byte_magic<2>(wa) : byte_magic<3>(wa);
-      const float fb = (q & 3) == 0 ? byte_magic<0>(wb) : (q & 3) == 1 ? byte_magic<1>(wb) : (q & 3) == 2 ? byte_magic<2>(wb) : byte_magic<3>(wb);
-      m0 = fmaf(fa - kMagic, sv[q], m0);
-      m1 = fmaf(fb - kMagic, sv[q], m1);
-    }
+  } else {
+    // one tile for the mins of the whole block: A = the eight mins of rows g / g + 8 in k slots 0-7 (this lane: slots
+    // 2j, 2j + 1), B = the eight per-32 sums of this lane's column (`xsum`: its hi or lo plane at the block, or null)
+    const __half2 q0 = __hsub2(u32_as_h2(__byte_perm((j & 2) ? mn0[1] : mn0[0], 0x64646464u, (j & 1) ? 0x4342 : 0x4140)), k1024);
+    const __half2 q1 = __hsub2(u32_as_h2(__byte_perm((j & 2) ? mn1[1] : mn1[0], 0x64646464u, (j & 1) ? 0x4342 : 0x4140)), k1024);
+    uint32_t xs2 = 0;
+    if (xsum) xs2 = __ldg(reinterpret_cast<const uint32_t*>(xsum) + j);
+    mma_f16(cm, h2_as_u32(q0), h2_as_u32(q1), 0u, 0u, xs2, 0u);
+    m0 = cm[0] + cm[1];
+    m1 = cm[2] + cm[3];
   }
   facc[0] += d0 * (c[0] + c[1]) - dm0 * m0;
   facc[1] += d1 * (c[2] + c[3]) - dm1 * m1;
@@ -346,32 +348,45 @@ DEVI void fp8_block_f16(uint32_t slab, int lane, const __half* bcol, const float
   }
 }
 
+// ring depth of a warp: as many stages of `stage_bytes` as fit beside the other warps' rings (2 to 5)
+constexpr int gemv_ring_stages(int stage_bytes) {
+  const int s = (208 * 1024) / (kGemvWarps * stage_bytes);
+  return s > 5 ? 5 : (s < 2 ? 2 : s);
+}
 template <int FMT> struct GemvLayout;
-// kPitch: bytes of a row slot; kChunks: 16-byte copies per row slot and block; kExtra: bytes per stage behind
-// the 16 row slots (scale tile pieces).
-template <> struct GemvLayout<kGemvQ4K> { static constexpr int kPitch = 160, kStages = 3, kChunks = 9, kExtra = 0; };
-template <> struct GemvLayout<kGemvQ6KR> { static constexpr int kPitch = 240, kStages = 2, kChunks = 14, kExtra = 0; };      // 13 data chunks + the d chunk
-template <> struct GemvLayout<kGemvNvfp4Linear> { static constexpr int kPitch = 144, kStages = 3, kChunks = 9, kExtra = 0; };  // 8 code chunks + 1 scale chunk
-template <> struct GemvLayout<kGemvFp8Block> { static constexpr int kPitch = 272, kStages = 2, kChunks = 16, kExtra = 0; };       // 256 payload bytes per row slot
-template <> struct GemvLayout<kGemvNvfp4Tiled> { static constexpr int kPitch = 144, kStages = 3, kChunks = 8, kExtra = 256; };  // codes; 16 scale pieces per stage
+// kPitch: bytes of a row slot; kChunks: 16-byte copies per row slot and block that are contiguous in global memory
+// (kBlk bytes per block and row); kExtra: bytes per stage behind the 16 row slots (scale tile pieces). Formats with
+// one more chunk per row slot that lives elsewhere (the Q6_K block scale d, the linear NVFP4 scales) copy it with
+// lanes 0-15 (one row slot each).
+template <> struct GemvLayout<kGemvQ4K> { static constexpr int kPitch = 160, kStages = gemv_ring_stages(16 * 160 + 0), kChunks = 9, kBlk = 144, kExtra = 0; };
+template <> struct GemvLayout<kGemvQ6KR> { static constexpr int kPitch = 240, kStages = gemv_ring_stages(16 * 240 + 0), kChunks = 13, kBlk = 208, kExtra = 0; };       // + the d chunk at 208
+template <> struct GemvLayout<kGemvNvfp4Linear> { static constexpr int kPitch = 144, kStages = gemv_ring_stages(16 * 144 + 0), kChunks = 8, kBlk = 128, kExtra = 0; }; // + the scale chunk at 128
+template <> struct GemvLayout<kGemvFp8Block> { static constexpr int kPitch = 272, kStages = gemv_ring_stages(16 * 272 + 0), kChunks = 16, kBlk = 256, kExtra = 0; };   // 256 payload bytes per row slot
+template <> struct GemvLayout<kGemvNvfp4Tiled> { static constexpr int kPitch = 144, kStages = gemv_ring_stages(16 * 144 + 256), kChunks = 8, kBlk = 128, kExtra = 256; }; // codes; 16 scale pieces per stage
 
 template <int FMT> __host__ __device__ constexpr int gemv_stage_bytes() { return 16 * GemvLayout<FMT>::kPitch + GemvLayout<FMT>::kExtra; }
 template <int FMT> __host__ __device__ constexpr int gemv_smem_bytes() {
   return kGemvWarps * GemvLayout<FMT>::kStages * gemv_stage_bytes<FMT>() + kGemvWarps * 4 * 16 * 4 + 16;
 }
 
-// Weight row of matrix-0 row slot `s` of slab `u` (rows are slabs of RPT consecutive rows, except for the tiled
-// NVFP4 layout where a slab takes 16 / RPT... base rows of a 128-row tile in all four 32-row quarters, so that
-// the 16-byte pieces of the scale tiles are used completely).
+// Weight row of matrix-0 row slot `s` of slab `u` = slab_row0(u) + slab_rowc(s). Rows are slabs of RPT consecutive
+// rows, except for the tiled NVFP4 layout where a slab takes 16 / RPT... base rows of a 128-row tile in all four
+// 32-row quarters, so that the 16-byte pieces of the scale tiles are used completely.
 template <int FMT, int DUAL>
-DEVI int slab_row(int u, int s) {
+DEVI int slab_row0(int u) {
   constexpr int RPT = DUAL ? 8 : 16;
-  if (FMT != kGemvNvfp4Tiled) return u * RPT + s;
+  if (FMT != kGemvNvfp4Tiled) return u * RPT;
   constexpr int per128 = 128 / RPT;                 // slabs per 128-row tile
-  const int t128 = u / per128, ul = u % per128;
-  const int pl = DUAL ? (s & 1) : (s & 3), q = DUAL ? (s >> 1) : (s >> 2);
-  return t128 * 128 + q * 32 + ul * (RPT / 4) + pl;
+  return (u / per128) * 128 + (u % per128) * (RPT / 4);
 }
+template <int FMT, int DUAL>
+DEVI int slab_rowc(int s) {
+  if (FMT != kGemvNvfp4Tiled) return s;
+  const int pl = DUAL ? (s & 1) : (s & 3), q = DUAL ? (s >> 1) : (s >> 2);
+  return q * 32 + pl;
+}
+template <int FMT, int DUAL>
+DEVI int slab_row(int u, int s) { return slab_row0<FMT, DUAL>(u) + slab_rowc<FMT, DUAL>(s); }
 
 // Hayate SwiGLU: inputs rounded to bf16, gate <= 10, up in [-10, 10], bf16(bf16(g * sigmoid(g)) * u)
 // (hayate cu/glm53/math.cuh:31-34, decode.cu:46).
@@ -394,23 +409,52 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
   constexpr int RPT = DUAL ? 8 : 16;                     // weight rows of matrix 0 per slab
   constexpr bool NV = FMT == kGemvNvfp4Linear || FMT == kGemvNvfp4Tiled;
   constexpr bool NATURAL = NV || FMT == kGemvFp8Block;    // activation planes in natural column order
-  const int tiles_per_group = (a.rows + RPT - 1) / RPT;
+  const unsigned tiles_per_group = (a.rows + RPT - 1) / RPT;
   const int nb_per = a.nblk / a.ks;
-  const long long items = (long long)a.max_groups * tiles_per_group * a.ks;
   const int groups = __ldcg(a.counters);
   const int g4 = lane >> 2, j = lane & 3;
   const int shared_row0 = a.out_shared_row;
   bool waited = !a.late_wait;
-  for (long long item = (long long)blockIdx.x * kGemvWarps + warp; item < items; item += (long long)gridDim.x * kGemvWarps) {
-    const int tile = int(item / a.ks), kpart = int(item % a.ks);
-    const int grp = tile / tiles_per_group, slab_u = tile % tiles_per_group;
-    const bool live = grp < groups;          // uniform over the ks warps of a slab (they share `tile`)
+  // ---- this lane's share of a stage: fixed for the whole launch -------------------------------------------
+  // The contiguous chunks of a block: LW lanes copy the NR row slots of one matrix (DUAL: lanes 0-15 the gate
+  // slots 0-7, lanes 16-31 the up slots 8-15). Chunk cm = lane % LW + LW * i -> (row slot, 16-byte part).
+  constexpr int LW = DUAL ? 16 : 32, NR = DUAL ? 8 : 16;
+  constexpr int NI = (NR * LY::kChunks + LW - 1) / LW;
+  const int lm = DUAL ? (lane >> 4) : 0, ll = lane & (LW - 1);
+  uint32_t src_c[NI], dst_c[NI];             // byte offsets from the slab's first row / from the stage
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    const int cm = ll + LW * i;
+    const int slot = cm / LY::kChunks, part = cm - slot * LY::kChunks;
+    dst_c[i] = (lm * 8 + slot) * LY::kPitch + part * 16;
+    src_c[i] = cm < NR * LY::kChunks ? uint32_t(slab_rowc<FMT, DUAL>(slot)) * uint32_t(a.row_bytes) + part * 16 : 0xffffffffu;
+  }
+  // lanes 0-15: the row slot whose extra chunk (Q6_K d, linear NVFP4 scales) or scale piece (tiled NVFP4) they copy
+  const int xm = DUAL ? (lane >> 3) & 1 : 0, xs8 = DUAL ? (lane & 7) : (lane & 15);
+  // ---- items: (group, slab, K part); the ks warps of a slab are neighbours in the CTA ------------------------
+  const unsigned ks = a.ks;
+  const unsigned w0 = blockIdx.x * kGemvWarps + warp;
+  const unsigned tile0 = w0 / ks;
+  const int kpart = int(w0 - tile0 * ks);
+  const unsigned tstep = gridDim.x * (kGemvWarps / ks);
+  unsigned grp = tile0 / tiles_per_group, slab_u = tile0 - grp * tiles_per_group;
+  const unsigned gstep = tstep / tiles_per_group, sstep = tstep - gstep * tiles_per_group;
+  const int b_first = kpart * nb_per;
+  auto next_item = [&]() {                   // tile += tstep, without a division
+    slab_u += sstep;
+    grp += gstep;
+    if (slab_u >= tiles_per_group) {
+      slab_u -= tiles_per_group;
+      ++grp;
+    }
+  };
+  for (; grp < unsigned(a.max_groups); next_item()) {
+    const bool live = int(grp) < groups;     // uniform over the ks warps of a slab
     // the plan array holds max_groups entries: the entry is fetched without waiting for the group count (two
     // dependent L2 round trips less before the first weight request), stale entries are masked by `live`
     int4 pl = __ldcg(a.plan + grp);
     if (!live) pl = make_int4(0, 0, 0, 0);
     const int e = pl.x, count = live ? pl.y : 0, offset = pl.z;
-    const int b_first = kpart * nb_per;
     // base of the two matrices of this group's expert
     const uint8_t* mbase[2];
 #pragma unroll
@@ -420,40 +464,46 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
       else mbase[m] = a.w[m] ? a.w[m] + size_t(e) * a.expert_stride[m] : nullptr;
     }
     // ---- weight stream: 16 row slots x one block per stage --------------------------------------------
-    auto issue = [&](int b, int stage) {
-      const uint32_t dst = ring + stage * STAGE;
-      for (int c = lane; c < 16 * LY::kChunks; c += 32) {
-        const int slot = c / LY::kChunks, part = c % LY::kChunks;
-        const int m = DUAL ? (slot >> 3) : 0, s8 = DUAL ? (slot & 7) : slot;
-        const int r = slab_row<FMT, DUAL>(slab_u, s8);
-        if (r < a.rows) {
-          const uint8_t* base = mbase[m] + size_t(r) * a.row_bytes;
-          const uint8_t* src;
-          if (FMT == kGemvQ4K) src = base + b * 144 + part * 16;
-          else if (FMT == kGemvQ6KR) src = part < 13 ? base + b * 208 + part * 16 : base + a.nblk * 208 + ((2 * b) & ~15);
-          else if (FMT == kGemvNvfp4Linear)
-            src = part < 8 ? base + b * 128 + part * 16 : mbase[m] + a.scale_offset[m] + size_t(r) * (a.k / 16) + b * 16;
-          else if (FMT == kGemvFp8Block) src = base + b * 256 + part * 16;
-          else src = base + b * 128 + part * 16;
-          cp_async16(dst + slot * LY::kPitch + part * 16, src);
-        }
-      }
-      if (FMT == kGemvNvfp4Tiled && lane < 16) {
+    const int row0 = slab_row0<FMT, DUAL>(int(slab_u));
+    // bytes of the slab's rows that exist (row slots past the last row of the matrix are not copied)
+    const uint32_t live_bytes = FMT == kGemvNvfp4Tiled ? 0xfffffffeu : uint32_t(min(a.rows - row0, NR)) * uint32_t(a.row_bytes);
+    const uint8_t* lane_rows = mbase[lm] + size_t(row0) * a.row_bytes + size_t(b_first) * LY::kBlk;
+    // extra chunk / scale pieces: source of block b_first (lanes 0-15)
+    const uint8_t* extra = nullptr;
+    if (lane < 16) {
+      if (FMT == kGemvQ6KR) {
+        const int r = row0 + xs8;
+        if (r < a.rows) extra = mbase[xm] + size_t(r) * a.row_bytes + a.nblk * 208;
+      } else if (FMT == kGemvNvfp4Linear) {
+        const int r = row0 + xs8;
+        if (r < a.rows) extra = mbase[xm] + a.scale_offset[xm] + size_t(r) * (a.k / 16) + b_first * 16;
+      } else if (FMT == kGemvNvfp4Tiled) {
         // scale tile pieces: piece = (matrix, local base row) x 4 tile columns; 16 bytes each
         const int piece = lane, tc = piece & 3, pm = piece >> 2;
         const int m = DUAL ? (pm >> 1) : 0, pl_ = DUAL ? (pm & 1) : pm;
-        const int r = slab_row<FMT, DUAL>(slab_u, pl_);                 // quarter 0 row of this base row
-        if (r < a.rows) {
-          const int cols = (a.k / 16 + 3) / 4 * 4;
-          const uint8_t* src = mbase[m] + a.scale_offset[m] + (size_t(r / 128) * (cols / 4) + (b * 4 + tc)) * 512 + (r % 32) * 16;
-          cp_async16(dst + 16 * LY::kPitch + piece * 16, src);
-        }
+        const int r = slab_row<FMT, DUAL>(int(slab_u), pl_);               // quarter 0 row of this base row
+        const int cols = (a.k / 16 + 3) / 4 * 4;
+        if (r < a.rows) extra = mbase[m] + a.scale_offset[m] + (size_t(r / 128) * (cols / 4) + (b_first * 4 + tc)) * 512 + (r % 32) * 16;
+      }
+    }
+    auto issue = [&](int i_blk, int stage) {              // block b_first + i_blk of this item
+      const uint32_t dst = ring + stage * STAGE;
+      const uint8_t* src = lane_rows + i_blk * LY::kBlk;
+#pragma unroll
+      for (int i = 0; i < NI; ++i)
+        if (src_c[i] < live_bytes) cp_async16(dst + dst_c[i], src + src_c[i]);
+      if (FMT == kGemvQ6KR) {
+        if (extra) cp_async16(dst + lane * LY::kPitch + 208, extra + ((2 * (b_first + i_blk)) & ~15));
+      } else if (FMT == kGemvNvfp4Linear) {
+        if (extra) cp_async16(dst + lane * LY::kPitch + 128, extra + i_blk * 16);
+      } else if (FMT == kGemvNvfp4Tiled) {
+        if (extra) cp_async16(dst + 16 * LY::kPitch + lane * 16, extra + i_blk * 2048);
       }
     };
     if (count > 0) {
 #pragma unroll
       for (int s = 0; s < LY::kStages - 1; ++s) {
-        if (s < nb_per) issue(b_first + s, s);
+        if (s < nb_per) issue(s, s);
         cp_async_commit();
       }
     }
@@ -499,33 +549,28 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
       // this lane's B column g4 -> token g4/2 of the pass, hi (even) or lo (odd) plane
       const int tcol = c0 + (g4 >> 1);
       const __half* plane = nullptr;
-      const float* xs = nullptr;
+      const __half* xs = nullptr;
       if (tcol < count) {
         const int as = e < 0 ? shared_row0 + tcol : int(__ldcg(a.assignments + offset + tcol));
         const int xrow = a.x_by_assignment ? as : (e < 0 ? a.shared_x_row0 + tcol : as / a.topk);
         plane = a.xplanes + (size_t(xrow) * 2 + (g4 & 1)) * a.k;
+        if (FMT == kGemvQ4K && !MINS_TILE && a.xsum_planes) xs = a.xsum_planes + (size_t(xrow) * 2 + (g4 & 1)) * (a.k / 32);
       }
       // this lane's result column pair 2j,2j+1 -> token j of the pass
       const int tres = c0 + j;
       int ares = -1;
-      if (tres < count) {
-        ares = e < 0 ? shared_row0 + tres : int(__ldcg(a.assignments + offset + tres));
-        if (FMT == kGemvQ4K && !MINS_TILE && a.xsum32) {
-          const int xrow = a.x_by_assignment ? ares : (e < 0 ? tres : ares / a.topk);
-          xs = a.xsum32 + size_t(xrow) * (a.k / 32);
-        }
-      }
+      if (tres < count) ares = e < 0 ? shared_row0 + tres : int(__ldcg(a.assignments + offset + tres));
       if (c0 > 0) {                                       // later passes stream the blocks again (L2 hits)
 #pragma unroll
         for (int s = 0; s < LY::kStages - 1; ++s) {
-          if (s < nb_per) issue(b_first + s, s);
+          if (s < nb_per) issue(s, s);
           cp_async_commit();
         }
       }
       float facc[2] = {0.f, 0.f};
       for (int i = 0; i < nb_per; ++i) {
         const int nxt = i + LY::kStages - 1;
-        if (nxt < nb_per) issue(b_first + nxt, nxt % LY::kStages);
+        if (nxt < nb_per) issue(nxt, nxt % LY::kStages);
         cp_async_commit();
         cp_async_wait<LY::kStages - 1>();
         __syncwarp();
@@ -597,7 +642,7 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const G
 // One block per row. planes[row] = k fp16 hi values then k fp16 lo values, groups of four as [x0,x2,x1,x3]
 // (or in natural order for the NVFP4 kernels).
 template <typename XT>
-DEVI void act_planes_row(const XT* x, int k, __half* planes, float* xsum32, bool natural) {
+DEVI void act_planes_row(const XT* x, int k, __half* planes, __half* xsum_planes, bool natural) {
   for (int base = 0; base < k / 4; base += blockDim.x) {            // uniform trip count: shuffles below
     const int i = base + threadIdx.x;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -621,12 +666,16 @@ DEVI void act_planes_row(const XT* x, int k, __half* planes, float* xsum32, bool
       *reinterpret_cast<uint2*>(planes + 4 * i) = make_uint2(h2_as_u32(__halves2half2(hi[0], hi[1])), h2_as_u32(__halves2half2(hi[2], hi[3])));
       *reinterpret_cast<uint2*>(planes + k + 4 * i) = make_uint2(h2_as_u32(__halves2half2(lo[0], lo[1])), h2_as_u32(__halves2half2(lo[2], lo[3])));
     }
-    if (xsum32) {
+    if (xsum_planes) {
       float p = (v.x + v.y) + (v.z + v.w);
       p += __shfl_xor_sync(0xffffffffu, p, 1);
       p += __shfl_xor_sync(0xffffffffu, p, 2);
       p += __shfl_xor_sync(0xffffffffu, p, 4);
-      if (i < k / 4 && (i & 7) == 0) xsum32[i >> 3] = p;
+      if (i < k / 4 && (i & 7) == 0) {
+        const __half hs = __float2half_rn(p);
+        xsum_planes[i >> 3] = hs;
+        xsum_planes[k / 32 + (i >> 3)] = __float2half_rn(p - __half2float(hs));
+      }
     }
   }
 }

@@ -22,6 +22,7 @@ inline cudaError_t launch_gemv(GemvArgs a, cudaStream_t stream) {
   constexpr int RPT = DUAL ? 8 : 16;
   const long long slabs = (long long)a.max_groups * ((a.rows + RPT - 1) / RPT);
   a.ks = gemv_k_split(a.nblk, slabs, sm_count());
+  if (slabs * a.ks >= (1ll << 31)) return cudaErrorInvalidValue;       // the kernel counts items in 32 bits
   if (a.out_shared_row == 0) a.out_shared_row = a.tokens * a.topk;
   if (FMT == kGemvNvfp4Tiled && a.rows % 128) return cudaErrorInvalidValue;
   const int smem = gemv_smem_bytes<FMT>();

@@ -52,7 +52,7 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct KogarashiWs {
   int* counters; unsigned* done; unsigned* status; int* active; unsigned* ranges; unsigned* assignments;
-  int4* plan; float* sg; __half* xplanes; float* xsum32; __half* hplanes; float* y; size_t bytes;
+  int4* plan; float* sg; __half* xplanes; __half* xsum_planes; __half* hplanes; float* y; size_t bytes;
 };
 static KogarashiWs carve(void* base, int hidden, int inter, int experts, int topk, int tokens) {
   KogarashiWs w;
@@ -68,7 +68,7 @@ static KogarashiWs carve(void* base, int hidden, int inter, int experts, int top
   w.plan = reinterpret_cast<int4*>(take(size_t(experts + 1) * 16));
   w.sg = reinterpret_cast<float*>(take(size_t(tokens) * 4));
   w.xplanes = reinterpret_cast<__half*>(take(size_t(tokens) * 2 * hidden * 2));
-  w.xsum32 = reinterpret_cast<float*>(take(size_t(tokens) * (hidden / 32) * 4));
+  w.xsum_planes = reinterpret_cast<__half*>(take(size_t(tokens) * (hidden / 32) * 4));
   const size_t rows = size_t(tokens) * topk + tokens;
   w.hplanes = reinterpret_cast<__half*>(take(rows * 2 * inter * 2));
   w.y = reinterpret_cast<float*>(take(rows * hidden * 4));
@@ -144,7 +144,7 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
   r.route = RouteArgs{d->logits, E, E, K, T, nullptr, 1.f, d->ids, d->prob, nullptr};
   r.perm = PermuteArgs{d->ids, T, K, E, w.assignments, w.ranges, w.active, w.counters, w.status, w.plan, shared ? T : 0};
   r.done = w.done; r.fuse = 1;
-  r.planes = w.xplanes; r.xsum32 = w.xsum32;
+  r.planes = w.xplanes; r.xsum_planes = w.xsum_planes;
   const int rblocks = E + (shared ? 1 : 0) + T;
   const size_t hist = size_t(E + 1) * 4 + size_t(T * K <= kRouteIdCache ? T * K : 0) * 4;
   const int mask = d->stage_mask ? d->stage_mask : 15;
@@ -164,7 +164,7 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
   a.row_bytes = row_bytes_of(d->gate_ty, H);
   a.expert_stride[0] = a.expert_stride[1] = (unsigned long long)a.row_bytes * F;
   a.k = H; a.rows = F; a.nblk = H / 256;
-  a.xplanes = w.xplanes; a.xsum32 = w.xsum32; a.x_by_assignment = 0;
+  a.xplanes = w.xplanes; a.xsum_planes = w.xsum_planes; a.x_by_assignment = 0;
   a.counters = w.counters + 2; a.plan = w.plan; a.assignments = w.assignments;
   a.tokens = T; a.topk = K; a.max_groups = max_groups;
   a.out_planes = w.hplanes; a.out = nullptr; a.status = w.status;
@@ -177,7 +177,7 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
   b.row_bytes = row_bytes_of(d->down_ty, F);
   b.expert_stride[0] = (unsigned long long)b.row_bytes * H; b.expert_stride[1] = 0;
   b.k = F; b.rows = H; b.nblk = F / 256;
-  b.xplanes = w.hplanes; b.xsum32 = nullptr; b.x_by_assignment = 1;
+  b.xplanes = w.hplanes; b.xsum_planes = nullptr; b.x_by_assignment = 1;
   b.out_planes = nullptr; b.out = w.y;
   b.late_wait = (mask & 2) ? 1 : 0;      // the plan is the router's, two launches back; only the products come from gate/up
   if ((mask & 4) && (e = launch_gemv_ggml<0>(d->down_ty, b, st))) return e;

@@ -48,7 +48,7 @@ struct RouterArgs {
   PermuteArgs perm;
   unsigned* done;       // counter, zero before the launch; reset to zero by the last block
   __half* planes;       // optional (float x only): blocks past the router rows write the activation planes
-  float* xsum32;        //   [T][2][hidden] and the per-32 sums [T][hidden/32] read by the expert kernels
+  __half* xsum_planes;  //   [T][2][hidden] and the per-32 sums as hi / lo planes [T][2][hidden/32] read by the expert kernels
   int planes_natural;   // plane element order: 0 GGUF fragment order, 1 natural (NVFP4)
   int fuse;             // 1: last block routes and permutes
 };
@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(128) router_kernel(RouterArgs a) {
     if (a.planes) {
       const int t = row - router_rows;
       act_planes_row(static_cast<const XT*>(a.x) + size_t(t) * a.hidden, a.hidden, a.planes + size_t(t) * 2 * a.hidden,
-                     a.xsum32 ? a.xsum32 + size_t(t) * (a.hidden / 32) : nullptr, a.planes_natural != 0);
+                     a.xsum_planes ? a.xsum_planes + size_t(t) * 2 * (a.hidden / 32) : nullptr, a.planes_natural != 0);
     }
     return;                            // not counted: only the router rows gate the routing below
   }

@@ -76,11 +76,11 @@ __global__ void __launch_bounds__(128) route_permute_kernel(RouteArgs r, Permute
 }
 
 template <typename XT>
-__global__ void __launch_bounds__(128) act_planes_kernel(const XT* x, int k, __half* planes, float* xsum32, int natural) {
+__global__ void __launch_bounds__(128) act_planes_kernel(const XT* x, int k, __half* planes, __half* xsum_planes, int natural) {
   pdl_wait();
   pdl_launch();
   const int t = blockIdx.x;
-  act_planes_row(x + size_t(t) * k, k, planes + size_t(t) * 2 * k, xsum32 ? xsum32 + size_t(t) * (k / 32) : nullptr, natural != 0);
+  act_planes_row(x + size_t(t) * k, k, planes + size_t(t) * 2 * k, xsum_planes ? xsum_planes + size_t(t) * 2 * (k / 32) : nullptr, natural != 0);
 }
 
 // ---- expert-parallel pieces ---------------------------------------------------------------------------------------
@@ -217,7 +217,7 @@ static cudaError_t route_window(const void* router_w, const float* x, const Rout
   }
   if ((e = launch_pdl(route_topk_kernel<kRouteTsumuji>, dim3((N + 3) / 4), dim3(128), 0, st, route))) return e;
   if ((e = launch_permute_large(perm, w.perm_scratch, st))) return e;
-  return launch_pdl(act_planes_kernel<float>, dim3(N), dim3(128), 0, st, x, H, w.xplanes, (float*)nullptr, 1);
+  return launch_pdl(act_planes_kernel<float>, dim3(N), dim3(128), 0, st, x, H, w.xplanes, (__half*)nullptr, 1);
 }
 
 // shared expert of a window: y_out[t] = W_down . silu(W_gate . x[t]) * (W_up . x[t]), two tcgen05 bf16 GEMMs over the
@@ -274,13 +274,13 @@ extern "C" int tsumuji_moe_layer(const TsumujiMoe* d, cudaStream_t st) {
     RouterArgs r = {};
     r.w = d->router_w; r.x = d->x; r.logits = d->rlogits; r.hidden = H; r.rows = E + 1; r.ld = E + 1; r.tokens = N;
     r.route = route; r.perm = perm; r.done = w.done; r.fuse = 1;
-    r.planes = w.xplanes; r.xsum32 = nullptr; r.planes_natural = 1;
+    r.planes = w.xplanes; r.xsum_planes = nullptr; r.planes_natural = 1;
     const size_t hist = size_t(E + 1) * 4 + size_t(N * K <= kRouteIdCache ? N * K : 0) * 4;
     if ((e = launch_pdl(router_kernel<__nv_bfloat16, float, kRouteTsumuji>, dim3(E + 1 + N), dim3(128), hist, st, r))) return e;
   } else {
     // logits supplied by the caller (the reference computes them with its dense GEMV, engine.rs:1589)
     if ((e = launch_pdl(route_permute_kernel<kRouteTsumuji>, dim3(1), dim3(128), size_t(E + 1) * 4, st, route, perm))) return e;
-    if ((e = launch_pdl(act_planes_kernel<float>, dim3(N), dim3(128), 0, st, d->x, H, w.xplanes, (float*)nullptr, 1))) return e;
+    if ((e = launch_pdl(act_planes_kernel<float>, dim3(N), dim3(128), 0, st, d->x, H, w.xplanes, (__half*)nullptr, 1))) return e;
   }
   const unsigned long long fh = (unsigned long long)F * H;
   const uint8_t* base = static_cast<const uint8_t*>(d->experts_w);
@@ -365,7 +365,7 @@ extern "C" int tsumuji_ep_dispatch(const TsumujiMoe* d, float* send_x, unsigned*
     r.w = d->router_w; r.x = d->x; r.logits = d->rlogits; r.hidden = H; r.rows = E + 1; r.ld = E + 1; r.tokens = N;
     r.route = route; r.perm = perm;
     r.done = w.done; r.fuse = 1;
-    r.planes = w.xplanes; r.xsum32 = nullptr; r.planes_natural = 1;
+    r.planes = w.xplanes; r.xsum_planes = nullptr; r.planes_natural = 1;
     const size_t hist = size_t(E + 1) * 4 + size_t(N * K <= kRouteIdCache ? N * K : 0) * 4;
     if ((e = launch_pdl(router_kernel<__nv_bfloat16, float, kRouteTsumuji>, dim3(E + 1 + N), dim3(128), hist, st, r))) return e;
   }
@@ -408,7 +408,7 @@ extern "C" int tsumuji_ep_experts(const void* experts_w, const float* gs, int hi
   if (rows > 2048) {
     if ((e = launch_permute_large(perm, perm_scratch, st))) return e;
   } else if ((e = launch_pdl(permute_kernel<0>, dim3(1), dim3(1024), size_t(local_experts + 1) * 4, st, perm))) return e;
-  if ((e = launch_pdl(act_planes_kernel<float>, dim3(rows), dim3(128), 0, st, x_rows, hidden, w.xplanes, (float*)nullptr, 1))) return e;
+  if ((e = launch_pdl(act_planes_kernel<float>, dim3(rows), dim3(128), 0, st, x_rows, hidden, w.xplanes, (__half*)nullptr, 1))) return e;
   GemvArgs a, b;
   routed_args(a, b, experts_w, gs, hidden, inter);
   a.xplanes = w.xplanes; a.x_by_assignment = 0;
