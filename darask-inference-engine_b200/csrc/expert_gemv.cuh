@@ -21,6 +21,7 @@
 #include "common.cuh"
 #include <cuda_fp4.h>
 #include <cuda_fp8.h>
+#include <type_traits>
 
 namespace dmoe {
 
@@ -69,7 +70,7 @@ struct GemvArgs {
 };
 
 #ifndef DMOE_GEMV_WARPS
-#define DMOE_GEMV_WARPS 24
+#define DMOE_GEMV_WARPS 16
 #endif
 constexpr int kGemvWarps = DMOE_GEMV_WARPS;
 
@@ -97,12 +98,19 @@ DEVI __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
 // storage position of logical column e inside a plane
 DEVI int plane_pos(int e) { return (e & ~3) | ((e & 1) << 1) | ((e >> 1) & 1); }
 
+// word i of a 16-byte vector (i is a compile-time constant after unrolling)
+DEVI uint32_t u4w(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+// The block functions below multiply one staged 256-column block of 16 row slots with up to NT groups of four
+// tokens: the weight fragments are built once and feed one tile per token group. `bcol[t]`: this lane's B plane
+// of group t (column g = lane/4 -> token g/2 of the group, hi or lo) at the block's first column, or null for an
+// empty column. `facc[t]`: the sums of rows g / g + 8 for token j = lane % 4 of group t.
+
 // ---- Q4_K -------------------------------------------------------------------------------------------
-// One 256-column block of 16 row slots staged at `slab` (row slot pitch PITCH: header 16 B, nibbles 128 B).
-// value = d*sc*q - dmin*m (kogarashi kernels/native.cu:26-34). `bcol`: this lane's B plane (column
-// g = lane/4 -> token g/2, hi or lo) at the block's first column, or null for an empty column.
-template <int PITCH, bool MINS_TILE>
-DEVI void q4k_block_f16(uint32_t slab, int lane, const __half* bcol, const __half* xsum, float (&facc)[2]) {
+// Row slot pitch PITCH: header 16 B, nibbles 128 B. value = d*sc*q - dmin*m (kogarashi kernels/native.cu:26-34).
+// `xsum[t]`: the per-32 sums of this lane's column (hi or lo plane) at the block, or null.
+template <int PITCH, bool MINS_TILE, int NT>
+DEVI void q4k_block_f16(uint32_t slab, int lane, const __half* const (&bcol)[NT], const __half* const (&xsum)[NT], float (&facc)[NT][2]) {
   const int g = lane >> 2, j = lane & 3;
   const uint32_t r0 = slab + g * PITCH, r1 = slab + (g + 8) * PITCH;
   const uint4 h0 = lds128(r0), h1 = lds128(r1);
@@ -112,8 +120,11 @@ DEVI void q4k_block_f16(uint32_t slab, int lane, const __half* bcol, const __hal
   const uint32_t mn0[2] = {h0.z & 0x3F3F3F3Fu, ((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u)};
   const uint32_t mn1[2] = {h1.z & 0x3F3F3F3Fu, ((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u)};
   const __half2 k1024 = __float2half2_rn(1024.f);
-  float c[4] = {0.f, 0.f, 0.f, 0.f};      // sum over the block of sc * q * x   (rows g, g+8; columns 2j, 2j+1)
-  float cm[4] = {0.f, 0.f, 0.f, 0.f};     // sum over the block of m * x        (MINS_TILE only)
+  float c[NT][4], cm[NT][4];               // sums over the block of sc * q * x and of m * x (rows g, g+8; columns 2j, 2j+1)
+#pragma unroll
+  for (int t = 0; t < NT; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[t][i] = cm[t][i] = 0.f;
 #pragma unroll
   for (int gp = 0; gp < 4; ++gp) {
     // byte [sc, 0x64] pairs -> half2(1024 + sc) - 1024 = (sc, sc), exact
@@ -127,13 +138,17 @@ DEVI void q4k_block_f16(uint32_t slab, int lane, const __half* bcol, const __hal
     const __half2 mh0 = __hmul2(sh0, __float2half2_rn(0.0625f)), mh1 = __hmul2(sh1, __float2half2_rn(0.0625f));
     const __half2 bh0 = __hmul2(sh0, __float2half2_rn(-64.f)), bh1 = __hmul2(sh1, __float2half2_rn(-64.f));
     const uint2 w0 = lds64(r0 + 16 + gp * 32 + 8 * j), w1 = lds64(r1 + 16 + gp * 32 + 8 * j);
-    uint4 blo = make_uint4(0, 0, 0, 0), bhi = make_uint4(0, 0, 0, 0);
-    if (bcol) {
-      blo = __ldg(reinterpret_cast<const uint4*>(bcol + gp * 64 + 8 * j));
-      bhi = __ldg(reinterpret_cast<const uint4*>(bcol + gp * 64 + 32 + 8 * j));
+    uint4 blo[NT], bhi[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      blo[t] = make_uint4(0, 0, 0, 0);
+      bhi[t] = make_uint4(0, 0, 0, 0);
+      if (bcol[t]) {
+        blo[t] = __ldg(reinterpret_cast<const uint4*>(bcol[t] + gp * 64 + 8 * j));
+        bhi[t] = __ldg(reinterpret_cast<const uint4*>(bcol[t] + gp * 64 + 32 + 8 * j));
+      }
     }
     const uint32_t words0[2] = {w0.x, w0.y}, words1[2] = {w1.x, w1.y};
-    const uint32_t bl[4] = {blo.x, blo.y, blo.z, blo.w}, bh[4] = {bhi.x, bhi.y, bhi.z, bhi.w};
 #pragma unroll
     for (int s = 0; s < 2; ++s) {          // the two 16-column slabs of a 32-column sub-block
       const uint32_t a = words0[s], b = words1[s];
@@ -142,13 +157,15 @@ DEVI void q4k_block_f16(uint32_t slab, int lane, const __half* bcol, const __hal
       uint32_t a2 = h2_as_u32(__hfma2(u32_as_h2(((a >> 8) & 0x000F000Fu) | 0x64006400u), sl0, bl0));
       uint32_t a1 = h2_as_u32(__hfma2(u32_as_h2((b & 0x000F000Fu) | 0x64006400u), sl1, bl1));
       uint32_t a3 = h2_as_u32(__hfma2(u32_as_h2(((b >> 8) & 0x000F000Fu) | 0x64006400u), sl1, bl1));
-      mma_f16(c, a0, a1, a2, a3, bl[2 * s], bl[2 * s + 1]);
+#pragma unroll
+      for (int t = 0; t < NT; ++t) mma_f16(c[t], a0, a1, a2, a3, u4w(blo[t], 2 * s), u4w(blo[t], 2 * s + 1));
       // high nibbles -> sub-block 2gp + 1
       a0 = h2_as_u32(__hfma2(u32_as_h2((a & 0x00F000F0u) | 0x64006400u), mh0, bh0));
       a2 = h2_as_u32(__hfma2(u32_as_h2(((a >> 8) & 0x00F000F0u) | 0x64006400u), mh0, bh0));
       a1 = h2_as_u32(__hfma2(u32_as_h2((b & 0x00F000F0u) | 0x64006400u), mh1, bh1));
       a3 = h2_as_u32(__hfma2(u32_as_h2(((b >> 8) & 0x00F000F0u) | 0x64006400u), mh1, bh1));
-      mma_f16(c, a0, a1, a2, a3, bh[2 * s], bh[2 * s + 1]);
+#pragma unroll
+      for (int t = 0; t < NT; ++t) mma_f16(c[t], a0, a1, a2, a3, u4w(bhi[t], 2 * s), u4w(bhi[t], 2 * s + 1));
       if (MINS_TILE) {
         // the min of a sub-block as a constant row of the A operand: the tile sums m * x over the slab
         const int msel = (gp & 1) ? 0x4342 : 0x4140;
@@ -156,36 +173,39 @@ DEVI void q4k_block_f16(uint32_t slab, int lane, const __half* bcol, const __hal
         const __half2 q1 = __hsub2(u32_as_h2(__byte_perm(mn1[gp >> 1], 0x64646464u, msel)), k1024);
         const uint32_t ml0 = h2_as_u32(__low2half2(q0)), mh0u = h2_as_u32(__high2half2(q0));
         const uint32_t ml1 = h2_as_u32(__low2half2(q1)), mh1u = h2_as_u32(__high2half2(q1));
-        mma_f16(cm, ml0, ml1, ml0, ml1, bl[2 * s], bl[2 * s + 1]);
-        mma_f16(cm, mh0u, mh1u, mh0u, mh1u, bh[2 * s], bh[2 * s + 1]);
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          mma_f16(cm[t], ml0, ml1, ml0, ml1, u4w(blo[t], 2 * s), u4w(blo[t], 2 * s + 1));
+          mma_f16(cm[t], mh0u, mh1u, mh0u, mh1u, u4w(bhi[t], 2 * s), u4w(bhi[t], 2 * s + 1));
+        }
       }
     }
   }
   const float d0 = half_lo(h0.x), dm0 = half_hi(h0.x), d1 = half_lo(h1.x), dm1 = half_hi(h1.x);
-  float m0 = 0.f, m1 = 0.f;
-  if (MINS_TILE) {
-    m0 = cm[0] + cm[1];
-    m1 = cm[2] + cm[3];
-  } else {
+  if (!MINS_TILE) {
     // one tile for the mins of the whole block: A = the eight mins of rows g / g + 8 in k slots 0-7 (this lane: slots
-    // 2j, 2j + 1), B = the eight per-32 sums of this lane's column (`xsum`: its hi or lo plane at the block, or null)
+    // 2j, 2j + 1), B = the eight per-32 sums of this lane's column
     const __half2 q0 = __hsub2(u32_as_h2(__byte_perm((j & 2) ? mn0[1] : mn0[0], 0x64646464u, (j & 1) ? 0x4342 : 0x4140)), k1024);
     const __half2 q1 = __hsub2(u32_as_h2(__byte_perm((j & 2) ? mn1[1] : mn1[0], 0x64646464u, (j & 1) ? 0x4342 : 0x4140)), k1024);
-    uint32_t xs2 = 0;
-    if (xsum) xs2 = __ldg(reinterpret_cast<const uint32_t*>(xsum) + j);
-    mma_f16(cm, h2_as_u32(q0), h2_as_u32(q1), 0u, 0u, xs2, 0u);
-    m0 = cm[0] + cm[1];
-    m1 = cm[2] + cm[3];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      uint32_t xs2 = 0;
+      if (xsum[t]) xs2 = __ldg(reinterpret_cast<const uint32_t*>(xsum[t]) + j);
+      mma_f16(cm[t], h2_as_u32(q0), h2_as_u32(q1), 0u, 0u, xs2, 0u);
+    }
   }
-  facc[0] += d0 * (c[0] + c[1]) - dm0 * m0;
-  facc[1] += d1 * (c[2] + c[3]) - dm1 * m1;
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    facc[t][0] += d0 * (c[t][0] + c[t][1]) - dm0 * (cm[t][0] + cm[t][1]);
+    facc[t][1] += d1 * (c[t][2] + c[t][3]) - dm1 * (cm[t][2] + cm[t][3]);
+  }
 }
 
 // ---- Q6_K (row-aligned device layout: per block ql 128 | qh 64 | int8 scales 16; d in a trailing chunk) --
 // value = d * scale * (q - 32) (kogarashi kernels/native.cu:35-40). Row slot: 208 data bytes, then the 16-byte
 // chunk of the row tail that holds this block's f16 d at byte `doff`.
-template <int PITCH>
-DEVI void q6k_block_f16(uint32_t slab, int lane, int doff, const __half* bcol, float (&facc)[2]) {
+template <int PITCH, int NT>
+DEVI void q6k_block_f16(uint32_t slab, int lane, int doff, const __half* const (&bcol)[NT], float (&facc)[NT][2]) {
   const int g = lane >> 2, j = lane & 3;
   const uint32_t r0 = slab + g * PITCH, r1 = slab + (g + 8) * PITCH;
   const uint4 s0v = lds128(r0 + 192), s1v = lds128(r1 + 192);
@@ -194,7 +214,9 @@ DEVI void q6k_block_f16(uint32_t slab, int lane, int doff, const __half* bcol, f
   const uint32_t dw0 = lds32(r0 + 208 + (doff & ~3)), dw1 = lds32(r1 + 208 + (doff & ~3));
   const float d0 = (doff & 2) ? half_hi(dw0) : half_lo(dw0), d1 = (doff & 2) ? half_hi(dw1) : half_lo(dw1);
   const __half2 k1056 = __float2half2_rn(1056.f);      // 1024 (magic) + 32 (code offset)
-  float a0 = 0.f, a1 = 0.f;
+  float a0[NT], a1[NT];
+#pragma unroll
+  for (int t = 0; t < NT; ++t) a0[t] = a1[t] = 0.f;
 #pragma unroll
   for (int n = 0; n < 2; ++n) {
 #pragma unroll
@@ -204,10 +226,15 @@ DEVI void q6k_block_f16(uint32_t slab, int lane, int doff, const __half* bcol, f
       for (int gb = 0; gb < 2; ++gb) {
         const uint32_t w0 = lds32(r0 + n * 64 + gb * 32 + lh * 16 + 4 * j), w1 = lds32(r1 + n * 64 + gb * 32 + lh * 16 + 4 * j);
         const int col = n * 128 + gb * 32 + lh * 16 + 4 * j;       // columns of the low-nibble group; +64: high nibbles
-        uint2 blo = make_uint2(0, 0), bhi = make_uint2(0, 0);
-        if (bcol) {
-          blo = __ldg(reinterpret_cast<const uint2*>(bcol + col));
-          bhi = __ldg(reinterpret_cast<const uint2*>(bcol + col + 64));
+        uint2 blo[NT], bhi[NT];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          blo[t] = make_uint2(0, 0);
+          bhi[t] = make_uint2(0, 0);
+          if (bcol[t]) {
+            blo[t] = __ldg(reinterpret_cast<const uint2*>(bcol[t] + col));
+            bhi[t] = __ldg(reinterpret_cast<const uint2*>(bcol[t] + col + 64));
+          }
         }
 #pragma unroll
         for (int hi = 0; hi < 2; ++hi) {
@@ -220,20 +247,26 @@ DEVI void q6k_block_f16(uint32_t slab, int lane, int doff, const __half* bcol, f
           const uint32_t f2 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(c0, 0x64646464u, 0x4341)), k1056));
           const uint32_t f1 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(c1, 0x64646464u, 0x4240)), k1056));
           const uint32_t f3 = h2_as_u32(__hsub2(u32_as_h2(__byte_perm(c1, 0x64646464u, 0x4341)), k1056));
-          float c[4] = {0.f, 0.f, 0.f, 0.f};
-          mma_f16(c, f0, f1, f2, f3, hi ? bhi.x : blo.x, hi ? bhi.y : blo.y);
           const int si = 8 * n + 2 * (gb + 2 * hi) + lh;            // scale index of this 16-column group
           const uint32_t wa = sw0[si >> 2], wb = sw1[si >> 2];
           const float fa = ((si & 3) == 0 ? byte_magic<0>(wa) : (si & 3) == 1 ? byte_magic<1>(wa) : (si & 3) == 2 ? byte_magic<2>(wa) : byte_magic<3>(wa)) - (kMagic + 128.f);
           const float fb = ((si & 3) == 0 ? byte_magic<0>(wb) : (si & 3) == 1 ? byte_magic<1>(wb) : (si & 3) == 2 ? byte_magic<2>(wb) : byte_magic<3>(wb)) - (kMagic + 128.f);
-          a0 = fmaf(fa, c[0] + c[1], a0);
-          a1 = fmaf(fb, c[2] + c[3], a1);
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            float c[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_f16(c, f0, f1, f2, f3, hi ? bhi[t].x : blo[t].x, hi ? bhi[t].y : blo[t].y);
+            a0[t] = fmaf(fa, c[0] + c[1], a0[t]);
+            a1[t] = fmaf(fb, c[2] + c[3], a1[t]);
+          }
         }
       }
     }
   }
-  facc[0] += d0 * a0;
-  facc[1] += d1 * a1;
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    facc[t][0] += d0 * a0[t];
+    facc[t][1] += d1 * a1[t];
+  }
 }
 
 
@@ -242,6 +275,11 @@ DEVI void q6k_block_f16(uint32_t slab, int lane, int doff, const __half* bcol, f
 // byte of row slot `slot` and 16-column group `c` of the block sits at sbase(slot) + c for the linear
 // layout (tsumuji weights.rs:10-12) and inside 16-byte pieces of the 128x4 scale tiles for the tiled one
 // (hayate math.cuh:41-49); SCALES tells which.
+DEVI uint32_t e4m3x2_to_h2(uint32_t two_bytes) {
+  uint32_t out;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(out) : "h"((unsigned short)two_bytes));
+  return out;
+}
 DEVI uint32_t e2m1x2_to_h2(uint32_t byte) {                             // one code byte -> half2(even column, odd column)
   const __half2_raw r = __nv_cvt_fp4x2_to_halfraw2(static_cast<__nv_fp4x2_storage_t>(byte & 0xffu), __NV_E2M1);
   return uint32_t(r.x) | (uint32_t(r.y) << 16);
@@ -249,11 +287,6 @@ DEVI uint32_t e2m1x2_to_h2(uint32_t byte) {                             // one c
 DEVI void e2m1x4_to_h2(uint32_t w16, uint32_t& lo, uint32_t& hi) {     // two code bytes -> 2 x half2
   lo = e2m1x2_to_h2(w16);
   hi = e2m1x2_to_h2(w16 >> 8);
-}
-DEVI __half2 e4m3_dup_h2(uint32_t byte) {                                // one scale byte -> half2(s, s)
-  uint32_t out;
-  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(out) : "h"((unsigned short)(byte | (byte << 8))));
-  return u32_as_h2(out);
 }
 // Address of the 16 scale bytes region helpers. Linear: the slot carries its 16 scale bytes behind the codes.
 // Tiled: the stage carries, behind the 16 row slots, pieces[piece][16] where a piece holds the four bytes
@@ -276,26 +309,46 @@ DEVI uint32_t round_bf16_pair(uint32_t v, float rm) {
   const float2 r = __bfloat1622float2(__floats2bfloat162_rn(f.x * rm, f.y * rm));
   return h2_as_u32(__floats2half2_rn(r.x, r.y));
 }
-template <int FMT, int DUAL, int PITCH, bool ROUNDED>
-DEVI void nvfp4_block_f16(uint32_t slab, int lane, const __half* bcol, float rm0, float rm1, float (&facc)[2]) {
+template <int FMT, int DUAL, int PITCH, bool ROUNDED, int NT>
+DEVI void nvfp4_block_f16(uint32_t slab, int lane, const __half* const (&bcol)[NT], float rm0, float rm1, float (&facc)[NT][2]) {
   const int g = lane >> 2, j = lane & 3;
   const uint32_t r0 = slab + g * PITCH, r1 = slab + (g + 8) * PITCH;
-  float c[4] = {0.f, 0.f, 0.f, 0.f};
+  // the 16 scale bytes of rows g / g + 8 for this block, four per word (word tc = scale columns 4tc .. 4tc + 3)
+  uint32_t sw0[4], sw1[4];
+  if (FMT == kGemvNvfp4Linear) {
+    const uint4 v0 = lds128(r0 + 128), v1 = lds128(r1 + 128);
+    sw0[0] = v0.x; sw0[1] = v0.y; sw0[2] = v0.z; sw0[3] = v0.w;
+    sw1[0] = v1.x; sw1[1] = v1.y; sw1[2] = v1.z; sw1[3] = v1.w;
+  } else {
+#pragma unroll
+    for (int tc = 0; tc < 4; ++tc) {
+      sw0[tc] = lds32(nvfp4_scale_addr<FMT, DUAL, PITCH>(slab, g, 4 * tc));
+      sw1[tc] = lds32(nvfp4_scale_addr<FMT, DUAL, PITCH>(slab, g + 8, 4 * tc));
+    }
+  }
+  // step q uses scale column 2q + j/2: byte 2(q & 1) + j/2 of word q/2, duplicated into the low half word
+  const uint32_t sel_even = (j >> 1) * 0x11u, sel_odd = sel_even + 0x22u;
+  float c[NT][4];
+#pragma unroll
+  for (int t = 0; t < NT; ++t)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) c[t][i] = 0.f;
 #pragma unroll
   for (int q = 0; q < 8; ++q) {                      // 32 columns per step: this lane owns columns 8j..8j+7 of them
     const uint32_t w0 = lds32(r0 + q * 16 + 4 * j), w1 = lds32(r1 + q * 16 + 4 * j);
-    const int sc = q * 2 + (j >> 1);
-    const uint32_t sa0 = nvfp4_scale_addr<FMT, DUAL, PITCH>(slab, g, sc), sa1 = nvfp4_scale_addr<FMT, DUAL, PITCH>(slab, g + 8, sc);
-    // byte loads through the aligned word that holds them
-    const uint32_t sw0 = lds32(sa0 & ~3u) >> (8 * (sa0 & 3u)), sw1 = lds32(sa1 & ~3u) >> (8 * (sa1 & 3u));
-    const __half2 s0 = e4m3_dup_h2(sw0 & 0xffu), s1 = e4m3_dup_h2(sw1 & 0xffu);
+    const __half2 s0 = u32_as_h2(e4m3x2_to_h2(__byte_perm(sw0[q >> 1], 0u, (q & 1) ? sel_odd : sel_even)));
+    const __half2 s1 = u32_as_h2(e4m3x2_to_h2(__byte_perm(sw1[q >> 1], 0u, (q & 1) ? sel_odd : sel_even)));
     uint32_t a01, a23, a45, a67, b01, b23, b45, b67;
     e2m1x4_to_h2(w0 & 0xffffu, a01, a23);
     e2m1x4_to_h2(w0 >> 16, a45, a67);
     e2m1x4_to_h2(w1 & 0xffffu, b01, b23);
     e2m1x4_to_h2(w1 >> 16, b45, b67);
-    uint4 x = make_uint4(0, 0, 0, 0);
-    if (bcol) x = __ldg(reinterpret_cast<const uint4*>(bcol + q * 32 + 8 * j));
+    uint4 x[NT];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      x[t] = make_uint4(0, 0, 0, 0);
+      if (bcol[t]) x[t] = __ldg(reinterpret_cast<const uint4*>(bcol[t] + q * 32 + 8 * j));
+    }
     a01 = h2_as_u32(__hmul2(u32_as_h2(a01), s0)); a23 = h2_as_u32(__hmul2(u32_as_h2(a23), s0));
     a45 = h2_as_u32(__hmul2(u32_as_h2(a45), s0)); a67 = h2_as_u32(__hmul2(u32_as_h2(a67), s0));
     b01 = h2_as_u32(__hmul2(u32_as_h2(b01), s1)); b23 = h2_as_u32(__hmul2(u32_as_h2(b23), s1));
@@ -304,24 +357,25 @@ DEVI void nvfp4_block_f16(uint32_t slab, int lane, const __half* bcol, float rm0
       a01 = round_bf16_pair(a01, rm0); a23 = round_bf16_pair(a23, rm0); a45 = round_bf16_pair(a45, rm0); a67 = round_bf16_pair(a67, rm0);
       b01 = round_bf16_pair(b01, rm1); b23 = round_bf16_pair(b23, rm1); b45 = round_bf16_pair(b45, rm1); b67 = round_bf16_pair(b67, rm1);
     }
-    mma_f16(c, a01, b01, a23, b23, x.x, x.y);
-    mma_f16(c, a45, b45, a67, b67, x.z, x.w);
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      mma_f16(c[t], a01, b01, a23, b23, x[t].x, x[t].y);
+      mma_f16(c[t], a45, b45, a67, b67, x[t].z, x[t].w);
+    }
   }
-  facc[0] += c[0] + c[1];
-  facc[1] += c[2] + c[3];
+#pragma unroll
+  for (int t = 0; t < NT; ++t) {
+    facc[t][0] += c[t][0] + c[t][1];
+    facc[t][1] += c[t][2] + c[t][3];
+  }
 }
 
 // ---- block-FP8 (e4m3 payload [rows][k], float32 scale per 128 x 128; hayate `Fp8Block`) ---------------------------
 // weight = bf16(e4m3 * scale) (hayate cu/glm53/math.cuh:40 `scaled_fp8`): formed per pair in float32, rounded to
 // bf16, kept in fp16 as bf16(..) * 2^s with s chosen per scale so that the values stay normal. One 256-column block =
 // two 128-column halves with their own scale. sc0 / sc1: the two scales of rows g / g + 8 for this block.
-DEVI uint32_t e4m3x2_to_h2(uint32_t two_bytes) {
-  uint32_t out;
-  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(out) : "h"((unsigned short)two_bytes));
-  return out;
-}
-template <int PITCH>
-DEVI void fp8_block_f16(uint32_t slab, int lane, const __half* bcol, const float* sc0, const float* sc1, float (&facc)[2]) {
+template <int PITCH, int NT>
+DEVI void fp8_block_f16(uint32_t slab, int lane, const __half* const (&bcol)[NT], const float* sc0, const float* sc1, float (&facc)[NT][2]) {
   const int g = lane >> 2, j = lane & 3;
   const uint32_t r0 = slab + g * PITCH, r1 = slab + (g + 8) * PITCH;
 #pragma unroll
@@ -329,22 +383,36 @@ DEVI void fp8_block_f16(uint32_t slab, int lane, const __half* bcol, const float
     const float s0 = __ldg(sc0 + hb), s1 = __ldg(sc1 + hb);
     const int e0 = 14 - ilogbf(448.f * s0), e1 = 14 - ilogbf(448.f * s1);
     const float rm0 = scalbnf(s0, e0), rm1 = scalbnf(s1, e1);
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    float c[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) c[t][i] = 0.f;
 #pragma unroll
     for (int q = 0; q < 4; ++q) {                    // 32 columns per step: this lane owns columns 8j..8j+7 of them
       const int col = hb * 128 + q * 32 + 8 * j;
       const uint2 w0 = lds64(r0 + col), w1 = lds64(r1 + col);
-      uint4 x = make_uint4(0, 0, 0, 0);
-      if (bcol) x = __ldg(reinterpret_cast<const uint4*>(bcol + col));
+      uint4 x[NT];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        x[t] = make_uint4(0, 0, 0, 0);
+        if (bcol[t]) x[t] = __ldg(reinterpret_cast<const uint4*>(bcol[t] + col));
+      }
       const uint32_t a01 = round_bf16_pair(e4m3x2_to_h2(w0.x & 0xffffu), rm0), a23 = round_bf16_pair(e4m3x2_to_h2(w0.x >> 16), rm0);
       const uint32_t a45 = round_bf16_pair(e4m3x2_to_h2(w0.y & 0xffffu), rm0), a67 = round_bf16_pair(e4m3x2_to_h2(w0.y >> 16), rm0);
       const uint32_t b01 = round_bf16_pair(e4m3x2_to_h2(w1.x & 0xffffu), rm1), b23 = round_bf16_pair(e4m3x2_to_h2(w1.x >> 16), rm1);
       const uint32_t b45 = round_bf16_pair(e4m3x2_to_h2(w1.y & 0xffffu), rm1), b67 = round_bf16_pair(e4m3x2_to_h2(w1.y >> 16), rm1);
-      mma_f16(c, a01, b01, a23, b23, x.x, x.y);
-      mma_f16(c, a45, b45, a67, b67, x.z, x.w);
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        mma_f16(c[t], a01, b01, a23, b23, x[t].x, x[t].y);
+        mma_f16(c[t], a45, b45, a67, b67, x[t].z, x[t].w);
+      }
     }
-    facc[0] += scalbnf(c[0] + c[1], -e0);
-    facc[1] += scalbnf(c[2] + c[3], -e1);
+#pragma unroll
+    for (int t = 0; t < NT; ++t) {
+      facc[t][0] += scalbnf(c[t][0] + c[t][1], -e0);
+      facc[t][1] += scalbnf(c[t][2] + c[t][3], -e1);
+    }
   }
 }
 
@@ -366,7 +434,7 @@ template <> struct GemvLayout<kGemvNvfp4Tiled> { static constexpr int kPitch = 1
 
 template <int FMT> __host__ __device__ constexpr int gemv_stage_bytes() { return 16 * GemvLayout<FMT>::kPitch + GemvLayout<FMT>::kExtra; }
 template <int FMT> __host__ __device__ constexpr int gemv_smem_bytes() {
-  return kGemvWarps * GemvLayout<FMT>::kStages * gemv_stage_bytes<FMT>() + kGemvWarps * 4 * 16 * 4 + 16;
+  return kGemvWarps * GemvLayout<FMT>::kStages * gemv_stage_bytes<FMT>() + kGemvWarps * 8 * 16 * 4 + 16;
 }
 
 // Weight row of matrix-0 row slot `s` of slab `u` = slab_row0(u) + slab_rowc(s). Rows are slabs of RPT consecutive
@@ -405,7 +473,7 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int STAGE = gemv_stage_bytes<FMT>();
   const uint32_t ring = smem_u32(smem) + warp * (LY::kStages * STAGE);
-  float* red = reinterpret_cast<float*>(smem + kGemvWarps * LY::kStages * STAGE);   // [warp][token 4][row 16]
+  float* red = reinterpret_cast<float*>(smem + kGemvWarps * LY::kStages * STAGE);   // [warp][token 8][row 16]
   constexpr int RPT = DUAL ? 8 : 16;                     // weight rows of matrix 0 per slab
   constexpr bool NV = FMT == kGemvNvfp4Linear || FMT == kGemvNvfp4Tiled;
   constexpr bool NATURAL = NV || FMT == kGemvFp8Block;    // activation planes in natural column order
@@ -545,21 +613,30 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
       pdl_wait();
       waited = true;
     }
-    for (int c0 = 0; c0 < count; c0 += 4) {               // up to four tokens of this group per pass
-      // this lane's B column g4 -> token g4/2 of the pass, hi (even) or lo (odd) plane
-      const int tcol = c0 + (g4 >> 1);
-      const __half* plane = nullptr;
-      const __half* xs = nullptr;
-      if (tcol < count) {
-        const int as = e < 0 ? shared_row0 + tcol : int(__ldcg(a.assignments + offset + tcol));
-        const int xrow = a.x_by_assignment ? as : (e < 0 ? a.shared_x_row0 + tcol : as / a.topk);
-        plane = a.xplanes + (size_t(xrow) * 2 + (g4 & 1)) * a.k;
-        if (FMT == kGemvQ4K && !MINS_TILE && a.xsum_planes) xs = a.xsum_planes + (size_t(xrow) * 2 + (g4 & 1)) * (a.k / 32);
+    // One pass over the item's blocks for the tokens c0 .. c0 + 4 NT - 1 of the group (NT groups of four: the weight
+    // fragments are built once per pass).
+    auto pass = [&](auto nt_tag, int c0) {
+      constexpr int NT = decltype(nt_tag)::value;
+      const __half* plane[NT];
+      const __half* xs[NT];
+      int ares[NT];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        // this lane's B column g4 -> token g4/2 of the group, hi (even) or lo (odd) plane
+        const int tcol = c0 + 4 * t + (g4 >> 1);
+        plane[t] = nullptr;
+        xs[t] = nullptr;
+        if (tcol < count) {
+          const int as = e < 0 ? shared_row0 + tcol : int(__ldcg(a.assignments + offset + tcol));
+          const int xrow = a.x_by_assignment ? as : (e < 0 ? a.shared_x_row0 + tcol : as / a.topk);
+          plane[t] = a.xplanes + (size_t(xrow) * 2 + (g4 & 1)) * a.k + size_t(b_first) * 256;
+          if (FMT == kGemvQ4K && !MINS_TILE && a.xsum_planes) xs[t] = a.xsum_planes + (size_t(xrow) * 2 + (g4 & 1)) * (a.k / 32) + b_first * 8;
+        }
+        // this lane's result column pair 2j,2j+1 -> token j of the group
+        const int tres = c0 + 4 * t + j;
+        ares[t] = -1;
+        if (tres < count) ares[t] = e < 0 ? shared_row0 + tres : int(__ldcg(a.assignments + offset + tres));
       }
-      // this lane's result column pair 2j,2j+1 -> token j of the pass
-      const int tres = c0 + j;
-      int ares = -1;
-      if (tres < count) ares = e < 0 ? shared_row0 + tres : int(__ldcg(a.assignments + offset + tres));
       if (c0 > 0) {                                       // later passes stream the blocks again (L2 hits)
 #pragma unroll
         for (int s = 0; s < LY::kStages - 1; ++s) {
@@ -567,7 +644,9 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
           cp_async_commit();
         }
       }
-      float facc[2] = {0.f, 0.f};
+      float facc[NT][2];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) facc[t][0] = facc[t][1] = 0.f;
       for (int i = 0; i < nb_per; ++i) {
         const int nxt = i + LY::kStages - 1;
         if (nxt < nb_per) issue(nxt, nxt % LY::kStages);
@@ -576,54 +655,77 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
         __syncwarp();
         const int b = b_first + i;
         const uint32_t slab = ring + (i % LY::kStages) * STAGE;
-        const __half* bcol = plane ? plane + b * 256 : nullptr;
-        if (FMT == kGemvQ4K) q4k_block_f16<LY::kPitch, MINS_TILE>(slab, lane, bcol, xs ? xs + b * 8 : nullptr, facc);
-        else if (FMT == kGemvQ6KR) q6k_block_f16<LY::kPitch>(slab, lane, (2 * b) & 15, bcol, facc);
-        else if (FMT == kGemvFp8Block) fp8_block_f16<LY::kPitch>(slab, lane, bcol, fsc0 + 2 * b, fsc1 + 2 * b, facc);
-        else if (rounded) nvfp4_block_f16<FMT, DUAL, LY::kPitch, true>(slab, lane, bcol, rm0, rm1, facc);
-        else nvfp4_block_f16<FMT, DUAL, LY::kPitch, false>(slab, lane, bcol, 0.f, 0.f, facc);
+        const __half* bcol[NT];
+        const __half* xsb[NT];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          bcol[t] = plane[t] ? plane[t] + i * 256 : nullptr;
+          xsb[t] = xs[t] ? xs[t] + i * 8 : nullptr;
+        }
+        if (FMT == kGemvQ4K) q4k_block_f16<LY::kPitch, MINS_TILE, NT>(slab, lane, bcol, xsb, facc);
+        else if (FMT == kGemvQ6KR) q6k_block_f16<LY::kPitch, NT>(slab, lane, (2 * b) & 15, bcol, facc);
+        else if (FMT == kGemvFp8Block) fp8_block_f16<LY::kPitch, NT>(slab, lane, bcol, fsc0 + 2 * b, fsc1 + 2 * b, facc);
+        else if (rounded) nvfp4_block_f16<FMT, DUAL, LY::kPitch, true, NT>(slab, lane, bcol, rm0, rm1, facc);
+        else nvfp4_block_f16<FMT, DUAL, LY::kPitch, false, NT>(slab, lane, bcol, 0.f, 0.f, facc);
         __syncwarp();
       }
       cp_async_wait<0>();
       // ---- sum over the K split (fixed order) and store ------------------------------------------------
       if (a.ks > 1) {
         const int bar = 1 + warp / a.ks;                  // one named barrier per slab group (<= 12)
-        red[(warp * 4 + j) * 16 + g4] = facc[0];
-        red[(warp * 4 + j) * 16 + 8 + g4] = facc[1];
+#pragma unroll
+        for (int t = 0; t < NT; ++t) {
+          red[(warp * 8 + 4 * t + j) * 16 + g4] = facc[t][0];
+          red[(warp * 8 + 4 * t + j) * 16 + 8 + g4] = facc[t][1];
+        }
         named_barrier(bar, a.ks * 32);
         if (kpart == 0) {
-          facc[0] = 0.f;
-          facc[1] = 0.f;
-          for (int q = 0; q < a.ks; ++q) {
-            facc[0] += red[((warp + q) * 4 + j) * 16 + g4];
-            facc[1] += red[((warp + q) * 4 + j) * 16 + 8 + g4];
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            facc[t][0] = 0.f;
+            facc[t][1] = 0.f;
+            for (int q = 0; q < a.ks; ++q) {
+              facc[t][0] += red[((warp + q) * 8 + 4 * t + j) * 16 + g4];
+              facc[t][1] += red[((warp + q) * 8 + 4 * t + j) * 16 + 8 + g4];
+            }
           }
         }
         named_barrier(bar, a.ks * 32);                    // partials are consumed before the next pass overwrites them
       }
-      if (kpart == 0 && ares >= 0) {
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        if (kpart != 0 || ares[t] < 0) continue;
         if (DUAL) {
           const int r = slab_row<FMT, DUAL>(slab_u, g4);
           if (r < a.rows) {
-            const float gv = facc[0] * gs0, uv = facc[1] * gs1;
+            const float gv = facc[t][0] * gs0, uv = facc[t][1] * gs1;
             const float h = OUT == kOutHayateProduct ? hayate_swiglu(gv, uv) : silu_mul(gv, uv);
             const __half hi = __float2half_rn(h);
             const __half lo = __float2half_rn(h - __half2float(hi));
-            __half* dst = a.out_planes + size_t(ares) * 2 * a.rows + (NATURAL ? r : plane_pos(r));
+            __half* dst = a.out_planes + size_t(ares[t]) * 2 * a.rows + (NATURAL ? r : plane_pos(r));
             dst[0] = hi;
             dst[a.rows] = lo;
-            if (OUT == kOutHayateProduct && a.out_bf16) a.out_bf16[size_t(ares) * a.rows + r] = __float2bfloat16_rn(h);
+            if (OUT == kOutHayateProduct && a.out_bf16) a.out_bf16[size_t(ares[t]) * a.rows + r] = __float2bfloat16_rn(h);
           }
         } else {
           const int r0 = slab_row<FMT, DUAL>(slab_u, g4), r1 = slab_row<FMT, DUAL>(slab_u, g4 + 8);
           if (OUT == kOutBf16) {
-            if (r0 < a.rows) a.out_bf16[size_t(ares) * a.rows + r0] = __float2bfloat16_rn(facc[0] * gs0);
-            if (r1 < a.rows) a.out_bf16[size_t(ares) * a.rows + r1] = __float2bfloat16_rn(facc[1] * gs0);
+            if (r0 < a.rows) a.out_bf16[size_t(ares[t]) * a.rows + r0] = __float2bfloat16_rn(facc[t][0] * gs0);
+            if (r1 < a.rows) a.out_bf16[size_t(ares[t]) * a.rows + r1] = __float2bfloat16_rn(facc[t][1] * gs0);
           } else {
-            if (r0 < a.rows) a.out[size_t(ares) * a.rows + r0] = facc[0] * gs0;
-            if (r1 < a.rows) a.out[size_t(ares) * a.rows + r1] = facc[1] * gs0;
+            if (r0 < a.rows) a.out[size_t(ares[t]) * a.rows + r0] = facc[t][0] * gs0;
+            if (r1 < a.rows) a.out[size_t(ares[t]) * a.rows + r1] = facc[t][1] * gs0;
           }
         }
+      }
+    };
+    for (int c0 = 0; c0 < count;) {
+      if (count - c0 > 4) {
+        pass(std::integral_constant<int, 2>{}, c0);
+        c0 += 8;
+      } else {
+        pass(std::integral_constant<int, 1>{}, c0);
+        c0 += 4;
       }
     }
   }
