@@ -81,11 +81,12 @@ static EncodeTiledFn encode_tiled_fn() {
 
 // also used by the Tsumuji token-window path (tsumuji.cu)
 cudaError_t launch_grouped_bf16(void* out, float* acc, const void* x, const void* w, const void* ranges, unsigned groups,
-                                       unsigned n, unsigned k, const float* scales, cudaStream_t st) {
+                                       unsigned n, unsigned k, const float* scales, cudaStream_t st, unsigned w_rows) {
   EncodeTiledFn enc = encode_tiled_fn();
   if (!enc) return cudaErrorInvalidValue;
   CUtensorMap mw;
-  const cuuint64_t dims[2] = {k, cuuint64_t(groups) * n}, strides[1] = {cuuint64_t(k) * 2};
+  // w_rows: rows the weight array really has (0: groups * n); tiles past it read zeros, never memory
+  const cuuint64_t dims[2] = {k, w_rows ? cuuint64_t(w_rows) : cuuint64_t(groups) * n}, strides[1] = {cuuint64_t(k) * 2};
   const cuuint32_t box[2] = {kGbTileK, 128}, estr[2] = {1, 1};
   if (enc(&mw, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(w), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -119,14 +120,14 @@ extern "C" int hayate_glm_grouped(void* out, const void* x, const void* w, const
                                   void* metadata, cudaStream_t st) {
   (void)metadata;           // the reference keeps its CUTLASS problem descriptors there; not needed here
   if (!out || !x || !w || !ranges || !grouped_shape_ok(groups, n, k)) return cudaErrorInvalidValue;
-  return launch_grouped_bf16(out, nullptr, x, w, ranges, groups, n, k, nullptr, st);
+  return launch_grouped_bf16(out, nullptr, x, w, ranges, groups, n, k, nullptr, st, 0);
 }
 
 extern "C" int hayate_glm_grouped_nvfp4(void* out, void* accumulator, const void* x, const void* w, const void* ranges, unsigned groups,
                                         unsigned n, unsigned k, void* metadata, const void* scales, unsigned max_rows, cudaStream_t st) {
   (void)metadata;
   if (!out || !accumulator || !x || !w || !ranges || !scales || !max_rows || !grouped_shape_ok(groups, n, k)) return cudaErrorInvalidValue;
-  return launch_grouped_bf16(out, static_cast<float*>(accumulator), x, w, ranges, groups, n, k, static_cast<const float*>(scales), st);
+  return launch_grouped_bf16(out, static_cast<float*>(accumulator), x, w, ranges, groups, n, k, static_cast<const float*>(scales), st, 0);
 }
 
 extern "C" int hayate_glm_nvfp4_restore(void* out, const void* image, unsigned n, unsigned k, cudaStream_t st) {

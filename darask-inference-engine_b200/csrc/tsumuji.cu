@@ -129,7 +129,7 @@ __global__ void __launch_bounds__(256) tsumuji_ep_combine_kernel(float* out, con
 // ---- shared expert of a token window on the tensor cores ---------------------------------------------------------
 // hayate_prefill.cu: ragged grouped bf16 GEMM (tcgen05), float32 accumulator output
 cudaError_t launch_grouped_bf16(void* out, float* acc, const void* x, const void* w, const void* ranges, unsigned groups,
-                                unsigned n, unsigned k, const float* scales, cudaStream_t st);
+                                unsigned n, unsigned k, const float* scales, cudaStream_t st, unsigned w_rows);
 // float32 rows -> bf16 "hi" rows [0, N) and bf16 "lo" rows [N, 2N) with x = hi + lo up to 2^-17 |x|; one group of 2N rows
 __global__ void __launch_bounds__(256) split_rows_kernel(const float* x, int rows, int k, __nv_bfloat16* hl, unsigned* ranges) {
   pdl_wait();
@@ -165,6 +165,16 @@ __global__ void __launch_bounds__(256) add_halves_kernel(const float* acc, int r
   if (i < total) y[i] = acc[i] + acc[total + i];
 }
 
+// acc [2N][ld_acc] (hi rows then lo rows of the router products) -> logits [N][rows]
+__global__ void __launch_bounds__(256) add_logits_kernel(const float* acc, int tokens, int ld_acc, int rows, float* logits) {
+  pdl_wait();
+  pdl_launch();
+  const size_t i = size_t(blockIdx.x) * 256 + threadIdx.x, total = size_t(tokens) * rows;
+  if (i >= total) return;
+  const size_t t = i / rows, c = i % rows;
+  logits[i] = acc[t * ld_acc + c] + acc[(t + tokens) * ld_acc + c];
+}
+
 constexpr int kWindowTokens = 16;      // more tokens than this: the batched front end and the tensor-core shared expert
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 struct TsumujiWs {
@@ -191,7 +201,10 @@ static TsumujiWs carve(void* base, int hidden, int inter, int experts, int topk,
   w.hplanes = reinterpret_cast<__half*>(take(rows * 2 * inter * 2));
   w.y = reinterpret_cast<float*>(take(rows * hidden * 4));
   w.perm_scratch = reinterpret_cast<int*>(take(permute_scratch_bytes(tokens, topk, experts)));
-  const size_t wide = size_t(hidden > 2 * inter ? hidden : 2 * inter), win = tokens > kWindowTokens ? size_t(tokens) : 0;
+  const size_t router_pad = (size_t(experts) + 1 + 127) / 128 * 128;     // router rows as a multiple of the 128-row weight tiles
+  size_t wide = size_t(hidden > 2 * inter ? hidden : 2 * inter);
+  if (router_pad > wide) wide = router_pad;
+  const size_t win = tokens > kWindowTokens ? size_t(tokens) : 0;
   w.sh_ranges = reinterpret_cast<unsigned*>(take(8));
   w.sh_x = reinterpret_cast<__nv_bfloat16*>(take(2 * win * hidden * 2));
   w.sh_acc = reinterpret_cast<float*>(take(2 * win * wide * 4));
@@ -205,7 +218,17 @@ static TsumujiWs carve(void* base, int hidden, int inter, int experts, int topk,
 static cudaError_t route_window(const void* router_w, const float* x, const RouteArgs& route, const PermuteArgs& perm, const TsumujiWs& w,
                                 int H, int E, int N, cudaStream_t st) {
   cudaError_t e;
-  if (router_w) {
+  const unsigned blocks_x = unsigned((size_t(N) * H + 255) / 256);
+  const bool tiles = H % 64 == 0;          // the float32 rows as bf16 hi + lo rows (also the shared expert's operand)
+  if (tiles && (e = launch_pdl(split_rows_kernel, dim3(blocks_x), dim3(256), 0, st, x, N, H, w.sh_x, w.sh_ranges))) return e;
+  if (router_w && tiles) {
+    // logits = W x on the tcgen05 bf16 grouped GEMM: one group of 2N rows against the E + 1 router rows (padded to
+    // 128-row tiles that read zeros), then hi + lo
+    const unsigned npad = unsigned((E + 1 + 127) / 128 * 128);
+    if ((e = launch_grouped_bf16(w.sh_out, w.sh_acc, w.sh_x, router_w, w.sh_ranges, 1, npad, unsigned(H), nullptr, st, unsigned(E + 1)))) return e;
+    if ((e = launch_pdl(add_logits_kernel, dim3(unsigned((size_t(N) * (E + 1) + 255) / 256)), dim3(256), 0, st, (const float*)w.sh_acc, N,
+                        int(npad), E + 1, const_cast<float*>(route.logits)))) return e;
+  } else if (router_w) {
     static bool configured = false;
     const size_t smem = size_t(kRouterBatchRows) * H * 2;
     if (!configured && smem > 48 * 1024) {
@@ -224,11 +247,11 @@ static cudaError_t route_window(const void* router_w, const float* x, const Rout
 // hi / lo split of the float32 operands (exact bf16 weights, float32 accumulation)
 static cudaError_t shared_expert_window(const TsumujiMoe* d, const TsumujiWs& w, int N, int H, int F, float* y_out, cudaStream_t st) {
   cudaError_t e;
+  // w.sh_x / w.sh_ranges: the hi / lo split of x, written by route_window
   const unsigned blocks_x = unsigned((size_t(N) * H + 255) / 256), blocks_h = unsigned((size_t(N) * F + 255) / 256);
-  if ((e = launch_pdl(split_rows_kernel, dim3(blocks_x), dim3(256), 0, st, d->x, N, H, w.sh_x, w.sh_ranges))) return e;
-  if ((e = launch_grouped_bf16(w.sh_out, w.sh_acc, w.sh_x, d->shared_gu, w.sh_ranges, 1, unsigned(2 * F), unsigned(H), nullptr, st))) return e;
+  if ((e = launch_grouped_bf16(w.sh_out, w.sh_acc, w.sh_x, d->shared_gu, w.sh_ranges, 1, unsigned(2 * F), unsigned(H), nullptr, st, 0))) return e;
   if ((e = launch_pdl(shared_swiglu_kernel, dim3(blocks_h), dim3(256), 0, st, (const float*)w.sh_acc, N, F, w.sh_h))) return e;
-  if ((e = launch_grouped_bf16(w.sh_out, w.sh_acc, w.sh_h, d->shared_down, w.sh_ranges, 1, unsigned(H), unsigned(F), nullptr, st))) return e;
+  if ((e = launch_grouped_bf16(w.sh_out, w.sh_acc, w.sh_h, d->shared_down, w.sh_ranges, 1, unsigned(H), unsigned(F), nullptr, st, 0))) return e;
   return launch_pdl(add_halves_kernel, dim3(blocks_x), dim3(256), 0, st, (const float*)w.sh_acc, N, H, y_out);
 }
 
