@@ -23,46 +23,6 @@ __global__ void __launch_bounds__(256) tsumuji_combine_kernel(float* out, const 
   out[size_t(n) * hidden + i] = accumulate ? out[size_t(n) * hidden + i] + o : o;
 }
 
-// Router projection for token windows (N > 16): logits[t][row] = W[row] . x[t]. A block keeps four bf16 router rows in
-// shared memory; each of its 8 warps takes every 8th token, reads the token's float32 row once and forms the four
-// dot products. (The one-block-per-row kernel re-reads all N token rows in every block.)
-constexpr int kRouterBatchRows = 4;
-__global__ void __launch_bounds__(256) router_batch_kernel(const __nv_bfloat16* w, const float* x, float* logits, int rows, int hidden,
-                                                           int ld, int tokens) {
-  extern __shared__ __align__(16) uint8_t rb_smem[];
-  __nv_bfloat16* ws = reinterpret_cast<__nv_bfloat16*>(rb_smem);      // [4][hidden]
-  const int row0 = blockIdx.x * kRouterBatchRows, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  for (int i = threadIdx.x; i < kRouterBatchRows * hidden / 8; i += 256) {
-    const int r = i / (hidden / 8), c = i % (hidden / 8);
-    reinterpret_cast<uint4*>(ws)[i] = row0 + r < rows ? __ldg(reinterpret_cast<const uint4*>(w + size_t(row0 + r) * hidden) + c)
-                                                      : make_uint4(0, 0, 0, 0);
-  }
-  pdl_wait();
-  pdl_launch();
-  __syncthreads();
-  for (int t = warp; t < tokens; t += 8) {
-    const float4* xr = reinterpret_cast<const float4*>(x + size_t(t) * hidden);
-    float acc[kRouterBatchRows] = {0.f, 0.f, 0.f, 0.f};
-    for (int c = lane; c < hidden / 4; c += 32) {
-      const float4 v = __ldg(xr + c);
-#pragma unroll
-      for (int r = 0; r < kRouterBatchRows; ++r) {
-        const uint2 q = *reinterpret_cast<const uint2*>(ws + size_t(r) * hidden + c * 4);
-        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&q.x), b = *reinterpret_cast<const __nv_bfloat162*>(&q.y);
-        acc[r] = fmaf(__low2float(a), v.x, acc[r]);
-        acc[r] = fmaf(__high2float(a), v.y, acc[r]);
-        acc[r] = fmaf(__low2float(b), v.z, acc[r]);
-        acc[r] = fmaf(__high2float(b), v.w, acc[r]);
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < kRouterBatchRows; ++r) {
-      const float v = warp_sum(acc[r]);
-      if (lane == 0 && row0 + r < rows) logits[size_t(t) * ld + row0 + r] = v;
-    }
-  }
-}
-
 // stand-alone routing of given logits followed by the permutation, one block
 template <int MODE>
 __global__ void __launch_bounds__(128) route_permute_kernel(RouteArgs r, PermuteArgs p) {
@@ -219,24 +179,15 @@ static cudaError_t route_window(const void* router_w, const float* x, const Rout
                                 int H, int E, int N, cudaStream_t st) {
   cudaError_t e;
   const unsigned blocks_x = unsigned((size_t(N) * H + 255) / 256);
-  const bool tiles = H % 64 == 0;          // the float32 rows as bf16 hi + lo rows (also the shared expert's operand)
-  if (tiles && (e = launch_pdl(split_rows_kernel, dim3(blocks_x), dim3(256), 0, st, x, N, H, w.sh_x, w.sh_ranges))) return e;
-  if (router_w && tiles) {
+  // the float32 rows as bf16 hi + lo rows (also the shared expert's operand); H is a multiple of 256 here
+  if ((e = launch_pdl(split_rows_kernel, dim3(blocks_x), dim3(256), 0, st, x, N, H, w.sh_x, w.sh_ranges))) return e;
+  if (router_w) {
     // logits = W x on the tcgen05 bf16 grouped GEMM: one group of 2N rows against the E + 1 router rows (padded to
     // 128-row tiles that read zeros), then hi + lo
     const unsigned npad = unsigned((E + 1 + 127) / 128 * 128);
     if ((e = launch_grouped_bf16(w.sh_out, w.sh_acc, w.sh_x, router_w, w.sh_ranges, 1, npad, unsigned(H), nullptr, st, unsigned(E + 1)))) return e;
     if ((e = launch_pdl(add_logits_kernel, dim3(unsigned((size_t(N) * (E + 1) + 255) / 256)), dim3(256), 0, st, (const float*)w.sh_acc, N,
                         int(npad), E + 1, const_cast<float*>(route.logits)))) return e;
-  } else if (router_w) {
-    static bool configured = false;
-    const size_t smem = size_t(kRouterBatchRows) * H * 2;
-    if (!configured && smem > 48 * 1024) {
-      if ((e = cudaFuncSetAttribute(router_batch_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)))) return e;
-      configured = true;
-    }
-    if ((e = launch_pdl(router_batch_kernel, dim3((E + 1 + kRouterBatchRows - 1) / kRouterBatchRows), dim3(256), smem, st,
-                        static_cast<const __nv_bfloat16*>(router_w), x, const_cast<float*>(route.logits), E + 1, H, E + 1, N))) return e;
   }
   if ((e = launch_pdl(route_topk_kernel<kRouteTsumuji>, dim3((N + 3) / 4), dim3(128), 0, st, route))) return e;
   if ((e = launch_permute_large(perm, w.perm_scratch, st))) return e;

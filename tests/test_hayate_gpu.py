@@ -56,6 +56,12 @@ def test_small_layer(tokens):
     check_layer(layer, acts)
 
 
+def test_many_tokens_per_expert():
+    # 8 experts, top-4, 19 tokens: an expert serves about ten tokens (eight-token passes, a second pass, ragged groups)
+    layer, acts = W.hayate_layer(42, hidden=512, inter=256, experts=8, topk=4, tokens=19, scale=2.5, pool=8)
+    check_layer(layer, acts)
+
+
 @pytest.mark.parametrize("tokens", [1, 8])
 def test_config3_glm_decode(tokens):
     # hidden 2048, 64 experts, sigmoid + bias, top-4, scale 1.8, intermediate 1536, NVFP4, one shared expert, seed 2
