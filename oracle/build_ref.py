@@ -7,7 +7,7 @@
   compiled unmodified for sm_100a, used on a GPU as a second opinion.
 
 The ``_ref`` outputs are only built when a reference checkout is present (path in the
-``DARASK_REFERENCE`` environment variable, default ``/root/reference``); sources are compiled
+``DARASK_REFERENCE`` environment variable, with a default for the build container); sources are compiled
 from where they lie and never copied.  Machines without the checkout use the prebuilt files.
 """
 from __future__ import annotations
