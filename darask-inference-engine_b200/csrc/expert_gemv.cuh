@@ -49,6 +49,10 @@ struct GemvArgs {
   unsigned long long gscale_in_matrix[2]; // non-zero: the multiplier is the float32 at this byte offset of the matrix itself
   int k, rows, nblk;            // columns, rows per matrix, k / 256
   int ks;                       // warps that split K for one row slab (divides nblk and the warps per CTA)
+  // derived on the host from ks and the grid (launch_gemv): blocks per item, 65536 / ks + 1, slab groups per CTA, and
+  // the slabs all CTAs advance per round as (whole groups, remainder)
+  int nb_per, ks_inv, slab_groups;
+  unsigned group_step, slab_step;
   const __half* xplanes;        // [x rows][2][k] activation planes
   const __half* xsum_planes;    // [x rows][2][k/32] sums of x over 32 columns as fp16 hi / lo planes (Q4_K mins); null: use tiles
   int x_by_assignment;          // 0: x row = token; 1: x row = assignment index
@@ -478,35 +482,31 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
   constexpr bool NV = FMT == kGemvNvfp4Linear || FMT == kGemvNvfp4Tiled;
   constexpr bool NATURAL = NV || FMT == kGemvFp8Block;    // activation planes in natural column order
   const unsigned tiles_per_group = (a.rows + RPT - 1) / RPT;
-  const int nb_per = a.nblk / a.ks;
+  const int nb_per = a.nb_per;
   const int groups = __ldcg(a.counters);
   const int g4 = lane >> 2, j = lane & 3;
   const int shared_row0 = a.out_shared_row;
   bool waited = !a.late_wait;
   // ---- this lane's share of a stage: fixed for the whole launch -------------------------------------------
   // The contiguous chunks of a block: LW lanes copy the NR row slots of one matrix (DUAL: lanes 0-15 the gate
-  // slots 0-7, lanes 16-31 the up slots 8-15). Chunk cm = lane % LW + LW * i -> (row slot, 16-byte part).
+  // slots 0-7, lanes 16-31 the up slots 8-15), P lanes per row slot (lane % P = the 16-byte part, parts past the
+  // row's chunks idle), copy i of a lane = row slot i * RPI + sub.
   constexpr int LW = DUAL ? 16 : 32, NR = DUAL ? 8 : 16;
-  constexpr int NI = (NR * LY::kChunks + LW - 1) / LW;
+  constexpr int P = LY::kChunks <= 8 ? 8 : 16, RPI = LW / P, NI = NR / RPI;
+  constexpr int ROW_STEP = FMT == kGemvNvfp4Tiled ? 32 : RPI;       // matrix rows between two copies of a lane
   const int lm = DUAL ? (lane >> 4) : 0, ll = lane & (LW - 1);
-  uint32_t src_c[NI], dst_c[NI];             // byte offsets from the slab's first row / from the stage
-#pragma unroll
-  for (int i = 0; i < NI; ++i) {
-    const int cm = ll + LW * i;
-    const int slot = cm / LY::kChunks, part = cm - slot * LY::kChunks;
-    dst_c[i] = (lm * 8 + slot) * LY::kPitch + part * 16;
-    src_c[i] = cm < NR * LY::kChunks ? uint32_t(slab_rowc<FMT, DUAL>(slot)) * uint32_t(a.row_bytes) + part * 16 : 0xffffffffu;
-  }
+  const int part = ll & (P - 1), sub = ll / P;
+  const uint32_t lane_dst = (lm * 8 + sub) * LY::kPitch + part * 16;   // + i * RPI * kPitch
+  const uint32_t lane_src = uint32_t(sub) * uint32_t(a.row_bytes) + part * 16;
+  const uint32_t src_step = uint32_t(ROW_STEP) * uint32_t(a.row_bytes);
   // lanes 0-15: the row slot whose extra chunk (Q6_K d, linear NVFP4 scales) or scale piece (tiled NVFP4) they copy
   const int xm = DUAL ? (lane >> 3) & 1 : 0, xs8 = DUAL ? (lane & 7) : (lane & 15);
   // ---- items: (group, slab, K part); the ks warps of a slab are neighbours in the CTA ------------------------
-  const unsigned ks = a.ks;
-  const unsigned w0 = blockIdx.x * kGemvWarps + warp;
-  const unsigned tile0 = w0 / ks;
-  const int kpart = int(w0 - tile0 * ks);
-  const unsigned tstep = gridDim.x * (kGemvWarps / ks);
+  const int slab_group = (warp * a.ks_inv) >> 16;             // warp / ks
+  const int kpart = warp - slab_group * a.ks;
+  const unsigned tile0 = blockIdx.x * unsigned(a.slab_groups) + unsigned(slab_group);
   unsigned grp = tile0 / tiles_per_group, slab_u = tile0 - grp * tiles_per_group;
-  const unsigned gstep = tstep / tiles_per_group, sstep = tstep - gstep * tiles_per_group;
+  const unsigned gstep = a.group_step, sstep = a.slab_step;
   const int b_first = kpart * nb_per;
   auto next_item = [&]() {                   // tile += tstep, without a division
     slab_u += sstep;
@@ -533,9 +533,10 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
     }
     // ---- weight stream: 16 row slots x one block per stage --------------------------------------------
     const int row0 = slab_row0<FMT, DUAL>(int(slab_u));
-    // bytes of the slab's rows that exist (row slots past the last row of the matrix are not copied)
-    const uint32_t live_bytes = FMT == kGemvNvfp4Tiled ? 0xfffffffeu : uint32_t(min(a.rows - row0, NR)) * uint32_t(a.row_bytes);
-    const uint8_t* lane_rows = mbase[lm] + size_t(row0) * a.row_bytes + size_t(b_first) * LY::kBlk;
+    // copies of this lane whose row exists (row slots past the last row of the matrix are not copied)
+    int n_copies = part < LY::kChunks ? NI : 0;
+    if (FMT != kGemvNvfp4Tiled) n_copies = min(n_copies, max(0, (a.rows - row0 - sub + RPI - 1) / RPI));
+    const uint8_t* lane_rows = mbase[lm] + size_t(row0) * a.row_bytes + size_t(b_first) * LY::kBlk + lane_src;
     // extra chunk / scale pieces: source of block b_first (lanes 0-15)
     const uint8_t* extra = nullptr;
     if (lane < 16) {
@@ -559,7 +560,7 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
       const uint8_t* src = lane_rows + i_blk * LY::kBlk;
 #pragma unroll
       for (int i = 0; i < NI; ++i)
-        if (src_c[i] < live_bytes) cp_async16(dst + dst_c[i], src + src_c[i]);
+        if (i < n_copies) cp_async16(dst + lane_dst + i * (RPI * LY::kPitch), src + size_t(i) * src_step);
       if (FMT == kGemvQ6KR) {
         if (extra) cp_async16(dst + lane * LY::kPitch + 208, extra + ((2 * (b_first + i_blk)) & ~15));
       } else if (FMT == kGemvNvfp4Linear) {

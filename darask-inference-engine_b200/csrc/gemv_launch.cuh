@@ -23,6 +23,13 @@ inline cudaError_t launch_gemv(GemvArgs a, cudaStream_t stream) {
   const long long slabs = (long long)a.max_groups * ((a.rows + RPT - 1) / RPT);
   a.ks = gemv_k_split(a.nblk, slabs, sm_count());
   if (slabs * a.ks >= (1ll << 31)) return cudaErrorInvalidValue;       // the kernel counts items in 32 bits
+  const unsigned tiles_per_group = unsigned((a.rows + RPT - 1) / RPT);
+  a.nb_per = a.nblk / a.ks;
+  a.ks_inv = 65536 / a.ks + 1;
+  a.slab_groups = kGemvWarps / a.ks;
+  const unsigned slab_round = unsigned(sm_count()) * unsigned(a.slab_groups);   // slabs all CTAs take per round
+  a.group_step = slab_round / tiles_per_group;
+  a.slab_step = slab_round % tiles_per_group;
   if (a.out_shared_row == 0) a.out_shared_row = a.tokens * a.topk;
   if (FMT == kGemvNvfp4Tiled && a.rows % 128) return cudaErrorInvalidValue;
   const int smem = gemv_smem_bytes<FMT>();
