@@ -107,8 +107,8 @@ DEVI uint32_t u4w(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : 
 
 // The block functions below multiply one staged 256-column block of 16 row slots with up to NT groups of four
 // tokens: the weight fragments are built once and feed one tile per token group. `bcol[t]`: this lane's B plane
-// of group t (column g = lane/4 -> token g/2 of the group, hi or lo) at the block's first column, or null for an
-// empty column. `facc[t]`: the sums of rows g / g + 8 for token j = lane % 4 of group t.
+// of group t (column g = lane/4 -> token g/2 of the group, hi or lo) at the block's first column; a column without
+// a token gets the plane of another token, its sums are discarded. `facc[t]`: the sums of rows g / g + 8 for token j = lane % 4 of group t.
 
 // ---- Q4_K -------------------------------------------------------------------------------------------
 // Row slot pitch PITCH: header 16 B, nibbles 128 B. value = d*sc*q - dmin*m (kogarashi kernels/native.cu:26-34).
@@ -145,12 +145,8 @@ DEVI void q4k_block_f16(uint32_t slab, int lane, const __half* const (&bcol)[NT]
     uint4 blo[NT], bhi[NT];
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
-      blo[t] = make_uint4(0, 0, 0, 0);
-      bhi[t] = make_uint4(0, 0, 0, 0);
-      if (bcol[t]) {
-        blo[t] = __ldg(reinterpret_cast<const uint4*>(bcol[t] + gp * 64 + 8 * j));
-        bhi[t] = __ldg(reinterpret_cast<const uint4*>(bcol[t] + gp * 64 + 32 + 8 * j));
-      }
+      blo[t] = __ldg(reinterpret_cast<const uint4*>(bcol[t] + gp * 64 + 8 * j));
+      bhi[t] = __ldg(reinterpret_cast<const uint4*>(bcol[t] + gp * 64 + 32 + 8 * j));
     }
     const uint32_t words0[2] = {w0.x, w0.y}, words1[2] = {w1.x, w1.y};
 #pragma unroll
@@ -233,12 +229,8 @@ DEVI void q6k_block_f16(uint32_t slab, int lane, int doff, const __half* const (
         uint2 blo[NT], bhi[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
-          blo[t] = make_uint2(0, 0);
-          bhi[t] = make_uint2(0, 0);
-          if (bcol[t]) {
-            blo[t] = __ldg(reinterpret_cast<const uint2*>(bcol[t] + col));
-            bhi[t] = __ldg(reinterpret_cast<const uint2*>(bcol[t] + col + 64));
-          }
+          blo[t] = __ldg(reinterpret_cast<const uint2*>(bcol[t] + col));
+          bhi[t] = __ldg(reinterpret_cast<const uint2*>(bcol[t] + col + 64));
         }
 #pragma unroll
         for (int hi = 0; hi < 2; ++hi) {
@@ -349,10 +341,7 @@ DEVI void nvfp4_block_f16(uint32_t slab, int lane, const __half* const (&bcol)[N
     e2m1x4_to_h2(w1 >> 16, b45, b67);
     uint4 x[NT];
 #pragma unroll
-    for (int t = 0; t < NT; ++t) {
-      x[t] = make_uint4(0, 0, 0, 0);
-      if (bcol[t]) x[t] = __ldg(reinterpret_cast<const uint4*>(bcol[t] + q * 32 + 8 * j));
-    }
+    for (int t = 0; t < NT; ++t) x[t] = __ldg(reinterpret_cast<const uint4*>(bcol[t] + q * 32 + 8 * j));
     a01 = h2_as_u32(__hmul2(u32_as_h2(a01), s0)); a23 = h2_as_u32(__hmul2(u32_as_h2(a23), s0));
     a45 = h2_as_u32(__hmul2(u32_as_h2(a45), s0)); a67 = h2_as_u32(__hmul2(u32_as_h2(a67), s0));
     b01 = h2_as_u32(__hmul2(u32_as_h2(b01), s1)); b23 = h2_as_u32(__hmul2(u32_as_h2(b23), s1));
@@ -398,10 +387,7 @@ DEVI void fp8_block_f16(uint32_t slab, int lane, const __half* const (&bcol)[NT]
       const uint2 w0 = lds64(r0 + col), w1 = lds64(r1 + col);
       uint4 x[NT];
 #pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        x[t] = make_uint4(0, 0, 0, 0);
-        if (bcol[t]) x[t] = __ldg(reinterpret_cast<const uint4*>(bcol[t] + col));
-      }
+      for (int t = 0; t < NT; ++t) x[t] = __ldg(reinterpret_cast<const uint4*>(bcol[t] + col));
       const uint32_t a01 = round_bf16_pair(e4m3x2_to_h2(w0.x & 0xffffu), rm0), a23 = round_bf16_pair(e4m3x2_to_h2(w0.x >> 16), rm0);
       const uint32_t a45 = round_bf16_pair(e4m3x2_to_h2(w0.y & 0xffffu), rm0), a67 = round_bf16_pair(e4m3x2_to_h2(w0.y >> 16), rm0);
       const uint32_t b01 = round_bf16_pair(e4m3x2_to_h2(w1.x & 0xffffu), rm1), b23 = round_bf16_pair(e4m3x2_to_h2(w1.x >> 16), rm1);
@@ -624,10 +610,10 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
 #pragma unroll
       for (int t = 0; t < NT; ++t) {
         // this lane's B column g4 -> token g4/2 of the group, hi (even) or lo (odd) plane
-        const int tcol = c0 + 4 * t + (g4 >> 1);
-        plane[t] = nullptr;
+        // (a column without a token reads the rows of token c0: its sums are never stored)
+        const int tcol = c0 + 4 * t + (g4 >> 1) < count ? c0 + 4 * t + (g4 >> 1) : c0;
         xs[t] = nullptr;
-        if (tcol < count) {
+        {
           const int as = e < 0 ? shared_row0 + tcol : int(__ldcg(a.assignments + offset + tcol));
           const int xrow = a.x_by_assignment ? as : (e < 0 ? a.shared_x_row0 + tcol : as / a.topk);
           plane[t] = a.xplanes + (size_t(xrow) * 2 + (g4 & 1)) * a.k + size_t(b_first) * 256;
@@ -660,7 +646,7 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
         const __half* xsb[NT];
 #pragma unroll
         for (int t = 0; t < NT; ++t) {
-          bcol[t] = plane[t] ? plane[t] + i * 256 : nullptr;
+          bcol[t] = plane[t] + i * 256;
           xsb[t] = xs[t] ? xs[t] + i * 8 : nullptr;
         }
         if (FMT == kGemvQ4K) q4k_block_f16<LY::kPitch, MINS_TILE, NT>(slab, lane, bcol, xsb, facc);
