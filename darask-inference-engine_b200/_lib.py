@@ -22,7 +22,7 @@ class KogarashiMoe(ctypes.Structure):
         ("down_w", c_void_p), ("down_ty", c_int),
         ("sh_gate_w", c_void_p), ("sh_up_w", c_void_p), ("sh_down_w", c_void_p), ("sh_inp_w", c_void_p),
         ("n", c_void_p), ("x", c_void_p), ("logits", c_void_p), ("ids", c_void_p), ("prob", c_void_p),
-        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("stage_mask", c_int),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("reserved", c_int),
     ]
 
 
@@ -126,6 +126,7 @@ _SIGNATURES = {
     "kogarashi_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "kogarashi_moe_workspace_init": (c_int, [c_void_p, c_size_t, c_void_p]),
     "kogarashi_moe_layer": (c_int, [ctypes.POINTER(KogarashiMoe), c_void_p]),
+    "kogarashi_moe_set_single_launch": (c_int, [c_int]),
     "kogarashi_moe_static_scratch_bytes": (c_size_t, []),
     "kogarashi_moe_layer_static": (c_int, [ctypes.POINTER(KogarashiMoe), c_void_p]),
     "kogarashi_moe_status": (c_int, [c_void_p, ctypes.POINTER(c_uint), c_void_p]),

@@ -1,0 +1,645 @@
+// One-token Kogarashi MoE FFN layer as ONE persistent launch (one CTA per SM).
+//
+//   phase R   every CTA projects its one or two router rows (fetched before the dependency wait), writes the logits,
+//             arrives at grid barrier 1; the producer warp of every CTA then selects the top-k itself (same result
+//             everywhere), so no CTA waits for a routing block and no plan travels through global memory
+//   phase 1   gate/up tiles (8 gate rows + the 8 matching up rows) x K parts, SwiGLU product written as fp16 hi/lo
+//   barrier 2 all products visible; every CTA stages the K+1 product vectors in shared memory
+//   phase 2   down tiles (16 rows of one expert) x K parts as float32 partial rows; the warp that completes a
+//             16-row tile (a counter per tile) adds the weighted experts in slot order and the gated shared expert
+//             into the residual stream
+//
+// The weight stream does not stop at the barriers: one producer warp issues `cp.async.bulk` row copies into a ring of
+// stages in a fixed unit order (shared expert first, then the routed experts, then the down units); while the gate/up
+// units are being multiplied the ring refills with down weights, which depend on the routing only.
+//
+// Arithmetic per 256-column block, `mma.sync.m16n8k16` (fp16 in, fp32 accumulate): the A operand holds the weight
+// codes as fp16 magic numbers (1024 + q, no conversion, no per-weight scaling); the B operand is block diagonal: the
+// sixteen k slots of a tile belong to four different scale groups of the block and column pair s of the tile holds
+// the activation (hi plane, lo plane) only in the four slots of group s. Column pair s of the accumulator is then the
+// raw code sum of scale group s, and the group scales, the 1024 offset (through per-group sums of the activations)
+// and the Q4_K minimum are applied once per block and lane in float32.
+//
+// Replaces kogarashi kernels/native.cu:46-117 (`gemv`, `activate`, `route`, `combine`) for one token; formulas of the
+// formats: native.cu:26-40 and :52-82.
+#pragma once
+#include "common.cuh"
+#include "expert_gemv.cuh"
+#include "route_impl.cuh"
+
+namespace dmoe {
+
+constexpr unsigned kStatusActRange = 4u;   // an activation does not fit the fp16 planes (|value| > 65504)
+
+constexpr int kFusedConsumers = 16;                          // consumer warps
+constexpr int kFusedThreads = (kFusedConsumers + 1) * 32;    // + the producer warp
+constexpr int kFusedSlots = 16;                              // gate/up tiles whose partial sums may be pending
+constexpr int kFusedMaxStages = 30;
+constexpr int kFusedZeroBytes = 2560;                        // zero fragments read by lanes outside a column's group
+
+struct FusedArgs {
+  const float* router_w; const float* router_bias; const float* sh_inp;
+  const uint8_t* gate_w; const uint8_t* up_w; const uint8_t* down_w;
+  const uint8_t* sh_gate; const uint8_t* sh_up; const uint8_t* sh_down;
+  const float* n; float* x; float* logits; int* ids; float* prob;
+  int H, F, E, K, G, has_shared;
+  int kp1, nbu1, pitch1, row_bytes1, tpg;         // gate/up: K parts, blocks per unit, row slot pitch, tiles per group
+  int kp2, nbu2, pitch2, row_bytes2, rt2, down_q6; // down: the same, 16-row tiles of the output
+  int nblk2;
+  int stage_bytes, nstage;
+  int off_bars, off_psum, off_zero, off_act, off_ring;   // shared-memory offsets
+  int act_lo1, act_xs1, act_rows;                 // phase R/1 inside the activation area: lo-plane stride, sums, router rows
+  int act_lo2, act_grp2, act_xs2;                 // phase 2: lo-plane stride, bytes per group, offset of the sums
+  unsigned* gbar; unsigned* tile_cnt; unsigned* status; __half* hbuf; float* y; float* sg;
+};
+
+// ---- small pieces -----------------------------------------------------------------------------------------
+DEVI unsigned ld_acquire_u32(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// One thread per CTA: arrive and wait until `target` CTAs have arrived. Bounded; false after the time limit.
+DEVI bool grid_arrive_wait(unsigned* counter, unsigned target, unsigned* status, volatile int* abort_flag) {
+  __threadfence();
+  atomicAdd(counter, 1u);
+  const uint64_t start = global_timer_ns();
+  for (uint32_t spin = 1;; ++spin) {
+    if (ld_acquire_u32(counter) >= target) return true;
+    if ((spin & 31u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - start > kWaitLimitNs) {
+        atomicOr(status, kStatusWaitTimeout);
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+DEVI bool grid_wait(const unsigned* counter, unsigned target, unsigned* status, volatile int* abort_flag) {
+  const uint64_t start = global_timer_ns();
+  for (uint32_t spin = 1;; ++spin) {
+    if (ld_acquire_u32(counter) >= target) return true;
+    if ((spin & 31u) == 0) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - start > kWaitLimitNs) {
+        atomicOr(status, kStatusWaitTimeout);
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+// mbarrier wait that also leaves when another role gave up
+DEVI bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, unsigned* status, volatile int* abort_flag) {
+  const uint32_t addr = smem_u32(bar);
+  uint64_t start = 0;
+  for (uint32_t spin = 0;; ++spin) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity), "r"(10000u)
+        : "memory");
+    if (ok) return true;
+    if (*abort_flag) return false;
+    if ((spin & 15u) == 0) {
+      const uint64_t now = global_timer_ns();
+      if (spin == 0) start = now;
+      else if (now - start > kWaitLimitNs) {
+        atomicOr(status, kStatusWaitTimeout);
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+DEVI float magic_u8(uint32_t v) { return __uint_as_float(0x4B000000u | v) - kMagic; }   // small unsigned integer -> float
+DEVI float quad_sum(float v) {            // over the four lanes that share g = lane / 4
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  return v;
+}
+
+// Lane constants of the block-diagonal tiles. Lane = (g, j), g = lane / 4, j = lane % 4.
+//   A side: lanes j = 0,1 supply k slots 0-3 (a0/a1) and 8-11 (a2/a3), lanes j = 2,3 slots 4-7 and 12-15.
+//   B side: column g of the tile belongs to column pair s = g / 2 (plane g % 2); of this lane's two B registers only
+//           the one whose slots lie in slot group s is non-zero, and only when j / 2 == s % 2.
+//   D side: this lane holds columns 2j, 2j+1 = (hi, lo) sums of slot group j for rows g and g + 8.
+struct DiagLane {
+  int g, j;
+  bool active, second;     // B: this lane carries activations; in b1 (slot groups 2, 3) instead of b0
+  int plane;               // B: 0 hi, 1 lo
+};
+DEVI DiagLane diag_lane(int lane) {
+  DiagLane d;
+  d.g = lane >> 2; d.j = lane & 3;
+  const int s = d.g >> 1;
+  d.plane = d.g & 1;
+  d.active = (d.j >> 1) == (s & 1);
+  d.second = s >= 2;
+  return d;
+}
+
+// ---- Q4_K: one block (16 row slots x 256 columns) against one activation vector ----------------------------------
+// Tile t of the block covers sub-blocks 4t .. 4t+3: slot group 0 = low nibbles of bytes 64t .. 64t+31 (sub-block 4t),
+// group 1 = low nibbles of bytes 64t+32 .. (sub-block 4t+2), groups 2 / 3 = the high nibbles of the same bytes
+// (sub-blocks 4t+1 / 4t+3). Lane j reads bytes 64t + 16j .. +15 of rows g and g + 8.
+//   rA / rB: shared-memory address of the block in row slots g / g + 8
+//   xb0 / xb1: address of this lane's B fragments of tile 0 (16 halves = columns base .. base+15 in [x0,x2,x1,x3]
+//              order) or of the zero area; the next tile is 256 bytes further in both
+//   xs: float sums of (hi + lo) over the eight sub-blocks of this block
+DEVI void q4k_block_diag(uint32_t rA, uint32_t rB, int j, uint32_t xb0, uint32_t xb1, uint32_t xs, float& acc0, float& acc1) {
+  const uint4 hA = lds128(rA), hB = lds128(rB);
+  const int sbl = 2 * (j & 1) + (j >> 1);         // this lane's sub-block inside a tile (slot group j)
+  const int sh = 8 * sbl;
+  const float nib = j >= 2 ? 0.0625f : 1.f;       // high nibbles enter the tiles as 1024 + 16 q
+  const float dA = half_lo(hA.x) * nib, mA = half_hi(hA.x), dB = half_lo(hB.x) * nib, mB = half_hi(hB.x);
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    const uint4 wA = lds128(rA + 16 + 64 * t + 16 * j), wB = lds128(rB + 16 + 64 * t + 16 * j);
+    const uint4 p0 = lds128(xb0 + 256 * t), p1 = lds128(xb0 + 256 * t + 16);
+    const uint4 q0 = lds128(xb1 + 256 * t), q1 = lds128(xb1 + 256 * t + 16);
+    float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t a = u4w(wA, q), b = u4w(wB, q), as = a >> 8, bs = b >> 8;
+      const uint32_t e0 = q < 2 ? u4w(p0, 2 * q) : u4w(p1, 2 * q - 4), e1 = q < 2 ? u4w(p0, 2 * q + 1) : u4w(p1, 2 * q - 3);
+      const uint32_t f0 = q < 2 ? u4w(q0, 2 * q) : u4w(q1, 2 * q - 4), f1 = q < 2 ? u4w(q0, 2 * q + 1) : u4w(q1, 2 * q - 3);
+      mma_f16(c, (a & 0x000F000Fu) | 0x64006400u, (b & 0x000F000Fu) | 0x64006400u, (a & 0x00F000F0u) | 0x64006400u,
+              (b & 0x00F000F0u) | 0x64006400u, e0, f0);
+      mma_f16(c, (as & 0x000F000Fu) | 0x64006400u, (bs & 0x000F000Fu) | 0x64006400u, (as & 0x00F000F0u) | 0x64006400u,
+              (bs & 0x00F000F0u) | 0x64006400u, e1, f1);
+    }
+    // six-bit scale and minimum of sub-block 4t + sbl of both rows (kogarashi kernels/native.cu:59-60)
+    uint32_t scA, mnA, scB, mnB;
+    if (t == 0) {
+      scA = (hA.y >> sh) & 63u; mnA = (hA.z >> sh) & 63u;
+      scB = (hB.y >> sh) & 63u; mnB = (hB.z >> sh) & 63u;
+    } else {
+      scA = ((hA.w >> sh) & 15u) | (((hA.y >> sh) >> 2) & 0x30u); mnA = ((hA.w >> (sh + 4)) & 15u) | (((hA.z >> sh) >> 2) & 0x30u);
+      scB = ((hB.w >> sh) & 15u) | (((hB.y >> sh) >> 2) & 0x30u); mnB = ((hB.w >> (sh + 4)) & 15u) | (((hB.z >> sh) >> 2) & 0x30u);
+    }
+    const float xsv = __uint_as_float(lds32(xs + 4 * (4 * t + sbl)));
+    // sum of (1024 + q) x = raw; d sc sum(q x) - dmin m sum(x) = S raw - (1024 S + dmin m) sum(x)
+    const float sA = dA * magic_u8(scA), sB = dB * magic_u8(scB);
+    const float tA = fmaf(1024.f, sA, mA * magic_u8(mnA)), tB = fmaf(1024.f, sB, mB * magic_u8(mnB));
+    acc0 = fmaf(sA, c[0] + c[1], acc0);
+    acc0 = fmaf(-tA, xsv, acc0);
+    acc1 = fmaf(sB, c[2] + c[3], acc1);
+    acc1 = fmaf(-tB, xsv, acc1);
+  }
+}
+
+// ---- Q6_K (row-aligned device layout: ql 128 | qh 64 | int8 scales 16 per block) ------------------------------------
+// Tile (n, A) covers the scale groups 8n + 2A + {0, 1, 4, 5}: slot groups 0 / 1 = low nibbles of ql bytes
+// 64n + 32A + [0,16) / [16,32) with qh bit pair A, groups 2 / 3 = the high nibbles with bit pair A + 2. Lane j reads ql
+// bytes 64n + 32A + 8j .. +7 and qh bytes 32n + 8j .. +7 of rows g and g + 8. Codes enter as 1024 + (q + 32).
+//   xb0 / xb1: this lane's B fragments of tile (0, 0) (8 halves); tile (n, A) is 256 n + 64 A bytes further
+//   xs: float sums of (hi + lo) over the sixteen 16-column groups of the block;  d: float block scales of the rows
+DEVI void q6k_block_diag(uint32_t rA, uint32_t rB, int j, float dA, float dB, uint32_t xb0, uint32_t xb1, uint32_t xs, float& acc0,
+                         float& acc1) {
+  const uint4 sA4 = lds128(rA + 192), sB4 = lds128(rB + 192);
+  const int sl = 4 * (j >> 1) + (j & 1);          // this lane's scale group inside a tile (slot group j)
+#pragma unroll
+  for (int n = 0; n < 2; ++n) {
+    const uint2 hA = lds64(rA + 128 + 32 * n + 8 * j), hB = lds64(rB + 128 + 32 * n + 8 * j);
+    // int8 scales of groups 8n + 4 (j / 2) .. + 3 as biased bytes
+    const uint32_t swA = ((j >> 1) ? (n ? sA4.w : sA4.y) : (n ? sA4.z : sA4.x)) ^ 0x80808080u;
+    const uint32_t swB = ((j >> 1) ? (n ? sB4.w : sB4.y) : (n ? sB4.z : sB4.x)) ^ 0x80808080u;
+#pragma unroll
+    for (int A = 0; A < 2; ++A) {
+      const uint2 lA = lds64(rA + 64 * n + 32 * A + 8 * j), lB = lds64(rB + 64 * n + 32 * A + 8 * j);
+      const uint4 p = lds128(xb0 + 256 * n + 64 * A), q = lds128(xb1 + 256 * n + 64 * A);
+      float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const uint32_t wa = u ? lA.y : lA.x, wb = u ? lB.y : lB.x, ha = u ? hA.y : hA.x, hb = u ? hB.y : hB.x;
+        // six-bit codes, four per word: low nibbles with qh bit pair A, high nibbles with bit pair A + 2
+        const uint32_t loa = (wa & 0x0F0F0F0Fu) | ((A ? ha << 2 : ha << 4) & 0x30303030u);
+        const uint32_t lob = (wb & 0x0F0F0F0Fu) | ((A ? hb << 2 : hb << 4) & 0x30303030u);
+        const uint32_t hia = ((wa >> 4) & 0x0F0F0F0Fu) | ((A ? ha >> 2 : ha) & 0x30303030u);
+        const uint32_t hib = ((wb >> 4) & 0x0F0F0F0Fu) | ((A ? hb >> 2 : hb) & 0x30303030u);
+        // bytes [b0, 0x64, b2, 0x64] = half2(1024 + b0, 1024 + b2)
+        mma_f16(c, __byte_perm(loa, 0x64646464u, 0x4240), __byte_perm(lob, 0x64646464u, 0x4240), __byte_perm(hia, 0x64646464u, 0x4240),
+                __byte_perm(hib, 0x64646464u, 0x4240), u4w(p, 2 * u), u4w(q, 2 * u));
+        mma_f16(c, __byte_perm(loa, 0x64646464u, 0x4341), __byte_perm(lob, 0x64646464u, 0x4341), __byte_perm(hia, 0x64646464u, 0x4341),
+                __byte_perm(hib, 0x64646464u, 0x4341), u4w(p, 2 * u + 1), u4w(q, 2 * u + 1));
+      }
+      const float xsv = __uint_as_float(lds32(xs + 4 * (8 * n + 2 * A + sl)));
+      const uint32_t sel = 0x7650u + 2 * A + (j & 1);
+      const float sA = dA * (__uint_as_float(__byte_perm(swA, 0x4B000000u, sel)) - (kMagic + 128.f));
+      const float sB = dB * (__uint_as_float(__byte_perm(swB, 0x4B000000u, sel)) - (kMagic + 128.f));
+      // sum of (1056 + (q - 32)) x = raw; d s sum((q - 32) x) = S raw - 1056 S sum(x)
+      acc0 = fmaf(sA, c[0] + c[1], acc0);
+      acc0 = fmaf(-1056.f * sA, xsv, acc0);
+      acc1 = fmaf(sB, c[2] + c[3], acc1);
+      acc1 = fmaf(-1056.f * sB, xsv, acc1);
+    }
+  }
+}
+
+// Four consecutive activations -> fp16 hi / lo in the fragment order [x0, x2, x1, x3]; returns sum of (hi + lo).
+DEVI float split_planes4(float4 v, uint2& hi, uint2& lo, bool& out_of_range) {
+  const float vals[4] = {v.x, v.z, v.y, v.w};
+  __half h[4], l[4];
+  float sum = 0.f;
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    h[q] = __float2half_rn(vals[q]);
+    l[q] = __float2half_rn(vals[q] - __half2float(h[q]));
+    sum += __half2float(h[q]) + __half2float(l[q]);
+    out_of_range |= fabsf(vals[q]) > 65504.f;
+  }
+  hi = make_uint2(h2_as_u32(__halves2half2(h[0], h[1])), h2_as_u32(__halves2half2(h[2], h[3])));
+  lo = make_uint2(h2_as_u32(__halves2half2(l[0], l[1])), h2_as_u32(__halves2half2(l[2], l[3])));
+  return sum;
+}
+
+DEVI void sts64(uint32_t a, uint2 v) { asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(v.x), "r"(v.y) : "memory"); }
+DEVI void sts32f(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory"); }
+
+// ---- the kernel ----------------------------------------------------------------------------------------------
+template <int DOWN_Q6>
+__global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(const FusedArgs a) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  pdl_launch();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int cta = blockIdx.x, grid = gridDim.x;
+  // ---- shared memory ----
+  int* sm_ids = reinterpret_cast<int*>(smem);                       // [32]
+  float* sm_prob = reinterpret_cast<float*>(smem + 128);             // [32]
+  float* sm_misc = reinterpret_cast<float*>(smem + 256);             // [0] sigmoid of the shared gate logit
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 272);
+  volatile int* go_flag = reinterpret_cast<volatile int*>(smem + 276);
+  int* tcnt = reinterpret_cast<int*>(smem + 288);                    // [kFusedSlots]
+  float* part = reinterpret_cast<float*>(smem + 352);                // [16][2] router partial sums
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + a.off_bars);   // [nstage]
+  uint64_t* empty = full + a.nstage;                                 // [nstage]
+  uint64_t* routed = empty + a.nstage;                               // routing published
+  float* psum = reinterpret_cast<float*>(smem + a.off_psum);         // [slot][kp1][16]
+  const uint32_t zero_base = smem_u32(smem + a.off_zero);
+  const uint32_t act = smem_u32(smem + a.off_act);
+  const uint32_t ring = smem_u32(smem + a.off_ring);
+  const int NS = a.nstage;
+
+  if (tid == 0) {
+    for (int s = 0; s < NS; ++s) {
+      mbar_init(full + s, 1);
+      mbar_init(empty + s, 1);
+    }
+    mbar_init(routed, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (tid < kFusedSlots) tcnt[tid] = 0;
+  for (int i = tid; i < kFusedZeroBytes / 4; i += kFusedThreads) reinterpret_cast<uint32_t*>(smem + a.off_zero)[i] = 0u;
+  __syncthreads();
+
+  // ---- the unit lists of this CTA (same arithmetic in producer and consumers) ----
+  const int tiles1 = a.G * a.tpg;                                    // gate/up tiles of the layer, shared expert first
+  const int my_tiles1 = cta < tiles1 ? (tiles1 - cta + grid - 1) / grid : 0;
+  const int n1 = my_tiles1 * a.kp1;
+  const int units2 = a.rt2 * a.G * a.kp2;
+  const int n2 = cta < units2 ? (units2 - cta + grid - 1) / grid : 0;
+  const int total = n1 + n2;
+  const int R = a.E + a.has_shared;                                  // router rows incl. the shared gate projection
+
+  if (warp == kFusedConsumers) {
+    // =========================== producer warp ===========================
+    // lanes 0-15 each copy one row slot of a unit
+    auto issue = [&](int p) -> bool {
+      const int stage = p % NS, use = p / NS;
+      if (use > 0 && !mbar_wait_abortable(empty + stage, (use - 1) & 1, a.status, abort_flag)) return false;
+      if (p < n1) {
+        const int lt = p / a.kp1, kp = p - lt * a.kp1;
+        const int tau = cta + lt * grid, gi = tau / a.tpg, tile = tau - gi * a.tpg;
+        const int bytes = a.nbu1 * 144;
+        if (lane == 0) mbar_arrive_expect_tx(full + stage, 16u * bytes);
+        __syncwarp();
+        if (lane < 16) {
+          const int m = lane >> 3, r = tile * 8 + (lane & 7);
+          const uint8_t* base;
+          if (a.has_shared && gi == 0) base = m ? a.sh_up : a.sh_gate;
+          else base = (m ? a.up_w : a.gate_w) + size_t(sm_ids[gi - a.has_shared]) * a.F * a.row_bytes1;
+          bulk_g2s(reinterpret_cast<void*>(smem + a.off_ring + stage * a.stage_bytes + lane * a.pitch1),
+                   base + size_t(r) * a.row_bytes1 + size_t(kp) * bytes, bytes, full + stage);
+        }
+      } else {
+        const int u2 = cta + (p - n1) * grid;
+        const int kp = u2 % a.kp2, rest = u2 / a.kp2, gi = rest % a.G, rt = rest / a.G;
+        const int blk = DOWN_Q6 ? 208 : 144, bytes = a.nbu2 * blk;
+        if (lane == 0) mbar_arrive_expect_tx(full + stage, 16u * (bytes + (DOWN_Q6 ? 16 : 0)));
+        __syncwarp();
+        if (lane < 16) {
+          const uint8_t* base = (a.has_shared && gi == 0) ? a.sh_down : a.down_w + size_t(sm_ids[gi - a.has_shared]) * a.H * a.row_bytes2;
+          const uint8_t* row = base + size_t(rt * 16 + lane) * a.row_bytes2;
+          uint8_t* slot = smem + a.off_ring + stage * a.stage_bytes + lane * a.pitch2;
+          bulk_g2s(slot, row + size_t(kp) * bytes, bytes, full + stage);
+          if (DOWN_Q6) bulk_g2s(slot + bytes, row + a.nblk2 * 208 + ((2 * kp * a.nbu2) & ~15), 16, full + stage);
+        }
+      }
+      return true;
+    };
+    int p = 0;
+    bool ok = true;
+    // the shared expert's first tile does not depend on anything: its weights are requested before the dependency wait
+    if (a.has_shared)
+      for (; ok && p < n1 && p < NS && (cta + (p / a.kp1) * grid) < a.tpg; ++p) ok = issue(p);
+    pdl_wait();
+    // grid barrier 1: every router row has been written
+    if (ok && lane == 0) ok = grid_wait(a.gbar, unsigned(grid), a.status, abort_flag);
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (ok) {
+      RouteArgs r{a.logits, a.E, a.E, a.K, 1, nullptr, 1.f, nullptr, nullptr, nullptr};
+      route_token_to<kRouteKogarashi>(r, 0, lane, sm_ids, sm_prob);
+      if (lane == 0 && a.has_shared) sm_misc[0] = sigmoid_precise(__ldcg(a.sg));
+      __syncwarp();
+      if (cta == 0 && lane < a.K) {
+        a.ids[lane] = sm_ids[lane];
+        a.prob[lane] = sm_prob[lane];
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(routed);
+      for (; ok && p < total; ++p) ok = issue(p);
+    }
+    if (!ok) {
+      // gave up: let the copies already requested land before the CTA's shared memory goes away
+      const uint64_t start = global_timer_ns();
+      for (int q = (p > NS ? p - NS : 0); q < p; ++q)
+        while (!mbar_test(full + q % NS, (q / NS) & 1) && global_timer_ns() - start < kWaitLimitNs) __nanosleep(256);
+    }
+    return;
+  }
+
+  // =========================== consumer warps ===========================
+  const DiagLane dl = diag_lane(lane);
+  const int g = dl.g, j = dl.j;
+  // ---- phase R: router rows of this CTA: row cta and row cta + grid ----
+  const int chunks = a.H / 4;                                        // float4 per row
+  const uint32_t rows_sm = act + a.act_rows;
+  int my_rows = 0;
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    const int row = cta + q * grid;
+    if (row < R) {
+      my_rows = q + 1;
+      const float* src = row < a.E ? a.router_w + size_t(row) * a.H : a.sh_inp;
+      for (int i = tid; i < chunks; i += kFusedConsumers * 32) cp_async16(rows_sm + (q * chunks + i) * 16, src + 4 * i);
+    }
+  }
+  cp_async_commit();
+  pdl_wait();
+  // the token's activations: this thread's chunks stay in registers for the planes below
+  constexpr int MAXC = 4;                                            // hidden <= 8192
+  float4 nv[MAXC];
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int i = tid + c * kFusedConsumers * 32;
+    nv[c] = i < chunks ? __ldcg(reinterpret_cast<const float4*>(a.n) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  cp_async_wait<0>();
+  float dot[2] = {0.f, 0.f};
+#pragma unroll
+  for (int q = 0; q < 2; ++q)
+    if (q < my_rows) {
+#pragma unroll
+      for (int c = 0; c < MAXC; ++c) {
+        const int i = tid + c * kFusedConsumers * 32;
+        if (i < chunks) {
+          const uint4 w = lds128(rows_sm + (q * chunks + i) * 16);
+          dot[q] = fmaf(__uint_as_float(w.x), nv[c].x, dot[q]);
+          dot[q] = fmaf(__uint_as_float(w.y), nv[c].y, dot[q]);
+          dot[q] = fmaf(__uint_as_float(w.z), nv[c].z, dot[q]);
+          dot[q] = fmaf(__uint_as_float(w.w), nv[c].w, dot[q]);
+        }
+      }
+    }
+  dot[0] = warp_sum(dot[0]);
+  dot[1] = warp_sum(dot[1]);
+  if (lane == 0) {
+    part[warp * 2] = dot[0];
+    part[warp * 2 + 1] = dot[1];
+  }
+  named_barrier(1, kFusedConsumers * 32);
+  if (tid == 0) {
+    for (int q = 0; q < my_rows; ++q) {
+      const int row = cta + q * grid;
+      float v = 0.f;
+      for (int w = 0; w < kFusedConsumers; ++w) v += part[w * 2 + q];
+      if (row < a.E) {
+        if (a.router_bias) v += a.router_bias[row];
+        a.logits[row] = v;
+      } else {
+        *a.sg = v;
+      }
+    }
+    if (cta == 0) a.gbar[1] = 0u;           // barrier 2 counter as the previous call on this workspace left it
+    __threadfence();
+    atomicAdd(a.gbar, 1u);                 // arrive at grid barrier 1; the producer warps wait for it
+  }
+  // ---- activation planes (fragment order) and per-32 sums ----
+  {
+    bool bad = false;
+#pragma unroll
+    for (int c = 0; c < MAXC; ++c) {
+      const int i = tid + c * kFusedConsumers * 32;
+      uint2 hi, lo;
+      float s = split_planes4(nv[c], hi, lo, bad);
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      if (i < chunks) {
+        sts64(act + 8 * i, hi);
+        sts64(act + a.act_lo1 + 8 * i, lo);
+        if ((i & 7) == 0) sts32f(act + a.act_xs1 + 4 * (i >> 3), s);
+      }
+    }
+    if (bad) atomicOr(a.status, kStatusActRange);
+  }
+  named_barrier(1, kFusedConsumers * 32);
+
+  // this lane's B fragment offsets inside a plane pair (bytes), relative to the first column of a block
+  const uint32_t lane_x4 = (dl.plane ? uint32_t(a.act_lo1) : 0u) + 2u * (32u * (2 * ((g >> 1) & 1) + (g >> 2)) + 16u * (j & 1));
+  bool ok = true;
+
+  // ---- phase 1: gate/up units ----
+  for (int p = warp; p < n1 && ok; p += kFusedConsumers) {
+    const int stage = p % NS, use = p / NS;
+    const int lt = p / a.kp1, kp = p - lt * a.kp1;
+    const int tau = cta + lt * grid, gi = tau / a.tpg, tile = tau - gi * a.tpg;
+    if (!mbar_wait_abortable(full + stage, use & 1, a.status, abort_flag)) { ok = false; break; }
+    const uint32_t slot0 = ring + stage * a.stage_bytes;
+    const uint32_t rA = slot0 + g * a.pitch1, rB = slot0 + (g + 8) * a.pitch1;
+    const int b0 = kp * a.nbu1;
+    const uint32_t xreal = act + lane_x4 + 512u * b0;
+    uint32_t xb0 = (dl.active && !dl.second) ? xreal : zero_base;
+    uint32_t xb1 = (dl.active && dl.second) ? xreal : zero_base;
+    uint32_t xs = act + a.act_xs1 + 32u * b0;
+    float acc0 = 0.f, acc1 = 0.f;
+    for (int b = 0; b < a.nbu1; ++b) {
+      q4k_block_diag(rA + b * 144, rB + b * 144, j, xb0, xb1, xs, acc0, acc1);
+      xb0 += 512; xb1 += 512; xs += 32;
+    }
+    acc0 = quad_sum(acc0);
+    acc1 = quad_sum(acc1);
+    const int slot = lt % kFusedSlots;
+    float* ps = psum + (slot * a.kp1 + kp) * 16;
+    if (j == 0) {
+      ps[g] = acc0;
+      ps[g + 8] = acc1;
+    }
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) {
+      __threadfence_block();
+      last = atomicAdd(&tcnt[slot], 1) == a.kp1 - 1;
+      __threadfence_block();
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      if (lane < 8) {
+        float gate = 0.f, up = 0.f;
+        for (int q = 0; q < a.kp1; ++q) {
+          gate += psum[(slot * a.kp1 + q) * 16 + lane];
+          up += psum[(slot * a.kp1 + q) * 16 + 8 + lane];
+        }
+        const float h = silu_mul(gate, up);
+        const __half hi = __float2half_rn(h);
+        const __half lo = __float2half_rn(h - __half2float(hi));
+        if (fabsf(h) > 65504.f) atomicOr(a.status, kStatusActRange);
+        __half* dst = a.hbuf + size_t(gi) * 2 * a.F + tile * 8 + lane;
+        dst[0] = hi;
+        dst[a.F] = lo;
+      }
+      __syncwarp();
+      if (lane == 0) tcnt[slot] = 0;
+    }
+    // The stage is handed back only now: a warp that is still summing a tile keeps the producer from running
+    // kFusedSlots tiles ahead, so a slot of partial sums is never reused while it is being read.
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty + stage);
+  }
+
+  // ---- grid barrier 2: every product is in global memory ----
+  if (!ok) *abort_flag = 1;
+  named_barrier(1, kFusedConsumers * 32);
+  if (tid == 0) {
+    bool good = !*abort_flag && mbar_wait_abortable(routed, 0, a.status, abort_flag);    // the producer has passed barrier 1
+    if (good) good = grid_arrive_wait(a.gbar + 1, unsigned(grid), a.status, abort_flag);
+    if (good && cta == 0) a.gbar[0] = 0u;       // every CTA has passed barrier 1: its counter is free for the next call
+    *go_flag = good ? 1 : 0;
+  }
+  named_barrier(1, kFusedConsumers * 32);
+  if (!*go_flag) return;                        // one thread decided: every consumer warp leaves or none
+  // ---- the K + 1 product vectors -> planes in fragment order, sums per 16 (Q6_K) or 32 (Q4_K) columns ----
+  {
+    const int per = a.F / 4, all = a.G * per;
+    for (int base = 0; base < all; base += kFusedConsumers * 32) {      // uniform trip count: shuffles below
+      const int idx = base + tid;
+      const bool live = idx < all;
+      const int gi = live ? idx / per : 0, i = live ? idx - gi * per : 0;
+      uint2 hi = make_uint2(0u, 0u), lo = make_uint2(0u, 0u);
+      if (live) {
+        hi = __ldcg(reinterpret_cast<const uint2*>(a.hbuf + size_t(gi) * 2 * a.F) + i);
+        lo = __ldcg(reinterpret_cast<const uint2*>(a.hbuf + size_t(gi) * 2 * a.F + a.F) + i);
+      }
+      const float2 h01 = __half22float2(u32_as_h2(hi.x)), h23 = __half22float2(u32_as_h2(hi.y));
+      const float2 l01 = __half22float2(u32_as_h2(lo.x)), l23 = __half22float2(u32_as_h2(lo.y));
+      float s = ((h01.x + l01.x) + (h01.y + l01.y)) + ((h23.x + l23.x) + (h23.y + l23.y));
+      s += __shfl_xor_sync(0xffffffffu, s, 1);
+      s += __shfl_xor_sync(0xffffffffu, s, 2);
+      if (!DOWN_Q6) s += __shfl_xor_sync(0xffffffffu, s, 4);
+      if (live) {
+        // [h0,h1,h2,h3] -> [h0,h2,h1,h3]
+        const uint2 ph = make_uint2(__byte_perm(hi.x, hi.y, 0x5410), __byte_perm(hi.x, hi.y, 0x7632));
+        const uint2 pq = make_uint2(__byte_perm(lo.x, lo.y, 0x5410), __byte_perm(lo.x, lo.y, 0x7632));
+        const uint32_t gb = act + gi * a.act_grp2;
+        sts64(gb + 8 * i, ph);
+        sts64(gb + a.act_lo2 + 8 * i, pq);
+        if (DOWN_Q6) {
+          if ((i & 3) == 0) sts32f(act + a.act_xs2 + 4 * (gi * (a.F / 16) + (i >> 2)), s);
+        } else {
+          if ((i & 7) == 0) sts32f(act + a.act_xs2 + 4 * (gi * (a.F / 32) + (i >> 3)), s);
+        }
+      }
+    }
+  }
+  named_barrier(1, kFusedConsumers * 32);
+
+  // ---- phase 2: down units ----
+  const uint32_t lane_x6 = (dl.plane ? uint32_t(a.act_lo2) : 0u) + 2u * (64u * (g >> 2) + 16u * ((g >> 1) & 1) + 8u * (j & 1));
+  const uint32_t lane_x4d = (dl.plane ? uint32_t(a.act_lo2) : 0u) + 2u * (32u * (2 * ((g >> 1) & 1) + (g >> 2)) + 16u * (j & 1));
+  for (int p = n1 + ((warp - n1 % kFusedConsumers + kFusedConsumers) % kFusedConsumers); p < total; p += kFusedConsumers) {
+    const int stage = p % NS, use = p / NS;
+    const int u2 = cta + (p - n1) * grid;
+    const int kp = u2 % a.kp2, rest = u2 / a.kp2, gi = rest % a.G, rt = rest / a.G;
+    if (!mbar_wait_abortable(full + stage, use & 1, a.status, abort_flag)) return;
+    const uint32_t slot0 = ring + stage * a.stage_bytes;
+    const uint32_t rA = slot0 + g * a.pitch2, rB = slot0 + (g + 8) * a.pitch2;
+    const int b0 = kp * a.nbu2;
+    const uint32_t xreal = act + gi * a.act_grp2 + (DOWN_Q6 ? lane_x6 : lane_x4d) + 512u * b0;
+    uint32_t xb0 = (dl.active && !dl.second) ? xreal : zero_base;
+    uint32_t xb1 = (dl.active && dl.second) ? xreal : zero_base;
+    float acc0 = 0.f, acc1 = 0.f;
+    if (DOWN_Q6) {
+      uint32_t xs = act + a.act_xs2 + 4u * (gi * (a.F / 16) + 16 * b0);
+      const uint32_t dchunkA = rA + a.nbu2 * 208, dchunkB = rB + a.nbu2 * 208;
+      for (int b = 0; b < a.nbu2; ++b) {
+        const int doff = (2 * (b0 + b)) & 15;
+        const uint32_t dwA = lds32(dchunkA + (doff & ~3)), dwB = lds32(dchunkB + (doff & ~3));
+        const float dA = (doff & 2) ? half_hi(dwA) : half_lo(dwA), dB = (doff & 2) ? half_hi(dwB) : half_lo(dwB);
+        q6k_block_diag(rA + b * 208, rB + b * 208, j, dA, dB, xb0, xb1, xs, acc0, acc1);
+        xb0 += 512; xb1 += 512; xs += 64;
+      }
+    } else {
+      uint32_t xs = act + a.act_xs2 + 4u * (gi * (a.F / 32) + 8 * b0);
+      for (int b = 0; b < a.nbu2; ++b) {
+        q4k_block_diag(rA + b * 144, rB + b * 144, j, xb0, xb1, xs, acc0, acc1);
+        xb0 += 512; xb1 += 512; xs += 32;
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty + stage);
+    acc0 = quad_sum(acc0);
+    acc1 = quad_sum(acc1);
+    // partial rows: y[kp][group][row]
+    float* y = a.y + (size_t(kp) * a.G + gi) * a.H + rt * 16;
+    if (j == 0) {
+      __stcg(y + g, acc0);
+      __stcg(y + g + 8, acc1);
+    }
+    __syncwarp();
+    int last = 0;
+    if (lane == 0) {
+      __threadfence();
+      last = atomicAdd(a.tile_cnt + rt, 1u) == unsigned(a.G * a.kp2 - 1);
+      __threadfence();
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (last) {
+      // x[i] += sum_s fma(p_s, down_s[i]) + sigmoid(sg) * shared[i]   (kogarashi kernels/native.cu:113-117)
+      if (lane < 16) {
+        const int row = rt * 16 + lane;
+        float v = 0.f;
+        for (int s = 0; s < a.K; ++s) {
+          float ys = 0.f;
+          for (int q = 0; q < a.kp2; ++q) ys += __ldcg(a.y + (size_t(q) * a.G + s + a.has_shared) * a.H + row);
+          v = fmaf(sm_prob[s], ys, v);
+        }
+        if (a.has_shared) {
+          float ys = 0.f;
+          for (int q = 0; q < a.kp2; ++q) ys += __ldcg(a.y + size_t(q) * a.G * a.H + row);
+          v += sm_misc[0] * ys;
+        }
+        a.x[row] += v;
+      }
+      __syncwarp();
+      if (lane == 0) a.tile_cnt[rt] = 0u;
+    }
+  }
+}
+
+}  // namespace dmoe

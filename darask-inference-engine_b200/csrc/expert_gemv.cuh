@@ -689,6 +689,7 @@ DEVI void gemv_items(const GemvArgs& a, uint8_t* smem) {
             const float h = OUT == kOutHayateProduct ? hayate_swiglu(gv, uv) : silu_mul(gv, uv);
             const __half hi = __float2half_rn(h);
             const __half lo = __float2half_rn(h - __half2float(hi));
+            if (fabsf(h) > 65504.f && a.status) atomicOr(a.status, 4u);       // does not fit the fp16 planes
             __half* dst = a.out_planes + size_t(ares[t]) * 2 * a.rows + (NATURAL ? r : plane_pos(r));
             dst[0] = hi;
             dst[a.rows] = lo;
@@ -731,7 +732,8 @@ __global__ void __launch_bounds__(kGemvWarps * 32, 1) expert_gemv_kernel(const G
 // One block per row. planes[row] = k fp16 hi values then k fp16 lo values, groups of four as [x0,x2,x1,x3]
 // (or in natural order for the NVFP4 kernels).
 template <typename XT>
-DEVI void act_planes_row(const XT* x, int k, __half* planes, __half* xsum_planes, bool natural) {
+DEVI void act_planes_row(const XT* x, int k, __half* planes, __half* xsum_planes, bool natural, unsigned* status = nullptr) {
+  bool out_of_range = false;        // |value| > 65504 does not fit the fp16 planes: reported in the status word (bit 4)
   for (int base = 0; base < k / 4; base += blockDim.x) {            // uniform trip count: shuffles below
     const int i = base + threadIdx.x;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -750,6 +752,7 @@ DEVI void act_planes_row(const XT* x, int k, __half* planes, __half* xsum_planes
     for (int q = 0; q < 4; ++q) {
       hi[q] = __float2half_rn(vals[q]);
       lo[q] = __float2half_rn(vals[q] - __half2float(hi[q]));
+      out_of_range |= fabsf(vals[q]) > 65504.f;
     }
     if (i < k / 4) {
       *reinterpret_cast<uint2*>(planes + 4 * i) = make_uint2(h2_as_u32(__halves2half2(hi[0], hi[1])), h2_as_u32(__halves2half2(hi[2], hi[3])));
@@ -767,6 +770,7 @@ DEVI void act_planes_row(const XT* x, int k, __half* planes, __half* xsum_planes
       }
     }
   }
+  if (out_of_range && status) atomicOr(status, 4u);
 }
 
 }  // namespace dmoe

@@ -9,6 +9,7 @@
 #include "route_kernels.cuh"
 #include "stream_launch.cuh"
 #include "gemv_launch.cuh"
+#include "decode_fused.cuh"
 #include <cstdio>
 
 namespace dmoe {
@@ -51,9 +52,11 @@ __global__ void q6k_repack_kernel(const uint8_t* src, uint8_t* dst, long long ro
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct KogarashiWs {
-  int* counters; unsigned* done; unsigned* status; int* active; unsigned* ranges; unsigned* assignments;
-  int4* plan; float* sg; __half* xplanes; __half* xsum_planes; __half* hplanes; float* y; size_t bytes;
+  int* counters; unsigned* done; unsigned* status; unsigned* gbar; unsigned* tile_cnt; int* active; unsigned* ranges;
+  unsigned* assignments; int4* plan; float* sg; __half* xplanes; __half* xsum_planes; __half* hplanes; float* y; size_t bytes;
 };
+constexpr int kFusedMaxKParts = 4;          // K parts of the one-token down products (partial rows kept per part)
+constexpr int kFusedMaxRowTiles = 512;      // 16-row output tiles with a completion counter (hidden <= 8192)
 static KogarashiWs carve(void* base, int hidden, int inter, int experts, int topk, int tokens) {
   KogarashiWs w;
   uint8_t* p = static_cast<uint8_t*>(base);
@@ -62,6 +65,8 @@ static KogarashiWs carve(void* base, int hidden, int inter, int experts, int top
   w.counters = reinterpret_cast<int*>(take(16));
   w.done = reinterpret_cast<unsigned*>(take(4));
   w.status = reinterpret_cast<unsigned*>(take(4));
+  w.gbar = reinterpret_cast<unsigned*>(take(16));                                   // two grid barrier counters
+  w.tile_cnt = reinterpret_cast<unsigned*>(take(size_t(kFusedMaxRowTiles) * 4));    // ends at byte 3072: inside the zeroed head
   w.active = reinterpret_cast<int*>(take(size_t(experts) * 4));
   w.ranges = reinterpret_cast<unsigned*>(take(size_t(experts) * 8));
   w.assignments = reinterpret_cast<unsigned*>(take(size_t(tokens) * topk * 4));
@@ -71,7 +76,7 @@ static KogarashiWs carve(void* base, int hidden, int inter, int experts, int top
   w.xsum_planes = reinterpret_cast<__half*>(take(size_t(tokens) * (hidden / 32) * 4));
   const size_t rows = size_t(tokens) * topk + tokens;
   w.hplanes = reinterpret_cast<__half*>(take(rows * 2 * inter * 2));
-  w.y = reinterpret_cast<float*>(take(rows * hidden * 4));
+  w.y = reinterpret_cast<float*>(take(rows * hidden * 4 * (tokens == 1 ? kFusedMaxKParts : 1)));
   w.bytes = off;
   return w;
 }
@@ -91,9 +96,107 @@ static cudaError_t launch_gemv_ggml(int ty, const GemvArgs& a, cudaStream_t st) 
   return cudaErrorInvalidValue;
 }
 
+// ---- the one-token layer as one launch (decode_fused.cuh) ---------------------------------------------------
+// K parts per row and blocks per unit: parts in {1, 2, 4, 8} (the consumer warps of a tile are neighbours), at most
+// four blocks per unit, as many parts as that allows.
+static bool fused_split(int nblk, int max_parts, int* parts, int* per) {
+  for (int pass = 0; pass < 2; ++pass)                 // first choice: two to four blocks per unit; else one
+    for (int kp = max_parts; kp >= 1; kp >>= 1) {
+      if (nblk % kp) continue;
+      const int n = nblk / kp;
+      if (n > 4 || (pass == 0 && n < 2)) continue;
+      *parts = kp;
+      *per = n;
+      return true;
+    }
+  return false;
+}
+static int fused_pitch(int payload, int residue_a, int residue_b) {      // smallest pitch >= payload, multiple of 16, = a or b mod 128
+  int p = (payload + 15) / 16 * 16;
+  while (p % 128 != residue_a && p % 128 != residue_b) p += 16;
+  return p;
+}
+
+// Fills `f` and returns true when the shape can take the single-launch path.
+static bool fused_plan(const KogarashiMoe* d, const KogarashiWs& w, FusedArgs* f, int* smem_bytes) {
+  const int H = d->hidden, F = d->inter, E = d->experts, K = d->topk;
+  if (d->tokens != 1 || d->router_ty != DARASK_GGML_F32 || d->gate_ty != DARASK_GGML_Q4_K) return false;
+  if (d->down_ty != DARASK_GGML_Q4_K && d->down_ty != DARASK_GGML_Q6_K) return false;
+  const bool shared = d->sh_gate_w != nullptr;
+  const int grid = sm_count();
+  if (E + (shared ? 1 : 0) > 2 * grid || H > 8192 || H / 16 > kFusedMaxRowTiles || F % 8) return false;
+  FusedArgs a = {};
+  a.H = H; a.F = F; a.E = E; a.K = K; a.has_shared = shared ? 1 : 0; a.G = K + a.has_shared;
+  a.down_q6 = d->down_ty == DARASK_GGML_Q6_K;
+  if (!fused_split(H / 256, 8, &a.kp1, &a.nbu1)) return false;
+  if (!fused_split(F / 256, kFusedMaxKParts, &a.kp2, &a.nbu2)) return false;
+  a.nblk2 = F / 256;
+  // Q6_K: the f16 block scales of a unit's blocks must lie in one 16-byte chunk of the row tail
+  if (a.down_q6 && (16 % (2 * a.nbu2)) != 0 && !(a.kp2 == 1 && 2 * a.nblk2 <= 16)) return false;
+  a.row_bytes1 = row_bytes_of(DARASK_GGML_Q4_K, H);
+  a.row_bytes2 = row_bytes_of(d->down_ty, F);
+  a.tpg = F / 8;
+  a.rt2 = H / 16;
+  a.pitch1 = fused_pitch(a.nbu1 * 144, 64, 64);                                 // 16-byte reads of two rows per quarter warp
+  a.pitch2 = a.down_q6 ? fused_pitch(a.nbu2 * 208 + 16, 32, 96) : fused_pitch(a.nbu2 * 144, 64, 64);   // Q6_K: 8-byte reads of four rows per half warp
+  a.stage_bytes = (16 * (a.pitch1 > a.pitch2 ? a.pitch1 : a.pitch2) + 127) / 128 * 128;
+  // shared memory: control words | barriers | partial sums | zero fragments | activation area | ring
+  a.off_bars = 512;
+  a.off_psum = a.off_bars + (2 * kFusedMaxStages + 1) * 8;
+  a.off_psum = (a.off_psum + 127) / 128 * 128;
+  a.off_zero = a.off_psum + kFusedSlots * a.kp1 * 16 * 4;
+  a.off_act = a.off_zero + kFusedZeroBytes;
+  a.off_act = (a.off_act + 127) / 128 * 128;
+  a.act_lo1 = H * 2 + 64;
+  a.act_xs1 = 2 * a.act_lo1;
+  a.act_rows = (a.act_xs1 + H / 32 * 4 + 127) / 128 * 128;
+  const int act1 = a.act_rows + 2 * H * 4;
+  a.act_lo2 = F * 2 + 64;
+  a.act_grp2 = 2 * a.act_lo2;
+  a.act_xs2 = a.G * a.act_grp2;
+  const int act2 = a.act_xs2 + a.G * (F / 16) * 4;
+  a.off_ring = (a.off_act + (act1 > act2 ? act1 : act2) + 127) / 128 * 128;
+  a.nstage = (kSmemBudget - a.off_ring) / a.stage_bytes;
+  if (a.nstage > kFusedMaxStages) a.nstage = kFusedMaxStages;
+  if (a.nstage < 4) return false;
+  *smem_bytes = a.off_ring + a.nstage * a.stage_bytes;
+  a.router_w = static_cast<const float*>(d->router_w); a.router_bias = d->router_bias; a.sh_inp = static_cast<const float*>(d->sh_inp_w);
+  a.gate_w = static_cast<const uint8_t*>(d->gate_w); a.up_w = static_cast<const uint8_t*>(d->up_w); a.down_w = static_cast<const uint8_t*>(d->down_w);
+  a.sh_gate = static_cast<const uint8_t*>(d->sh_gate_w); a.sh_up = static_cast<const uint8_t*>(d->sh_up_w); a.sh_down = static_cast<const uint8_t*>(d->sh_down_w);
+  a.n = d->n; a.x = d->x; a.logits = d->logits; a.ids = d->ids; a.prob = d->prob;
+  a.gbar = w.gbar; a.tile_cnt = w.tile_cnt; a.status = w.status; a.hbuf = w.hplanes; a.y = w.y; a.sg = w.sg;
+  *f = a;
+  return true;
+}
+
+static cudaError_t launch_fused(const FusedArgs& a, int smem_bytes, cudaStream_t st) {
+  static bool configured[64][2] = {};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  auto k6 = kogarashi_decode1_kernel<1>;
+  auto k4 = kogarashi_decode1_kernel<0>;
+  if (!configured[dev][a.down_q6]) {
+    e = a.down_q6 ? cudaFuncSetAttribute(k6, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget)
+                  : cudaFuncSetAttribute(k4, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (e != cudaSuccess) return e;
+    configured[dev][a.down_q6] = true;
+  }
+  return a.down_q6 ? launch_pdl(k6, dim3(sm_count()), dim3(kFusedThreads), size_t(smem_bytes), st, a)
+                   : launch_pdl(k4, dim3(sm_count()), dim3(kFusedThreads), size_t(smem_bytes), st, a);
+}
+
+static thread_local bool g_force_staged = false;    // host-thread-local: take the staged launches for one token too
+
 }  // namespace dmoe
 
 using namespace dmoe;
+
+extern "C" int kogarashi_moe_set_single_launch(int enabled) {
+  g_force_staged = !enabled;
+  return cudaSuccess;
+}
 
 extern "C" size_t kogarashi_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens) {
   return carve(nullptr, hidden, inter, experts, topk, tokens).bytes;
@@ -136,6 +239,14 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
   if (shared && (!d->sh_up_w || !d->sh_down_w || !d->sh_inp_w)) return cudaErrorInvalidValue;
   if (d->workspace_bytes < kogarashi_moe_workspace_bytes(H, F, E, K, T)) return cudaErrorInvalidValue;
   const KogarashiWs w = carve(d->workspace, H, F, E, K, T);
+  if (d->reserved) return cudaErrorInvalidValue;
+
+  // one token: the whole layer is one persistent launch
+  {
+    FusedArgs f;
+    int smem_bytes = 0;
+    if (!g_force_staged && fused_plan(d, w, &f, &smem_bytes)) return launch_fused(f, smem_bytes, st);
+  }
 
   // 1. router projection, top-k, permutation
   RouterArgs r = {};
@@ -147,10 +258,8 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
   r.planes = w.xplanes; r.xsum_planes = w.xsum_planes;
   const int rblocks = E + (shared ? 1 : 0) + T;
   const size_t hist = size_t(E + 1) * 4 + size_t(T * K <= kRouteIdCache ? T * K : 0) * 4;
-  const int mask = d->stage_mask ? d->stage_mask : 15;
   cudaError_t e = cudaSuccess;
-  if (!(mask & 1)) {}
-  else if (d->router_ty == DARASK_GGML_F32) e = launch_pdl(router_kernel<float, float, kRouteKogarashi>, dim3(rblocks), dim3(128), hist, st, r);
+  if (d->router_ty == DARASK_GGML_F32) e = launch_pdl(router_kernel<float, float, kRouteKogarashi>, dim3(rblocks), dim3(128), hist, st, r);
   else if (d->router_ty == DARASK_GGML_BF16) e = launch_pdl(router_kernel<__nv_bfloat16, float, kRouteKogarashi>, dim3(rblocks), dim3(128), hist, st, r);
   else if (d->router_ty == DARASK_GGML_F16) e = launch_pdl(router_kernel<__half, float, kRouteKogarashi>, dim3(rblocks), dim3(128), hist, st, r);
   else return cudaErrorInvalidValue;
@@ -168,7 +277,7 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
   a.counters = w.counters + 2; a.plan = w.plan; a.assignments = w.assignments;
   a.tokens = T; a.topk = K; a.max_groups = max_groups;
   a.out_planes = w.hplanes; a.out = nullptr; a.status = w.status;
-  if ((mask & 2) && (e = launch_gemv_ggml<1>(d->gate_ty, a, st))) return e;
+  if ((e = launch_gemv_ggml<1>(d->gate_ty, a, st))) return e;
 
   // 3. down
   GemvArgs b = a;
@@ -179,11 +288,10 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
   b.k = F; b.rows = H; b.nblk = F / 256;
   b.xplanes = w.hplanes; b.xsum_planes = nullptr; b.x_by_assignment = 1;
   b.out_planes = nullptr; b.out = w.y;
-  b.late_wait = (mask & 2) ? 1 : 0;      // the plan is the router's, two launches back; only the products come from gate/up
-  if ((mask & 4) && (e = launch_gemv_ggml<0>(d->down_ty, b, st))) return e;
+  b.late_wait = 1;                       // the plan is the router's, two launches back; only the products come from gate/up
+  if ((e = launch_gemv_ggml<0>(d->down_ty, b, st))) return e;
 
   // 4. combine
-  if (!(mask & 8)) return cudaSuccess;
   return launch_pdl(kogarashi_combine_kernel, dim3((H + 255) / 256, T), dim3(256), 0, st, d->x, (const float*)w.y,
                     (const float*)d->prob, (const float*)w.sg, H, K, T, shared ? 1 : 0);
 }

@@ -25,101 +25,120 @@ struct RouteArgs {
   float* shared_gate;    // Tsumuji: [T] = sigmoid(logits[E]); may be null
 };
 
-// One warp routes one token. MAXV * 32 >= experts.
-template <int MODE, int MAXV>
-DEVI void route_token(const RouteArgs& a, int token, int lane) {
-  const float* lg = a.logits + size_t(token) * a.ld;
+// ---- selection as an arg-max over packed 64-bit words -------------------------------------------
+// A candidate is one word: the float32 key mapped to an unsigned integer of the same order in the
+// high half, (2^32 - 1 - expert id) in the low half. The largest word is the largest key and, among
+// equal keys, the lowest id; a taken or absent candidate is the word 0. Results equal k rounds of
+// "first maximum wins" over the float keys, which is what the three reference routers do.
+DEVI uint32_t ordered_bits(float key) {
+  if (!(key == key)) key = -INFINITY;          // a NaN key never wins against a number
+  const uint32_t b = __float_as_uint(key + 0.f);   // -0 and +0 are the same key
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+DEVI float ordered_value(uint32_t o) { return __uint_as_float((o & 0x80000000u) ? (o & 0x7fffffffu) : ~o); }
+DEVI unsigned long long pack_candidate(float key, int expert) {
+  return (static_cast<unsigned long long>(ordered_bits(key)) << 32) | (0xffffffffu - static_cast<uint32_t>(expert));
+}
+DEVI unsigned long long warp_max_u64(unsigned long long v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = other > v ? other : v;
+  }
+  return v;
+}
+
+// One warp routes one token; lane l owns experts l, l + 32, ... (PER * 32 >= experts). `ids_out` / `w_out`
+// (k entries each) may point to global or shared memory.
+template <int MODE, int PER>
+DEVI void route_token(const RouteArgs& a, int token, int lane, int* ids_out, float* w_out) {
+  const float* row = a.logits + size_t(token) * a.ld;
   const int E = a.experts, K = a.topk;
-  float v[MAXV];
-  float score[MODE == kRouteHayate ? MAXV : 1];
-  float m = -INFINITY;
+  float logit[PER];
 #pragma unroll
-  for (int i = 0; i < MAXV; ++i) {
-    const int e = lane + 32 * i;
-    v[i] = e < E ? __ldcg(lg + e) : -INFINITY;   // L2 read: another block may just have written it
-    m = fmaxf(m, v[i]);
-  }
-  float s = 0.f;
-  if (MODE == kRouteTsumuji) {
-    m = warp_max(m);
-#pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
-      v[i] = lane + 32 * i < E ? expf(v[i] - m) : -1.f;   // -1: not a candidate
-      s += fmaxf(v[i], 0.f);
-    }
-    s = warp_sum(s);
-  } else if (MODE == kRouteHayate) {
-#pragma unroll
-    for (int i = 0; i < MAXV; ++i) {
-      const int e = lane + 32 * i;
-      score[i] = e < E ? 1.f / (1.f + expf(-v[i])) : 0.f;
-      v[i] = e < E ? score[i] + a.bias[e] : -INFINITY;
-    }
-  }
-  const float floor_value = MODE == kRouteTsumuji ? -1.f : -INFINITY;
-  const float taken_value = MODE == kRouteTsumuji ? -2.f : -INFINITY;
-  float mine = 0.f;     // lane t keeps what slot t needs for the weights
-  float total = 0.f;    // Tsumuji / Hayate: running sum in selection order
-  float first = 0.f;    // Kogarashi: the largest logit
-  for (int t = 0; t < K; ++t) {
-    float bv = floor_value;
-    int bi = MODE == kRouteTsumuji ? 0x7fffffff : 0;   // defaults of the reference kernels
-    float bs = 0.f;
-#pragma unroll
-    for (int i = 0; i < MAXV; ++i)
-      if (v[i] > bv) {      // ascending index inside a lane: the first maximum wins
-        bv = v[i];
-        bi = lane + 32 * i;
-        if (MODE == kRouteHayate) bs = score[i];
-      }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      const float os = MODE == kRouteHayate ? __shfl_xor_sync(0xffffffffu, bs, o) : 0.f;
-      if (ov > bv || (ov == bv && oi < bi)) {
-        bv = ov;
-        bi = oi;
-        bs = os;
-      }
-    }
-    if ((bi & 31) == lane) {
-#pragma unroll
-      for (int i = 0; i < MAXV; ++i)
-        if (lane + 32 * i == bi) v[i] = taken_value;
-    }
-    if (lane == 0) a.ids[token * K + t] = bi;
-    if (MODE == kRouteKogarashi) {
-      if (t == 0) first = bv;
-      if (lane == t) mine = bv;
-    } else if (MODE == kRouteTsumuji) {
-      if (lane == t) mine = bv / s;
-      total += bv / s;
-    } else {
-      if (lane == t) mine = bs;
-      total += bs;
-    }
-  }
-  float* w = a.weights + size_t(token) * K;
+  for (int i = 0; i < PER; ++i) logit[i] = lane + 32 * i < E ? __ldcg(row + lane + 32 * i) : -INFINITY;   // L2: another block may have written it
+  unsigned long long cand[PER];
+  float score[MODE == kRouteHayate ? PER : 1];
+  float norm = 1.f;                          // Tsumuji: sum over all experts of exp(logit - max)
   if (MODE == kRouteKogarashi) {
-    // softmax over the selected logits; K <= 32, lane s holds logit s
-    float z = lane < K ? expf(mine - first) : 0.f;
-    const float denom = warp_sum(z);
-    if (lane < K) w[lane] = z / denom;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) cand[i] = lane + 32 * i < E ? pack_candidate(logit[i], lane + 32 * i) : 0ull;
   } else if (MODE == kRouteTsumuji) {
-    if (lane < K) w[lane] = mine / total;
-    if (lane == 0 && a.shared_gate) a.shared_gate[token] = 1.f / (1.f + expf(-__ldcg(lg + E)));
+    float top = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) top = fmaxf(top, logit[i]);
+    top = warp_max(top);
+    float part = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const bool live = lane + 32 * i < E;
+      const float key = live ? expf(logit[i] - top) : 0.f;
+      part += key;
+      cand[i] = live ? pack_candidate(key, lane + 32 * i) : 0ull;
+    }
+    norm = warp_sum(part);
   } else {
-    if (lane < K) w[lane] = mine / (total + 1.e-20f) * a.scale;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const int e = lane + 32 * i;
+      score[i] = e < E ? 1.f / (1.f + expf(-logit[i])) : 0.f;
+      cand[i] = e < E ? pack_candidate(score[i] + a.bias[e], e) : 0ull;
+    }
+  }
+  float keep = 0.f;       // lane t keeps the quantity slot t's weight is made from
+  float running = 0.f;    // Tsumuji / Hayate: sum over the selected, in selection order
+  float lead = 0.f;       // Kogarashi: the first (largest) selected logit
+  for (int t = 0; t < K; ++t) {
+    unsigned long long best = 0ull;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) best = cand[i] > best ? cand[i] : best;
+    best = warp_max_u64(best);
+    const int winner = int(0xffffffffu - static_cast<uint32_t>(best));
+    const float key = ordered_value(static_cast<uint32_t>(best >> 32));
+    float won_score = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      const bool hit = (winner & 31) == lane && (winner >> 5) == i;
+      if (MODE == kRouteHayate && hit) won_score = score[i];
+      if (hit) cand[i] = 0ull;
+    }
+    if (lane == 0) ids_out[t] = winner;
+    if (MODE == kRouteKogarashi) {
+      if (t == 0) lead = key;
+      if (lane == t) keep = key;
+    } else if (MODE == kRouteTsumuji) {
+      const float p = key / norm;
+      if (lane == t) keep = p;
+      running += p;
+    } else {
+      won_score = __shfl_sync(0xffffffffu, won_score, winner & 31);
+      if (lane == t) keep = won_score;
+      running += won_score;
+    }
+  }
+  if (MODE == kRouteKogarashi) {       // softmax over the selected logits (K <= 32: lane s holds logit s)
+    const float z = lane < K ? expf(keep - lead) : 0.f;
+    const float denom = warp_sum(z);
+    if (lane < K) w_out[lane] = z / denom;
+  } else if (MODE == kRouteTsumuji) {
+    if (lane < K) w_out[lane] = keep / running;
+    if (lane == 0 && a.shared_gate) a.shared_gate[token] = 1.f / (1.f + expf(-__ldcg(row + E)));
+  } else {
+    if (lane < K) w_out[lane] = keep / (running + 1.e-20f) * a.scale;
   }
 }
 
 template <int MODE>
+DEVI void route_token_to(const RouteArgs& a, int token, int lane, int* ids_out, float* w_out) {
+  if (a.experts <= 128) route_token<MODE, 4>(a, token, lane, ids_out, w_out);
+  else if (a.experts <= 256) route_token<MODE, 8>(a, token, lane, ids_out, w_out);
+  else if (a.experts <= 512) route_token<MODE, 16>(a, token, lane, ids_out, w_out);
+  else route_token<MODE, 32>(a, token, lane, ids_out, w_out);
+}
+
+template <int MODE>
 DEVI void route_token_any(const RouteArgs& a, int token, int lane) {
-  if (a.experts <= 128) route_token<MODE, 4>(a, token, lane);
-  else if (a.experts <= 256) route_token<MODE, 8>(a, token, lane);
-  else if (a.experts <= 512) route_token<MODE, 16>(a, token, lane);
-  else route_token<MODE, 32>(a, token, lane);
+  route_token_to<MODE>(a, token, lane, a.ids + size_t(token) * a.topk, a.weights + size_t(token) * a.topk);
 }
 
 // ---- dispatch permutation -------------------------------------------------------------------

@@ -1,7 +1,7 @@
 // Kernels around route_impl.cuh: stand-alone top-k, the router projection (logits) fused with
 // top-k and the dispatch permutation through a "last block finishes" counter, and the
-// stand-alone permutation. Included by route.cu (precise math: Kogarashi, Tsumuji) and by
-// route_hayate.cu (fast math: Hayate).
+// stand-alone permutation. Included by kogarashi.cu and tsumuji.cu (precise math) and by
+// hayate.cu (compiled with --use_fast_math, as the reference builds its GLM kernels).
 #pragma once
 #include "route_impl.cuh"
 #include "expert_gemv.cuh"
@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(128) router_kernel(RouterArgs a) {
     if (a.planes) {
       const int t = row - router_rows;
       act_planes_row(static_cast<const XT*>(a.x) + size_t(t) * a.hidden, a.hidden, a.planes + size_t(t) * 2 * a.hidden,
-                     a.xsum_planes ? a.xsum_planes + size_t(t) * 2 * (a.hidden / 32) : nullptr, a.planes_natural != 0);
+                     a.xsum_planes ? a.xsum_planes + size_t(t) * 2 * (a.hidden / 32) : nullptr, a.planes_natural != 0, a.perm.status);
     }
     return;                            // not counted: only the router rows gate the routing below
   }

@@ -69,7 +69,7 @@ class KogarashiMoeLayer:
         w = self.weights.get(name)
         return (w.data.data_ptr(), w.ty) if w is not None else (None, 0)
 
-    def forward(self, x: torch.Tensor, n: torch.Tensor, stage_mask: int = 0) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, n: torch.Tensor) -> torch.Tensor:
         """x [T,H] float32 residual stream (updated in place), n [T,H] float32 normalised input."""
         t = n.shape[0]
         if t > self.max_tokens or n.shape != x.shape or n.shape[1] != self.hidden:
@@ -90,7 +90,6 @@ class KogarashiMoeLayer:
         d.n, d.x = n.data_ptr(), x.data_ptr()
         d.logits, d.ids, d.prob = self.logits.data_ptr(), self.ids.data_ptr(), self.prob.data_ptr()
         d.workspace, d.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
-        d.stage_mask = stage_mask
         _lib.check(_lib.lib().kogarashi_moe_layer(ctypes.byref(d), self._stream()), "kogarashi_moe_layer")
         return x
 

@@ -23,7 +23,12 @@ typedef struct CUstream_st* darask_stream_t;
 enum { DARASK_GGML_F32 = 0, DARASK_GGML_F16 = 1, DARASK_GGML_Q4_K = 12, DARASK_GGML_Q6_K = 14, DARASK_GGML_BF16 = 30 };
 enum { DARASK_ROUTE_KOGARASHI = 0, DARASK_ROUTE_TSUMUJI = 1, DARASK_ROUTE_HAYATE = 2 };
 /* bits of the status word kept in every workspace */
-enum { DARASK_STATUS_WAIT_TIMEOUT = 1, DARASK_STATUS_BAD_ROUTE = 2 };
+enum {
+  DARASK_STATUS_WAIT_TIMEOUT = 1,  /* a bounded device-side wait ran out; re-initialise the workspace before the next call */
+  DARASK_STATUS_BAD_ROUTE = 2,     /* an expert id out of range or repeated inside a token was dropped */
+  DARASK_STATUS_ACT_RANGE = 4      /* an activation or SwiGLU product exceeds 65504 in magnitude: the decode kernels hold
+                                      activations as two fp16 planes (the reference reads float32), the result is not finite */
+};
 
 /* ---- routing ------------------------------------------------------------------------------
  * Top-k and gate weights from float32 logits [tokens][ld], bit-exact in ids and order with
@@ -108,12 +113,17 @@ typedef struct {
   int* ids;                                            /* [tokens][topk]      ("ids")               */
   float* prob;                                         /* [tokens][topk]      ("prob")              */
   void* workspace; size_t workspace_bytes;
-  int stage_mask;                                      /* 0: whole layer; else bits 1 router+top-k, 2 gate/up, 4 down, 8 combine */
+  int reserved;                                        /* must be 0 */
 } KogarashiMoe;
 size_t kogarashi_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens);
 /* zeroes the control words once after allocation */
 int kogarashi_moe_workspace_init(void* workspace, size_t bytes, darask_stream_t stream);
 int kogarashi_moe_layer(const KogarashiMoe* desc /* host */, darask_stream_t stream);
+/* One token with an F32 router and Q4_K gate/up runs as ONE persistent launch (router rows, top-k in every CTA,
+ * gate/up, down and combine behind two bounded grid barriers, the weight stream running across them); other shapes
+ * take four launches.  enabled = 0 makes the calling host thread take the four launches for one token as well
+ * (no counterpart in the reference; used to compare the two paths). */
+int kogarashi_moe_set_single_launch(int enabled);
 /* copies the status word to *host_status and synchronizes the stream */
 int kogarashi_moe_status(const void* workspace, unsigned* host_status /* host */, darask_stream_t stream);
 

@@ -101,14 +101,19 @@ def tsumuji_logits(layer: TsumujiLayer, x: np.ndarray) -> np.ndarray:
     return (x.astype(np.float64) @ layer.router.astype(np.float64).T).astype(np.float32)
 
 
-def tsumuji_forward(layer: TsumujiLayer, x: np.ndarray, logits=None):
+def tsumuji_forward(layer: TsumujiLayer, x: np.ndarray, logits=None, ids=None):
     """x float32 [N,H] -> dict(logits, ids, w, shared_gate, out float32 [N,H]);
     out = sum_s w_s y_s + shared_gate * y_shared (ops.cu:217-223, without the residual
     stream write-back)."""
     h, f, k = layer.hidden, layer.inter, layer.topk
     if logits is None:
         logits = tsumuji_logits(layer, x)
-    ids, w, sgate = R.route_tsumuji(logits, layer.experts, k)
+    sel, w, sgate = R.route_tsumuji(logits, layer.experts, k)
+    if ids is None:
+        ids = sel
+    else:                                   # a given selection (near-tie resolved differently): its own weights
+        ids = np.asarray(ids, np.int32)
+        w = R.weights_for_ids(R.TSUMUJI, logits, ids, layer.experts)
     out = np.zeros((x.shape[0], h), np.float64)
     cache = {}
     for t in range(x.shape[0]):
@@ -165,7 +170,7 @@ def _hayate_mats(img, stride, h, f, rounded):
             F.nvfp4_tiled_decode(img[2 * stride:], h, f, rounded=rounded).astype(np.float64))
 
 
-def hayate_forward(layer: HayateLayer, x: np.ndarray, logits=None):
+def hayate_forward(layer: HayateLayer, x: np.ndarray, logits=None, ids=None):
     """x bf16-valued float32 [T,H] -> dict(logits, ids, weights, out bf16-valued [T,H]).
     Routed experts: unrounded NVFP4 weights; shared expert: bf16-rounded weights
     (decode.cu:44-45,52). Products and expert outputs are rounded to bf16, experts are
@@ -174,7 +179,12 @@ def hayate_forward(layer: HayateLayer, x: np.ndarray, logits=None):
     h, f, k = layer.hidden, layer.inter, layer.topk
     if logits is None:
         logits = hayate_logits(layer, x)
-    ids, w = R.route_hayate(logits, layer.bias, k, layer.scale)
+    sel, w = R.route_hayate(logits, layer.bias, k, layer.scale)
+    if ids is None:
+        ids = sel
+    else:
+        ids = np.asarray(ids, np.int32)
+        w = R.weights_for_ids(R.HAYATE, logits, ids, layer.experts, layer.bias, layer.scale)
     out = np.zeros((x.shape[0], h), np.float32)
     cache = {}
     sg, su, sd = _hayate_mats(layer.shared, layer.stride, h, f, True)

@@ -88,6 +88,32 @@ def route_hayate(logits: np.ndarray, bias: np.ndarray, k: int = 8, scale: float 
     return ids, w
 
 
+def weights_for_ids(mode: int, logits: np.ndarray, ids: np.ndarray, experts: int, bias=None, scale: float = 1.0):
+    """Gate weights of a GIVEN selection (ids [T,k], selection order), formed as each router forms them. Used when a
+    device resolved a near-tie of two selection keys differently from numpy: the outputs are then compared on the
+    device's own selection."""
+    logits = np.atleast_2d(_f32(logits))
+    ids = np.atleast_2d(np.asarray(ids, np.int64))
+    w = np.empty(ids.shape, np.float32)
+    for t in range(ids.shape[0]):
+        row = logits[t, :experts]
+        if mode == KOGARASHI:
+            v = row[ids[t]]
+            z = _exp32(v - v[0])
+            w[t] = (z / z.astype(np.float64).sum().astype(np.float32)).astype(np.float32)
+        elif mode == TSUMUJI:
+            key = _exp32(row - row.max())
+            p = (key[ids[t]] / np.float32(key.astype(np.float64).sum())).astype(np.float32)
+            w[t] = (p / np.float32(p.astype(np.float64).sum())).astype(np.float32)
+        else:
+            sel = _sigmoid32(row)[ids[t]]
+            total = np.float32(0)
+            for v in sel:
+                total = np.float32(total + v)
+            w[t] = ((sel / np.float32(total + np.float32(1e-20))).astype(np.float32) * np.float32(scale)).astype(np.float32)
+    return w
+
+
 def selection_keys(mode: int, logits: np.ndarray, experts: int, bias=None) -> np.ndarray:
     """The float32 keys each router sorts by, as the oracle forms them."""
     logits = np.atleast_2d(_f32(logits))[:, :experts]

@@ -82,6 +82,8 @@ def test_tsumuji_virtual_ranks_on_one_gpu(world, tokens):
     hidden, inter, experts, topk = 512, 256, 16, 4
     local = experts // world
     layer, acts = W.tsumuji_layer(60 + world, hidden, inter, experts, topk, tokens * world, pool=experts)
+    # float32 rows that bf16 cannot hold: the hi / lo split of the window front end (more than 16 tokens) carries information
+    acts["x"] = W.normal(W.rng_for(600 + world), (tokens * world, hidden), 1.0)
     t = torch.from_numpy
     backends, sent = [], []
     for r in range(world):
@@ -110,9 +112,17 @@ def test_tsumuji_virtual_ranks_on_one_gpu(world, tokens):
     for r in range(world):
         out = backends[r].combine(y_home[r], sent[r][0]).cpu().numpy()
         xs = acts["x"][r * tokens:(r + 1) * tokens]
-        ref = L.tsumuji_forward(layer, xs, logits=backends[r].rlogits[:tokens].cpu().numpy())
-        if not np.array_equal(sent[r][0]["ids"].cpu().numpy(), ref["ids"]):
-            pytest.skip("a near-tie in the softmax keys resolved differently")
+        logits = backends[r].rlogits[:tokens].cpu().numpy()
+        assert np.allclose(logits, L.tsumuji_logits(layer, xs), rtol=1e-4, atol=1e-4)
+        ref = L.tsumuji_forward(layer, xs, logits=logits)
+        ids = sent[r][0]["ids"].cpu().numpy()
+        if not np.array_equal(ids, ref["ids"]):          # only keys within 4 ulp of each other may swap (expf rounding)
+            from oracle import routing as R
+            keys = R.selection_keys(R.TSUMUJI, logits, layer.experts)
+            for tok in np.nonzero((ids != ref["ids"]).any(1))[0]:
+                a, b = keys[tok, ids[tok]], keys[tok, ref["ids"][tok]]
+                assert np.all(np.abs(a - b) <= 4 * np.spacing(np.maximum(a, b)))
+            ref = L.tsumuji_forward(layer, xs, logits=logits, ids=ids)
         W.check_output(out, ref["out"])
 
 

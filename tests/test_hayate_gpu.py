@@ -43,8 +43,8 @@ def check_layer(layer, acts):
     assert np.allclose(logits, L.hayate_logits(layer, acts["x"]), rtol=1e-4, atol=1e-4)
     ref = L.hayate_forward(layer, acts["x"], logits=logits)
     keys = R.selection_keys(R.HAYATE, logits, layer.experts, layer.bias)
-    if not check_ids(m.ids[:t].cpu().numpy(), ref["ids"], keys):
-        pytest.skip("near-equal selection keys resolved differently; outputs not comparable")
+    if not check_ids(m.ids[:t].cpu().numpy(), ref["ids"], keys):     # near-tie: compare on the device's own selection
+        ref = L.hayate_forward(layer, acts["x"], logits=logits, ids=m.ids[:t].cpu().numpy())
     assert np.allclose(m.weights[:t].cpu().numpy(), ref["weights"], rtol=1e-4)
     # outputs are bf16: one rounding flip is 2^-8 of the value, so the max-abs bar is one bf16 step of max|ref|
     return W.check_output(out, ref["out"], rel=1e-3, max_abs=2.0 ** -8)
@@ -94,7 +94,7 @@ def test_reference_named_decode_launchers():
     ref = L.hayate_forward(layer, acts["x"], logits=logits.cpu().numpy()[None])
     keys = R.selection_keys(R.HAYATE, logits.cpu().numpy()[None], E, layer.bias)
     if not check_ids(ids.cpu().numpy()[None], ref["ids"], keys):
-        pytest.skip("near-equal selection keys")
+        ref = L.hayate_forward(layer, acts["x"], logits=logits.cpu().numpy()[None], ids=ids.cpu().numpy()[None])
     # the host looks the images up (all resident): device array of top-k pointers in route order
     table = torch.tensor([images.data_ptr() + int(e) * images.shape[1] for e in ids.cpu().numpy()], dtype=torch.int64, device=dev)
     stride = layer.stride
