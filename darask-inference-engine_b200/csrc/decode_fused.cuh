@@ -3,15 +3,18 @@
 //   phase R   every CTA projects its one or two router rows (fetched before the dependency wait), writes the logits,
 //             arrives at grid barrier 1; the producer warp of every CTA then selects the top-k itself (same result
 //             everywhere), so no CTA waits for a routing block and no plan travels through global memory
-//   phase 1   gate/up tiles (8 gate rows + the 8 matching up rows) x K parts, SwiGLU product written as fp16 hi/lo
+//   phase 1   gate/up tiles (8 gate rows + the 8 matching up rows), SwiGLU product written as fp16 hi/lo
 //   barrier 2 all products visible; every CTA stages the K+1 product vectors in shared memory
-//   phase 2   down tiles (16 rows of one expert) x K parts as float32 partial rows; the warp that completes a
+//   phase 2   down tiles (16 rows of one expert) as float32 rows; the warp that completes the last expert of a
 //             16-row tile (a counter per tile) adds the weighted experts in slot order and the gated shared expert
 //             into the residual stream
 //
-// The weight stream does not stop at the barriers: one producer warp issues `cp.async.bulk` row copies into a ring of
-// stages in a fixed unit order (shared expert first, then the routed experts, then the down units); while the gate/up
-// units are being multiplied the ring refills with down weights, which depend on the routing only.
+// The weight stream does not stop at the barriers: one producer thread issues ONE `cp.async.bulk` copy per chunk of
+// whole, consecutive weight rows (8 gate rows, the 8 matching up rows, or 16 down rows: 7 to 37 KB, contiguous in
+// global memory) into a ring of chunk slots in a fixed order (shared expert first, then the routed experts, then the
+// down tiles); while the gate/up tiles are being multiplied the ring refills with down weights, which depend on the
+// routing only. A tile is multiplied by a quad of warps that take its 256-column blocks in turn (warp k: blocks
+// k, k + 4, ...) and add their partial sums through shared memory.
 //
 // Arithmetic per 256-column block, `mma.sync.m16n8k16` (fp16 in, fp32 accumulate): the A operand holds the weight
 // codes as fp16 magic numbers (1024 + q, no conversion, no per-weight scaling); the B operand is block diagonal: the
@@ -33,9 +36,10 @@ constexpr unsigned kStatusActRange = 4u;   // an activation does not fit the fp1
 
 constexpr int kFusedConsumers = 16;                          // consumer warps
 constexpr int kFusedThreads = (kFusedConsumers + 1) * 32;    // + the producer warp
-constexpr int kFusedSlots = 16;                              // gate/up tiles whose partial sums may be pending
+constexpr int kFusedSlots = 32;                              // partial-sum slots: a slot is reused 32 tiles later, further than the ring reaches
 constexpr int kFusedMaxStages = 30;
-constexpr int kFusedZeroBytes = 2560;                        // zero fragments read by lanes outside a column's group
+constexpr int kFusedZeroBytes = 512;                         // zero fragments read by lanes outside a column's group
+constexpr int kFusedQuad = 4;                                // warps that share a tile
 
 struct FusedArgs {
   const float* router_w; const float* router_bias; const float* sh_inp;
@@ -43,10 +47,9 @@ struct FusedArgs {
   const uint8_t* sh_gate; const uint8_t* sh_up; const uint8_t* sh_down;
   const float* n; float* x; float* logits; int* ids; float* prob;
   int H, F, E, K, G, has_shared;
-  int kp1, nbu1, pitch1, row_bytes1, tpg;         // gate/up: K parts, blocks per unit, row slot pitch, tiles per group
-  int kp2, nbu2, pitch2, row_bytes2, rt2, down_q6; // down: the same, 16-row tiles of the output
-  int nblk2;
-  int stage_bytes, nstage;
+  int nblk1, row_bytes1, tpg;                     // gate/up: 256-column blocks per row, bytes per row, tiles per group
+  int nblk2, row_bytes2, rt2, down_q6;            // down: the same, 16-row tiles of the output
+  int stage_bytes, nstage;                        // chunk slot size and number of slots of the ring
   int off_bars, off_psum, off_zero, off_act, off_ring;   // shared-memory offsets
   int act_lo1, act_xs1, act_rows;                 // phase R/1 inside the activation area: lo-plane stride, sums, router rows
   int act_lo2, act_grp2, act_xs2;                 // phase 2: lo-plane stride, bytes per group, offset of the sums
@@ -275,11 +278,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 272);
   volatile int* go_flag = reinterpret_cast<volatile int*>(smem + 276);
   int* tcnt = reinterpret_cast<int*>(smem + 288);                    // [kFusedSlots]
-  float* part = reinterpret_cast<float*>(smem + 352);                // [16][2] router partial sums
+  float* part = reinterpret_cast<float*>(smem + 448);                // [16][2] router partial sums
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + a.off_bars);   // [nstage]
   uint64_t* empty = full + a.nstage;                                 // [nstage]
   uint64_t* routed = empty + a.nstage;                               // routing published
-  float* psum = reinterpret_cast<float*>(smem + a.off_psum);         // [slot][kp1][16]
+  float* psum = reinterpret_cast<float*>(smem + a.off_psum);         // [slot][warp of the quad][16]
   const uint32_t zero_base = smem_u32(smem + a.off_zero);
   const uint32_t act = smem_u32(smem + a.off_act);
   const uint32_t ring = smem_u32(smem + a.off_ring);
@@ -288,7 +291,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(full + s, 1);
-      mbar_init(empty + s, 1);
+      mbar_init(empty + s, kFusedQuad);
     }
     mbar_init(routed, 1);
     *abort_flag = 0;
@@ -298,60 +301,53 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   for (int i = tid; i < kFusedZeroBytes / 4; i += kFusedThreads) reinterpret_cast<uint32_t*>(smem + a.off_zero)[i] = 0u;
   __syncthreads();
 
-  // ---- the unit lists of this CTA (same arithmetic in producer and consumers) ----
-  const int tiles1 = a.G * a.tpg;                                    // gate/up tiles of the layer, shared expert first
-  const int my_tiles1 = cta < tiles1 ? (tiles1 - cta + grid - 1) / grid : 0;
-  const int n1 = my_tiles1 * a.kp1;
-  const int units2 = a.rt2 * a.G * a.kp2;
-  const int n2 = cta < units2 ? (units2 - cta + grid - 1) / grid : 0;
-  const int total = n1 + n2;
+  // ---- the work lists of this CTA (same arithmetic in producer and consumers) ----
+  // gate/up tiles tau = cta, cta + grid, ... of G * tpg (group-major, shared expert first); down tiles likewise of
+  // rt2 * G (row-tile-major). Chunks of the ring, in order: (gate rows, up rows) per gate/up tile, then one per down tile.
+  const int tiles1 = a.G * a.tpg;
+  const int n1 = cta < tiles1 ? (tiles1 - cta + grid - 1) / grid : 0;
+  const int tiles2 = a.rt2 * a.G;
+  const int n2 = cta < tiles2 ? (tiles2 - cta + grid - 1) / grid : 0;
+  const int chunks = 2 * n1 + n2;
   const int R = a.E + a.has_shared;                                  // router rows incl. the shared gate projection
 
   if (warp == kFusedConsumers) {
     // =========================== producer warp ===========================
-    // lanes 0-15 each copy one row slot of a unit
-    auto issue = [&](int p) -> bool {
-      const int stage = p % NS, use = p / NS;
+    // lane 0 issues one bulk copy per chunk; the whole warp selects the top-k in between
+    auto issue = [&](int c) -> bool {
+      const int stage = c % NS, use = c / NS;
       if (use > 0 && !mbar_wait_abortable(empty + stage, (use - 1) & 1, a.status, abort_flag)) return false;
-      if (p < n1) {
-        const int lt = p / a.kp1, kp = p - lt * a.kp1;
+      const uint8_t* src;
+      uint32_t bytes;
+      if (c < 2 * n1) {
+        const int lt = c >> 1, m = c & 1;
         const int tau = cta + lt * grid, gi = tau / a.tpg, tile = tau - gi * a.tpg;
-        const int bytes = a.nbu1 * 144;
-        if (lane == 0) mbar_arrive_expect_tx(full + stage, 16u * bytes);
-        __syncwarp();
-        if (lane < 16) {
-          const int m = lane >> 3, r = tile * 8 + (lane & 7);
-          const uint8_t* base;
-          if (a.has_shared && gi == 0) base = m ? a.sh_up : a.sh_gate;
-          else base = (m ? a.up_w : a.gate_w) + size_t(sm_ids[gi - a.has_shared]) * a.F * a.row_bytes1;
-          bulk_g2s(reinterpret_cast<void*>(smem + a.off_ring + stage * a.stage_bytes + lane * a.pitch1),
-                   base + size_t(r) * a.row_bytes1 + size_t(kp) * bytes, bytes, full + stage);
-        }
+        const uint8_t* base;
+        if (a.has_shared && gi == 0) base = m ? a.sh_up : a.sh_gate;
+        else base = (m ? a.up_w : a.gate_w) + size_t(sm_ids[gi - a.has_shared]) * a.F * a.row_bytes1;
+        src = base + size_t(tile) * 8 * a.row_bytes1;
+        bytes = 8u * a.row_bytes1;
       } else {
-        const int u2 = cta + (p - n1) * grid;
-        const int kp = u2 % a.kp2, rest = u2 / a.kp2, gi = rest % a.G, rt = rest / a.G;
-        const int blk = DOWN_Q6 ? 208 : 144, bytes = a.nbu2 * blk;
-        if (lane == 0) mbar_arrive_expect_tx(full + stage, 16u * (bytes + (DOWN_Q6 ? 16 : 0)));
-        __syncwarp();
-        if (lane < 16) {
-          const uint8_t* base = (a.has_shared && gi == 0) ? a.sh_down : a.down_w + size_t(sm_ids[gi - a.has_shared]) * a.H * a.row_bytes2;
-          const uint8_t* row = base + size_t(rt * 16 + lane) * a.row_bytes2;
-          uint8_t* slot = smem + a.off_ring + stage * a.stage_bytes + lane * a.pitch2;
-          bulk_g2s(slot, row + size_t(kp) * bytes, bytes, full + stage);
-          if (DOWN_Q6) bulk_g2s(slot + bytes, row + a.nblk2 * 208 + ((2 * kp * a.nbu2) & ~15), 16, full + stage);
-        }
+        const int u2 = cta + (c - 2 * n1) * grid, gi = u2 % a.G, rt = u2 / a.G;
+        const uint8_t* base = (a.has_shared && gi == 0) ? a.sh_down : a.down_w + size_t(sm_ids[gi - a.has_shared]) * a.H * a.row_bytes2;
+        src = base + size_t(rt) * 16 * a.row_bytes2;
+        bytes = 16u * a.row_bytes2;
       }
+      mbar_arrive_expect_tx(full + stage, bytes);
+      bulk_g2s(smem + a.off_ring + stage * a.stage_bytes, src, bytes, full + stage);
       return true;
     };
-    int p = 0;
-    bool ok = true;
+    int c = 0;
+    int ok = 1;
     // the shared expert's first tile does not depend on anything: its weights are requested before the dependency wait
-    if (a.has_shared)
-      for (; ok && p < n1 && p < NS && (cta + (p / a.kp1) * grid) < a.tpg; ++p) ok = issue(p);
+    if (lane == 0 && a.has_shared && n1 > 0 && cta < a.tpg)
+      for (; ok && c < 2 && c < NS; ++c) ok = issue(c) ? 1 : 0;
+    __syncwarp();
     pdl_wait();
     // grid barrier 1: every router row has been written
-    if (ok && lane == 0) ok = grid_wait(a.gbar, unsigned(grid), a.status, abort_flag);
-    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (ok && lane == 0) ok = grid_wait(a.gbar, unsigned(grid), a.status, abort_flag) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    c = __shfl_sync(0xffffffffu, c, 0);
     if (ok) {
       RouteArgs r{a.logits, a.E, a.E, a.K, 1, nullptr, 1.f, nullptr, nullptr, nullptr};
       route_token_to<kRouteKogarashi>(r, 0, lane, sm_ids, sm_prob);
@@ -362,13 +358,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
         a.prob[lane] = sm_prob[lane];
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(routed);
-      for (; ok && p < total; ++p) ok = issue(p);
+      if (lane == 0) {
+        mbar_arrive(routed);
+        for (; ok && c < chunks; ++c) ok = issue(c) ? 1 : 0;
+      }
     }
-    if (!ok) {
+    if (lane == 0 && !ok) {
       // gave up: let the copies already requested land before the CTA's shared memory goes away
       const uint64_t start = global_timer_ns();
-      for (int q = (p > NS ? p - NS : 0); q < p; ++q)
+      for (int q = (c > NS ? c - NS : 0); q < c; ++q)
         while (!mbar_test(full + q % NS, (q / NS) & 1) && global_timer_ns() - start < kWaitLimitNs) __nanosleep(256);
     }
     return;
@@ -377,8 +375,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   // =========================== consumer warps ===========================
   const DiagLane dl = diag_lane(lane);
   const int g = dl.g, j = dl.j;
+  const int quad = warp >> 2, kq = warp & 3;                          // tiles go to quads in turn; warp kq takes blocks kq, kq + 4, ...
   // ---- phase R: router rows of this CTA: row cta and row cta + grid ----
-  const int chunks = a.H / 4;                                        // float4 per row
+  const int chunks4 = a.H / 4;                                       // float4 per row
   const uint32_t rows_sm = act + a.act_rows;
   int my_rows = 0;
 #pragma unroll
@@ -387,7 +386,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
     if (row < R) {
       my_rows = q + 1;
       const float* src = row < a.E ? a.router_w + size_t(row) * a.H : a.sh_inp;
-      for (int i = tid; i < chunks; i += kFusedConsumers * 32) cp_async16(rows_sm + (q * chunks + i) * 16, src + 4 * i);
+      for (int i = tid; i < chunks4; i += kFusedConsumers * 32) cp_async16(rows_sm + (q * chunks4 + i) * 16, src + 4 * i);
     }
   }
   cp_async_commit();
@@ -398,7 +397,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
 #pragma unroll
   for (int c = 0; c < MAXC; ++c) {
     const int i = tid + c * kFusedConsumers * 32;
-    nv[c] = i < chunks ? __ldcg(reinterpret_cast<const float4*>(a.n) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    nv[c] = i < chunks4 ? __ldcg(reinterpret_cast<const float4*>(a.n) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   cp_async_wait<0>();
   float dot[2] = {0.f, 0.f};
@@ -408,8 +407,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
 #pragma unroll
       for (int c = 0; c < MAXC; ++c) {
         const int i = tid + c * kFusedConsumers * 32;
-        if (i < chunks) {
-          const uint4 w = lds128(rows_sm + (q * chunks + i) * 16);
+        if (i < chunks4) {
+          const uint4 w = lds128(rows_sm + (q * chunks4 + i) * 16);
           dot[q] = fmaf(__uint_as_float(w.x), nv[c].x, dot[q]);
           dot[q] = fmaf(__uint_as_float(w.y), nv[c].y, dot[q]);
           dot[q] = fmaf(__uint_as_float(w.z), nv[c].z, dot[q]);
@@ -447,46 +446,32 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
     for (int c = 0; c < MAXC; ++c) {
       const int i = tid + c * kFusedConsumers * 32;
       uint2 hi, lo;
-      float s = split_planes4(nv[c], hi, lo, bad);
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
-      s += __shfl_xor_sync(0xffffffffu, s, 4);
-      if (i < chunks) {
+      float sum = split_planes4(nv[c], hi, lo, bad);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      if (i < chunks4) {
         sts64(act + 8 * i, hi);
         sts64(act + a.act_lo1 + 8 * i, lo);
-        if ((i & 7) == 0) sts32f(act + a.act_xs1 + 4 * (i >> 3), s);
+        if ((i & 7) == 0) sts32f(act + a.act_xs1 + 4 * (i >> 3), sum);
       }
     }
     if (bad) atomicOr(a.status, kStatusActRange);
   }
   named_barrier(1, kFusedConsumers * 32);
 
-  // this lane's B fragment offsets inside a plane pair (bytes), relative to the first column of a block
+  // This lane's B fragments: offset inside a plane pair (bytes) from the first column of a block, and the step from
+  // block to block (0 for the lanes that read the zero area).
   const uint32_t lane_x4 = (dl.plane ? uint32_t(a.act_lo1) : 0u) + 2u * (32u * (2 * ((g >> 1) & 1) + (g >> 2)) + 16u * (j & 1));
+  const uint32_t step0 = (dl.active && !dl.second) ? 512u : 0u, step1 = (dl.active && dl.second) ? 512u : 0u;
   bool ok = true;
 
-  // ---- phase 1: gate/up units ----
-  for (int p = warp; p < n1 && ok; p += kFusedConsumers) {
-    const int stage = p % NS, use = p / NS;
-    const int lt = p / a.kp1, kp = p - lt * a.kp1;
-    const int tau = cta + lt * grid, gi = tau / a.tpg, tile = tau - gi * a.tpg;
-    if (!mbar_wait_abortable(full + stage, use & 1, a.status, abort_flag)) { ok = false; break; }
-    const uint32_t slot0 = ring + stage * a.stage_bytes;
-    const uint32_t rA = slot0 + g * a.pitch1, rB = slot0 + (g + 8) * a.pitch1;
-    const int b0 = kp * a.nbu1;
-    const uint32_t xreal = act + lane_x4 + 512u * b0;
-    uint32_t xb0 = (dl.active && !dl.second) ? xreal : zero_base;
-    uint32_t xb1 = (dl.active && dl.second) ? xreal : zero_base;
-    uint32_t xs = act + a.act_xs1 + 32u * b0;
-    float acc0 = 0.f, acc1 = 0.f;
-    for (int b = 0; b < a.nbu1; ++b) {
-      q4k_block_diag(rA + b * 144, rB + b * 144, j, xb0, xb1, xs, acc0, acc1);
-      xb0 += 512; xb1 += 512; xs += 32;
-    }
+  // Sum of the quad's partial rows; the last warp to arrive gets all sixteen rows (lanes 0-15) and owns the epilogue.
+  // `slot`: partial-sum slot of the tile (tiles of one quad that may be pending at the same time have different slots).
+  auto quad_reduce = [&](int slot, float acc0, float acc1, float& row_sum) -> bool {
     acc0 = quad_sum(acc0);
     acc1 = quad_sum(acc1);
-    const int slot = lt % kFusedSlots;
-    float* ps = psum + (slot * a.kp1 + kp) * 16;
+    float* ps = psum + (slot * kFusedQuad + kq) * 16;
     if (j == 0) {
       ps[g] = acc0;
       ps[g + 8] = acc1;
@@ -495,18 +480,42 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
     int last = 0;
     if (lane == 0) {
       __threadfence_block();
-      last = atomicAdd(&tcnt[slot], 1) == a.kp1 - 1;
+      last = atomicAdd(&tcnt[slot], 1) == kFusedQuad - 1;
       __threadfence_block();
     }
     last = __shfl_sync(0xffffffffu, last, 0);
     if (last) {
+      row_sum = 0.f;
+      if (lane < 16)
+        for (int q = 0; q < kFusedQuad; ++q) row_sum += psum[(slot * kFusedQuad + q) * 16 + lane];
+      __syncwarp();
+      if (lane == 0) tcnt[slot] = 0;
+    }
+    return last != 0;
+  };
+
+  // ---- phase 1: gate/up tiles ----
+  for (int lt = quad; lt < n1 && ok; lt += kFusedConsumers / kFusedQuad) {
+    const int cg = 2 * lt, cu = cg + 1;
+    const int tau = cta + lt * grid, gi = tau / a.tpg, tile = tau - gi * a.tpg;
+    float acc0 = 0.f, acc1 = 0.f;
+    if (kq < a.nblk1) {
+      if (!mbar_wait_abortable(full + cg % NS, (cg / NS) & 1, a.status, abort_flag) ||
+          !mbar_wait_abortable(full + cu % NS, (cu / NS) & 1, a.status, abort_flag)) { ok = false; break; }
+      const uint32_t rA = ring + (cg % NS) * a.stage_bytes + g * a.row_bytes1;      // gate row g of the tile
+      const uint32_t rB = ring + (cu % NS) * a.stage_bytes + g * a.row_bytes1;      // up row g
+      const uint32_t xreal = act + lane_x4;
+      const uint32_t xb0 = step0 ? xreal : zero_base, xb1 = step1 ? xreal : zero_base;
+      for (int b = kq; b < a.nblk1; b += kFusedQuad)
+        q4k_block_diag(rA + b * 144, rB + b * 144, j, xb0 + b * step0, xb1 + b * step1, act + a.act_xs1 + 32u * b, acc0, acc1);
+    }
+    float rows = 0.f;
+    const bool last = quad_reduce(lt % kFusedSlots, acc0, acc1, rows);
+    if (last) {
+      // lanes 0-7 hold the gate rows, lanes 8-15 the up rows
+      const float up = __shfl_down_sync(0xffffffffu, rows, 8);
       if (lane < 8) {
-        float gate = 0.f, up = 0.f;
-        for (int q = 0; q < a.kp1; ++q) {
-          gate += psum[(slot * a.kp1 + q) * 16 + lane];
-          up += psum[(slot * a.kp1 + q) * 16 + 8 + lane];
-        }
-        const float h = silu_mul(gate, up);
+        const float h = silu_mul(rows, up);
         const __half hi = __float2half_rn(h);
         const __half lo = __float2half_rn(h - __half2float(hi));
         if (fabsf(h) > 65504.f) atomicOr(a.status, kStatusActRange);
@@ -514,13 +523,14 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
         dst[0] = hi;
         dst[a.F] = lo;
       }
-      __syncwarp();
-      if (lane == 0) tcnt[slot] = 0;
     }
-    // The stage is handed back only now: a warp that is still summing a tile keeps the producer from running
+    // The chunks are handed back only now: a warp that is still summing a tile keeps the producer from running
     // kFusedSlots tiles ahead, so a slot of partial sums is never reused while it is being read.
     __syncwarp();
-    if (lane == 0) mbar_arrive(empty + stage);
+    if (lane == 0) {
+      mbar_arrive(empty + cg % NS);
+      mbar_arrive(empty + cu % NS);
+    }
   }
 
   // ---- grid barrier 2: every product is in global memory ----
@@ -548,10 +558,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
       }
       const float2 h01 = __half22float2(u32_as_h2(hi.x)), h23 = __half22float2(u32_as_h2(hi.y));
       const float2 l01 = __half22float2(u32_as_h2(lo.x)), l23 = __half22float2(u32_as_h2(lo.y));
-      float s = ((h01.x + l01.x) + (h01.y + l01.y)) + ((h23.x + l23.x) + (h23.y + l23.y));
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
-      if (!DOWN_Q6) s += __shfl_xor_sync(0xffffffffu, s, 4);
+      float sum = ((h01.x + l01.x) + (h01.y + l01.y)) + ((h23.x + l23.x) + (h23.y + l23.y));
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if (!DOWN_Q6) sum += __shfl_xor_sync(0xffffffffu, sum, 4);
       if (live) {
         // [h0,h1,h2,h3] -> [h0,h2,h1,h3]
         const uint2 ph = make_uint2(__byte_perm(hi.x, hi.y, 0x5410), __byte_perm(hi.x, hi.y, 0x7632));
@@ -560,85 +570,70 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
         sts64(gb + 8 * i, ph);
         sts64(gb + a.act_lo2 + 8 * i, pq);
         if (DOWN_Q6) {
-          if ((i & 3) == 0) sts32f(act + a.act_xs2 + 4 * (gi * (a.F / 16) + (i >> 2)), s);
+          if ((i & 3) == 0) sts32f(act + a.act_xs2 + 4 * (gi * (a.F / 16) + (i >> 2)), sum);
         } else {
-          if ((i & 7) == 0) sts32f(act + a.act_xs2 + 4 * (gi * (a.F / 32) + (i >> 3)), s);
+          if ((i & 7) == 0) sts32f(act + a.act_xs2 + 4 * (gi * (a.F / 32) + (i >> 3)), sum);
         }
       }
     }
   }
   named_barrier(1, kFusedConsumers * 32);
 
-  // ---- phase 2: down units ----
+  // ---- phase 2: down tiles ----
   const uint32_t lane_x6 = (dl.plane ? uint32_t(a.act_lo2) : 0u) + 2u * (64u * (g >> 2) + 16u * ((g >> 1) & 1) + 8u * (j & 1));
   const uint32_t lane_x4d = (dl.plane ? uint32_t(a.act_lo2) : 0u) + 2u * (32u * (2 * ((g >> 1) & 1) + (g >> 2)) + 16u * (j & 1));
-  for (int p = n1 + ((warp - n1 % kFusedConsumers + kFusedConsumers) % kFusedConsumers); p < total; p += kFusedConsumers) {
-    const int stage = p % NS, use = p / NS;
-    const int u2 = cta + (p - n1) * grid;
-    const int kp = u2 % a.kp2, rest = u2 / a.kp2, gi = rest % a.G, rt = rest / a.G;
-    if (!mbar_wait_abortable(full + stage, use & 1, a.status, abort_flag)) return;
-    const uint32_t slot0 = ring + stage * a.stage_bytes;
-    const uint32_t rA = slot0 + g * a.pitch2, rB = slot0 + (g + 8) * a.pitch2;
-    const int b0 = kp * a.nbu2;
-    const uint32_t xreal = act + gi * a.act_grp2 + (DOWN_Q6 ? lane_x6 : lane_x4d) + 512u * b0;
-    uint32_t xb0 = (dl.active && !dl.second) ? xreal : zero_base;
-    uint32_t xb1 = (dl.active && dl.second) ? xreal : zero_base;
+  for (int t2 = quad; t2 < n2; t2 += kFusedConsumers / kFusedQuad) {
+    const int c = 2 * n1 + t2, stage = c % NS;
+    const int u2 = cta + t2 * grid, gi = u2 % a.G, rt = u2 / a.G;
     float acc0 = 0.f, acc1 = 0.f;
-    if (DOWN_Q6) {
-      uint32_t xs = act + a.act_xs2 + 4u * (gi * (a.F / 16) + 16 * b0);
-      const uint32_t dchunkA = rA + a.nbu2 * 208, dchunkB = rB + a.nbu2 * 208;
-      for (int b = 0; b < a.nbu2; ++b) {
-        const int doff = (2 * (b0 + b)) & 15;
-        const uint32_t dwA = lds32(dchunkA + (doff & ~3)), dwB = lds32(dchunkB + (doff & ~3));
-        const float dA = (doff & 2) ? half_hi(dwA) : half_lo(dwA), dB = (doff & 2) ? half_hi(dwB) : half_lo(dwB);
-        q6k_block_diag(rA + b * 208, rB + b * 208, j, dA, dB, xb0, xb1, xs, acc0, acc1);
-        xb0 += 512; xb1 += 512; xs += 64;
+    if (kq < a.nblk2) {
+      if (!mbar_wait_abortable(full + stage, (c / NS) & 1, a.status, abort_flag)) return;
+      const uint32_t slot0 = ring + stage * a.stage_bytes;
+      const uint32_t rA = slot0 + g * a.row_bytes2, rB = slot0 + (g + 8) * a.row_bytes2;
+      const uint32_t xreal = act + gi * a.act_grp2 + (DOWN_Q6 ? lane_x6 : lane_x4d);
+      const uint32_t xb0 = step0 ? xreal : zero_base, xb1 = step1 ? xreal : zero_base;
+      if (DOWN_Q6) {
+        const uint32_t xs = act + a.act_xs2 + 4u * (gi * (a.F / 16));
+        for (int b = kq; b < a.nblk2; b += kFusedQuad) {
+          // the f16 block scales follow the blocks of a row
+          const uint32_t dwA = lds32(rA + a.nblk2 * 208 + ((2 * b) & ~3)), dwB = lds32(rB + a.nblk2 * 208 + ((2 * b) & ~3));
+          const float dA = (b & 1) ? half_hi(dwA) : half_lo(dwA), dB = (b & 1) ? half_hi(dwB) : half_lo(dwB);
+          q6k_block_diag(rA + b * 208, rB + b * 208, j, dA, dB, xb0 + b * step0, xb1 + b * step1, xs + 64u * b, acc0, acc1);
+        }
+      } else {
+        const uint32_t xs = act + a.act_xs2 + 4u * (gi * (a.F / 32));
+        for (int b = kq; b < a.nblk2; b += kFusedQuad)
+          q4k_block_diag(rA + b * 144, rB + b * 144, j, xb0 + b * step0, xb1 + b * step1, xs + 32u * b, acc0, acc1);
       }
-    } else {
-      uint32_t xs = act + a.act_xs2 + 4u * (gi * (a.F / 32) + 8 * b0);
-      for (int b = 0; b < a.nbu2; ++b) {
-        q4k_block_diag(rA + b * 144, rB + b * 144, j, xb0, xb1, xs, acc0, acc1);
-        xb0 += 512; xb1 += 512; xs += 32;
+    }
+    float rows = 0.f;
+    const bool last = quad_reduce(t2 % kFusedSlots, acc0, acc1, rows);
+    if (last) {
+      // the finished rows of this expert, then the count of finished experts of the row tile
+      if (lane < 16) __stcg(a.y + size_t(gi) * a.H + rt * 16 + lane, rows);
+      __syncwarp();
+      int done = 0;
+      if (lane == 0) {
+        __threadfence();
+        done = atomicAdd(a.tile_cnt + rt, 1u) == unsigned(a.G - 1);
+        __threadfence();
+      }
+      done = __shfl_sync(0xffffffffu, done, 0);
+      if (done) {
+        // x[i] += sum_s fma(p_s, down_s[i]) + sigmoid(sg) * shared[i]   (kogarashi kernels/native.cu:113-117)
+        if (lane < 16) {
+          const int row = rt * 16 + lane;
+          float v = 0.f;
+          for (int s2 = 0; s2 < a.K; ++s2) v = fmaf(sm_prob[s2], __ldcg(a.y + size_t(s2 + a.has_shared) * a.H + row), v);
+          if (a.has_shared) v += sm_misc[0] * __ldcg(a.y + row);
+          a.x[row] += v;
+        }
+        __syncwarp();
+        if (lane == 0) a.tile_cnt[rt] = 0u;
       }
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty + stage);
-    acc0 = quad_sum(acc0);
-    acc1 = quad_sum(acc1);
-    // partial rows: y[kp][group][row]
-    float* y = a.y + (size_t(kp) * a.G + gi) * a.H + rt * 16;
-    if (j == 0) {
-      __stcg(y + g, acc0);
-      __stcg(y + g + 8, acc1);
-    }
-    __syncwarp();
-    int last = 0;
-    if (lane == 0) {
-      __threadfence();
-      last = atomicAdd(a.tile_cnt + rt, 1u) == unsigned(a.G * a.kp2 - 1);
-      __threadfence();
-    }
-    last = __shfl_sync(0xffffffffu, last, 0);
-    if (last) {
-      // x[i] += sum_s fma(p_s, down_s[i]) + sigmoid(sg) * shared[i]   (kogarashi kernels/native.cu:113-117)
-      if (lane < 16) {
-        const int row = rt * 16 + lane;
-        float v = 0.f;
-        for (int s = 0; s < a.K; ++s) {
-          float ys = 0.f;
-          for (int q = 0; q < a.kp2; ++q) ys += __ldcg(a.y + (size_t(q) * a.G + s + a.has_shared) * a.H + row);
-          v = fmaf(sm_prob[s], ys, v);
-        }
-        if (a.has_shared) {
-          float ys = 0.f;
-          for (int q = 0; q < a.kp2; ++q) ys += __ldcg(a.y + size_t(q) * a.G * a.H + row);
-          v += sm_misc[0] * ys;
-        }
-        a.x[row] += v;
-      }
-      __syncwarp();
-      if (lane == 0) a.tile_cnt[rt] = 0u;
-    }
   }
 }
 

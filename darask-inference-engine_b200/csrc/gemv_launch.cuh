@@ -34,11 +34,13 @@ inline cudaError_t launch_gemv(GemvArgs a, cudaStream_t stream) {
   if (FMT == kGemvNvfp4Tiled && a.rows % 128) return cudaErrorInvalidValue;
   const int smem = gemv_smem_bytes<FMT>();
   auto kernel = expert_gemv_kernel<FMT, DUAL, MINS_TILE, OUT>;
-  static bool configured = false;       // one opt-in per instantiation (and process)
-  if (!configured) {
+  static bool configured[64] = {};      // one opt-in per instantiation and device
+  const int dev = current_device_slot();
+  if (dev < 0) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
     const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured[dev] = true;
   }
   return launch_pdl(kernel, dim3(sm_count()), dim3(kGemvWarps * 32), size_t(smem), stream, a);
 }

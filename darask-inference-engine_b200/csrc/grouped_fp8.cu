@@ -116,12 +116,6 @@ static bool make_map(CUtensorMap* m, const void* base, unsigned long long rows, 
              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-#ifdef DMOE_G8_TRACE
-#include <cstdlib>
-static long long* g_g8_trace = nullptr;
-extern "C" void darask_g8_set_trace(long long* p) { g_g8_trace = p; }
-#endif
-
 static cudaError_t launch_grouped(const void* a_codes, const float* a_scales, unsigned long long a_rows, const void* w0,
                                   const void* w1, const float* sw0, const float* sw1, int experts, int n, int k, int mode,
                                   const unsigned* ranges, void* out, float* out_scales, const unsigned* out_row_map,
@@ -139,19 +133,17 @@ static cudaError_t launch_grouped(const void* a_codes, const float* a_scales, un
   g.out_bf16 = mode == kG8GateUpBf16 ? static_cast<__nv_bfloat16*>(out) : nullptr;
   g.out_codes = mode == kG8GateUpFp8 ? static_cast<uint8_t*>(out) : nullptr;
   g.out_scales = out_scales; g.out_row_map = out_row_map; g.status = status;
-#ifdef DMOE_G8_TRACE
-  g.trace = g_g8_trace;
-  { const char* dbg = getenv("DMOE_G8_DEBUG"); g.debug = dbg ? atoi(dbg) : 0; }
-#endif
   const size_t smem = size_t(kG8FixedSmem) + size_t(experts + 1) * sizeof(int);
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};      // the opt-in is per device
+  const int dev = current_device_slot();
+  if (dev < 0) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
     const int most = int(size_t(kG8FixedSmem) + size_t(kG8MaxExperts + 1) * sizeof(int));
     cudaError_t e = cudaFuncSetAttribute(grouped_fp8_kernel<kG8Plain>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (!e) e = cudaFuncSetAttribute(grouped_fp8_kernel<kG8GateUpBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (!e) e = cudaFuncSetAttribute(grouped_fp8_kernel<kG8GateUpFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, most);
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured[dev] = true;
   }
   const dim3 grid(sm_count()), block(kG8Threads);
   if (mode == kG8Plain) return launch_pdl(grouped_fp8_kernel<kG8Plain>, grid, block, smem, st, ma, mw0, mw1, g);

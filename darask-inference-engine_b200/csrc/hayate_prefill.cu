@@ -98,12 +98,14 @@ cudaError_t launch_grouped_bf16(void* out, float* acc, const void* x, const void
   g.out = static_cast<__nv_bfloat16*>(out);
   g.acc = acc; g.scales = scales; g.status = nullptr;
   const size_t smem = size_t(kGbFixedSmem) + size_t(groups + 1) * sizeof(int);
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};      // the opt-in is per device
+  const int dev = current_device_slot();
+  if (dev < 0) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
     const cudaError_t e = cudaFuncSetAttribute(grouped_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                                int(kGbFixedSmem + 1025 * sizeof(int)));
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured[dev] = true;
   }
   return launch_pdl(grouped_bf16_kernel, dim3(sm_count()), dim3(kGbThreads), smem, st, mw, g);
 }

@@ -55,7 +55,6 @@ struct KogarashiWs {
   int* counters; unsigned* done; unsigned* status; unsigned* gbar; unsigned* tile_cnt; int* active; unsigned* ranges;
   unsigned* assignments; int4* plan; float* sg; __half* xplanes; __half* xsum_planes; __half* hplanes; float* y; size_t bytes;
 };
-constexpr int kFusedMaxKParts = 4;          // K parts of the one-token down products (partial rows kept per part)
 constexpr int kFusedMaxRowTiles = 512;      // 16-row output tiles with a completion counter (hidden <= 8192)
 static KogarashiWs carve(void* base, int hidden, int inter, int experts, int topk, int tokens) {
   KogarashiWs w;
@@ -76,7 +75,7 @@ static KogarashiWs carve(void* base, int hidden, int inter, int experts, int top
   w.xsum_planes = reinterpret_cast<__half*>(take(size_t(tokens) * (hidden / 32) * 4));
   const size_t rows = size_t(tokens) * topk + tokens;
   w.hplanes = reinterpret_cast<__half*>(take(rows * 2 * inter * 2));
-  w.y = reinterpret_cast<float*>(take(rows * hidden * 4 * (tokens == 1 ? kFusedMaxKParts : 1)));
+  w.y = reinterpret_cast<float*>(take(rows * hidden * 4));
   w.bytes = off;
   return w;
 }
@@ -97,26 +96,6 @@ static cudaError_t launch_gemv_ggml(int ty, const GemvArgs& a, cudaStream_t st) 
 }
 
 // ---- the one-token layer as one launch (decode_fused.cuh) ---------------------------------------------------
-// K parts per row and blocks per unit: parts in {1, 2, 4, 8} (the consumer warps of a tile are neighbours), at most
-// four blocks per unit, as many parts as that allows.
-static bool fused_split(int nblk, int max_parts, int* parts, int* per) {
-  for (int pass = 0; pass < 2; ++pass)                 // first choice: two to four blocks per unit; else one
-    for (int kp = max_parts; kp >= 1; kp >>= 1) {
-      if (nblk % kp) continue;
-      const int n = nblk / kp;
-      if (n > 4 || (pass == 0 && n < 2)) continue;
-      *parts = kp;
-      *per = n;
-      return true;
-    }
-  return false;
-}
-static int fused_pitch(int payload, int residue_a, int residue_b) {      // smallest pitch >= payload, multiple of 16, = a or b mod 128
-  int p = (payload + 15) / 16 * 16;
-  while (p % 128 != residue_a && p % 128 != residue_b) p += 16;
-  return p;
-}
-
 // Fills `f` and returns true when the shape can take the single-launch path.
 static bool fused_plan(const KogarashiMoe* d, const KogarashiWs& w, FusedArgs* f, int* smem_bytes) {
   const int H = d->hidden, F = d->inter, E = d->experts, K = d->topk;
@@ -128,25 +107,19 @@ static bool fused_plan(const KogarashiMoe* d, const KogarashiWs& w, FusedArgs* f
   FusedArgs a = {};
   a.H = H; a.F = F; a.E = E; a.K = K; a.has_shared = shared ? 1 : 0; a.G = K + a.has_shared;
   a.down_q6 = d->down_ty == DARASK_GGML_Q6_K;
-  if (!fused_split(H / 256, 8, &a.kp1, &a.nbu1)) return false;
-  if (!fused_split(F / 256, kFusedMaxKParts, &a.kp2, &a.nbu2)) return false;
-  a.nblk2 = F / 256;
-  // Q6_K: the f16 block scales of a unit's blocks must lie in one 16-byte chunk of the row tail
-  if (a.down_q6 && (16 % (2 * a.nbu2)) != 0 && !(a.kp2 == 1 && 2 * a.nblk2 <= 16)) return false;
+  a.nblk1 = H / 256; a.nblk2 = F / 256;
   a.row_bytes1 = row_bytes_of(DARASK_GGML_Q4_K, H);
   a.row_bytes2 = row_bytes_of(d->down_ty, F);
   a.tpg = F / 8;
   a.rt2 = H / 16;
-  a.pitch1 = fused_pitch(a.nbu1 * 144, 64, 64);                                 // 16-byte reads of two rows per quarter warp
-  a.pitch2 = a.down_q6 ? fused_pitch(a.nbu2 * 208 + 16, 32, 96) : fused_pitch(a.nbu2 * 144, 64, 64);   // Q6_K: 8-byte reads of four rows per half warp
-  a.stage_bytes = (16 * (a.pitch1 > a.pitch2 ? a.pitch1 : a.pitch2) + 127) / 128 * 128;
+  // a chunk = 8 gate rows, 8 up rows or 16 down rows, whole rows, one bulk copy
+  const int chunk = 8 * a.row_bytes1 > 16 * a.row_bytes2 ? 8 * a.row_bytes1 : 16 * a.row_bytes2;
+  a.stage_bytes = (chunk + 127) / 128 * 128;
   // shared memory: control words | barriers | partial sums | zero fragments | activation area | ring
-  a.off_bars = 512;
-  a.off_psum = a.off_bars + (2 * kFusedMaxStages + 1) * 8;
-  a.off_psum = (a.off_psum + 127) / 128 * 128;
-  a.off_zero = a.off_psum + kFusedSlots * a.kp1 * 16 * 4;
-  a.off_act = a.off_zero + kFusedZeroBytes;
-  a.off_act = (a.off_act + 127) / 128 * 128;
+  a.off_bars = 640;
+  a.off_psum = (a.off_bars + (2 * kFusedMaxStages + 1) * 8 + 127) / 128 * 128;
+  a.off_zero = a.off_psum + kFusedSlots * kFusedQuad * 16 * 4;
+  a.off_act = (a.off_zero + kFusedZeroBytes + 127) / 128 * 128;
   a.act_lo1 = H * 2 + 64;
   a.act_xs1 = 2 * a.act_lo1;
   a.act_rows = (a.act_xs1 + H / 32 * 4 + 127) / 128 * 128;

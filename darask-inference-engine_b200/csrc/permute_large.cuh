@@ -127,11 +127,13 @@ inline cudaError_t launch_permute_large(const PermuteArgs& p, void* scratch, cud
   const int chunks = int(((long long)p.tokens * p.topk + kPermChunk - 1) / kPermChunk);
   int* counts = static_cast<int*>(scratch);
   const size_t place_smem = size_t(32) * p.experts * sizeof(unsigned short);
-  static bool configured = false;
-  if (!configured) {
+  static bool configured[64] = {};      // the opt-in is per device
+  const int dev = current_device_slot();
+  if (dev < 0) return cudaErrorInvalidDevice;
+  if (!configured[dev]) {
     const cudaError_t e = cudaFuncSetAttribute(permute_place_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 1024 * 2);
     if (e != cudaSuccess) return e;
-    configured = true;
+    configured[dev] = true;
   }
   cudaError_t e;
   if ((e = launch_pdl(permute_count_kernel<0>, dim3(chunks), dim3(kPermChunk), size_t(p.experts) * 4, st, p, counts))) return e;

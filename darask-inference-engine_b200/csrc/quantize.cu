@@ -104,42 +104,58 @@ __global__ void q6k_quant_kernel(const float* __restrict__ src, uint8_t* __restr
 }
 
 // ---- NVFP4 ---------------------------------------------------------------------------------------
-// amax[m] = max |x| of matrix m as float bits (non-negative floats order like their bits).
-__global__ void amax_kernel(const float* __restrict__ src, long long n, long long stride, unsigned* amax, int as_bf16) {
+// Largest magnitude of matrix blockIdx.y, kept as the bit pattern of a non-negative float so that one integer
+// atomicMax per thread block combines the blocks (float32 magnitudes and their bit patterns sort alike).
+__global__ void __launch_bounds__(256) amax_kernel(const float* __restrict__ src, long long n, long long stride, unsigned* amax, int as_bf16) {
+  __shared__ float warp_top[8];
   const float* w = src + blockIdx.y * stride;
-  float a = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
-    a = fmaxf(a, fabsf(as_bf16 ? bf16r(w[i]) : w[i]));
-  a = warp_max(a);
-  if ((threadIdx.x & 31) == 0) atomicMax(amax + blockIdx.y, __float_as_uint(a));
+  float top = 0.f;
+  const long long first = (long long)blockIdx.x * blockDim.x + threadIdx.x, step = (long long)gridDim.x * blockDim.x;
+  for (long long i = first; i < n; i += step) {
+    const float v = as_bf16 ? bf16r(w[i]) : w[i];
+    top = fmaxf(top, fabsf(v));
+  }
+  top = warp_max(top);
+  if ((threadIdx.x & 31) == 0) warp_top[threadIdx.x >> 5] = top;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int q = 1; q < int(blockDim.x >> 5); ++q) top = fmaxf(top, warp_top[q]);
+    atomicMax(amax + blockIdx.y, __float_as_uint(top));
+  }
 }
 
-// Tsumuji layout: one thread per 16-element block of matrix blockIdx.y; source rounded to bf16 first
-// (the reference quantizes bf16 checkpoints).
-__global__ void nvfp4_linear_quant_kernel(const float* __restrict__ src, long long src_stride, int rows, int cols,
-                                          const unsigned* __restrict__ amax, uint8_t* __restrict__ dst,
-                                          long long dst_stride, long long codes_off, long long scales_off,
-                                          float* __restrict__ gs, int gs_stride) {
-  const int m = blockIdx.y;
-  const long long b = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  float global = __uint_as_float(amax[m]) / (6.f * 448.f);
-  if (global == 0.f) global = 1.f;
-  if (b == 0) gs[m * gs_stride] = global;
-  if (b >= (long long)rows * cols / 16) return;
-  const float* x = src + m * src_stride + b * 16;
-  float v[16], a = 0.f;
-  for (int i = 0; i < 16; ++i) {
-    v[i] = bf16r(x[i]);
-    a = fmaxf(a, fabsf(v[i]));
-  }
-  const uint8_t s = e4m3_rn(a / 6.f / global);
-  const float d = e4m3_value(s) * global;
+// Tsumuji (ModelOpt) NVFP4 of matrix blockIdx.y, source rounded to bf16 first (the reference quantizes bf16
+// checkpoints: tsumuji kernels/decode/quant.cu:77-114). Half a warp owns one 16-element block: lane i of the half holds
+// element i, the block maximum travels by shuffles, every lane encodes its own element and the even lanes pair their
+// code with the neighbour's into one byte. A warp reads 32 consecutive floats per round.
+//   matrix scale g = amax / (6 * 448) (1 for an all-zero matrix); block scale byte = e4m3(max / 6 / g);
+//   code = e2m1(element / (e4m3 value * g)) with the sign in bit 3; element 2i in the low nibble of byte i.
+__global__ void __launch_bounds__(256) nvfp4_linear_quant_kernel(const float* __restrict__ src, long long src_stride, int rows, int cols,
+                                                                 const unsigned* __restrict__ amax, uint8_t* __restrict__ dst,
+                                                                 long long dst_stride, long long codes_off, long long scales_off,
+                                                                 float* __restrict__ gs, int gs_stride) {
+  const int m = blockIdx.y, lane = threadIdx.x & 31, sub = lane & 15;
+  float matrix_scale = __uint_as_float(amax[m]) / (6.f * 448.f);
+  if (matrix_scale == 0.f) matrix_scale = 1.f;
+  if (blockIdx.x == 0 && threadIdx.x == 0) gs[m * gs_stride] = matrix_scale;
+  const long long blocks = (long long)rows * cols / 16;
+  const float* x = src + m * src_stride;
   uint8_t* out = dst + m * dst_stride;
-  out[scales_off + b] = s;
-  for (int i = 0; i < 8; ++i) {
-    const float q0 = d > 0.f ? v[2 * i] / d : 0.f, q1 = d > 0.f ? v[2 * i + 1] / d : 0.f;
-    const unsigned c0 = e2m1_code(fabsf(q0)) | (signbit(q0) ? 8u : 0u), c1 = e2m1_code(fabsf(q1)) | (signbit(q1) ? 8u : 0u);
-    out[codes_off + b * 8 + i] = uint8_t(c0 | (c1 << 4));
+  const long long warps = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long pair = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); pair * 2 < blocks; pair += warps) {
+    const long long b = pair * 2 + (lane >> 4);                     // this half warp's block
+    const bool live = b < blocks;
+    const float v = live ? bf16r(x[b * 16 + sub]) : 0.f;
+    float top = fabsf(v);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, o));
+    const uint8_t scale_byte = e4m3_rn(top / 6.f / matrix_scale);
+    const float unit = e4m3_value(scale_byte) * matrix_scale;
+    const float q = unit > 0.f ? v / unit : 0.f;
+    const unsigned code = e2m1_code(fabsf(q)) | (signbit(q) ? 8u : 0u);
+    const unsigned neighbour = __shfl_down_sync(0xffffffffu, code, 1);
+    if (live && sub == 0) out[scales_off + b] = scale_byte;
+    if (live && (sub & 1) == 0) out[codes_off + b * 8 + (sub >> 1)] = uint8_t(code | (neighbour << 4));
   }
 }
 
@@ -242,7 +258,8 @@ extern "C" int darask_quantize_nvfp4_linear(void* dst, long long dst_stride, lon
   if (e) return e;
   const long long n = (long long)rows * cols;
   amax_kernel<<<dim3(unsigned(n / 4096 > 1024 ? 1024 : (n + 4095) / 4096), matrices), 256, 0, st>>>(src, n, src_stride, amax_scratch, 1);
-  nvfp4_linear_quant_kernel<<<dim3(unsigned((n / 16 + 255) / 256), matrices), 256, 0, st>>>(
+  const long long warp_rounds = (n / 32 + 7) / 8;                  // thread blocks if every warp took one round
+  nvfp4_linear_quant_kernel<<<dim3(unsigned(warp_rounds > 8192 ? 8192 : (warp_rounds < 1 ? 1 : warp_rounds)), matrices), 256, 0, st>>>(
       src, src_stride, rows, cols, amax_scratch, static_cast<uint8_t*>(dst), dst_stride, codes_off, scales_off, gs, gs_stride);
   return cudaGetLastError();
 }

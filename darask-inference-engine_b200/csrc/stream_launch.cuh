@@ -15,6 +15,13 @@ inline int sm_count() {
 
 constexpr int kSmemBudget = 227 * 1024;
 
+// Index of the current device for per-device one-time set-up (function attributes are per device), or -1.
+inline int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  return dev;
+}
+
 // Launch with the programmatic-dependent-launch attribute: the kernel may start while its
 // predecessor in the stream drains; every kernel here calls griddepcontrol.wait before it reads
 // anything the predecessor wrote.
