@@ -35,6 +35,7 @@ class TsumujiMoe(ctypes.Structure):
         ("x", c_void_p), ("out", c_void_p), ("rlogits", c_void_p), ("sel", c_void_p), ("rw", c_void_p),
         ("shared_gate", c_void_p), ("accumulate", c_int),
         ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+        ("R", c_void_p), ("di", c_void_p), ("Sd", c_int), ("ld", c_int), ("rank", c_int), ("HC", c_int), ("ss", c_void_p),
     ]
 
 
@@ -129,6 +130,7 @@ _SIGNATURES = {
     "kogarashi_moe_set_single_launch": (c_int, [c_int]),
     "kogarashi_moe_static_scratch_bytes": (c_size_t, []),
     "kogarashi_moe_layer_static": (c_int, [ctypes.POINTER(KogarashiMoe), c_void_p]),
+    "kogarashi_moe_static_status": (c_int, [ctypes.POINTER(c_uint), c_void_p]),
     "kogarashi_moe_status": (c_int, [c_void_p, ctypes.POINTER(c_uint), c_void_p]),
 }
 

@@ -5,16 +5,20 @@
 //             everywhere), so no CTA waits for a routing block and no plan travels through global memory
 //   phase 1   gate/up tiles (8 gate rows + the 8 matching up rows), SwiGLU product written as fp16 hi/lo
 //   barrier 2 all products visible; every CTA stages the K+1 product vectors in shared memory
-//   phase 2   down tiles (16 rows of one expert) as float32 rows; the warp that completes the last expert of a
-//             16-row tile (a counter per tile) adds the weighted experts in slot order and the gated shared expert
-//             into the residual stream
+//   phase 2   down tiles (16 rows of one expert) as float32 rows
+//   barrier 3 all rows visible; every CTA adds the weighted experts (slot order) and the gated shared expert into its
+//             share of the residual stream
 //
-// The weight stream does not stop at the barriers: one producer thread issues ONE `cp.async.bulk` copy per chunk of
-// whole, consecutive weight rows (8 gate rows, the 8 matching up rows, or 16 down rows: 7 to 37 KB, contiguous in
-// global memory) into a ring of chunk slots in a fixed order (shared expert first, then the routed experts, then the
-// down tiles); while the gate/up tiles are being multiplied the ring refills with down weights, which depend on the
-// routing only. A tile is multiplied by a quad of warps that take its 256-column blocks in turn (warp k: blocks
-// k, k + 4, ...) and add their partial sums through shared memory.
+// The weight stream does not stop at the barriers: producer threads issue ONE `cp.async.bulk` copy per chunk of
+// whole, consecutive weight rows (8 gate rows, the 8 matching up rows, or 16 down rows: about 14 KB at the benchmark
+// shape, contiguous in global memory; the copies of one thread are carried out one after the other at about half a
+// microsecond each whatever their size, so two issuing threads are needed to keep HBM busy with chunks of this size)
+// into a ring of chunk slots in a fixed order (shared expert first, then the routed experts, then the down tiles);
+// while the gate/up tiles are being multiplied the ring refills with down weights, which depend on the routing only.
+// A tile is multiplied by a quad of warps that take its 256-column blocks in turn (warp k: blocks k, k + 4, ...) and
+// add their partial sums through shared memory. The block loop is bound by shared-memory wavefronts and the
+// half-rate integer pipe, not by the tensor pipe: the activation fragments of a block are loaded once into
+// registers, and the zero halves of the block-diagonal operand never travel through shared memory.
 //
 // Arithmetic per 256-column block, `mma.sync.m16n8k16` (fp16 in, fp32 accumulate): the A operand holds the weight
 // codes as fp16 magic numbers (1024 + q, no conversion, no per-weight scaling); the B operand is block diagonal: the
@@ -35,11 +39,12 @@ namespace dmoe {
 constexpr unsigned kStatusActRange = 4u;   // an activation does not fit the fp16 planes (|value| > 65504)
 
 constexpr int kFusedConsumers = 16;                          // consumer warps
-constexpr int kFusedThreads = (kFusedConsumers + 1) * 32;    // + the producer warp
-constexpr int kFusedSlots = 32;                              // partial-sum slots: a slot is reused 32 tiles later, further than the ring reaches
-constexpr int kFusedMaxStages = 30;
-constexpr int kFusedZeroBytes = 512;                         // zero fragments read by lanes outside a column's group
+constexpr int kFusedProducers = 2;                           // warps that issue bulk copies (one thread each)
+constexpr int kFusedThreads = (kFusedConsumers + kFusedProducers) * 32;
+constexpr int kFusedSlots = 16;                              // partial-sum slots: a slot is reused 16 tiles later, further than the ring reaches
+constexpr int kFusedMaxStages = 14;
 constexpr int kFusedQuad = 4;                                // warps that share a tile
+constexpr int kFusedPasses = 1;                              // 16-row MMA passes per tile: a tile is 8 gate + 8 up rows, or 16 down rows, per pass
 
 struct FusedArgs {
   const float* router_w; const float* router_bias; const float* sh_inp;
@@ -47,13 +52,13 @@ struct FusedArgs {
   const uint8_t* sh_gate; const uint8_t* sh_up; const uint8_t* sh_down;
   const float* n; float* x; float* logits; int* ids; float* prob;
   int H, F, E, K, G, has_shared;
-  int nblk1, row_bytes1, tpg;                     // gate/up: 256-column blocks per row, bytes per row, tiles per group
-  int nblk2, row_bytes2, rt2, down_q6;            // down: the same, 16-row tiles of the output
+  int nblk1, row_bytes1, tps;                     // gate/up: 256-column blocks per row, bytes per row, tiles per group
+  int nblk2, row_bytes2, rt2, down_q6;            // down: the same, row tiles of the output
   int stage_bytes, nstage;                        // chunk slot size and number of slots of the ring
-  int off_bars, off_psum, off_zero, off_act, off_ring;   // shared-memory offsets
+  int off_bars, off_psum, off_act, off_ring;             // shared-memory offsets
   int act_lo1, act_xs1, act_rows;                 // phase R/1 inside the activation area: lo-plane stride, sums, router rows
   int act_lo2, act_grp2, act_xs2;                 // phase 2: lo-plane stride, bytes per group, offset of the sums
-  unsigned* gbar; unsigned* tile_cnt; unsigned* status; __half* hbuf; float* y; float* sg;
+  unsigned* gbar; unsigned* status; __half* hbuf; float* y; float* sg;
 };
 
 // ---- small pieces -----------------------------------------------------------------------------------------
@@ -108,6 +113,7 @@ DEVI bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, unsigned* status, 
         : "memory");
     if (ok) return true;
     if (*abort_flag) return false;
+    __nanosleep(64);                       // waiting warps leave the issue slots to the warps that have data
     if ((spin & 15u) == 0) {
       const uint64_t now = global_timer_ns();
       if (spin == 0) start = now;
@@ -146,15 +152,55 @@ DEVI DiagLane diag_lane(int lane) {
   return d;
 }
 
-// ---- Q4_K: one block (16 row slots x 256 columns) against one activation vector ----------------------------------
-// Tile t of the block covers sub-blocks 4t .. 4t+3: slot group 0 = low nibbles of bytes 64t .. 64t+31 (sub-block 4t),
-// group 1 = low nibbles of bytes 64t+32 .. (sub-block 4t+2), groups 2 / 3 = the high nibbles of the same bytes
-// (sub-blocks 4t+1 / 4t+3). Lane j reads bytes 64t + 16j .. +15 of rows g and g + 8.
-//   rA / rB: shared-memory address of the block in row slots g / g + 8
-//   xb0 / xb1: address of this lane's B fragments of tile 0 (16 halves = columns base .. base+15 in [x0,x2,x1,x3]
-//              order) or of the zero area; the next tile is 256 bytes further in both
-//   xs: float sums of (hi + lo) over the eight sub-blocks of this block
-DEVI void q4k_block_diag(uint32_t rA, uint32_t rB, int j, uint32_t xb0, uint32_t xb1, uint32_t xs, float& acc0, float& acc1) {
+// The activation side of one 256-column block for this lane, loaded once and used for every 16-row pass of the block:
+//   b0[i] / b1[i]: the B registers (slot groups 0-1 / 2-3) of tile i, four MMAs each; a lane carries real values in
+//   at most one of the two sets, the other set stays zero for the whole launch (which set is a property of the lane),
+//   so the sets are zeroed once and only the live one is ever loaded: no zero fragments travel through shared memory.
+//   xs[i]: the float sum of (hi + lo) over the scale group this lane owns in tile i.
+struct BlockFrags {
+  uint4 b0[4], b1[4];
+  float xs[4];
+};
+DEVI void frags_clear(BlockFrags& f) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f.b0[i] = f.b1[i] = make_uint4(0u, 0u, 0u, 0u);
+    f.xs[i] = 0.f;
+  }
+}
+// Q4_K: tile t of a block covers sub-blocks 4t .. 4t+3; this lane's fragments of tile t are 16 halves (32 bytes) at
+// xb + 256 t; xs_addr: the eight float sums of the block.
+DEVI void q4k_load_frags(BlockFrags& f, uint32_t xb, bool first, bool second, uint32_t xs_addr, int sbl) {
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    if (first) {
+      f.b0[2 * t] = lds128(xb + 256 * t);
+      f.b0[2 * t + 1] = lds128(xb + 256 * t + 16);
+    }
+    if (second) {
+      f.b1[2 * t] = lds128(xb + 256 * t);
+      f.b1[2 * t + 1] = lds128(xb + 256 * t + 16);
+    }
+    f.xs[t] = __uint_as_float(lds32(xs_addr + 4 * (4 * t + sbl)));
+  }
+}
+// Q6_K: tile (n, A) covers the scale groups 8n + 2A + {0, 1, 4, 5}; this lane's fragments of it are 8 halves at
+// xb + 256 n + 64 A; xs_addr: the sixteen float sums of the block.
+DEVI void q6k_load_frags(BlockFrags& f, uint32_t xb, bool first, bool second, uint32_t xs_addr, int sl) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int n = i >> 1, A = i & 1;
+    if (first) f.b0[i] = lds128(xb + 256 * n + 64 * A);
+    if (second) f.b1[i] = lds128(xb + 256 * n + 64 * A);
+    f.xs[i] = __uint_as_float(lds32(xs_addr + 4 * (8 * n + 2 * A + sl)));
+  }
+}
+
+// ---- Q4_K: 16 row slots x one 256-column block against the block's fragments ----------------------------------------
+// Tile t covers sub-blocks 4t .. 4t+3: slot group 0 = low nibbles of bytes 64t .. 64t+31 (sub-block 4t), group 1 = low
+// nibbles of bytes 64t+32 .. (sub-block 4t+2), groups 2 / 3 = the high nibbles of the same bytes (sub-blocks 4t+1 /
+// 4t+3). Lane j reads bytes 64t + 16j .. +15 of rows g and g + 8 (rA / rB: shared-memory address of the block in them).
+DEVI void q4k_rows(uint32_t rA, uint32_t rB, int j, const BlockFrags& f, float& acc0, float& acc1) {
   const uint4 hA = lds128(rA), hB = lds128(rB);
   const int sbl = 2 * (j & 1) + (j >> 1);         // this lane's sub-block inside a tile (slot group j)
   const int sh = 8 * sbl;
@@ -163,14 +209,12 @@ DEVI void q4k_block_diag(uint32_t rA, uint32_t rB, int j, uint32_t xb0, uint32_t
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const uint4 wA = lds128(rA + 16 + 64 * t + 16 * j), wB = lds128(rB + 16 + 64 * t + 16 * j);
-    const uint4 p0 = lds128(xb0 + 256 * t), p1 = lds128(xb0 + 256 * t + 16);
-    const uint4 q0 = lds128(xb1 + 256 * t), q1 = lds128(xb1 + 256 * t + 16);
     float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const uint32_t a = u4w(wA, q), b = u4w(wB, q), as = a >> 8, bs = b >> 8;
-      const uint32_t e0 = q < 2 ? u4w(p0, 2 * q) : u4w(p1, 2 * q - 4), e1 = q < 2 ? u4w(p0, 2 * q + 1) : u4w(p1, 2 * q - 3);
-      const uint32_t f0 = q < 2 ? u4w(q0, 2 * q) : u4w(q1, 2 * q - 4), f1 = q < 2 ? u4w(q0, 2 * q + 1) : u4w(q1, 2 * q - 3);
+      const uint32_t e0 = u4w(f.b0[2 * t + (q >> 1)], 2 * (q & 1)), e1 = u4w(f.b0[2 * t + (q >> 1)], 2 * (q & 1) + 1);
+      const uint32_t f0 = u4w(f.b1[2 * t + (q >> 1)], 2 * (q & 1)), f1 = u4w(f.b1[2 * t + (q >> 1)], 2 * (q & 1) + 1);
       mma_f16(c, (a & 0x000F000Fu) | 0x64006400u, (b & 0x000F000Fu) | 0x64006400u, (a & 0x00F000F0u) | 0x64006400u,
               (b & 0x00F000F0u) | 0x64006400u, e0, f0);
       mma_f16(c, (as & 0x000F000Fu) | 0x64006400u, (bs & 0x000F000Fu) | 0x64006400u, (as & 0x00F000F0u) | 0x64006400u,
@@ -185,7 +229,7 @@ DEVI void q4k_block_diag(uint32_t rA, uint32_t rB, int j, uint32_t xb0, uint32_t
       scA = ((hA.w >> sh) & 15u) | (((hA.y >> sh) >> 2) & 0x30u); mnA = ((hA.w >> (sh + 4)) & 15u) | (((hA.z >> sh) >> 2) & 0x30u);
       scB = ((hB.w >> sh) & 15u) | (((hB.y >> sh) >> 2) & 0x30u); mnB = ((hB.w >> (sh + 4)) & 15u) | (((hB.z >> sh) >> 2) & 0x30u);
     }
-    const float xsv = __uint_as_float(lds32(xs + 4 * (4 * t + sbl)));
+    const float xsv = f.xs[t];
     // sum of (1024 + q) x = raw; d sc sum(q x) - dmin m sum(x) = S raw - (1024 S + dmin m) sum(x)
     const float sA = dA * magic_u8(scA), sB = dB * magic_u8(scB);
     const float tA = fmaf(1024.f, sA, mA * magic_u8(mnA)), tB = fmaf(1024.f, sB, mB * magic_u8(mnB));
@@ -200,12 +244,9 @@ DEVI void q4k_block_diag(uint32_t rA, uint32_t rB, int j, uint32_t xb0, uint32_t
 // Tile (n, A) covers the scale groups 8n + 2A + {0, 1, 4, 5}: slot groups 0 / 1 = low nibbles of ql bytes
 // 64n + 32A + [0,16) / [16,32) with qh bit pair A, groups 2 / 3 = the high nibbles with bit pair A + 2. Lane j reads ql
 // bytes 64n + 32A + 8j .. +7 and qh bytes 32n + 8j .. +7 of rows g and g + 8. Codes enter as 1024 + (q + 32).
-//   xb0 / xb1: this lane's B fragments of tile (0, 0) (8 halves); tile (n, A) is 256 n + 64 A bytes further
-//   xs: float sums of (hi + lo) over the sixteen 16-column groups of the block;  d: float block scales of the rows
-DEVI void q6k_block_diag(uint32_t rA, uint32_t rB, int j, float dA, float dB, uint32_t xb0, uint32_t xb1, uint32_t xs, float& acc0,
-                         float& acc1) {
+// dA / dB: the float block scales of the two rows.
+DEVI void q6k_rows(uint32_t rA, uint32_t rB, int j, float dA, float dB, const BlockFrags& f, float& acc0, float& acc1) {
   const uint4 sA4 = lds128(rA + 192), sB4 = lds128(rB + 192);
-  const int sl = 4 * (j >> 1) + (j & 1);          // this lane's scale group inside a tile (slot group j)
 #pragma unroll
   for (int n = 0; n < 2; ++n) {
     const uint2 hA = lds64(rA + 128 + 32 * n + 8 * j), hB = lds64(rB + 128 + 32 * n + 8 * j);
@@ -215,7 +256,7 @@ DEVI void q6k_block_diag(uint32_t rA, uint32_t rB, int j, float dA, float dB, ui
 #pragma unroll
     for (int A = 0; A < 2; ++A) {
       const uint2 lA = lds64(rA + 64 * n + 32 * A + 8 * j), lB = lds64(rB + 64 * n + 32 * A + 8 * j);
-      const uint4 p = lds128(xb0 + 256 * n + 64 * A), q = lds128(xb1 + 256 * n + 64 * A);
+      const uint4 p = f.b0[2 * n + A], q = f.b1[2 * n + A];
       float c[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
@@ -231,7 +272,7 @@ DEVI void q6k_block_diag(uint32_t rA, uint32_t rB, int j, float dA, float dB, ui
         mma_f16(c, __byte_perm(loa, 0x64646464u, 0x4341), __byte_perm(lob, 0x64646464u, 0x4341), __byte_perm(hia, 0x64646464u, 0x4341),
                 __byte_perm(hib, 0x64646464u, 0x4341), u4w(p, 2 * u + 1), u4w(q, 2 * u + 1));
       }
-      const float xsv = __uint_as_float(lds32(xs + 4 * (8 * n + 2 * A + sl)));
+      const float xsv = f.xs[2 * n + A];
       const uint32_t sel = 0x7650u + 2 * A + (j & 1);
       const float sA = dA * (__uint_as_float(__byte_perm(swA, 0x4B000000u, sel)) - (kMagic + 128.f));
       const float sB = dB * (__uint_as_float(__byte_perm(swB, 0x4B000000u, sel)) - (kMagic + 128.f));
@@ -277,13 +318,13 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   float* sm_misc = reinterpret_cast<float*>(smem + 256);             // [0] sigmoid of the shared gate logit
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 272);
   volatile int* go_flag = reinterpret_cast<volatile int*>(smem + 276);
-  int* tcnt = reinterpret_cast<int*>(smem + 288);                    // [kFusedSlots]
   float* part = reinterpret_cast<float*>(smem + 448);                // [16][2] router partial sums
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + a.off_bars);   // [nstage]
   uint64_t* empty = full + a.nstage;                                 // [nstage]
   uint64_t* routed = empty + a.nstage;                               // routing published
+  uint64_t* qbar = routed + 1;                                       // [4] one per quad: partial sums of a tile written
+  volatile int* fill_id = reinterpret_cast<volatile int*>(smem + 576);   // [nstage] how many times a slot has been filled (requests issued)
   float* psum = reinterpret_cast<float*>(smem + a.off_psum);         // [slot][warp of the quad][16]
-  const uint32_t zero_base = smem_u32(smem + a.off_zero);
   const uint32_t act = smem_u32(smem + a.off_act);
   const uint32_t ring = smem_u32(smem + a.off_ring);
   const int NS = a.nstage;
@@ -291,29 +332,33 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   if (tid == 0) {
     for (int s = 0; s < NS; ++s) {
       mbar_init(full + s, 1);
-      mbar_init(empty + s, kFusedQuad);
+      mbar_init(empty + s, kFusedQuad);           // the four warps of the quad that owns a fill hand it back
     }
     mbar_init(routed, 1);
+    for (int q = 0; q < 4; ++q) mbar_init(qbar + q, kFusedQuad);
+    for (int s2 = 0; s2 < NS; ++s2) fill_id[s2] = 0;
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (tid < kFusedSlots) tcnt[tid] = 0;
-  for (int i = tid; i < kFusedZeroBytes / 4; i += kFusedThreads) reinterpret_cast<uint32_t*>(smem + a.off_zero)[i] = 0u;
   __syncthreads();
 
   // ---- the work lists of this CTA (same arithmetic in producer and consumers) ----
-  // gate/up tiles tau = cta, cta + grid, ... of G * tpg (group-major, shared expert first); down tiles likewise of
-  // rt2 * G (row-tile-major). Chunks of the ring, in order: (gate rows, up rows) per gate/up tile, then one per down tile.
-  const int tiles1 = a.G * a.tpg;
+  // gate/up tiles sigma = cta, cta + grid, ... of G * tps (group-major, shared expert first; a tile = 16 rows of the gate
+  // matrix and the same 16 rows of the up matrix); down tiles likewise of rt2 * G (row-tile-major; 32 rows). Chunks of
+  // the ring, in order: (gate rows, up rows) per gate/up tile, then one per down tile.
+  const int tiles1 = a.G * a.tps;
   const int n1 = cta < tiles1 ? (tiles1 - cta + grid - 1) / grid : 0;
   const int tiles2 = a.rt2 * a.G;
   const int n2 = cta < tiles2 ? (tiles2 - cta + grid - 1) / grid : 0;
   const int chunks = 2 * n1 + n2;
   const int R = a.E + a.has_shared;                                  // router rows incl. the shared gate projection
 
-  if (warp == kFusedConsumers) {
-    // =========================== producer warp ===========================
-    // lane 0 issues one bulk copy per chunk; the whole warp selects the top-k in between
+  if (warp >= kFusedConsumers) {
+    // =========================== producer warps ===========================
+    // Lane 0 of producer warp p issues the bulk copies of chunks p, p + 4, ... (the copies one thread issues are
+    // carried out one after the other, about half a microsecond each whatever their size up to ~28 KB; four issuing
+    // threads keep the HBM stream at its full rate). Producer warp 0 also selects the top-k, as a whole warp.
+    const int prod = warp - kFusedConsumers;
     auto issue = [&](int c) -> bool {
       const int stage = c % NS, use = c / NS;
       if (use > 0 && !mbar_wait_abortable(empty + stage, (use - 1) & 1, a.status, abort_flag)) return false;
@@ -321,53 +366,67 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
       uint32_t bytes;
       if (c < 2 * n1) {
         const int lt = c >> 1, m = c & 1;
-        const int tau = cta + lt * grid, gi = tau / a.tpg, tile = tau - gi * a.tpg;
+        const int sigma = cta + lt * grid, gi = sigma / a.tps, tile = sigma - gi * a.tps;
         const uint8_t* base;
         if (a.has_shared && gi == 0) base = m ? a.sh_up : a.sh_gate;
         else base = (m ? a.up_w : a.gate_w) + size_t(sm_ids[gi - a.has_shared]) * a.F * a.row_bytes1;
-        src = base + size_t(tile) * 8 * a.row_bytes1;
-        bytes = 8u * a.row_bytes1;
+        src = base + size_t(tile) * (8 * kFusedPasses) * a.row_bytes1;
+        bytes = uint32_t(8 * kFusedPasses) * a.row_bytes1;
       } else {
         const int u2 = cta + (c - 2 * n1) * grid, gi = u2 % a.G, rt = u2 / a.G;
         const uint8_t* base = (a.has_shared && gi == 0) ? a.sh_down : a.down_w + size_t(sm_ids[gi - a.has_shared]) * a.H * a.row_bytes2;
-        src = base + size_t(rt) * 16 * a.row_bytes2;
-        bytes = 16u * a.row_bytes2;
+        src = base + size_t(rt) * (16 * kFusedPasses) * a.row_bytes2;
+        bytes = uint32_t(16 * kFusedPasses) * a.row_bytes2;
       }
+      fill_id[stage] = use + 1;                  // consumers of fill `use` wait for this before they trust the parity
       mbar_arrive_expect_tx(full + stage, bytes);
       bulk_g2s(smem + a.off_ring + stage * a.stage_bytes, src, bytes, full + stage);
       return true;
     };
-    int c = 0;
+    int c = prod;
     int ok = 1;
     // the shared expert's first tile does not depend on anything: its weights are requested before the dependency wait
-    if (lane == 0 && a.has_shared && n1 > 0 && cta < a.tpg)
-      for (; ok && c < 2 && c < NS; ++c) ok = issue(c) ? 1 : 0;
-    __syncwarp();
-    pdl_wait();
-    // grid barrier 1: every router row has been written
-    if (ok && lane == 0) ok = grid_wait(a.gbar, unsigned(grid), a.status, abort_flag) ? 1 : 0;
-    ok = __shfl_sync(0xffffffffu, ok, 0);
-    c = __shfl_sync(0xffffffffu, c, 0);
-    if (ok) {
-      RouteArgs r{a.logits, a.E, a.E, a.K, 1, nullptr, 1.f, nullptr, nullptr, nullptr};
-      route_token_to<kRouteKogarashi>(r, 0, lane, sm_ids, sm_prob);
-      if (lane == 0 && a.has_shared) sm_misc[0] = sigmoid_precise(__ldcg(a.sg));
+    if (lane == 0 && a.has_shared && n1 > 0 && cta < a.tps && c < 2 && c < NS) {
+      ok = issue(c) ? 1 : 0;
+      c += kFusedProducers;
+    }
+    if (prod == 0) {
       __syncwarp();
-      if (cta == 0 && lane < a.K) {
-        a.ids[lane] = sm_ids[lane];
-        a.prob[lane] = sm_prob[lane];
+      {
+        // Rehearsal: the selection below runs once per launch on the critical path between the two halves of the weight
+        // stream, where every instruction-cache line it touches for the first time is a miss. The time before the
+        // dependency wait is idle, so the same code runs here once on stand-in values (a router row); what it writes
+        // to shared memory is overwritten by the real selection.
+        RouteArgs r{a.router_w, a.E, a.E, a.K, 1, nullptr, 1.f, nullptr, nullptr, nullptr};
+        route_token_to<kRouteKogarashi>(r, 0, lane, sm_ids, sm_prob);
+        __syncwarp();
       }
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(routed);
-        for (; ok && c < chunks; ++c) ok = issue(c) ? 1 : 0;
+      pdl_wait();
+      // grid barrier 1: every router row has been written
+      if (ok && lane == 0) ok = grid_wait(a.gbar, unsigned(grid), a.status, abort_flag) ? 1 : 0;
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (ok) {
+        RouteArgs r{a.logits, a.E, a.E, a.K, 1, nullptr, 1.f, nullptr, nullptr, nullptr};
+        route_token_to<kRouteKogarashi>(r, 0, lane, sm_ids, sm_prob);
+        if (lane == 0 && a.has_shared) sm_misc[0] = sigmoid_precise(__ldcg(a.sg));
+        __syncwarp();
+        if (cta == 0 && lane < a.K) {
+          a.ids[lane] = sm_ids[lane];
+          a.prob[lane] = sm_prob[lane];
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(routed);
       }
     }
-    if (lane == 0 && !ok) {
-      // gave up: let the copies already requested land before the CTA's shared memory goes away
+    if (lane != 0) return;
+    if (ok && prod != 0) ok = mbar_wait_abortable(routed, 0, a.status, abort_flag) ? 1 : 0;
+    for (; ok && c < chunks; c += kFusedProducers) ok = issue(c) ? 1 : 0;
+    if (!ok) {
+      // gave up: let the copies this thread requested land before the CTA's shared memory goes away
       const uint64_t start = global_timer_ns();
-      for (int q = (c > NS ? c - NS : 0); q < c; ++q)
-        while (!mbar_test(full + q % NS, (q / NS) & 1) && global_timer_ns() - start < kWaitLimitNs) __nanosleep(256);
+      for (int q = prod; q < c && q < chunks; q += kFusedProducers)
+        if (q + NS >= c)               // only the last ring's worth of chunks can still be in flight
+          while (!mbar_test(full + q % NS, (q / NS) & 1) && global_timer_ns() - start < kWaitLimitNs) __nanosleep(256);
     }
     return;
   }
@@ -390,57 +449,66 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
     }
   }
   cp_async_commit();
-  pdl_wait();
-  // the token's activations: this thread's chunks stay in registers for the planes below
   constexpr int MAXC = 4;                                            // hidden <= 8192
-  float4 nv[MAXC];
+  {
+    constexpr int pass = 1;
+    pdl_wait();
+    const float* nsrc = a.n;
+    // the token's activations: this thread's chunks stay in registers for the planes below
+    float4 nv[MAXC];
 #pragma unroll
-  for (int c = 0; c < MAXC; ++c) {
-    const int i = tid + c * kFusedConsumers * 32;
-    nv[c] = i < chunks4 ? __ldcg(reinterpret_cast<const float4*>(a.n) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-  }
-  cp_async_wait<0>();
-  float dot[2] = {0.f, 0.f};
+    for (int c = 0; c < MAXC; ++c) {
+      const int i = tid + c * kFusedConsumers * 32;
+      nv[c] = i < chunks4 ? __ldcg(reinterpret_cast<const float4*>(nsrc) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    cp_async_wait<0>();
+    float dot[2] = {0.f, 0.f};
 #pragma unroll
-  for (int q = 0; q < 2; ++q)
-    if (q < my_rows) {
+    for (int q = 0; q < 2; ++q)
+      if (q < my_rows) {
 #pragma unroll
-      for (int c = 0; c < MAXC; ++c) {
-        const int i = tid + c * kFusedConsumers * 32;
-        if (i < chunks4) {
-          const uint4 w = lds128(rows_sm + (q * chunks4 + i) * 16);
-          dot[q] = fmaf(__uint_as_float(w.x), nv[c].x, dot[q]);
-          dot[q] = fmaf(__uint_as_float(w.y), nv[c].y, dot[q]);
-          dot[q] = fmaf(__uint_as_float(w.z), nv[c].z, dot[q]);
-          dot[q] = fmaf(__uint_as_float(w.w), nv[c].w, dot[q]);
+        for (int c = 0; c < MAXC; ++c) {
+          const int i = tid + c * kFusedConsumers * 32;
+          if (i < chunks4) {
+            const uint4 w = lds128(rows_sm + (q * chunks4 + i) * 16);
+            dot[q] = fmaf(__uint_as_float(w.x), nv[c].x, dot[q]);
+            dot[q] = fmaf(__uint_as_float(w.y), nv[c].y, dot[q]);
+            dot[q] = fmaf(__uint_as_float(w.z), nv[c].z, dot[q]);
+            dot[q] = fmaf(__uint_as_float(w.w), nv[c].w, dot[q]);
+          }
         }
       }
+    dot[0] = warp_sum(dot[0]);
+    dot[1] = warp_sum(dot[1]);
+    if (lane == 0) {
+      part[warp * 2] = dot[0];
+      part[warp * 2 + 1] = dot[1];
     }
-  dot[0] = warp_sum(dot[0]);
-  dot[1] = warp_sum(dot[1]);
-  if (lane == 0) {
-    part[warp * 2] = dot[0];
-    part[warp * 2 + 1] = dot[1];
-  }
-  named_barrier(1, kFusedConsumers * 32);
-  if (tid == 0) {
-    for (int q = 0; q < my_rows; ++q) {
-      const int row = cta + q * grid;
-      float v = 0.f;
-      for (int w = 0; w < kFusedConsumers; ++w) v += part[w * 2 + q];
-      if (row < a.E) {
-        if (a.router_bias) v += a.router_bias[row];
-        a.logits[row] = v;
-      } else {
-        *a.sg = v;
+    named_barrier(1, kFusedConsumers * 32);
+    if (warp == 0) {
+      // lanes 0-15 hold the partial sums of row 0, lanes 16-31 those of row 1; summed in a fixed tree
+      float v = part[(lane & 15) * 2 + (lane >> 4)];
+      v += __shfl_xor_sync(0xffffffffu, v, 8);
+      v += __shfl_xor_sync(0xffffffffu, v, 4);
+      v += __shfl_xor_sync(0xffffffffu, v, 2);
+      v += __shfl_xor_sync(0xffffffffu, v, 1);
+      const int q = lane >> 4, row = cta + q * grid;
+      if (pass == 1 && (lane & 15) == 0 && q < my_rows) {
+        if (row < a.E) {
+          if (a.router_bias) v += a.router_bias[row];
+          a.logits[row] = v;
+        } else {
+          *a.sg = v;
+        }
+      }
+      __syncwarp();
+      if (pass == 1 && lane == 0) {
+        if (cta == 0) a.gbar[1] = a.gbar[2] = 0u;   // the later barriers' counters as the previous call on this workspace left them
+        __threadfence();
+        atomicAdd(a.gbar, 1u);               // arrive at grid barrier 1; the producer warps wait for it
       }
     }
-    if (cta == 0) a.gbar[1] = 0u;           // barrier 2 counter as the previous call on this workspace left it
-    __threadfence();
-    atomicAdd(a.gbar, 1u);                 // arrive at grid barrier 1; the producer warps wait for it
-  }
-  // ---- activation planes (fragment order) and per-32 sums ----
-  {
+    // ---- activation planes (fragment order) and per-32 sums ----
     bool bad = false;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
@@ -456,76 +524,107 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
         if ((i & 7) == 0) sts32f(act + a.act_xs1 + 4 * (i >> 3), sum);
       }
     }
-    if (bad) atomicOr(a.status, kStatusActRange);
+    if (bad && pass == 1) atomicOr(a.status, kStatusActRange);
+    named_barrier(1, kFusedConsumers * 32);
   }
-  named_barrier(1, kFusedConsumers * 32);
 
-  // This lane's B fragments: offset inside a plane pair (bytes) from the first column of a block, and the step from
-  // block to block (0 for the lanes that read the zero area).
+  // This lane's B fragments: offset inside a plane pair (bytes) from the first column of a block; which of its two B
+  // register sets carries values (neither for half of the lanes)
   const uint32_t lane_x4 = (dl.plane ? uint32_t(a.act_lo1) : 0u) + 2u * (32u * (2 * ((g >> 1) & 1) + (g >> 2)) + 16u * (j & 1));
-  const uint32_t step0 = (dl.active && !dl.second) ? 512u : 0u, step1 = (dl.active && dl.second) ? 512u : 0u;
+  const bool first = dl.active && !dl.second, second = dl.active && dl.second;
+  const int sbl = 2 * (j & 1) + (j >> 1), sl = 4 * (j >> 1) + (j & 1);     // this lane's scale group inside a tile (Q4_K / Q6_K)
+  BlockFrags fr;
+  frags_clear(fr);
   bool ok = true;
 
-  // Sum of the quad's partial rows; the last warp to arrive gets all sixteen rows (lanes 0-15) and owns the epilogue.
-  // `slot`: partial-sum slot of the tile (tiles of one quad that may be pending at the same time have different slots).
-  auto quad_reduce = [&](int slot, float acc0, float acc1, float& row_sum) -> bool {
-    acc0 = quad_sum(acc0);
-    acc1 = quad_sum(acc1);
-    float* ps = psum + (slot * kFusedQuad + kq) * 16;
-    if (j == 0) {
-      ps[g] = acc0;
-      ps[g + 8] = acc1;
+  // Sum of the quad's partial rows: every warp writes its rows, the quad meets at its mbarrier (arrive = release,
+  // wait = acquire: no fence), and warp 0 of the quad gets all rows (lane l: pass l / 16, row l % 16) and owns the
+  // epilogue while the other three go on to their next tile. `slot`: partial-sum slot of the tile (tiles of one quad that may be pending
+  // at the same time have different slots). Returns false when the wait was given up.
+  int quad_syncs = 0;
+  auto quad_reduce = [&](int slot, float (&acc)[kFusedPasses][2], float& row_sum) -> bool {
+    float* ps = psum + (slot * kFusedQuad + kq) * (16 * kFusedPasses);
+#pragma unroll
+    for (int p = 0; p < kFusedPasses; ++p) {
+      const float r0 = quad_sum(acc[p][0]), r1 = quad_sum(acc[p][1]);
+      if (j == 0) {
+        ps[p * 16 + g] = r0;
+        ps[p * 16 + 8 + g] = r1;
+      }
     }
     __syncwarp();
-    int last = 0;
-    if (lane == 0) {
-      __threadfence_block();
-      last = atomicAdd(&tcnt[slot], 1) == kFusedQuad - 1;
-      __threadfence_block();
+    if (lane == 0) mbar_arrive(qbar + quad);
+    const int parity = quad_syncs++ & 1;
+    // every warp waits (a warp that ran ahead would arrive for the next tile inside this tile's phase)
+    if (!mbar_wait_abortable(qbar + quad, parity, a.status, abort_flag)) return false;
+    if (kq != 0) return true;
+    row_sum = 0.f;
+    if (lane < 16 * kFusedPasses) {
+#pragma unroll
+      for (int q = 0; q < kFusedQuad; ++q) row_sum += psum[(slot * kFusedQuad + q) * (16 * kFusedPasses) + lane];
     }
-    last = __shfl_sync(0xffffffffu, last, 0);
-    if (last) {
-      row_sum = 0.f;
-      if (lane < 16)
-        for (int q = 0; q < kFusedQuad; ++q) row_sum += psum[(slot * kFusedQuad + q) * 16 + lane];
-      __syncwarp();
-      if (lane == 0) tcnt[slot] = 0;
-    }
-    return last != 0;
+    return true;
   };
+
+  // Waits until chunk c has landed in its slot. A parity wait can only tell the current fill of a slot from the one
+  // before it, and a quad does not see every fill of a slot (other quads consume some): so the producer publishes the
+  // number of fills it has requested per slot, and a consumer first waits until its fill has been requested (the
+  // barrier is then in that fill's phase or just past it) and only then for the parity.
+  auto wait_chunk = [&](int c) -> bool {
+    const int stage = c % NS, use = c / NS;
+    if (use > 0 && fill_id[stage] <= use) {
+      const uint64_t start = global_timer_ns();
+      while (fill_id[stage] <= use) {
+        __nanosleep(32);
+        if (*abort_flag) return false;
+        if (global_timer_ns() - start > kWaitLimitNs) {
+          atomicOr(a.status, kStatusWaitTimeout);
+          *abort_flag = 1;
+          return false;
+        }
+      }
+    }
+    return mbar_wait_abortable(full + stage, use & 1, a.status, abort_flag);
+  };
+
+  // The tiles start only when the selection is done, the shared expert's (whose weights are already here) included:
+  // a consumer warp that multiplies while the producer warp selects slows the selection down several times (they
+  // share a scheduler), and the selection, not the shared expert, is on the critical path.
+  if (!mbar_wait_abortable(routed, 0, a.status, abort_flag)) ok = false;
 
   // ---- phase 1: gate/up tiles ----
   for (int lt = quad; lt < n1 && ok; lt += kFusedConsumers / kFusedQuad) {
     const int cg = 2 * lt, cu = cg + 1;
-    const int tau = cta + lt * grid, gi = tau / a.tpg, tile = tau - gi * a.tpg;
-    float acc0 = 0.f, acc1 = 0.f;
+    if (!wait_chunk(cg) || !wait_chunk(cu)) { ok = false; break; }
+    const int sigma = cta + lt * grid, gi = sigma / a.tps, tile = sigma - gi * a.tps;
+    float acc[kFusedPasses][2] = {};
     if (kq < a.nblk1) {
-      if (!mbar_wait_abortable(full + cg % NS, (cg / NS) & 1, a.status, abort_flag) ||
-          !mbar_wait_abortable(full + cu % NS, (cu / NS) & 1, a.status, abort_flag)) { ok = false; break; }
-      const uint32_t rA = ring + (cg % NS) * a.stage_bytes + g * a.row_bytes1;      // gate row g of the tile
-      const uint32_t rB = ring + (cu % NS) * a.stage_bytes + g * a.row_bytes1;      // up row g
-      const uint32_t xreal = act + lane_x4;
-      const uint32_t xb0 = step0 ? xreal : zero_base, xb1 = step1 ? xreal : zero_base;
-      for (int b = kq; b < a.nblk1; b += kFusedQuad)
-        q4k_block_diag(rA + b * 144, rB + b * 144, j, xb0 + b * step0, xb1 + b * step1, act + a.act_xs1 + 32u * b, acc0, acc1);
+      const uint32_t gate_rows = ring + (cg % NS) * a.stage_bytes + g * a.row_bytes1;    // row g of the tile's gate rows
+      const uint32_t up_rows = ring + (cu % NS) * a.stage_bytes + g * a.row_bytes1;
+      for (int b = kq; b < a.nblk1; b += kFusedQuad) {
+        q4k_load_frags(fr, act + lane_x4 + 512u * b, first, second, act + a.act_xs1 + 32u * b, sbl);
+#pragma unroll
+        for (int p = 0; p < kFusedPasses; ++p)       // eight rows of the tile per pass: gate row in MMA row g, up row in MMA row g + 8
+          q4k_rows(gate_rows + 8 * p * a.row_bytes1 + b * 144, up_rows + 8 * p * a.row_bytes1 + b * 144, j, fr, acc[p][0], acc[p][1]);
+      }
     }
     float rows = 0.f;
-    const bool last = quad_reduce(lt % kFusedSlots, acc0, acc1, rows);
-    if (last) {
-      // lanes 0-7 hold the gate rows, lanes 8-15 the up rows
+    if (!quad_reduce(lt % kFusedSlots, acc, rows)) { ok = false; break; }
+    if (kq == 0) {
+      // lane l: pass l / 16; lanes 0-7 of a pass hold its gate rows, lanes 8-15 its up rows
       const float up = __shfl_down_sync(0xffffffffu, rows, 8);
-      if (lane < 8) {
+      if (lane < 16 * kFusedPasses && (lane & 15) < 8) {
         const float h = silu_mul(rows, up);
         const __half hi = __float2half_rn(h);
         const __half lo = __float2half_rn(h - __half2float(hi));
         if (fabsf(h) > 65504.f) atomicOr(a.status, kStatusActRange);
-        __half* dst = a.hbuf + size_t(gi) * 2 * a.F + tile * 8 + lane;
+        __half* dst = a.hbuf + size_t(gi) * 2 * a.F + tile * (8 * kFusedPasses) + 8 * (lane >> 4) + (lane & 7);
         dst[0] = hi;
         dst[a.F] = lo;
       }
     }
-    // The chunks are handed back only now: a warp that is still summing a tile keeps the producer from running
-    // kFusedSlots tiles ahead, so a slot of partial sums is never reused while it is being read.
+    // The chunks are handed back only now: the warp that sums a tile keeps the producer from running kFusedSlots tiles
+    // ahead, so a slot of partial sums is never reused while it is being read.
     __syncwarp();
     if (lane == 0) {
       mbar_arrive(empty + cg % NS);
@@ -547,32 +646,42 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   // ---- the K + 1 product vectors -> planes in fragment order, sums per 16 (Q6_K) or 32 (Q4_K) columns ----
   {
     const int per = a.F / 4, all = a.G * per;
-    for (int base = 0; base < all; base += kFusedConsumers * 32) {      // uniform trip count: shuffles below
-      const int idx = base + tid;
-      const bool live = idx < all;
-      const int gi = live ? idx / per : 0, i = live ? idx - gi * per : 0;
-      uint2 hi = make_uint2(0u, 0u), lo = make_uint2(0u, 0u);
-      if (live) {
-        hi = __ldcg(reinterpret_cast<const uint2*>(a.hbuf + size_t(gi) * 2 * a.F) + i);
-        lo = __ldcg(reinterpret_cast<const uint2*>(a.hbuf + size_t(gi) * 2 * a.F + a.F) + i);
+    constexpr int BATCH = 3;                                              // loads of three rounds in flight together
+    for (int base = 0; base < all; base += BATCH * kFusedConsumers * 32) {  // uniform trip count: shuffles below
+      uint2 hi[BATCH], lo[BATCH];
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        const int idx = base + u * kFusedConsumers * 32 + tid;
+        hi[u] = lo[u] = make_uint2(0u, 0u);
+        if (idx < all) {
+          const int gi = idx / per, i = idx - gi * per;
+          hi[u] = __ldcg(reinterpret_cast<const uint2*>(a.hbuf + size_t(gi) * 2 * a.F) + i);
+          lo[u] = __ldcg(reinterpret_cast<const uint2*>(a.hbuf + size_t(gi) * 2 * a.F + a.F) + i);
+        }
       }
-      const float2 h01 = __half22float2(u32_as_h2(hi.x)), h23 = __half22float2(u32_as_h2(hi.y));
-      const float2 l01 = __half22float2(u32_as_h2(lo.x)), l23 = __half22float2(u32_as_h2(lo.y));
-      float sum = ((h01.x + l01.x) + (h01.y + l01.y)) + ((h23.x + l23.x) + (h23.y + l23.y));
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      if (!DOWN_Q6) sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-      if (live) {
-        // [h0,h1,h2,h3] -> [h0,h2,h1,h3]
-        const uint2 ph = make_uint2(__byte_perm(hi.x, hi.y, 0x5410), __byte_perm(hi.x, hi.y, 0x7632));
-        const uint2 pq = make_uint2(__byte_perm(lo.x, lo.y, 0x5410), __byte_perm(lo.x, lo.y, 0x7632));
-        const uint32_t gb = act + gi * a.act_grp2;
-        sts64(gb + 8 * i, ph);
-        sts64(gb + a.act_lo2 + 8 * i, pq);
-        if (DOWN_Q6) {
-          if ((i & 3) == 0) sts32f(act + a.act_xs2 + 4 * (gi * (a.F / 16) + (i >> 2)), sum);
-        } else {
-          if ((i & 7) == 0) sts32f(act + a.act_xs2 + 4 * (gi * (a.F / 32) + (i >> 3)), sum);
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        const int idx = base + u * kFusedConsumers * 32 + tid;
+        const bool live = idx < all;
+        const int gi = live ? idx / per : 0, i = live ? idx - gi * per : 0;
+        const float2 h01 = __half22float2(u32_as_h2(hi[u].x)), h23 = __half22float2(u32_as_h2(hi[u].y));
+        const float2 l01 = __half22float2(u32_as_h2(lo[u].x)), l23 = __half22float2(u32_as_h2(lo[u].y));
+        float sum = ((h01.x + l01.x) + (h01.y + l01.y)) + ((h23.x + l23.x) + (h23.y + l23.y));
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        if (!DOWN_Q6) sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+        if (live) {
+          // [h0,h1,h2,h3] -> [h0,h2,h1,h3]
+          const uint2 ph = make_uint2(__byte_perm(hi[u].x, hi[u].y, 0x5410), __byte_perm(hi[u].x, hi[u].y, 0x7632));
+          const uint2 pq = make_uint2(__byte_perm(lo[u].x, lo[u].y, 0x5410), __byte_perm(lo[u].x, lo[u].y, 0x7632));
+          const uint32_t gb = act + gi * a.act_grp2;
+          sts64(gb + 8 * i, ph);
+          sts64(gb + a.act_lo2 + 8 * i, pq);
+          if (DOWN_Q6) {
+            if ((i & 3) == 0) sts32f(act + a.act_xs2 + 4 * (gi * (a.F / 16) + (i >> 2)), sum);
+          } else {
+            if ((i & 7) == 0) sts32f(act + a.act_xs2 + 4 * (gi * (a.F / 32) + (i >> 3)), sum);
+          }
         }
       }
     }
@@ -584,56 +693,63 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   const uint32_t lane_x4d = (dl.plane ? uint32_t(a.act_lo2) : 0u) + 2u * (32u * (2 * ((g >> 1) & 1) + (g >> 2)) + 16u * (j & 1));
   for (int t2 = quad; t2 < n2; t2 += kFusedConsumers / kFusedQuad) {
     const int c = 2 * n1 + t2, stage = c % NS;
+    if (!wait_chunk(c)) { ok = false; break; }
     const int u2 = cta + t2 * grid, gi = u2 % a.G, rt = u2 / a.G;
-    float acc0 = 0.f, acc1 = 0.f;
+    float acc[kFusedPasses][2] = {};
     if (kq < a.nblk2) {
-      if (!mbar_wait_abortable(full + stage, (c / NS) & 1, a.status, abort_flag)) return;
-      const uint32_t slot0 = ring + stage * a.stage_bytes;
-      const uint32_t rA = slot0 + g * a.row_bytes2, rB = slot0 + (g + 8) * a.row_bytes2;
+      const uint32_t rowg = ring + stage * a.stage_bytes + g * a.row_bytes2;            // row g of the tile
       const uint32_t xreal = act + gi * a.act_grp2 + (DOWN_Q6 ? lane_x6 : lane_x4d);
-      const uint32_t xb0 = step0 ? xreal : zero_base, xb1 = step1 ? xreal : zero_base;
-      if (DOWN_Q6) {
-        const uint32_t xs = act + a.act_xs2 + 4u * (gi * (a.F / 16));
-        for (int b = kq; b < a.nblk2; b += kFusedQuad) {
-          // the f16 block scales follow the blocks of a row
-          const uint32_t dwA = lds32(rA + a.nblk2 * 208 + ((2 * b) & ~3)), dwB = lds32(rB + a.nblk2 * 208 + ((2 * b) & ~3));
-          const float dA = (b & 1) ? half_hi(dwA) : half_lo(dwA), dB = (b & 1) ? half_hi(dwB) : half_lo(dwB);
-          q6k_block_diag(rA + b * 208, rB + b * 208, j, dA, dB, xb0 + b * step0, xb1 + b * step1, xs + 64u * b, acc0, acc1);
+      for (int b = kq; b < a.nblk2; b += kFusedQuad) {
+        if (DOWN_Q6) {
+          q6k_load_frags(fr, xreal + 512u * b, first, second, act + a.act_xs2 + 4u * (gi * (a.F / 16)) + 64u * b, sl);
+#pragma unroll
+          for (int p = 0; p < kFusedPasses; ++p) {     // sixteen rows of the tile per pass
+            const uint32_t rA = rowg + 16 * p * a.row_bytes2, rB = rA + 8 * a.row_bytes2;
+            // the f16 block scales follow the blocks of a row
+            const uint32_t dwA = lds32(rA + a.nblk2 * 208 + ((2 * b) & ~3)), dwB = lds32(rB + a.nblk2 * 208 + ((2 * b) & ~3));
+            const float dA = (b & 1) ? half_hi(dwA) : half_lo(dwA), dB = (b & 1) ? half_hi(dwB) : half_lo(dwB);
+            q6k_rows(rA + b * 208, rB + b * 208, j, dA, dB, fr, acc[p][0], acc[p][1]);
+          }
+        } else {
+          q4k_load_frags(fr, xreal + 512u * b, first, second, act + a.act_xs2 + 4u * (gi * (a.F / 32)) + 32u * b, sbl);
+#pragma unroll
+          for (int p = 0; p < kFusedPasses; ++p) {
+            const uint32_t rA = rowg + 16 * p * a.row_bytes2, rB = rA + 8 * a.row_bytes2;
+            q4k_rows(rA + b * 144, rB + b * 144, j, fr, acc[p][0], acc[p][1]);
+          }
         }
-      } else {
-        const uint32_t xs = act + a.act_xs2 + 4u * (gi * (a.F / 32));
-        for (int b = kq; b < a.nblk2; b += kFusedQuad)
-          q4k_block_diag(rA + b * 144, rB + b * 144, j, xb0 + b * step0, xb1 + b * step1, xs + 32u * b, acc0, acc1);
       }
     }
     float rows = 0.f;
-    const bool last = quad_reduce(t2 % kFusedSlots, acc0, acc1, rows);
-    if (last) {
-      // the finished rows of this expert, then the count of finished experts of the row tile
-      if (lane < 16) __stcg(a.y + size_t(gi) * a.H + rt * 16 + lane, rows);
-      __syncwarp();
-      int done = 0;
-      if (lane == 0) {
-        __threadfence();
-        done = atomicAdd(a.tile_cnt + rt, 1u) == unsigned(a.G - 1);
-        __threadfence();
-      }
-      done = __shfl_sync(0xffffffffu, done, 0);
-      if (done) {
-        // x[i] += sum_s fma(p_s, down_s[i]) + sigmoid(sg) * shared[i]   (kogarashi kernels/native.cu:113-117)
-        if (lane < 16) {
-          const int row = rt * 16 + lane;
-          float v = 0.f;
-          for (int s2 = 0; s2 < a.K; ++s2) v = fmaf(sm_prob[s2], __ldcg(a.y + size_t(s2 + a.has_shared) * a.H + row), v);
-          if (a.has_shared) v += sm_misc[0] * __ldcg(a.y + row);
-          a.x[row] += v;
-        }
-        __syncwarp();
-        if (lane == 0) a.tile_cnt[rt] = 0u;
-      }
-    }
+    if (!quad_reduce(t2 % kFusedSlots, acc, rows)) { ok = false; break; }
+    // the finished rows of this expert: lane l holds row 16 (l / 16) + (l % 16) of the tile
+    if (kq == 0 && lane < 16 * kFusedPasses) __stcg(a.y + size_t(gi) * a.H + rt * (16 * kFusedPasses) + lane, rows);
     __syncwarp();
     if (lane == 0) mbar_arrive(empty + stage);
+  }
+
+  // ---- grid barrier 3: every expert's rows are in global memory; then each CTA combines its share of the rows ----
+  if (!ok) *abort_flag = 1;
+  named_barrier(1, kFusedConsumers * 32);
+  if (tid == 0) *go_flag = (!*abort_flag && grid_arrive_wait(a.gbar + 2, unsigned(grid), a.status, abort_flag)) ? 1 : 0;
+  named_barrier(1, kFusedConsumers * 32);
+  if (!*go_flag) return;
+  // x[i] += sum_s fma(p_s, down_s[i]) + sigmoid(sg) * shared[i]   (kogarashi kernels/native.cu:113-117); row i = tid * grid + cta
+  const int row = tid * grid + cta;
+  if (row < a.H) {
+    const float xin = a.x[row];
+    const float ysh = a.has_shared ? __ldcg(a.y + row) : 0.f;
+    float v = 0.f;
+    for (int s0 = 0; s0 < a.K; s0 += 8) {          // eight loads in flight at a time; the sum itself stays in slot order
+      float ys[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) ys[q] = s0 + q < a.K ? __ldcg(a.y + size_t(s0 + q + a.has_shared) * a.H + row) : 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        if (s0 + q < a.K) v = fmaf(sm_prob[s0 + q], ys[q], v);
+    }
+    if (a.has_shared) v += sm_misc[0] * ysh;
+    a.x[row] = xin + v;
   }
 }
 

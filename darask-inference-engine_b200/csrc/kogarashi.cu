@@ -64,7 +64,7 @@ static KogarashiWs carve(void* base, int hidden, int inter, int experts, int top
   w.counters = reinterpret_cast<int*>(take(16));
   w.done = reinterpret_cast<unsigned*>(take(4));
   w.status = reinterpret_cast<unsigned*>(take(4));
-  w.gbar = reinterpret_cast<unsigned*>(take(16));                                   // two grid barrier counters
+  w.gbar = reinterpret_cast<unsigned*>(take(16));                                   // three grid barrier counters
   w.tile_cnt = reinterpret_cast<unsigned*>(take(size_t(kFusedMaxRowTiles) * 4));    // ends at byte 3072: inside the zeroed head
   w.active = reinterpret_cast<int*>(take(size_t(experts) * 4));
   w.ranges = reinterpret_cast<unsigned*>(take(size_t(experts) * 8));
@@ -103,23 +103,23 @@ static bool fused_plan(const KogarashiMoe* d, const KogarashiWs& w, FusedArgs* f
   if (d->down_ty != DARASK_GGML_Q4_K && d->down_ty != DARASK_GGML_Q6_K) return false;
   const bool shared = d->sh_gate_w != nullptr;
   const int grid = sm_count();
-  if (E + (shared ? 1 : 0) > 2 * grid || H > 8192 || H / 16 > kFusedMaxRowTiles || F % 8) return false;
+  if (E + (shared ? 1 : 0) > 2 * grid || H > 8192 || H % (16 * kFusedPasses) || F % (8 * kFusedPasses)) return false;
   FusedArgs a = {};
   a.H = H; a.F = F; a.E = E; a.K = K; a.has_shared = shared ? 1 : 0; a.G = K + a.has_shared;
   a.down_q6 = d->down_ty == DARASK_GGML_Q6_K;
   a.nblk1 = H / 256; a.nblk2 = F / 256;
   a.row_bytes1 = row_bytes_of(DARASK_GGML_Q4_K, H);
   a.row_bytes2 = row_bytes_of(d->down_ty, F);
-  a.tpg = F / 8;
-  a.rt2 = H / 16;
-  // a chunk = 8 gate rows, 8 up rows or 16 down rows, whole rows, one bulk copy
-  const int chunk = 8 * a.row_bytes1 > 16 * a.row_bytes2 ? 8 * a.row_bytes1 : 16 * a.row_bytes2;
+  a.tps = F / (8 * kFusedPasses);
+  a.rt2 = H / (16 * kFusedPasses);
+  // a chunk = the gate rows or the up rows of a tile, or the rows of a down tile: whole rows, one bulk copy
+  const int c1 = 8 * kFusedPasses * a.row_bytes1, c2 = 16 * kFusedPasses * a.row_bytes2;
+  const int chunk = c1 > c2 ? c1 : c2;
   a.stage_bytes = (chunk + 127) / 128 * 128;
-  // shared memory: control words | barriers | partial sums | zero fragments | activation area | ring
+  // shared memory: control words | barriers | partial sums | activation area | ring
   a.off_bars = 640;
-  a.off_psum = (a.off_bars + (2 * kFusedMaxStages + 1) * 8 + 127) / 128 * 128;
-  a.off_zero = a.off_psum + kFusedSlots * kFusedQuad * 16 * 4;
-  a.off_act = (a.off_zero + kFusedZeroBytes + 127) / 128 * 128;
+  a.off_psum = (a.off_bars + (2 * kFusedMaxStages + 1 + 4) * 8 + 127) / 128 * 128;
+  a.off_act = (a.off_psum + kFusedSlots * kFusedQuad * 16 * kFusedPasses * 4 + 127) / 128 * 128;
   a.act_lo1 = H * 2 + 64;
   a.act_xs1 = 2 * a.act_lo1;
   a.act_rows = (a.act_xs1 + H / 32 * 4 + 127) / 128 * 128;
@@ -131,13 +131,13 @@ static bool fused_plan(const KogarashiMoe* d, const KogarashiWs& w, FusedArgs* f
   a.off_ring = (a.off_act + (act1 > act2 ? act1 : act2) + 127) / 128 * 128;
   a.nstage = (kSmemBudget - a.off_ring) / a.stage_bytes;
   if (a.nstage > kFusedMaxStages) a.nstage = kFusedMaxStages;
-  if (a.nstage < 4) return false;
+  if (a.nstage < 3) return false;
   *smem_bytes = a.off_ring + a.nstage * a.stage_bytes;
   a.router_w = static_cast<const float*>(d->router_w); a.router_bias = d->router_bias; a.sh_inp = static_cast<const float*>(d->sh_inp_w);
   a.gate_w = static_cast<const uint8_t*>(d->gate_w); a.up_w = static_cast<const uint8_t*>(d->up_w); a.down_w = static_cast<const uint8_t*>(d->down_w);
   a.sh_gate = static_cast<const uint8_t*>(d->sh_gate_w); a.sh_up = static_cast<const uint8_t*>(d->sh_up_w); a.sh_down = static_cast<const uint8_t*>(d->sh_down_w);
   a.n = d->n; a.x = d->x; a.logits = d->logits; a.ids = d->ids; a.prob = d->prob;
-  a.gbar = w.gbar; a.tile_cnt = w.tile_cnt; a.status = w.status; a.hbuf = w.hplanes; a.y = w.y; a.sg = w.sg;
+  a.gbar = w.gbar; a.status = w.status; a.hbuf = w.hplanes; a.y = w.y; a.sg = w.sg;
   *f = a;
   return true;
 }
@@ -201,18 +201,24 @@ extern "C" int darask_q6k_repack(void* dst, const void* src, long long rows, int
 
 extern "C" size_t darask_q6k_repacked_bytes(long long rows, int k) { return size_t(rows) * q6k_r16_row_bytes(k); }
 
-extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
-  if (!d || !d->router_w || !d->gate_w || !d->up_w || !d->down_w || !d->n || !d->x || !d->logits || !d->ids ||
-      !d->prob || !d->workspace)
-    return cudaErrorInvalidValue;
+// Everything about a descriptor that can be checked without its workspace.
+static bool descriptor_ok(const KogarashiMoe* d) {
+  if (!d || !d->router_w || !d->gate_w || !d->up_w || !d->down_w || !d->n || !d->x || !d->logits || !d->ids || !d->prob) return false;
   const int H = d->hidden, F = d->inter, E = d->experts, K = d->topk, T = d->tokens;
-  if (H <= 0 || F <= 0 || H % 256 || F % 256 || E < K || E > 1024 || K < 1 || K > 32 || T < 1) return cudaErrorInvalidValue;
-  if (d->gate_ty != d->up_ty) return cudaErrorInvalidValue;
+  if (H <= 0 || F <= 0 || H % 256 || F % 256 || E < K || E > 1024 || K < 1 || K > 32 || T < 1) return false;
+  if (d->gate_ty != d->up_ty || d->reserved) return false;
+  if (d->router_ty != DARASK_GGML_F32 && d->router_ty != DARASK_GGML_BF16 && d->router_ty != DARASK_GGML_F16) return false;
+  if (row_bytes_of(d->gate_ty, H) == 0 || row_bytes_of(d->down_ty, F) == 0) return false;
+  if (d->sh_gate_w && (!d->sh_up_w || !d->sh_down_w || !d->sh_inp_w)) return false;
+  return true;
+}
+
+extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
+  if (!descriptor_ok(d) || !d->workspace) return cudaErrorInvalidValue;
+  const int H = d->hidden, F = d->inter, E = d->experts, K = d->topk, T = d->tokens;
   const bool shared = d->sh_gate_w != nullptr;
-  if (shared && (!d->sh_up_w || !d->sh_down_w || !d->sh_inp_w)) return cudaErrorInvalidValue;
   if (d->workspace_bytes < kogarashi_moe_workspace_bytes(H, F, E, K, T)) return cudaErrorInvalidValue;
   const KogarashiWs w = carve(d->workspace, H, F, E, K, T);
-  if (d->reserved) return cudaErrorInvalidValue;
 
   // one token: the whole layer is one persistent launch
   {
@@ -308,8 +314,25 @@ static __device__ __align__(256) unsigned char g_kogarashi_static_scratch[KOGARA
 
 extern "C" size_t kogarashi_moe_static_scratch_bytes(void) { return KOGARASHI_STATIC_SCRATCH_BYTES; }
 
+// Device address of the built-in array on the current device (looked up once per device, with that device current:
+// the array's name is only a host-side handle), or null with *err set.
+static void* static_scratch_address(cudaError_t* err) {
+  static void* address[64] = {nullptr};
+  int dev = 0;
+  *err = cudaGetDevice(&dev);
+  if (*err != cudaSuccess) return nullptr;
+  if (dev < 0 || dev >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
+  if (!address[dev]) {
+    void* p = nullptr;
+    *err = cudaGetSymbolAddress(&p, g_kogarashi_static_scratch);
+    if (*err != cudaSuccess) return nullptr;
+    address[dev] = p;
+  }
+  return address[dev];
+}
+
 extern "C" int kogarashi_moe_layer_static(const KogarashiMoe* d, cudaStream_t st) {
-  if (!d) return cudaErrorInvalidValue;
+  if (!descriptor_ok(d)) return cudaErrorInvalidValue;        // nothing is enqueued for a descriptor that is refused
   const size_t need = kogarashi_moe_workspace_bytes(d->hidden, d->inter, d->experts, d->topk, d->tokens);
   if (need > KOGARASHI_STATIC_SCRATCH_BYTES) {
     fprintf(stderr,
@@ -318,24 +341,22 @@ extern "C" int kogarashi_moe_layer_static(const KogarashiMoe* d, cudaStream_t st
             need, KOGARASHI_STATIC_SCRATCH_BYTES);
     return cudaErrorInvalidValue;
   }
-  // The array's name is only a host-side handle: its device address is looked up once per device,
-  // with that device current, and kept.
-  static void* address[64] = {nullptr};
-  int dev = 0;
-  cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
-  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  if (!address[dev]) {
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_kogarashi_static_scratch);
-    if (e != cudaSuccess) return e;
-    address[dev] = p;
-  }
-  // The array keeps whatever the previous call left: the control words must start at zero.
-  e = cudaMemsetAsync(address[dev], 0, 4096, st);
+  cudaError_t e = cudaSuccess;
+  void* scratch = static_scratch_address(&e);
+  if (!scratch) return e;
+  // The array keeps whatever the previous call left: the control words (counters, barrier words, status) start at zero.
+  e = cudaMemsetAsync(scratch, 0, 4096, st);
   if (e != cudaSuccess) return e;
   KogarashiMoe copy = *d;
-  copy.workspace = address[dev];
+  copy.workspace = scratch;
   copy.workspace_bytes = KOGARASHI_STATIC_SCRATCH_BYTES;
   return kogarashi_moe_layer(&copy, st);
+}
+
+extern "C" int kogarashi_moe_static_status(unsigned* host_status, cudaStream_t st) {
+  if (!host_status) return cudaErrorInvalidValue;
+  cudaError_t e = cudaSuccess;
+  void* scratch = static_scratch_address(&e);
+  if (!scratch) return e;
+  return kogarashi_moe_status(scratch, host_status, st);
 }

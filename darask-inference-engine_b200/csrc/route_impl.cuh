@@ -39,13 +39,13 @@ DEVI float ordered_value(uint32_t o) { return __uint_as_float((o & 0x80000000u) 
 DEVI unsigned long long pack_candidate(float key, int expert) {
   return (static_cast<unsigned long long>(ordered_bits(key)) << 32) | (0xffffffffu - static_cast<uint32_t>(expert));
 }
+// Largest packed candidate of the warp: the largest key by one hardware reduction, then among the lanes that hold
+// it the largest low half (= the lowest expert id) by a second one.
 DEVI unsigned long long warp_max_u64(unsigned long long v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
-    v = other > v ? other : v;
-  }
-  return v;
+  const uint32_t hi = static_cast<uint32_t>(v >> 32), lo = static_cast<uint32_t>(v);
+  const uint32_t top = __reduce_max_sync(0xffffffffu, hi);
+  const uint32_t low = __reduce_max_sync(0xffffffffu, hi == top ? lo : 0u);
+  return (static_cast<unsigned long long>(top) << 32) | low;
 }
 
 // One warp routes one token; lane l owns experts l, l + 32, ... (PER * 32 >= experts). `ids_out` / `w_out`

@@ -10,17 +10,54 @@
 
 namespace dmoe {
 
-// out[n][i] = sum_s fma(w[n][s], y[n*k+s][i]) then fma(shared_gate[n], y[N*k+n][i])   (ops.cu:217-223)
+// Residual-stream write-back of the reference's `moe_combine` (tsumuji kernels/decode/ops.cu:76-94, 202-230), optional.
+struct TsumujiWriteback {
+  float* R;            // [N][HC][H] residual streams, R[n][i] += inj_i * out[n]
+  const float* di;     // [Sd][N][ld] partial sums of the stream-gate projection; inj_i = 2 sigmoid(sum_s di[s][n][rank + i] / HC)
+  int Sd, ld, rank, HC;
+  float* ss;           // [N][blocks of 256 columns][HC]: sum of squares of the new R over the block's columns
+};
+
+// out[n][i] = sum_s fma(w[n][s], y[n*k+s][i]) then fma(shared_gate[n], y[N*k+n][i])   (ops.cu:217-223);
+// with a write-back: the HC streams of token n take inj_i * out and every block leaves its share of their
+// sums of squares (one block = 256 columns of one token, as in the reference, so `ss` has the same layout).
 __global__ void __launch_bounds__(256) tsumuji_combine_kernel(float* out, const float* y, const float* w, const float* sgate,
-                                                              int hidden, int topk, int tokens, int accumulate) {
+                                                              int hidden, int topk, int tokens, int accumulate, TsumujiWriteback wb) {
+  __shared__ float gate_of_stream[8];
+  __shared__ float warp_part[8][8];
   pdl_wait();
   pdl_launch();
   const int i = blockIdx.x * 256 + threadIdx.x, n = blockIdx.y;
-  if (i >= hidden) return;
   float o = 0.f;
-  for (int s = 0; s < topk; ++s) o = fmaf(__ldcg(w + n * topk + s), __ldcg(y + size_t(n * topk + s) * hidden + i), o);
-  o = fmaf(__ldcg(sgate + n), __ldcg(y + size_t(tokens * topk + n) * hidden + i), o);
-  out[size_t(n) * hidden + i] = accumulate ? out[size_t(n) * hidden + i] + o : o;
+  if (i < hidden) {
+    for (int s = 0; s < topk; ++s) o = fmaf(__ldcg(w + n * topk + s), __ldcg(y + size_t(n * topk + s) * hidden + i), o);
+    o = fmaf(__ldcg(sgate + n), __ldcg(y + size_t(tokens * topk + n) * hidden + i), o);
+    if (out) out[size_t(n) * hidden + i] = accumulate ? out[size_t(n) * hidden + i] + o : o;
+  }
+  if (!wb.R) return;
+  if (threadIdx.x < wb.HC) {
+    float a = 0.f;
+    for (int s = 0; s < wb.Sd; ++s) a += __ldcg(wb.di + size_t(s * tokens + n) * wb.ld + wb.rank + threadIdx.x);
+    gate_of_stream[threadIdx.x] = 2.f * (1.f / (1.f + expf(-(a / float(wb.HC)))));
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int st = 0; st < wb.HC; ++st) {
+    float v = 0.f;
+    if (i < hidden) {
+      float* r = wb.R + (size_t(n) * wb.HC + st) * hidden + i;
+      v = *r + gate_of_stream[st] * o;
+      *r = v;
+    }
+    const float sq = warp_sum(v * v);
+    if (lane == 0) warp_part[st][warp] = sq;
+  }
+  __syncthreads();
+  if (threadIdx.x < wb.HC) {
+    float total = 0.f;
+    for (int q = 0; q < 8; ++q) total += warp_part[threadIdx.x][q];      // fixed order
+    wb.ss[(size_t(n) * gridDim.x + blockIdx.x) * wb.HC + threadIdx.x] = total;
+  }
 }
 
 // stand-alone routing of given logits followed by the permutation, one block
@@ -228,7 +265,7 @@ extern "C" int tsumuji_moe_workspace_init(void* workspace, size_t bytes, cudaStr
 }
 
 extern "C" int tsumuji_moe_layer(const TsumujiMoe* d, cudaStream_t st) {
-  if (!d || !d->experts_w || !d->gs || !d->shared_gu || !d->shared_down || !d->x || !d->out || !d->rlogits || !d->sel ||
+  if (!d || !d->experts_w || !d->gs || !d->shared_gu || !d->shared_down || !d->x || (!d->out && !d->R) || !d->rlogits || !d->sel ||
       !d->rw || !d->shared_gate || !d->workspace)
     return cudaErrorInvalidValue;
   const int H = d->hidden, F = d->inter, E = d->experts, K = d->topk, N = d->tokens;
@@ -298,8 +335,13 @@ extern "C" int tsumuji_moe_layer(const TsumujiMoe* d, cudaStream_t st) {
     t.xplanes = w.hplanes; t.x_row0 = N * K; t.tokens = N; t.out = w.y; t.out_row0 = N * K;
     if ((e = launch_pdl(dense_gemv_kernel<0>, dim3(sm_count()), dim3(kGemvWarps * 32), 0, st, t))) return e;
   }
+  TsumujiWriteback wb = {};
+  if (d->R) {
+    if (!d->di || !d->ss || d->HC < 1 || d->HC > 8 || d->Sd < 1 || d->ld < d->rank + d->HC || d->rank < 0) return cudaErrorInvalidValue;
+    wb = TsumujiWriteback{d->R, d->di, d->Sd, d->ld, d->rank, d->HC, d->ss};
+  }
   return launch_pdl(tsumuji_combine_kernel, dim3((H + 255) / 256, N), dim3(256), 0, st, d->out, (const float*)w.y,
-                    (const float*)d->rw, (const float*)d->shared_gate, H, K, N, d->accumulate);
+                    (const float*)d->rw, (const float*)d->shared_gate, H, K, N, d->accumulate, wb);
 }
 
 // ---- expert-parallel entry points (rank g holds experts [g*E/G, (g+1)*E/G) and its own tokens) ---------------------------

@@ -44,8 +44,10 @@ class TsumujiMoeLayer:
         self.experts_w, self.gs = to(experts_w, torch.uint8), to(gs, torch.float32)
         self.shared_gu, self.shared_down = to(shared_gu, torch.bfloat16), to(shared_down, torch.bfloat16)
 
-    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
-        """x float32 [N,H] -> out float32 [N,H] = sum_s w_s y_s + shared_gate y_shared."""
+    def forward(self, x: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False, writeback=None) -> torch.Tensor:
+        """x float32 [N,H] -> out float32 [N,H] = sum_s w_s y_s + shared_gate y_shared.
+        writeback: optional dict(R float32 [N,HC,H] updated in place, di float32 [Sd,N,ld], rank int, ss float32
+        [N, ceil(H/256), HC] written) -- the residual-stream part of the reference's `moe_combine`."""
         n = x.shape[0]
         if n > self.max_tokens or x.shape[1] != self.hidden or x.dtype != torch.float32 or not x.is_contiguous():
             raise ValueError("x must be contiguous float32 [N<=max_tokens, hidden]")
@@ -60,6 +62,14 @@ class TsumujiMoeLayer:
         d.rlogits, d.sel, d.rw, d.shared_gate = (self.rlogits.data_ptr(), self.sel.data_ptr(), self.rw.data_ptr(),
                                                  self.sgate.data_ptr())
         d.accumulate = 1 if accumulate else 0
+        if writeback is not None:
+            r, di, ss = writeback["R"], writeback["di"], writeback["ss"]
+            hc = r.shape[1]
+            if r.dtype != torch.float32 or tuple(r.shape) != (n, hc, self.hidden) or not r.is_contiguous() or di.dtype != torch.float32 \
+                    or di.shape[1] != n or not di.is_contiguous() or tuple(ss.shape) != (n, (self.hidden + 255) // 256, hc):
+                raise ValueError("writeback: R [N,HC,H], di [Sd,N,ld], ss [N,ceil(H/256),HC], all float32")
+            d.R, d.di, d.ss = r.data_ptr(), di.data_ptr(), ss.data_ptr()
+            d.Sd, d.ld, d.rank, d.HC = di.shape[0], di.shape[2], int(writeback["rank"]), hc
         d.workspace, d.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
         _lib.check(_lib.lib().tsumuji_moe_layer(ctypes.byref(d), self._stream()), "tsumuji_moe_layer")
         return out

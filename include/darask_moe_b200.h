@@ -137,9 +137,13 @@ int kogarashi_moe_status(const void* workspace, unsigned* host_status /* host */
  * message on stderr.  The call itself allocates nothing.  The first call on each device looks up
  * the array's device address (with that device current); make that first call before any stream
  * capture.  All calls on a device share the one array: calls whose kernels can overlap on the
- * GPU (different streams) race; serialize them. */
+ * GPU (different streams) race; serialize them.  Every call first clears the array's control
+ * words, the status word among them: read the status of a call (kogarashi_moe_static_status,
+ * which synchronizes the stream) before the next call if it matters.  A descriptor that fails
+ * validation is refused before anything is enqueued. */
 size_t kogarashi_moe_static_scratch_bytes(void);
 int kogarashi_moe_layer_static(const KogarashiMoe* desc /* host */, darask_stream_t stream);
+int kogarashi_moe_static_status(unsigned* host_status /* host */, darask_stream_t stream);
 
 /* ---- Tsumuji MoE FFN layer ----------------------------------------------------------------------------
  * One call replaces `router_topk`, `moe_gate_up`, `moe_down` and the expert part of `moe_combine`
@@ -149,8 +153,10 @@ int kogarashi_moe_layer_static(const KogarashiMoe* desc /* host */, darask_strea
  *   [gate codes | up codes | down codes | gate sf | up sf | down sf] (engines/tsumuji/crates/tsumuji-engine/src/weights.rs:10-12),
  * gs: float32 [experts][3] global scales; shared_gu bf16 [2F][H] (gate rows, then up rows), shared_down bf16 [H][F].
  * router_w: bf16 [experts+1][H] (row `experts` = shared-expert gate) or NULL when rlogits already holds the
- * logits.  out[n] = sum_s w_s y_s + shared_gate y_shared (accumulate != 0: added to out).  The write-back
- * into the residual streams R and the sum-of-squares statistics of `moe_combine` stay with the caller. */
+ * logits.  out[n] = sum_s w_s y_s + shared_gate y_shared (accumulate != 0: added to out; out may be NULL when R is
+ * given).  R != NULL adds the rest of `moe_combine` (ops.cu:76-94, 202-230) to the same launch: the write-back
+ * R[n][i] += inj_i * out[n] into the HC residual streams with inj_i = 2 sigmoid(sum_s di[s][n][rank+i] / HC), and
+ * ss[n][b][i] = sum over the 256 columns of block b of the new R[n][i]^2 (the statistics the next norm reads). */
 typedef struct {
   int hidden, inter, experts, topk, tokens;
   const void* router_w;
@@ -163,6 +169,10 @@ typedef struct {
   float* shared_gate;             /* [tokens]                                                  */
   int accumulate;
   void* workspace; size_t workspace_bytes;
+  float* R;                       /* [tokens][HC][hidden] residual streams, updated in place; NULL: no write-back */
+  const float* di;                /* [Sd][tokens][ld] partial sums of the stream-gate projection                  */
+  int Sd, ld, rank, HC;           /* HC <= 8 streams; their gate logits are di[..][rank .. rank+HC)               */
+  float* ss;                      /* [tokens][ceil(hidden/256)][HC]                                               */
 } TsumujiMoe;
 size_t tsumuji_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens);
 /* zeroes the control words once after allocation (same as kogarashi_moe_workspace_init) */

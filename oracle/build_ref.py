@@ -19,7 +19,8 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
-REF = Path(os.environ.get("DARASK_REFERENCE", "/root/reference"))
+# the reference checkout: $DARASK_REFERENCE, else a directory named "reference" beside this repository
+REF = Path(os.environ["DARASK_REFERENCE"]) if os.environ.get("DARASK_REFERENCE") else HERE.parent.parent / "reference"
 OUT = HERE / "_ref"
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 

@@ -14,7 +14,8 @@ import torch
 
 os.environ.setdefault("PYTHONDONTWRITEBYTECODE", "1")
 sys.dont_write_bytecode = True
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+# the reference checkout: first argument, else a directory named "reference" beside this repository
+ref = sys.argv[1] if len(sys.argv) > 1 else os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "..", "reference")
 pkg = types.ModuleType("hayate_tools")
 pkg.__path__ = [os.path.join(ref, "engines/hayate/python-tools/hayate_tools")]
 sys.modules["hayate_tools"] = pkg

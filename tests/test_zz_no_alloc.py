@@ -34,11 +34,11 @@ def _descriptor(D, layer, bufs, t):
     return d
 
 
-def test_static_scratch_entry_matches_workspace_entry():
+@pytest.mark.parametrize("t", [2, 1])          # two tokens: four launches; one token: the single persistent launch
+def test_static_scratch_entry_matches_workspace_entry(t):
     import darask_inference_engine_b200 as D
     lib = D._lib.lib()
     dev = torch.device("cuda", 0)
-    t = 2
     layer, acts = W.kogarashi_layer(21, hidden=768, inter=512, experts=16, topk=4, tokens=t, shared=True, pool=16)
     up8 = lambda a: torch.from_numpy(np.ascontiguousarray(a).view(np.uint8).reshape(-1)).to(dev)
     st = torch.cuda.current_stream(dev).cuda_stream
@@ -80,6 +80,8 @@ def test_static_scratch_entry_matches_workspace_entry():
         assert np.array_equal(bufs["ids"].cpu().numpy(), expected_ids), call
         W.check_output(got.astype(np.float64) - acts["x"], expected.astype(np.float64) - acts["x"])
         assert np.array_equal(got, expected), call      # same kernels, same order: identical bits
+        word = ctypes.c_uint(99)
+        assert lib.kogarashi_moe_static_status(ctypes.byref(word), st) == 0 and word.value == 0
 
     # a shape whose scratch need exceeds the built-in array is refused, nothing is launched
     d.tokens = 64
