@@ -152,49 +152,57 @@ DEVI DiagLane diag_lane(int lane) {
   return d;
 }
 
-// The activation side of one 256-column block for this lane, loaded once and used for every 16-row pass of the block:
-//   b0[i] / b1[i]: the B registers (slot groups 0-1 / 2-3) of tile i, four MMAs each; a lane carries real values in
-//   at most one of the two sets, the other set stays zero for the whole launch (which set is a property of the lane),
-//   so the sets are zeroed once and only the live one is ever loaded: no zero fragments travel through shared memory.
+// The activation side of one 256-column block for this lane. pair[i] = the (b0, b1) operand registers of MMA i of
+// the block (Q4_K: tile i / 8; Q6_K: tile i / 4). A lane carries real values in at most one of the two registers of
+// a pair (always the same one) and zero in the other; which one is a property of the lane. The pairs are zeroed once
+// per launch and a block load writes only the live half, straight into the register the MMA reads (two predicated
+// 32-bit loads per pair: no zero fragments in shared memory, no register moves to assemble the operand).
 //   xs[i]: the float sum of (hi + lo) over the scale group this lane owns in tile i.
 struct BlockFrags {
-  uint4 b0[4], b1[4];
+  uint2 pair[16];
   float xs[4];
 };
 DEVI void frags_clear(BlockFrags& f) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    f.b0[i] = f.b1[i] = make_uint4(0u, 0u, 0u, 0u);
-    f.xs[i] = 0.f;
-  }
+  for (int i = 0; i < 16; ++i) f.pair[i] = make_uint2(0u, 0u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) f.xs[i] = 0.f;
 }
-// Q4_K: tile t of a block covers sub-blocks 4t .. 4t+3; this lane's fragments of tile t are 16 halves (32 bytes) at
+// Q4_K: tile t of a block covers sub-blocks 4t .. 4t+3; this lane's fragments of tile t are 16 halves (8 words) at
 // xb + 256 t; xs_addr: the eight float sums of the block.
 DEVI void q4k_load_frags(BlockFrags& f, uint32_t xb, bool first, bool second, uint32_t xs_addr, int sbl) {
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    if (first) {
-      f.b0[2 * t] = lds128(xb + 256 * t);
-      f.b0[2 * t + 1] = lds128(xb + 256 * t + 16);
-    }
-    if (second) {
-      f.b1[2 * t] = lds128(xb + 256 * t);
-      f.b1[2 * t + 1] = lds128(xb + 256 * t + 16);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (first) f.pair[8 * t + i].x = lds32(xb + 256 * t + 4 * i);
+      if (second) f.pair[8 * t + i].y = lds32(xb + 256 * t + 4 * i);
     }
     f.xs[t] = __uint_as_float(lds32(xs_addr + 4 * (4 * t + sbl)));
   }
 }
-// Q6_K: tile (n, A) covers the scale groups 8n + 2A + {0, 1, 4, 5}; this lane's fragments of it are 8 halves at
-// xb + 256 n + 64 A; xs_addr: the sixteen float sums of the block.
+// Q6_K: tile (n, A) covers the scale groups 8n + 2A + {0, 1, 4, 5}; this lane's fragments of it are 8 halves (4 words)
+// at xb + 256 n + 64 A; xs_addr: the sixteen float sums of the block.
 DEVI void q6k_load_frags(BlockFrags& f, uint32_t xb, bool first, bool second, uint32_t xs_addr, int sl) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int n = i >> 1, A = i & 1;
-    if (first) f.b0[i] = lds128(xb + 256 * n + 64 * A);
-    if (second) f.b1[i] = lds128(xb + 256 * n + 64 * A);
-    f.xs[i] = __uint_as_float(lds32(xs_addr + 4 * (8 * n + 2 * A + sl)));
+  for (int t = 0; t < 4; ++t) {
+    const int n = t >> 1, A = t & 1;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (first) f.pair[4 * t + i].x = lds32(xb + 256 * n + 64 * A + 4 * i);
+      if (second) f.pair[4 * t + i].y = lds32(xb + 256 * n + 64 * A + 4 * i);
+    }
+    f.xs[t] = __uint_as_float(lds32(xs_addr + 4 * (8 * n + 2 * A + sl)));
   }
 }
+// D = A x B with a zero accumulator held in registers that are never written (the first MMA of a tile)
+DEVI void mma_f16_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1, float zero) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(zero));
+}
+// byte `sel & 3` of `word` as a float (the byte is the low mantissa byte of 2^23, minus 2^23)
+DEVI float byte_to_float(uint32_t word, uint32_t sel) { return __uint_as_float(__byte_perm(word, 0x4B000000u, sel)) - kMagic; }
 
 // ---- Q4_K: 16 row slots x one 256-column block against the block's fragments ----------------------------------------
 // Tile t covers sub-blocks 4t .. 4t+3: slot group 0 = low nibbles of bytes 64t .. 64t+31 (sub-block 4t), group 1 = low
@@ -203,36 +211,36 @@ DEVI void q6k_load_frags(BlockFrags& f, uint32_t xb, bool first, bool second, ui
 DEVI void q4k_rows(uint32_t rA, uint32_t rB, int j, const BlockFrags& f, float& acc0, float& acc1) {
   const uint4 hA = lds128(rA), hB = lds128(rB);
   const int sbl = 2 * (j & 1) + (j >> 1);         // this lane's sub-block inside a tile (slot group j)
-  const int sh = 8 * sbl;
+  const uint32_t pick = 0x7650u + sbl;            // byte sbl of a word into the low byte of a magic float
   const float nib = j >= 2 ? 0.0625f : 1.f;       // high nibbles enter the tiles as 1024 + 16 q
   const float dA = half_lo(hA.x) * nib, mA = half_hi(hA.x), dB = half_lo(hB.x) * nib, mB = half_hi(hB.x);
+  // the six-bit scales and minimums of the eight sub-blocks, four per word (kogarashi kernels/native.cu:59-60):
+  // sub-blocks 0-3: bytes of y / z & 63; sub-blocks 4-7: (w & 15) | ((y >> 6) << 4) and (w >> 4) | ((z >> 6) << 4)
+  const uint32_t scA[2] = {hA.y & 0x3F3F3F3Fu, (hA.w & 0x0F0F0F0Fu) | ((hA.y >> 2) & 0x30303030u)};
+  const uint32_t mnA[2] = {hA.z & 0x3F3F3F3Fu, ((hA.w >> 4) & 0x0F0F0F0Fu) | ((hA.z >> 2) & 0x30303030u)};
+  const uint32_t scB[2] = {hB.y & 0x3F3F3F3Fu, (hB.w & 0x0F0F0F0Fu) | ((hB.y >> 2) & 0x30303030u)};
+  const uint32_t mnB[2] = {hB.z & 0x3F3F3F3Fu, ((hB.w >> 4) & 0x0F0F0F0Fu) | ((hB.z >> 2) & 0x30303030u)};
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const uint4 wA = lds128(rA + 16 + 64 * t + 16 * j), wB = lds128(rB + 16 + 64 * t + 16 * j);
-    float c[4] = {0.f, 0.f, 0.f, 0.f};
+    float c[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       const uint32_t a = u4w(wA, q), b = u4w(wB, q), as = a >> 8, bs = b >> 8;
-      const uint32_t e0 = u4w(f.b0[2 * t + (q >> 1)], 2 * (q & 1)), e1 = u4w(f.b0[2 * t + (q >> 1)], 2 * (q & 1) + 1);
-      const uint32_t f0 = u4w(f.b1[2 * t + (q >> 1)], 2 * (q & 1)), f1 = u4w(f.b1[2 * t + (q >> 1)], 2 * (q & 1) + 1);
-      mma_f16(c, (a & 0x000F000Fu) | 0x64006400u, (b & 0x000F000Fu) | 0x64006400u, (a & 0x00F000F0u) | 0x64006400u,
-              (b & 0x00F000F0u) | 0x64006400u, e0, f0);
+      const uint2 e = f.pair[8 * t + 2 * q], o = f.pair[8 * t + 2 * q + 1];
+      if (q == 0)
+        mma_f16_first(c, (a & 0x000F000Fu) | 0x64006400u, (b & 0x000F000Fu) | 0x64006400u, (a & 0x00F000F0u) | 0x64006400u,
+                      (b & 0x00F000F0u) | 0x64006400u, e.x, e.y, 0.f);
+      else
+        mma_f16(c, (a & 0x000F000Fu) | 0x64006400u, (b & 0x000F000Fu) | 0x64006400u, (a & 0x00F000F0u) | 0x64006400u,
+                (b & 0x00F000F0u) | 0x64006400u, e.x, e.y);
       mma_f16(c, (as & 0x000F000Fu) | 0x64006400u, (bs & 0x000F000Fu) | 0x64006400u, (as & 0x00F000F0u) | 0x64006400u,
-              (bs & 0x00F000F0u) | 0x64006400u, e1, f1);
-    }
-    // six-bit scale and minimum of sub-block 4t + sbl of both rows (kogarashi kernels/native.cu:59-60)
-    uint32_t scA, mnA, scB, mnB;
-    if (t == 0) {
-      scA = (hA.y >> sh) & 63u; mnA = (hA.z >> sh) & 63u;
-      scB = (hB.y >> sh) & 63u; mnB = (hB.z >> sh) & 63u;
-    } else {
-      scA = ((hA.w >> sh) & 15u) | (((hA.y >> sh) >> 2) & 0x30u); mnA = ((hA.w >> (sh + 4)) & 15u) | (((hA.z >> sh) >> 2) & 0x30u);
-      scB = ((hB.w >> sh) & 15u) | (((hB.y >> sh) >> 2) & 0x30u); mnB = ((hB.w >> (sh + 4)) & 15u) | (((hB.z >> sh) >> 2) & 0x30u);
+              (bs & 0x00F000F0u) | 0x64006400u, o.x, o.y);
     }
     const float xsv = f.xs[t];
     // sum of (1024 + q) x = raw; d sc sum(q x) - dmin m sum(x) = S raw - (1024 S + dmin m) sum(x)
-    const float sA = dA * magic_u8(scA), sB = dB * magic_u8(scB);
-    const float tA = fmaf(1024.f, sA, mA * magic_u8(mnA)), tB = fmaf(1024.f, sB, mB * magic_u8(mnB));
+    const float sA = dA * byte_to_float(scA[t], pick), sB = dB * byte_to_float(scB[t], pick);
+    const float tA = fmaf(1024.f, sA, mA * byte_to_float(mnA[t], pick)), tB = fmaf(1024.f, sB, mB * byte_to_float(mnB[t], pick));
     acc0 = fmaf(sA, c[0] + c[1], acc0);
     acc0 = fmaf(-tA, xsv, acc0);
     acc1 = fmaf(sB, c[2] + c[3], acc1);
@@ -256,8 +264,7 @@ DEVI void q6k_rows(uint32_t rA, uint32_t rB, int j, float dA, float dB, const Bl
 #pragma unroll
     for (int A = 0; A < 2; ++A) {
       const uint2 lA = lds64(rA + 64 * n + 32 * A + 8 * j), lB = lds64(rB + 64 * n + 32 * A + 8 * j);
-      const uint4 p = f.b0[2 * n + A], q = f.b1[2 * n + A];
-      float c[4] = {0.f, 0.f, 0.f, 0.f};
+      float c[4];
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const uint32_t wa = u ? lA.y : lA.x, wb = u ? lB.y : lB.x, ha = u ? hA.y : hA.x, hb = u ? hB.y : hB.x;
@@ -266,11 +273,16 @@ DEVI void q6k_rows(uint32_t rA, uint32_t rB, int j, float dA, float dB, const Bl
         const uint32_t lob = (wb & 0x0F0F0F0Fu) | ((A ? hb << 2 : hb << 4) & 0x30303030u);
         const uint32_t hia = ((wa >> 4) & 0x0F0F0F0Fu) | ((A ? ha >> 2 : ha) & 0x30303030u);
         const uint32_t hib = ((wb >> 4) & 0x0F0F0F0Fu) | ((A ? hb >> 2 : hb) & 0x30303030u);
+        const uint2 e = f.pair[4 * (2 * n + A) + 2 * u], o = f.pair[4 * (2 * n + A) + 2 * u + 1];
         // bytes [b0, 0x64, b2, 0x64] = half2(1024 + b0, 1024 + b2)
-        mma_f16(c, __byte_perm(loa, 0x64646464u, 0x4240), __byte_perm(lob, 0x64646464u, 0x4240), __byte_perm(hia, 0x64646464u, 0x4240),
-                __byte_perm(hib, 0x64646464u, 0x4240), u4w(p, 2 * u), u4w(q, 2 * u));
+        if (u == 0)
+          mma_f16_first(c, __byte_perm(loa, 0x64646464u, 0x4240), __byte_perm(lob, 0x64646464u, 0x4240), __byte_perm(hia, 0x64646464u, 0x4240),
+                        __byte_perm(hib, 0x64646464u, 0x4240), e.x, e.y, 0.f);
+        else
+          mma_f16(c, __byte_perm(loa, 0x64646464u, 0x4240), __byte_perm(lob, 0x64646464u, 0x4240), __byte_perm(hia, 0x64646464u, 0x4240),
+                  __byte_perm(hib, 0x64646464u, 0x4240), e.x, e.y);
         mma_f16(c, __byte_perm(loa, 0x64646464u, 0x4341), __byte_perm(lob, 0x64646464u, 0x4341), __byte_perm(hia, 0x64646464u, 0x4341),
-                __byte_perm(hib, 0x64646464u, 0x4341), u4w(p, 2 * u + 1), u4w(q, 2 * u + 1));
+                __byte_perm(hib, 0x64646464u, 0x4341), o.x, o.y);
       }
       const float xsv = f.xs[2 * n + A];
       const uint32_t sel = 0x7650u + 2 * A + (j & 1);
