@@ -20,12 +20,18 @@
 // half-rate integer pipe, not by the tensor pipe: the activation fragments of a block are loaded once into
 // registers, and the zero halves of the block-diagonal operand never travel through shared memory.
 //
-// Arithmetic per 256-column block, `mma.sync.m16n8k16` (fp16 in, fp32 accumulate): the A operand holds the weight
-// codes as fp16 magic numbers (1024 + q, no conversion, no per-weight scaling); the B operand is block diagonal: the
-// sixteen k slots of a tile belong to four different scale groups of the block and column pair s of the tile holds
-// the activation (hi plane, lo plane) only in the four slots of group s. Column pair s of the accumulator is then the
-// raw code sum of scale group s, and the group scales, the 1024 offset (through per-group sums of the activations)
-// and the Q4_K minimum are applied once per block and lane in float32.
+// Arithmetic per 256-column block, `mma.sync.m16n8k32` on 8-bit integers (u8 weight codes x s8 activations, s32
+// accumulate; the legacy tensor path issues one such instruction per 8 cycles and scheduler, twice the weights of the
+// f16 shape, and the codes need no float conversion: the block loop is bound by the half-rate integer pipe that
+// unpacks the codes, so instructions per weight are what counts). The activations are held as 16-bit fixed point of
+// the largest magnitude inside their own scale group (32 columns for Q4_K, 16 for Q6_K): x ~ (256 hi + lo) / S with two
+// signed bytes per value, error <= max|x over the group| / 64000 per value, so an outlier costs precision only among
+// its own 15 or 31 neighbours; hi and lo are two columns of the B operand. B is block diagonal: the
+// 32 k slots of an MMA belong to four different scale groups of the block and column pair s of the tile holds the
+// activation bytes only in the eight slots of group s, so that column pair s of the accumulator is the exact integer
+// code sum of scale group s; 1 / S of the group, the group scales, the Q4_K minimum (through per-group float sums of
+// the activations) and the Q6_K code offset 32 (through per-group integer sums) are applied once per block and lane
+// in float32.
 //
 // Replaces kogarashi kernels/native.cu:46-117 (`gemv`, `activate`, `route`, `combine`) for one token; formulas of the
 // formats: native.cu:26-40 and :52-82.
@@ -36,7 +42,8 @@
 
 namespace dmoe {
 
-constexpr unsigned kStatusActRange = 4u;   // an activation does not fit the fp16 planes (|value| > 65504)
+constexpr float kFixedPointRange = 32000.f;     // the largest magnitude of a scale group maps to this integer
+constexpr unsigned kStatusActRange = 4u;   // an activation is not finite (the staged kernels: does not fit fp16 planes)
 
 constexpr int kFusedConsumers = 16;                          // consumer warps
 constexpr int kFusedProducers = 2;                           // warps that issue bulk copies (one thread each)
@@ -56,9 +63,9 @@ struct FusedArgs {
   int nblk2, row_bytes2, rt2, down_q6;            // down: the same, row tiles of the output
   int stage_bytes, nstage;                        // chunk slot size and number of slots of the ring
   int off_bars, off_psum, off_act, off_ring;             // shared-memory offsets
-  int act_lo1, act_xs1, act_rows;                 // phase R/1 inside the activation area: lo-plane stride, sums, router rows
-  int act_lo2, act_grp2, act_xs2;                 // phase 2: lo-plane stride, bytes per group, offset of the sums
-  unsigned* gbar; unsigned* status; __half* hbuf; float* y; float* sg;
+  int act_lo1, act_xs1, act_rows;                 // phase R/1 inside the activation area: lo-plane offset, (sum, 1/S) pairs, router rows
+  int act_lo2, act_grp2, act_xs2;                 // phase 2: lo-plane offset, bytes per expert group, offset of the (sum, 1/S) pairs
+  unsigned* gbar; unsigned* status; float* hbuf; float* y; float* sg;
 };
 
 // ---- small pieces -----------------------------------------------------------------------------------------
@@ -153,53 +160,66 @@ DEVI DiagLane diag_lane(int lane) {
 }
 
 // The activation side of one 256-column block for this lane. pair[i] = the (b0, b1) operand registers of MMA i of
-// the block (Q4_K: tile i / 8; Q6_K: tile i / 4). A lane carries real values in at most one of the two registers of
-// a pair (always the same one) and zero in the other; which one is a property of the lane. The pairs are zeroed once
-// per launch and a block load writes only the live half, straight into the register the MMA reads (two predicated
-// 32-bit loads per pair: no zero fragments in shared memory, no register moves to assemble the operand).
-//   xs[i]: the float sum of (hi + lo) over the scale group this lane owns in tile i.
+// the block. A lane carries real values in at most one of the two registers of a pair (always the same one) and zero
+// in the other; which one is a property of the lane. The pairs are zeroed once per launch and a block load writes only
+// the live half, straight into the register the MMA reads (predicated 32-bit loads: no zero fragments in shared
+// memory, no register moves to assemble the operand).
+//   xs[i]: the sum of the activations over the scale group this lane owns in tile i (Q4_K: float sum of x over a
+//   sub-block; Q6_K: the integer sum of the fixed-point values over 16 columns, as a float); inv[i]: 1 / S of that group.
 struct BlockFrags {
-  uint2 pair[16];
-  float xs[4];
+  uint2 pair[8];
+  float xs[4], inv[4];
 };
 DEVI void frags_clear(BlockFrags& f) {
 #pragma unroll
-  for (int i = 0; i < 16; ++i) f.pair[i] = make_uint2(0u, 0u);
+  for (int i = 0; i < 8; ++i) f.pair[i] = make_uint2(0u, 0u);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) f.xs[i] = 0.f;
+  for (int i = 0; i < 4; ++i) f.xs[i] = f.inv[i] = 0.f;
 }
-// Q4_K: tile t of a block covers sub-blocks 4t .. 4t+3; this lane's fragments of tile t are 16 halves (8 words) at
-// xb + 256 t; xs_addr: the eight float sums of the block.
+// Q4_K: tile t of a block covers sub-blocks 4t .. 4t+3; this lane's fragments of tile t are 16 activation bytes at
+// xb + 128 t (natural column order); xs_addr: the eight (sum, 1 / S) pairs of the block.
 DEVI void q4k_load_frags(BlockFrags& f, uint32_t xb, bool first, bool second, uint32_t xs_addr, int sbl) {
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (first) f.pair[8 * t + i].x = lds32(xb + 256 * t + 4 * i);
-      if (second) f.pair[8 * t + i].y = lds32(xb + 256 * t + 4 * i);
+    for (int i = 0; i < 4; ++i) {
+      if (first) f.pair[4 * t + i].x = lds32(xb + 128 * t + 4 * i);
+      if (second) f.pair[4 * t + i].y = lds32(xb + 128 * t + 4 * i);
     }
-    f.xs[t] = __uint_as_float(lds32(xs_addr + 4 * (4 * t + sbl)));
+    const uint2 v = lds64(xs_addr + 8 * (4 * t + sbl));
+    f.xs[t] = __uint_as_float(v.x);
+    f.inv[t] = __uint_as_float(v.y);
   }
 }
-// Q6_K: tile (n, A) covers the scale groups 8n + 2A + {0, 1, 4, 5}; this lane's fragments of it are 8 halves (4 words)
-// at xb + 256 n + 64 A; xs_addr: the sixteen float sums of the block.
+// Q6_K: tile (n, A) covers the scale groups 8n + 2A + {0, 1, 4, 5}; this lane's fragments of it are 8 activation bytes at
+// xb + 128 n + 32 A; xs_addr: the sixteen (sum, 1 / S) pairs of the block.
 DEVI void q6k_load_frags(BlockFrags& f, uint32_t xb, bool first, bool second, uint32_t xs_addr, int sl) {
 #pragma unroll
   for (int t = 0; t < 4; ++t) {
     const int n = t >> 1, A = t & 1;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      if (first) f.pair[4 * t + i].x = lds32(xb + 256 * n + 64 * A + 4 * i);
-      if (second) f.pair[4 * t + i].y = lds32(xb + 256 * n + 64 * A + 4 * i);
+    for (int i = 0; i < 2; ++i) {
+      if (first) f.pair[2 * t + i].x = lds32(xb + 128 * n + 32 * A + 4 * i);
+      if (second) f.pair[2 * t + i].y = lds32(xb + 128 * n + 32 * A + 4 * i);
     }
-    f.xs[t] = __uint_as_float(lds32(xs_addr + 4 * (8 * n + 2 * A + sl)));
+    const uint2 v = lds64(xs_addr + 8 * (8 * n + 2 * A + sl));
+    f.xs[t] = __uint_as_float(v.x);
+    f.inv[t] = __uint_as_float(v.y);
   }
 }
-// D = A x B with a zero accumulator held in registers that are never written (the first MMA of a tile)
-DEVI void mma_f16_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1, float zero) {
-  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
-               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
-               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(zero));
+// D[16x8] (+)= A[16x32] (u8, row) x B[32x8] (s8, col), s32 accumulate. Thread (g = lane/4, j = lane%4):
+// a0/a1: rows g / g+8, k 4j..4j+3; a2/a3: same rows, k 16+4j..; b0: column g, k 4j..4j+3; b1: k 16+4j..;
+// c0,c1: row g, columns 2j,2j+1; c2,c3: row g+8.
+DEVI void mma_i8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// the first MMA of a tile: the zero accumulator is one register that is never written
+DEVI void mma_i8_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1, int zero) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(zero));
 }
 // byte `sel & 3` of `word` as a float (the byte is the low mantissa byte of 2^23, minus 2^23)
 DEVI float byte_to_float(uint32_t word, uint32_t sel) { return __uint_as_float(__byte_perm(word, 0x4B000000u, sel)) - kMagic; }
@@ -207,13 +227,13 @@ DEVI float byte_to_float(uint32_t word, uint32_t sel) { return __uint_as_float(_
 // ---- Q4_K: 16 row slots x one 256-column block against the block's fragments ----------------------------------------
 // Tile t covers sub-blocks 4t .. 4t+3: slot group 0 = low nibbles of bytes 64t .. 64t+31 (sub-block 4t), group 1 = low
 // nibbles of bytes 64t+32 .. (sub-block 4t+2), groups 2 / 3 = the high nibbles of the same bytes (sub-blocks 4t+1 /
-// 4t+3). Lane j reads bytes 64t + 16j .. +15 of rows g and g + 8 (rA / rB: shared-memory address of the block in them).
+// 4t+3). Lane j reads bytes 64t + 16j .. +15 of rows g and g + 8 (rA / rB: shared-memory address of the block in them);
+// word q of them feeds MMA q of the tile: its low nibbles are four k slots of a0 / a1, its high nibbles of a2 / a3.
 DEVI void q4k_rows(uint32_t rA, uint32_t rB, int j, const BlockFrags& f, float& acc0, float& acc1) {
   const uint4 hA = lds128(rA), hB = lds128(rB);
   const int sbl = 2 * (j & 1) + (j >> 1);         // this lane's sub-block inside a tile (slot group j)
   const uint32_t pick = 0x7650u + sbl;            // byte sbl of a word into the low byte of a magic float
-  const float nib = j >= 2 ? 0.0625f : 1.f;       // high nibbles enter the tiles as 1024 + 16 q
-  const float dA = half_lo(hA.x) * nib, mA = half_hi(hA.x), dB = half_lo(hB.x) * nib, mB = half_hi(hB.x);
+  const float dA = half_lo(hA.x), mA = half_hi(hA.x), dB = half_lo(hB.x), mB = half_hi(hB.x);
   // the six-bit scales and minimums of the eight sub-blocks, four per word (kogarashi kernels/native.cu:59-60):
   // sub-blocks 0-3: bytes of y / z & 63; sub-blocks 4-7: (w & 15) | ((y >> 6) << 4) and (w >> 4) | ((z >> 6) << 4)
   const uint32_t scA[2] = {hA.y & 0x3F3F3F3Fu, (hA.w & 0x0F0F0F0Fu) | ((hA.y >> 2) & 0x30303030u)};
@@ -223,35 +243,29 @@ DEVI void q4k_rows(uint32_t rA, uint32_t rB, int j, const BlockFrags& f, float& 
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
     const uint4 wA = lds128(rA + 16 + 64 * t + 16 * j), wB = lds128(rB + 16 + 64 * t + 16 * j);
-    float c[4];
+    int c[4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
-      const uint32_t a = u4w(wA, q), b = u4w(wB, q), as = a >> 8, bs = b >> 8;
-      const uint2 e = f.pair[8 * t + 2 * q], o = f.pair[8 * t + 2 * q + 1];
-      if (q == 0)
-        mma_f16_first(c, (a & 0x000F000Fu) | 0x64006400u, (b & 0x000F000Fu) | 0x64006400u, (a & 0x00F000F0u) | 0x64006400u,
-                      (b & 0x00F000F0u) | 0x64006400u, e.x, e.y, 0.f);
-      else
-        mma_f16(c, (a & 0x000F000Fu) | 0x64006400u, (b & 0x000F000Fu) | 0x64006400u, (a & 0x00F000F0u) | 0x64006400u,
-                (b & 0x00F000F0u) | 0x64006400u, e.x, e.y);
-      mma_f16(c, (as & 0x000F000Fu) | 0x64006400u, (bs & 0x000F000Fu) | 0x64006400u, (as & 0x00F000F0u) | 0x64006400u,
-              (bs & 0x00F000F0u) | 0x64006400u, o.x, o.y);
+      const uint32_t a = u4w(wA, q), b = u4w(wB, q);
+      const uint2 e = f.pair[4 * t + q];
+      if (q == 0) mma_i8_first(c, a & 0x0F0F0F0Fu, b & 0x0F0F0F0Fu, (a >> 4) & 0x0F0F0F0Fu, (b >> 4) & 0x0F0F0F0Fu, e.x, e.y, 0);
+      else mma_i8(c, a & 0x0F0F0F0Fu, b & 0x0F0F0F0Fu, (a >> 4) & 0x0F0F0F0Fu, (b >> 4) & 0x0F0F0F0Fu, e.x, e.y);
     }
+    // sum of q x = (256 c_hi + c_lo) / S; value = d sc sum(q x) - dmin m sum(x)
+    const float rawA = __int2float_rn(256 * c[0] + c[1]) * f.inv[t], rawB = __int2float_rn(256 * c[2] + c[3]) * f.inv[t];
     const float xsv = f.xs[t];
-    // sum of (1024 + q) x = raw; d sc sum(q x) - dmin m sum(x) = S raw - (1024 S + dmin m) sum(x)
-    const float sA = dA * byte_to_float(scA[t], pick), sB = dB * byte_to_float(scB[t], pick);
-    const float tA = fmaf(1024.f, sA, mA * byte_to_float(mnA[t], pick)), tB = fmaf(1024.f, sB, mB * byte_to_float(mnB[t], pick));
-    acc0 = fmaf(sA, c[0] + c[1], acc0);
-    acc0 = fmaf(-tA, xsv, acc0);
-    acc1 = fmaf(sB, c[2] + c[3], acc1);
-    acc1 = fmaf(-tB, xsv, acc1);
+    acc0 = fmaf(dA * byte_to_float(scA[t], pick), rawA, acc0);
+    acc0 = fmaf(-(mA * byte_to_float(mnA[t], pick)), xsv, acc0);
+    acc1 = fmaf(dB * byte_to_float(scB[t], pick), rawB, acc1);
+    acc1 = fmaf(-(mB * byte_to_float(mnB[t], pick)), xsv, acc1);
   }
 }
 
 // ---- Q6_K (row-aligned device layout: ql 128 | qh 64 | int8 scales 16 per block) ------------------------------------
 // Tile (n, A) covers the scale groups 8n + 2A + {0, 1, 4, 5}: slot groups 0 / 1 = low nibbles of ql bytes
 // 64n + 32A + [0,16) / [16,32) with qh bit pair A, groups 2 / 3 = the high nibbles with bit pair A + 2. Lane j reads ql
-// bytes 64n + 32A + 8j .. +7 and qh bytes 32n + 8j .. +7 of rows g and g + 8. Codes enter as 1024 + (q + 32).
+// bytes 64n + 32A + 8j .. +7 and qh bytes 32n + 8j .. +7 of rows g and g + 8; word u of them feeds MMA u of the tile.
+// The codes enter unsigned (value + 32); the offset comes back through the integer group sums.
 // dA / dB: the float block scales of the two rows.
 DEVI void q6k_rows(uint32_t rA, uint32_t rB, int j, float dA, float dB, const BlockFrags& f, float& acc0, float& acc1) {
   const uint4 sA4 = lds128(rA + 192), sB4 = lds128(rB + 192);
@@ -264,7 +278,7 @@ DEVI void q6k_rows(uint32_t rA, uint32_t rB, int j, float dA, float dB, const Bl
 #pragma unroll
     for (int A = 0; A < 2; ++A) {
       const uint2 lA = lds64(rA + 64 * n + 32 * A + 8 * j), lB = lds64(rB + 64 * n + 32 * A + 8 * j);
-      float c[4];
+      int c[4];
 #pragma unroll
       for (int u = 0; u < 2; ++u) {
         const uint32_t wa = u ? lA.y : lA.x, wb = u ? lB.y : lB.x, ha = u ? hA.y : hA.x, hb = u ? hB.y : hB.x;
@@ -273,47 +287,48 @@ DEVI void q6k_rows(uint32_t rA, uint32_t rB, int j, float dA, float dB, const Bl
         const uint32_t lob = (wb & 0x0F0F0F0Fu) | ((A ? hb << 2 : hb << 4) & 0x30303030u);
         const uint32_t hia = ((wa >> 4) & 0x0F0F0F0Fu) | ((A ? ha >> 2 : ha) & 0x30303030u);
         const uint32_t hib = ((wb >> 4) & 0x0F0F0F0Fu) | ((A ? hb >> 2 : hb) & 0x30303030u);
-        const uint2 e = f.pair[4 * (2 * n + A) + 2 * u], o = f.pair[4 * (2 * n + A) + 2 * u + 1];
-        // bytes [b0, 0x64, b2, 0x64] = half2(1024 + b0, 1024 + b2)
-        if (u == 0)
-          mma_f16_first(c, __byte_perm(loa, 0x64646464u, 0x4240), __byte_perm(lob, 0x64646464u, 0x4240), __byte_perm(hia, 0x64646464u, 0x4240),
-                        __byte_perm(hib, 0x64646464u, 0x4240), e.x, e.y, 0.f);
-        else
-          mma_f16(c, __byte_perm(loa, 0x64646464u, 0x4240), __byte_perm(lob, 0x64646464u, 0x4240), __byte_perm(hia, 0x64646464u, 0x4240),
-                  __byte_perm(hib, 0x64646464u, 0x4240), e.x, e.y);
-        mma_f16(c, __byte_perm(loa, 0x64646464u, 0x4341), __byte_perm(lob, 0x64646464u, 0x4341), __byte_perm(hia, 0x64646464u, 0x4341),
-                __byte_perm(hib, 0x64646464u, 0x4341), o.x, o.y);
+        const uint2 e = f.pair[2 * (2 * n + A) + u];
+        if (u == 0) mma_i8_first(c, loa, lob, hia, hib, e.x, e.y, 0);
+        else mma_i8(c, loa, lob, hia, hib, e.x, e.y);
       }
-      const float xsv = f.xs[2 * n + A];
       const uint32_t sel = 0x7650u + 2 * A + (j & 1);
-      const float sA = dA * (__uint_as_float(__byte_perm(swA, 0x4B000000u, sel)) - (kMagic + 128.f));
-      const float sB = dB * (__uint_as_float(__byte_perm(swB, 0x4B000000u, sel)) - (kMagic + 128.f));
-      // sum of (1056 + (q - 32)) x = raw; d s sum((q - 32) x) = S raw - 1056 S sum(x)
-      acc0 = fmaf(sA, c[0] + c[1], acc0);
-      acc0 = fmaf(-1056.f * sA, xsv, acc0);
-      acc1 = fmaf(sB, c[2] + c[3], acc1);
-      acc1 = fmaf(-1056.f * sB, xsv, acc1);
+      const float dinvA = dA * f.inv[2 * n + A], dinvB = dB * f.inv[2 * n + A];
+      const float sA = dinvA * (__uint_as_float(__byte_perm(swA, 0x4B000000u, sel)) - (kMagic + 128.f));
+      const float sB = dinvB * (__uint_as_float(__byte_perm(swB, 0x4B000000u, sel)) - (kMagic + 128.f));
+      // sum of (code - 32) x = (256 c_hi + c_lo - 32 sum(x_int)) / S
+      const float xsv = f.xs[2 * n + A];
+      acc0 = fmaf(sA, fmaf(-32.f, xsv, __int2float_rn(256 * c[0] + c[1])), acc0);
+      acc1 = fmaf(sB, fmaf(-32.f, xsv, __int2float_rn(256 * c[2] + c[3])), acc1);
     }
   }
 }
 
-// Four consecutive activations -> fp16 hi / lo in the fragment order [x0, x2, x1, x3]; returns sum of (hi + lo).
-DEVI float split_planes4(float4 v, uint2& hi, uint2& lo, bool& out_of_range) {
-  const float vals[4] = {v.x, v.z, v.y, v.w};
-  __half h[4], l[4];
-  float sum = 0.f;
+// Fixed-point scale of a scale group whose largest magnitude is `top`; `inv` = 1 / S.
+DEVI float group_scale(float top, float& inv) {
+  inv = top * (1.f / kFixedPointRange);
+  return top > 0.f ? kFixedPointRange / top : 0.f;
+}
+DEVI float max4(float4 v) { return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))); }
+DEVI bool finite4(float4 v) { return fabsf(v.x) <= 3.0e38f && fabsf(v.y) <= 3.0e38f && fabsf(v.z) <= 3.0e38f && fabsf(v.w) <= 3.0e38f; }
+// Four consecutive activations times S -> 16-bit fixed point, split into two signed bytes each (value = 256 hi + lo,
+// lo in [-128, 127]); returns the integer sum of the four fixed-point values.
+DEVI int split_bytes4(float4 v, float S, uint32_t& hi, uint32_t& lo) {
+  const float vals[4] = {v.x, v.y, v.z, v.w};
+  int sum = 0;
+  hi = lo = 0u;
 #pragma unroll
   for (int q = 0; q < 4; ++q) {
-    h[q] = __float2half_rn(vals[q]);
-    l[q] = __float2half_rn(vals[q] - __half2float(h[q]));
-    sum += __half2float(h[q]) + __half2float(l[q]);
-    out_of_range |= fabsf(vals[q]) > 65504.f;
+    const int xi = __float2int_rn(vals[q] * S);
+    const int l = ((xi + 128) & 255) - 128;
+    const int h = (xi - l) >> 8;
+    sum += xi;
+    hi |= uint32_t(h & 255) << (8 * q);
+    lo |= uint32_t(l & 255) << (8 * q);
   }
-  hi = make_uint2(h2_as_u32(__halves2half2(h[0], h[1])), h2_as_u32(__halves2half2(h[2], h[3])));
-  lo = make_uint2(h2_as_u32(__halves2half2(l[0], l[1])), h2_as_u32(__halves2half2(l[2], l[3])));
   return sum;
 }
 
+DEVI void sts32(uint32_t a, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(a), "r"(v) : "memory"); }
 DEVI void sts64(uint32_t a, uint2 v) { asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(v.x), "r"(v.y) : "memory"); }
 DEVI void sts32f(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory"); }
 
@@ -513,36 +528,40 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
           *a.sg = v;
         }
       }
-      __syncwarp();
       if (pass == 1 && lane == 0) {
         if (cta == 0) a.gbar[1] = a.gbar[2] = 0u;   // the later barriers' counters as the previous call on this workspace left them
         __threadfence();
         atomicAdd(a.gbar, 1u);               // arrive at grid barrier 1; the producer warps wait for it
       }
     }
-    // ---- activation planes (fragment order) and per-32 sums ----
-    bool bad = false;
+    // ---- the token as 16-bit fixed point per 32 columns: two byte planes, and (float sum, 1 / S) per 32 columns ----
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
       const int i = tid + c * kFusedConsumers * 32;
-      uint2 hi, lo;
-      float sum = split_planes4(nv[c], hi, lo, bad);
+      float top = max4(nv[c]);
+      top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 1));
+      top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 2));
+      top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 4));
+      float inv;
+      const float S = group_scale(top, inv);
+      uint32_t hi, lo;
+      int sum = split_bytes4(nv[c], S, hi, lo);
       sum += __shfl_xor_sync(0xffffffffu, sum, 1);
       sum += __shfl_xor_sync(0xffffffffu, sum, 2);
       sum += __shfl_xor_sync(0xffffffffu, sum, 4);
       if (i < chunks4) {
-        sts64(act + 8 * i, hi);
-        sts64(act + a.act_lo1 + 8 * i, lo);
-        if ((i & 7) == 0) sts32f(act + a.act_xs1 + 4 * (i >> 3), sum);
+        if (!finite4(nv[c])) atomicOr(a.status, kStatusActRange);
+        sts32(act + 4 * i, hi);
+        sts32(act + a.act_lo1 + 4 * i, lo);
+        if ((i & 7) == 0) sts64(act + a.act_xs1 + 8 * (i >> 3), make_uint2(__float_as_uint(inv * __int2float_rn(sum)), __float_as_uint(inv)));
       }
     }
-    if (bad && pass == 1) atomicOr(a.status, kStatusActRange);
     named_barrier(1, kFusedConsumers * 32);
   }
 
   // This lane's B fragments: offset inside a plane pair (bytes) from the first column of a block; which of its two B
   // register sets carries values (neither for half of the lanes)
-  const uint32_t lane_x4 = (dl.plane ? uint32_t(a.act_lo1) : 0u) + 2u * (32u * (2 * ((g >> 1) & 1) + (g >> 2)) + 16u * (j & 1));
+  const uint32_t lane_x4 = (dl.plane ? uint32_t(a.act_lo1) : 0u) + 32u * (2 * ((g >> 1) & 1) + (g >> 2)) + 16u * (j & 1);
   const bool first = dl.active && !dl.second, second = dl.active && dl.second;
   const int sbl = 2 * (j & 1) + (j >> 1), sl = 4 * (j >> 1) + (j & 1);     // this lane's scale group inside a tile (Q4_K / Q6_K)
   BlockFrags fr;
@@ -614,7 +633,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
       const uint32_t gate_rows = ring + (cg % NS) * a.stage_bytes + g * a.row_bytes1;    // row g of the tile's gate rows
       const uint32_t up_rows = ring + (cu % NS) * a.stage_bytes + g * a.row_bytes1;
       for (int b = kq; b < a.nblk1; b += kFusedQuad) {
-        q4k_load_frags(fr, act + lane_x4 + 512u * b, first, second, act + a.act_xs1 + 32u * b, sbl);
+        q4k_load_frags(fr, act + lane_x4 + 256u * b, first, second, act + a.act_xs1 + 64u * b, sbl);
 #pragma unroll
         for (int p = 0; p < kFusedPasses; ++p)       // eight rows of the tile per pass: gate row in MMA row g, up row in MMA row g + 8
           q4k_rows(gate_rows + 8 * p * a.row_bytes1 + b * 144, up_rows + 8 * p * a.row_bytes1 + b * 144, j, fr, acc[p][0], acc[p][1]);
@@ -625,15 +644,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
     if (kq == 0) {
       // lane l: pass l / 16; lanes 0-7 of a pass hold its gate rows, lanes 8-15 its up rows
       const float up = __shfl_down_sync(0xffffffffu, rows, 8);
+      float h = 0.f;
       if (lane < 16 * kFusedPasses && (lane & 15) < 8) {
-        const float h = silu_mul(rows, up);
-        const __half hi = __float2half_rn(h);
-        const __half lo = __float2half_rn(h - __half2float(hi));
-        if (fabsf(h) > 65504.f) atomicOr(a.status, kStatusActRange);
-        __half* dst = a.hbuf + size_t(gi) * 2 * a.F + tile * (8 * kFusedPasses) + 8 * (lane >> 4) + (lane & 7);
-        dst[0] = hi;
-        dst[a.F] = lo;
+        h = silu_mul(rows, up);
+        a.hbuf[size_t(gi) * a.F + tile * (8 * kFusedPasses) + 8 * (lane >> 4) + (lane & 7)] = h;
       }
+      if (!(fabsf(h) <= 3.0e38f)) atomicOr(a.status, kStatusActRange);
     }
     // The chunks are handed back only now: the warp that sums a tile keeps the producer from running kFusedSlots tiles
     // ahead, so a slot of partial sums is never reused while it is being read.
@@ -655,20 +671,20 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   }
   named_barrier(1, kFusedConsumers * 32);
   if (!*go_flag) return;                        // one thread decided: every consumer warp leaves or none
-  // ---- the K + 1 product vectors -> planes in fragment order, sums per 16 (Q6_K) or 32 (Q4_K) columns ----
+  // ---- the K + 1 product vectors -> 16-bit fixed point per scale group of the down format: byte planes, and per 16
+  //      (Q6_K: integer sum) or 32 (Q4_K: float sum) columns the pair (sum, 1 / S) ----
   {
     const int per = a.F / 4, all = a.G * per;
     constexpr int BATCH = 3;                                              // loads of three rounds in flight together
     for (int base = 0; base < all; base += BATCH * kFusedConsumers * 32) {  // uniform trip count: shuffles below
-      uint2 hi[BATCH], lo[BATCH];
+      float4 hv[BATCH];
 #pragma unroll
       for (int u = 0; u < BATCH; ++u) {
         const int idx = base + u * kFusedConsumers * 32 + tid;
-        hi[u] = lo[u] = make_uint2(0u, 0u);
+        hv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (idx < all) {
           const int gi = idx / per, i = idx - gi * per;
-          hi[u] = __ldcg(reinterpret_cast<const uint2*>(a.hbuf + size_t(gi) * 2 * a.F) + i);
-          lo[u] = __ldcg(reinterpret_cast<const uint2*>(a.hbuf + size_t(gi) * 2 * a.F + a.F) + i);
+          hv[u] = __ldcg(reinterpret_cast<const float4*>(a.hbuf + size_t(gi) * a.F) + i);
         }
       }
 #pragma unroll
@@ -676,23 +692,25 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
         const int idx = base + u * kFusedConsumers * 32 + tid;
         const bool live = idx < all;
         const int gi = live ? idx / per : 0, i = live ? idx - gi * per : 0;
-        const float2 h01 = __half22float2(u32_as_h2(hi[u].x)), h23 = __half22float2(u32_as_h2(hi[u].y));
-        const float2 l01 = __half22float2(u32_as_h2(lo[u].x)), l23 = __half22float2(u32_as_h2(lo[u].y));
-        float sum = ((h01.x + l01.x) + (h01.y + l01.y)) + ((h23.x + l23.x) + (h23.y + l23.y));
+        float top = max4(hv[u]);
+        top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 1));
+        top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 2));
+        if (!DOWN_Q6) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 4));
+        float inv;
+        const float S = group_scale(top, inv);
+        uint32_t hi, lo;
+        int sum = split_bytes4(hv[u], S, hi, lo);
         sum += __shfl_xor_sync(0xffffffffu, sum, 1);
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         if (!DOWN_Q6) sum += __shfl_xor_sync(0xffffffffu, sum, 4);
         if (live) {
-          // [h0,h1,h2,h3] -> [h0,h2,h1,h3]
-          const uint2 ph = make_uint2(__byte_perm(hi[u].x, hi[u].y, 0x5410), __byte_perm(hi[u].x, hi[u].y, 0x7632));
-          const uint2 pq = make_uint2(__byte_perm(lo[u].x, lo[u].y, 0x5410), __byte_perm(lo[u].x, lo[u].y, 0x7632));
           const uint32_t gb = act + gi * a.act_grp2;
-          sts64(gb + 8 * i, ph);
-          sts64(gb + a.act_lo2 + 8 * i, pq);
+          sts32(gb + 4 * i, hi);
+          sts32(gb + a.act_lo2 + 4 * i, lo);
           if (DOWN_Q6) {
-            if ((i & 3) == 0) sts32f(act + a.act_xs2 + 4 * (gi * (a.F / 16) + (i >> 2)), sum);
+            if ((i & 3) == 0) sts64(act + a.act_xs2 + 8 * (gi * (a.F / 16) + (i >> 2)), make_uint2(__float_as_uint(__int2float_rn(sum)), __float_as_uint(inv)));
           } else {
-            if ((i & 7) == 0) sts32f(act + a.act_xs2 + 4 * (gi * (a.F / 32) + (i >> 3)), sum);
+            if ((i & 7) == 0) sts64(act + a.act_xs2 + 8 * (gi * (a.F / 32) + (i >> 3)), make_uint2(__float_as_uint(inv * __int2float_rn(sum)), __float_as_uint(inv)));
           }
         }
       }
@@ -701,8 +719,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   named_barrier(1, kFusedConsumers * 32);
 
   // ---- phase 2: down tiles ----
-  const uint32_t lane_x6 = (dl.plane ? uint32_t(a.act_lo2) : 0u) + 2u * (64u * (g >> 2) + 16u * ((g >> 1) & 1) + 8u * (j & 1));
-  const uint32_t lane_x4d = (dl.plane ? uint32_t(a.act_lo2) : 0u) + 2u * (32u * (2 * ((g >> 1) & 1) + (g >> 2)) + 16u * (j & 1));
+  const uint32_t lane_x6 = (dl.plane ? uint32_t(a.act_lo2) : 0u) + 64u * (g >> 2) + 16u * ((g >> 1) & 1) + 8u * (j & 1);
+  const uint32_t lane_x4d = (dl.plane ? uint32_t(a.act_lo2) : 0u) + 32u * (2 * ((g >> 1) & 1) + (g >> 2)) + 16u * (j & 1);
   for (int t2 = quad; t2 < n2; t2 += kFusedConsumers / kFusedQuad) {
     const int c = 2 * n1 + t2, stage = c % NS;
     if (!wait_chunk(c)) { ok = false; break; }
@@ -713,7 +731,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
       const uint32_t xreal = act + gi * a.act_grp2 + (DOWN_Q6 ? lane_x6 : lane_x4d);
       for (int b = kq; b < a.nblk2; b += kFusedQuad) {
         if (DOWN_Q6) {
-          q6k_load_frags(fr, xreal + 512u * b, first, second, act + a.act_xs2 + 4u * (gi * (a.F / 16)) + 64u * b, sl);
+          q6k_load_frags(fr, xreal + 256u * b, first, second, act + a.act_xs2 + 8u * (gi * (a.F / 16)) + 128u * b, sl);
 #pragma unroll
           for (int p = 0; p < kFusedPasses; ++p) {     // sixteen rows of the tile per pass
             const uint32_t rA = rowg + 16 * p * a.row_bytes2, rB = rA + 8 * a.row_bytes2;
@@ -723,7 +741,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
             q6k_rows(rA + b * 208, rB + b * 208, j, dA, dB, fr, acc[p][0], acc[p][1]);
           }
         } else {
-          q4k_load_frags(fr, xreal + 512u * b, first, second, act + a.act_xs2 + 4u * (gi * (a.F / 32)) + 32u * b, sbl);
+          q4k_load_frags(fr, xreal + 256u * b, first, second, act + a.act_xs2 + 8u * (gi * (a.F / 32)) + 64u * b, sbl);
 #pragma unroll
           for (int p = 0; p < kFusedPasses; ++p) {
             const uint32_t rA = rowg + 16 * p * a.row_bytes2, rB = rA + 8 * a.row_bytes2;

@@ -65,7 +65,7 @@ static KogarashiWs carve(void* base, int hidden, int inter, int experts, int top
   w.done = reinterpret_cast<unsigned*>(take(4));
   w.status = reinterpret_cast<unsigned*>(take(4));
   w.gbar = reinterpret_cast<unsigned*>(take(16));                                   // three grid barrier counters
-  w.tile_cnt = reinterpret_cast<unsigned*>(take(size_t(kFusedMaxRowTiles) * 4));    // ends at byte 3072: inside the zeroed head
+  w.tile_cnt = reinterpret_cast<unsigned*>(take(size_t(kFusedMaxRowTiles) * 4));    // per-group maxima of the one-token kernel; ends at byte 3072: inside the zeroed head
   w.active = reinterpret_cast<int*>(take(size_t(experts) * 4));
   w.ranges = reinterpret_cast<unsigned*>(take(size_t(experts) * 8));
   w.assignments = reinterpret_cast<unsigned*>(take(size_t(tokens) * topk * 4));
@@ -120,14 +120,16 @@ static bool fused_plan(const KogarashiMoe* d, const KogarashiWs& w, FusedArgs* f
   a.off_bars = 640;
   a.off_psum = (a.off_bars + (2 * kFusedMaxStages + 1 + 4) * 8 + 127) / 128 * 128;
   a.off_act = (a.off_psum + kFusedSlots * kFusedQuad * 16 * kFusedPasses * 4 + 127) / 128 * 128;
-  a.act_lo1 = H * 2 + 64;
-  a.act_xs1 = 2 * a.act_lo1;
-  a.act_rows = (a.act_xs1 + H / 32 * 4 + 127) / 128 * 128;
+  // phase R / 1: the token's two byte planes (the second 32 bytes off the bank phase of the first), (sum, 1 / S) per 32
+  // columns, the router rows; phase 2: per expert group two byte planes, then all (sum, 1 / S) pairs
+  a.act_lo1 = H + 32;
+  a.act_xs1 = (2 * a.act_lo1 + 15) / 16 * 16;
+  a.act_rows = (a.act_xs1 + H / 32 * 8 + 127) / 128 * 128;
   const int act1 = a.act_rows + 2 * H * 4;
-  a.act_lo2 = F * 2 + 64;
-  a.act_grp2 = 2 * a.act_lo2;
+  a.act_lo2 = F + 32;
+  a.act_grp2 = (2 * a.act_lo2 + 15) / 16 * 16;
   a.act_xs2 = a.G * a.act_grp2;
-  const int act2 = a.act_xs2 + a.G * (F / 16) * 4;
+  const int act2 = a.act_xs2 + a.G * (F / 16) * 8;
   a.off_ring = (a.off_act + (act1 > act2 ? act1 : act2) + 127) / 128 * 128;
   a.nstage = (kSmemBudget - a.off_ring) / a.stage_bytes;
   if (a.nstage > kFusedMaxStages) a.nstage = kFusedMaxStages;
@@ -137,7 +139,7 @@ static bool fused_plan(const KogarashiMoe* d, const KogarashiWs& w, FusedArgs* f
   a.gate_w = static_cast<const uint8_t*>(d->gate_w); a.up_w = static_cast<const uint8_t*>(d->up_w); a.down_w = static_cast<const uint8_t*>(d->down_w);
   a.sh_gate = static_cast<const uint8_t*>(d->sh_gate_w); a.sh_up = static_cast<const uint8_t*>(d->sh_up_w); a.sh_down = static_cast<const uint8_t*>(d->sh_down_w);
   a.n = d->n; a.x = d->x; a.logits = d->logits; a.ids = d->ids; a.prob = d->prob;
-  a.gbar = w.gbar; a.status = w.status; a.hbuf = w.hplanes; a.y = w.y; a.sg = w.sg;
+  a.gbar = w.gbar; a.status = w.status; a.hbuf = reinterpret_cast<float*>(w.hplanes); a.y = w.y; a.sg = w.sg;
   *f = a;
   return true;
 }
