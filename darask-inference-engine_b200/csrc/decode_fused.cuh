@@ -1,15 +1,24 @@
-// One-token Kogarashi MoE FFN layer as ONE persistent launch (one CTA per SM).
+// One-token Kogarashi MoE FFN layer as ONE persistent launch (one CTA per SM), without grid-wide barriers.
 //
-//   phase R   every CTA projects its one or two router rows (fetched before the dependency wait), writes the logits,
-//             arrives at grid barrier 1; the producer warp of every CTA then selects the top-k itself (same result
+//   phase R   every CTA projects its one or two router rows (fetched before the dependency wait) and publishes the
+//             logits; a producer warp of every CTA collects all logits and selects the top-k itself (same result
 //             everywhere), so no CTA waits for a routing block and no plan travels through global memory
-//   phase 1   gate/up tiles (8 gate rows + the 8 matching up rows), SwiGLU product written as fp16 hi/lo
-//   barrier 2 all products visible; every CTA stages the K+1 product vectors in shared memory
-//   phase 2   down tiles (16 rows of one expert) as float32 rows
-//   barrier 3 all rows visible; every CTA adds the weighted experts (slot order) and the gated shared expert into its
-//             share of the residual stream
+//   phase 1   gate/up tiles (8 gate rows + the 8 matching up rows of one expert), SwiGLU products published as float32
+//   phase 2   down tiles (16 rows of one expert), expert-major: a quad of warps stages the product vector of the
+//             tile's expert (16-bit fixed point) and publishes the tile's rows as float32
+//   combine   every CTA adds the weighted experts (slot order) and the gated shared expert into its share of the
+//             residual stream
 //
-// The weight stream does not stop at the barriers: producer threads issue ONE `cp.async.bulk` copy per chunk of
+// What one CTA publishes for the others (logits, products, down rows) travels as 8-byte words {float, tag}, written
+// with one 64-bit store each and read by polling (the scheme of low-latency collectives): the tag is derived from a
+// call counter kept in the workspace, which every CTA reads at the start and CTA 0 advances at the end, so a word is
+// valid exactly when its tag is this call's. A consumer therefore waits only for the values it needs: the experts'
+// products become complete one after the other during phase 1 and the down tiles take the experts in the same
+// order, so only the last tiles of a CTA can meet a product that is still being computed, and the weight stream runs
+// through from the first gate row to the last down row. (Grid-wide barriers cost three L2 round trips each, about
+// 2 us, three times per layer.)
+//
+// Producer threads issue ONE `cp.async.bulk` copy per chunk of
 // whole, consecutive weight rows (8 gate rows, the 8 matching up rows, or 16 down rows: about 14 KB at the benchmark
 // shape, contiguous in global memory; the copies of one thread are carried out one after the other at about half a
 // microsecond each whatever their size, so two issuing threads are needed to keep HBM busy with chunks of this size)
@@ -58,14 +67,15 @@ struct FusedArgs {
   const uint8_t* gate_w; const uint8_t* up_w; const uint8_t* down_w;
   const uint8_t* sh_gate; const uint8_t* sh_up; const uint8_t* sh_down;
   const float* n; float* x; float* logits; int* ids; float* prob;
-  int H, F, E, K, G, has_shared;
+  int H, F, E, K, G, has_shared, ldlog;
   int nblk1, row_bytes1, tps;                     // gate/up: 256-column blocks per row, bytes per row, tiles per group
   int nblk2, row_bytes2, rt2, down_q6;            // down: the same, row tiles of the output
   int stage_bytes, nstage;                        // chunk slot size and number of slots of the ring
-  int off_bars, off_psum, off_act, off_ring;             // shared-memory offsets
+  int off_bars, off_psum, off_log, off_act, off_ring;    // shared-memory offsets
   int act_lo1, act_xs1, act_rows;                 // phase R/1 inside the activation area: lo-plane offset, (sum, 1/S) pairs, router rows
-  int act_lo2, act_grp2, act_xs2;                 // phase 2: lo-plane offset, bytes per expert group, offset of the (sum, 1/S) pairs
-  unsigned* gbar; unsigned* status; float* hbuf; float* y; float* sg;
+  int act_q, act_qs, act_lo2, act_xs2;            // phase 2: first quad area, bytes per quad area; inside its planes: lo-plane offset, (sum, 1/S) pairs
+  unsigned* status; unsigned* epoch; unsigned* seen;    // call counter of the workspace; CTAs of this call that have read it
+  unsigned long long* tlog; unsigned long long* th; unsigned long long* ty;   // tagged: logits [CTA][ldlog], products [G][F], down rows [G][H]
 };
 
 // ---- small pieces -----------------------------------------------------------------------------------------
@@ -74,35 +84,93 @@ DEVI unsigned ld_acquire_u32(const unsigned* p) {
   asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
-// One thread per CTA: arrive and wait until `target` CTAs have arrived. Bounded; false after the time limit.
-DEVI bool grid_arrive_wait(unsigned* counter, unsigned target, unsigned* status, volatile int* abort_flag) {
-  __threadfence();
-  atomicAdd(counter, 1u);
-  const uint64_t start = global_timer_ns();
-  for (uint32_t spin = 1;; ++spin) {
-    if (ld_acquire_u32(counter) >= target) return true;
-    if ((spin & 31u) == 0) {
-      if (*abort_flag) return false;
-      if (global_timer_ns() - start > kWaitLimitNs) {
-        atomicOr(status, kStatusWaitTimeout);
-        *abort_flag = 1;
-        return false;
-      }
+// ---- tagged words: {float value, 32-bit tag} in one 64-bit store --------------------------------------------------
+DEVI unsigned make_tag(unsigned epoch) { return 0x80000001u + epoch % 0x7FFFFFFEu; }     // never 0, never the bits of -0.0f
+DEVI void st_tagged(unsigned long long* p, float v, unsigned tag) {
+  const unsigned long long w = (static_cast<unsigned long long>(tag) << 32) | __float_as_uint(v);
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+DEVI unsigned long long ld_tagged(const unsigned long long* p) {
+  unsigned long long w;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+  return w;
+}
+DEVI uint4 ld_tagged2(const unsigned long long* p) {          // two words: (value, tag, value, tag)
+  unsigned long long w0, w1;
+  asm volatile("ld.relaxed.gpu.global.v2.u64 {%0,%1}, [%2];" : "=l"(w0), "=l"(w1) : "l"(p) : "memory");
+  return make_uint4(unsigned(w0), unsigned(w0 >> 32), unsigned(w1), unsigned(w1 >> 32));
+}
+// One poll site gives up after the time limit or when another role of the CTA has: status bit, abort flag, false.
+struct PollClock {
+  uint64_t start;
+  uint32_t spin;
+  DEVI PollClock() : start(0), spin(0) {}
+  DEVI bool expired(unsigned* status, volatile int* abort_flag) {
+    if ((++spin & 15u) != 0) return false;
+    if (*abort_flag) return true;
+    const uint64_t now = global_timer_ns();
+    if (start == 0) start = now;
+    else if (now - start > kWaitLimitNs) {
+      atomicOr(status, kStatusWaitTimeout);
+      *abort_flag = 1;
+      return true;
     }
+    __nanosleep(64);
+    return false;
+  }
+};
+// A warp collects entries lane, lane + 32, ... (< n <= 320) of a tagged array into `dst`. Uniform result.
+DEVI bool gather_tagged(const unsigned long long* src, int n, unsigned tag, float* dst, int lane, unsigned* status, volatile int* abort_flag) {
+  constexpr int MAXQ = 10;
+  unsigned pend = 0;
+#pragma unroll
+  for (int q = 0; q < MAXQ; ++q)
+    if (lane + 32 * q < n) pend |= 1u << q;
+  PollClock clk;
+  for (;;) {
+    unsigned long long w[MAXQ];
+#pragma unroll
+    for (int q = 0; q < MAXQ; ++q)                    // all loads first: they are in flight together
+      if (pend >> q & 1) w[q] = ld_tagged(src + lane + 32 * q);
+#pragma unroll
+    for (int q = 0; q < MAXQ; ++q)
+      if ((pend >> q & 1) && unsigned(w[q] >> 32) == tag) {
+        dst[lane + 32 * q] = __uint_as_float(unsigned(w[q]));
+        pend &= ~(1u << q);
+      }
+    if (!__any_sync(0xffffffffu, pend != 0)) return true;
+    int quit = (lane == 0 && clk.expired(status, abort_flag)) ? 1 : 0;
+    quit = __shfl_sync(0xffffffffu, quit, 0);
+    if (quit) return false;
   }
 }
-DEVI bool grid_wait(const unsigned* counter, unsigned target, unsigned* status, volatile int* abort_flag) {
-  const uint64_t start = global_timer_ns();
-  for (uint32_t spin = 1;; ++spin) {
-    if (ld_acquire_u32(counter) >= target) return true;
-    if ((spin & 31u) == 0) {
-      if (*abort_flag) return false;
-      if (global_timer_ns() - start > kWaitLimitNs) {
-        atomicOr(status, kStatusWaitTimeout);
-        *abort_flag = 1;
-        return false;
+// One thread: up to eight entries base[q * stride], q < n, all in flight together.
+DEVI bool poll_strided(const unsigned long long* base, size_t stride, int n, unsigned tag, float (&out)[8], unsigned* status, volatile int* abort_flag) {
+  unsigned pend = (1u << n) - 1u;
+  PollClock clk;
+  for (;;) {
+    unsigned long long w[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      if (pend >> q & 1) w[q] = ld_tagged(base + q * stride);
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      if ((pend >> q & 1) && unsigned(w[q] >> 32) == tag) {
+        out[q] = __uint_as_float(unsigned(w[q]));
+        pend &= ~(1u << q);
       }
-    }
+    if (!pend) return true;
+    if (clk.expired(status, abort_flag)) return false;
+  }
+}
+// One thread: four consecutive entries as (v, t, v, t) x 2.
+DEVI bool poll_four(const unsigned long long* p, unsigned tag, uint4& r0, uint4& r1, unsigned* status, volatile int* abort_flag) {
+  PollClock clk;
+  for (;;) {
+    r0 = ld_tagged2(p);
+    r1 = ld_tagged2(p + 2);
+    if (r0.y == tag && r0.w == tag && r1.y == tag && r1.w == tag) return true;
+    if (clk.expired(status, abort_flag)) return false;
   }
 }
 // mbarrier wait that also leaves when another role gave up
@@ -344,7 +412,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   float* sm_prob = reinterpret_cast<float*>(smem + 128);             // [32]
   float* sm_misc = reinterpret_cast<float*>(smem + 256);             // [0] sigmoid of the shared gate logit
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 272);
-  volatile int* go_flag = reinterpret_cast<volatile int*>(smem + 276);
   float* part = reinterpret_cast<float*>(smem + 448);                // [16][2] router partial sums
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + a.off_bars);   // [nstage]
   uint64_t* empty = full + a.nstage;                                 // [nstage]
@@ -352,6 +419,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   uint64_t* qbar = routed + 1;                                       // [4] one per quad: partial sums of a tile written
   volatile int* fill_id = reinterpret_cast<volatile int*>(smem + 576);   // [nstage] how many times a slot has been filled (requests issued)
   float* psum = reinterpret_cast<float*>(smem + a.off_psum);         // [slot][warp of the quad][16]
+  float* sm_log = reinterpret_cast<float*>(smem + a.off_log);        // [E + 1] the logits as collected by the selecting warp
   const uint32_t act = smem_u32(smem + a.off_act);
   const uint32_t ring = smem_u32(smem + a.off_ring);
   const int NS = a.nstage;
@@ -371,8 +439,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
 
   // ---- the work lists of this CTA (same arithmetic in producer and consumers) ----
   // gate/up tiles sigma = cta, cta + grid, ... of G * tps (group-major, shared expert first; a tile = 16 rows of the gate
-  // matrix and the same 16 rows of the up matrix); down tiles likewise of rt2 * G (row-tile-major; 32 rows). Chunks of
-  // the ring, in order: (gate rows, up rows) per gate/up tile, then one per down tile.
+  // matrix and the same 16 rows of the up matrix); down tiles likewise of G * rt2 (also group-major: the products of
+  // the groups become complete in this order). Chunks of the ring, in order: (gate rows, up rows) per gate/up tile,
+  // then one per down tile.
   const int tiles1 = a.G * a.tps;
   const int n1 = cta < tiles1 ? (tiles1 - cta + grid - 1) / grid : 0;
   const int tiles2 = a.rt2 * a.G;
@@ -400,7 +469,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
         src = base + size_t(tile) * (8 * kFusedPasses) * a.row_bytes1;
         bytes = uint32_t(8 * kFusedPasses) * a.row_bytes1;
       } else {
-        const int u2 = cta + (c - 2 * n1) * grid, gi = u2 % a.G, rt = u2 / a.G;
+        const int u2 = cta + (c - 2 * n1) * grid, gi = u2 / a.rt2, rt = u2 - gi * a.rt2;
         const uint8_t* base = (a.has_shared && gi == 0) ? a.sh_down : a.down_w + size_t(sm_ids[gi - a.has_shared]) * a.H * a.row_bytes2;
         src = base + size_t(rt) * (16 * kFusedPasses) * a.row_bytes2;
         bytes = uint32_t(16 * kFusedPasses) * a.row_bytes2;
@@ -429,13 +498,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
         __syncwarp();
       }
       pdl_wait();
-      // grid barrier 1: every router row has been written
-      if (ok && lane == 0) ok = grid_wait(a.gbar, unsigned(grid), a.status, abort_flag) ? 1 : 0;
+      const unsigned tag = make_tag(__ldcg(a.epoch));
       ok = __shfl_sync(0xffffffffu, ok, 0);
+      // every router row of this call, as the CTAs publish them
+      if (ok) ok = gather_tagged(a.tlog + size_t(cta) * a.ldlog, R, tag, sm_log, lane, a.status, abort_flag) ? 1 : 0;
+      __syncwarp();
       if (ok) {
-        RouteArgs r{a.logits, a.E, a.E, a.K, 1, nullptr, 1.f, nullptr, nullptr, nullptr};
+        RouteArgs r{sm_log, a.E, a.E, a.K, 1, nullptr, 1.f, nullptr, nullptr, nullptr};
         route_token_to<kRouteKogarashi>(r, 0, lane, sm_ids, sm_prob);
-        if (lane == 0 && a.has_shared) sm_misc[0] = sigmoid_precise(__ldcg(a.sg));
+        if (lane == 0 && a.has_shared) sm_misc[0] = sigmoid_precise(sm_log[a.E]);
         __syncwarp();
         if (cta == 0 && lane < a.K) {
           a.ids[lane] = sm_ids[lane];
@@ -477,9 +548,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   }
   cp_async_commit();
   constexpr int MAXC = 4;                                            // hidden <= 8192
+  unsigned epoch_now, tag;
   {
-    constexpr int pass = 1;
     pdl_wait();
+    epoch_now = __ldcg(a.epoch);
+    tag = make_tag(epoch_now);
+    if (tid == 0) atomicAdd(a.seen, 1u);            // CTA 0 advances the counter only when every CTA has read it
     const float* nsrc = a.n;
     // the token's activations: this thread's chunks stay in registers for the planes below
     float4 nv[MAXC];
@@ -520,18 +594,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
       v += __shfl_xor_sync(0xffffffffu, v, 2);
       v += __shfl_xor_sync(0xffffffffu, v, 1);
       const int q = lane >> 4, row = cta + q * grid;
-      if (pass == 1 && (lane & 15) == 0 && q < my_rows) {
-        if (row < a.E) {
-          if (a.router_bias) v += a.router_bias[row];
-          a.logits[row] = v;
-        } else {
-          *a.sg = v;
-        }
+      if ((lane & 15) == 0 && q < my_rows && row < a.E) {
+        if (a.router_bias) v += a.router_bias[row];
+        a.logits[row] = v;
       }
-      if (pass == 1 && lane == 0) {
-        if (cta == 0) a.gbar[1] = a.gbar[2] = 0u;   // the later barriers' counters as the previous call on this workspace left them
-        __threadfence();
-        atomicAdd(a.gbar, 1u);               // arrive at grid barrier 1; the producer warps wait for it
+      // one copy of the logits per CTA, each polled by its owner only (148 CTAs polling the same lines would queue
+      // up at those lines' L2 slices); row E: the shared expert's gate logit
+      const float v0 = __shfl_sync(0xffffffffu, v, 0), v1 = __shfl_sync(0xffffffffu, v, 16);
+      for (int d = lane; d < grid; d += 32) {
+        unsigned long long* copy = a.tlog + size_t(d) * a.ldlog;
+        if (my_rows > 0) st_tagged(copy + cta, v0, tag);
+        if (my_rows > 1) st_tagged(copy + cta + grid, v1, tag);
       }
     }
     // ---- the token as 16-bit fixed point per 32 columns: two byte planes, and (float sum, 1 / S) per 32 columns ----
@@ -573,6 +646,15 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   // epilogue while the other three go on to their next tile. `slot`: partial-sum slot of the tile (tiles of one quad that may be pending
   // at the same time have different slots). Returns false when the wait was given up.
   int quad_syncs = 0;
+  // The four warps of a quad meet (arrive = release, wait = acquire: what they wrote to shared memory before is visible
+  // after). Every warp waits: a warp that ran ahead would arrive for the next meeting inside this one's phase. The wait
+  // can be given up, unlike a `bar.sync`: false then.
+  auto quad_sync = [&]() -> bool {
+    __syncwarp();
+    if (lane == 0) mbar_arrive(qbar + quad);
+    const int parity = quad_syncs++ & 1;
+    return mbar_wait_abortable(qbar + quad, parity, a.status, abort_flag);
+  };
   auto quad_reduce = [&](int slot, float (&acc)[kFusedPasses][2], float& row_sum) -> bool {
     float* ps = psum + (slot * kFusedQuad + kq) * (16 * kFusedPasses);
 #pragma unroll
@@ -583,11 +665,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
         ps[p * 16 + 8 + g] = r1;
       }
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(qbar + quad);
-    const int parity = quad_syncs++ & 1;
-    // every warp waits (a warp that ran ahead would arrive for the next tile inside this tile's phase)
-    if (!mbar_wait_abortable(qbar + quad, parity, a.status, abort_flag)) return false;
+    if (!quad_sync()) return false;
     if (kq != 0) return true;
     row_sum = 0.f;
     if (lane < 16 * kFusedPasses) {
@@ -618,6 +696,59 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
     return mbar_wait_abortable(full + stage, use & 1, a.status, abort_flag);
   };
 
+  // ---- the product vector of one expert group for this quad's down tiles ----
+  // Raw tagged words are copied asynchronously (every thread copies, and later reads, its own 32 bytes: four values)
+  // into the quad's area ahead of time; staging checks the tags (a word that was not there yet is polled from global
+  // memory), converts to fixed point per scale group of the down format: byte planes, and per 16 (Q6_K: integer sum) or
+  // 32 (Q4_K: float sum) columns the pair (sum, 1 / S); then the quad meets. False when a wait was given up.
+  const int qt = tid & (32 * kFusedQuad - 1);
+  const uint32_t qraw = act + a.act_q + quad * a.act_qs, qpl = qraw + 8u * a.F, qxs = qpl + a.act_xs2;
+  int pre = -1;                                                          // group whose raw words are on their way
+  auto prefetch_group = [&](int gi) {
+    const unsigned long long* src = a.th + size_t(gi) * a.F;
+    for (int i = qt; i < a.F / 4; i += 32 * kFusedQuad) {
+      cp_async16(qraw + 32u * i, src + 4 * i);
+      cp_async16(qraw + 32u * i + 16u, src + 4 * i + 2);
+    }
+    cp_async_commit();
+  };
+  auto stage_group = [&](int gi) -> bool {
+    cp_async_wait<0>();
+    for (int base = 0; base < a.F / 4; base += 32 * kFusedQuad) {        // uniform trip count: shuffles below
+      const int i = base + qt;
+      const bool live = i < a.F / 4;
+      float4 hv = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (live) {
+        uint4 r0 = lds128(qraw + 32u * i), r1 = lds128(qraw + 32u * i + 16u);
+        bool have = r0.y == tag && r0.w == tag && r1.y == tag && r1.w == tag;
+        if (!have) have = poll_four(a.th + size_t(gi) * a.F + 4 * i, tag, r0, r1, a.status, abort_flag);
+        if (have) hv = make_float4(__uint_as_float(r0.x), __uint_as_float(r0.z), __uint_as_float(r1.x), __uint_as_float(r1.z));
+      }
+      __syncwarp();
+      float top = max4(hv);
+      top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 1));
+      top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 2));
+      if (!DOWN_Q6) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 4));
+      float inv;
+      const float S = group_scale(top, inv);
+      uint32_t hi, lo;
+      int sum = split_bytes4(hv, S, hi, lo);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if (!DOWN_Q6) sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      if (live) {
+        sts32(qpl + 4 * i, hi);
+        sts32(qpl + a.act_lo2 + 4 * i, lo);
+        if (DOWN_Q6) {
+          if ((i & 3) == 0) sts64(qxs + 8 * (i >> 2), make_uint2(__float_as_uint(__int2float_rn(sum)), __float_as_uint(inv)));
+        } else {
+          if ((i & 7) == 0) sts64(qxs + 8 * (i >> 3), make_uint2(__float_as_uint(inv * __int2float_rn(sum)), __float_as_uint(inv)));
+        }
+      }
+    }
+    return quad_sync() && !*abort_flag;
+  };
+
   // The tiles start only when the selection is done, the shared expert's (whose weights are already here) included:
   // a consumer warp that multiplies while the producer warp selects slows the selection down several times (they
   // share a scheduler), and the selection, not the shared expert, is on the critical path.
@@ -626,6 +757,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   // ---- phase 1: gate/up tiles ----
   for (int lt = quad; lt < n1 && ok; lt += kFusedConsumers / kFusedQuad) {
     const int cg = 2 * lt, cu = cg + 1;
+    if (lt + kFusedConsumers / kFusedQuad >= n1 && quad < n2) {       // the quad's last gate/up tile: its first down tile's products
+      pre = (cta + quad * grid) / a.rt2;
+      prefetch_group(pre);
+    }
     if (!wait_chunk(cg) || !wait_chunk(cu)) { ok = false; break; }
     const int sigma = cta + lt * grid, gi = sigma / a.tps, tile = sigma - gi * a.tps;
     float acc[kFusedPasses][2] = {};
@@ -647,7 +782,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
       float h = 0.f;
       if (lane < 16 * kFusedPasses && (lane & 15) < 8) {
         h = silu_mul(rows, up);
-        a.hbuf[size_t(gi) * a.F + tile * (8 * kFusedPasses) + 8 * (lane >> 4) + (lane & 7)] = h;
+        st_tagged(a.th + size_t(gi) * a.F + tile * (8 * kFusedPasses) + 8 * (lane >> 4) + (lane & 7), h, tag);
       }
       if (!(fabsf(h) <= 3.0e38f)) atomicOr(a.status, kStatusActRange);
     }
@@ -660,78 +795,34 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
     }
   }
 
-  // ---- grid barrier 2: every product is in global memory ----
-  if (!ok) *abort_flag = 1;
-  named_barrier(1, kFusedConsumers * 32);
-  if (tid == 0) {
-    bool good = !*abort_flag && mbar_wait_abortable(routed, 0, a.status, abort_flag);    // the producer has passed barrier 1
-    if (good) good = grid_arrive_wait(a.gbar + 1, unsigned(grid), a.status, abort_flag);
-    if (good && cta == 0) a.gbar[0] = 0u;       // every CTA has passed barrier 1: its counter is free for the next call
-    *go_flag = good ? 1 : 0;
-  }
-  named_barrier(1, kFusedConsumers * 32);
-  if (!*go_flag) return;                        // one thread decided: every consumer warp leaves or none
-  // ---- the K + 1 product vectors -> 16-bit fixed point per scale group of the down format: byte planes, and per 16
-  //      (Q6_K: integer sum) or 32 (Q4_K: float sum) columns the pair (sum, 1 / S) ----
-  {
-    const int per = a.F / 4, all = a.G * per;
-    constexpr int BATCH = 3;                                              // loads of three rounds in flight together
-    for (int base = 0; base < all; base += BATCH * kFusedConsumers * 32) {  // uniform trip count: shuffles below
-      float4 hv[BATCH];
-#pragma unroll
-      for (int u = 0; u < BATCH; ++u) {
-        const int idx = base + u * kFusedConsumers * 32 + tid;
-        hv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (idx < all) {
-          const int gi = idx / per, i = idx - gi * per;
-          hv[u] = __ldcg(reinterpret_cast<const float4*>(a.hbuf + size_t(gi) * a.F) + i);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < BATCH; ++u) {
-        const int idx = base + u * kFusedConsumers * 32 + tid;
-        const bool live = idx < all;
-        const int gi = live ? idx / per : 0, i = live ? idx - gi * per : 0;
-        float top = max4(hv[u]);
-        top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 1));
-        top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 2));
-        if (!DOWN_Q6) top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 4));
-        float inv;
-        const float S = group_scale(top, inv);
-        uint32_t hi, lo;
-        int sum = split_bytes4(hv[u], S, hi, lo);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        if (!DOWN_Q6) sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-        if (live) {
-          const uint32_t gb = act + gi * a.act_grp2;
-          sts32(gb + 4 * i, hi);
-          sts32(gb + a.act_lo2 + 4 * i, lo);
-          if (DOWN_Q6) {
-            if ((i & 3) == 0) sts64(act + a.act_xs2 + 8 * (gi * (a.F / 16) + (i >> 2)), make_uint2(__float_as_uint(__int2float_rn(sum)), __float_as_uint(inv)));
-          } else {
-            if ((i & 7) == 0) sts64(act + a.act_xs2 + 8 * (gi * (a.F / 32) + (i >> 3)), make_uint2(__float_as_uint(inv * __int2float_rn(sum)), __float_as_uint(inv)));
-          }
-        }
-      }
-    }
-  }
-  named_barrier(1, kFusedConsumers * 32);
-
   // ---- phase 2: down tiles ----
   const uint32_t lane_x6 = (dl.plane ? uint32_t(a.act_lo2) : 0u) + 64u * (g >> 2) + 16u * ((g >> 1) & 1) + 8u * (j & 1);
   const uint32_t lane_x4d = (dl.plane ? uint32_t(a.act_lo2) : 0u) + 32u * (2 * ((g >> 1) & 1) + (g >> 2)) + 16u * (j & 1);
-  for (int t2 = quad; t2 < n2; t2 += kFusedConsumers / kFusedQuad) {
+  int staged = -1;                                                       // group whose planes the quad holds
+  for (int t2 = quad; t2 < n2 && ok; t2 += kFusedConsumers / kFusedQuad) {
     const int c = 2 * n1 + t2, stage = c % NS;
+    const int u2 = cta + t2 * grid, gi = u2 / a.rt2, rt = u2 - gi * a.rt2;
+    if (gi != staged) {
+      if (pre != gi) prefetch_group(gi);
+      pre = -1;
+      if (!stage_group(gi)) { ok = false; break; }
+      staged = gi;
+    }
+    if (pre < 0 && t2 + kFusedConsumers / kFusedQuad < n2) {             // the next tile's products, while this tile is multiplied
+      const int gn = (u2 + (kFusedConsumers / kFusedQuad) * grid) / a.rt2;
+      if (gn != staged) {
+        pre = gn;
+        prefetch_group(gn);
+      }
+    }
     if (!wait_chunk(c)) { ok = false; break; }
-    const int u2 = cta + t2 * grid, gi = u2 % a.G, rt = u2 / a.G;
     float acc[kFusedPasses][2] = {};
     if (kq < a.nblk2) {
       const uint32_t rowg = ring + stage * a.stage_bytes + g * a.row_bytes2;            // row g of the tile
-      const uint32_t xreal = act + gi * a.act_grp2 + (DOWN_Q6 ? lane_x6 : lane_x4d);
+      const uint32_t xreal = qpl + (DOWN_Q6 ? lane_x6 : lane_x4d);
       for (int b = kq; b < a.nblk2; b += kFusedQuad) {
         if (DOWN_Q6) {
-          q6k_load_frags(fr, xreal + 256u * b, first, second, act + a.act_xs2 + 8u * (gi * (a.F / 16)) + 128u * b, sl);
+          q6k_load_frags(fr, xreal + 256u * b, first, second, qxs + 128u * b, sl);
 #pragma unroll
           for (int p = 0; p < kFusedPasses; ++p) {     // sixteen rows of the tile per pass
             const uint32_t rA = rowg + 16 * p * a.row_bytes2, rB = rA + 8 * a.row_bytes2;
@@ -741,7 +832,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
             q6k_rows(rA + b * 208, rB + b * 208, j, dA, dB, fr, acc[p][0], acc[p][1]);
           }
         } else {
-          q4k_load_frags(fr, xreal + 256u * b, first, second, act + a.act_xs2 + 8u * (gi * (a.F / 32)) + 64u * b, sbl);
+          q4k_load_frags(fr, xreal + 256u * b, first, second, qxs + 64u * b, sbl);
 #pragma unroll
           for (int p = 0; p < kFusedPasses; ++p) {
             const uint32_t rA = rowg + 16 * p * a.row_bytes2, rB = rA + 8 * a.row_bytes2;
@@ -753,33 +844,39 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
     float rows = 0.f;
     if (!quad_reduce(t2 % kFusedSlots, acc, rows)) { ok = false; break; }
     // the finished rows of this expert: lane l holds row 16 (l / 16) + (l % 16) of the tile
-    if (kq == 0 && lane < 16 * kFusedPasses) __stcg(a.y + size_t(gi) * a.H + rt * (16 * kFusedPasses) + lane, rows);
+    if (kq == 0 && lane < 16 * kFusedPasses) st_tagged(a.ty + size_t(gi) * a.H + rt * (16 * kFusedPasses) + lane, rows, tag);
     __syncwarp();
     if (lane == 0) mbar_arrive(empty + stage);
   }
-
-  // ---- grid barrier 3: every expert's rows are in global memory; then each CTA combines its share of the rows ----
   if (!ok) *abort_flag = 1;
-  named_barrier(1, kFusedConsumers * 32);
-  if (tid == 0) *go_flag = (!*abort_flag && grid_arrive_wait(a.gbar + 2, unsigned(grid), a.status, abort_flag)) ? 1 : 0;
-  named_barrier(1, kFusedConsumers * 32);
-  if (!*go_flag) return;
-  // x[i] += sum_s fma(p_s, down_s[i]) + sigmoid(sg) * shared[i]   (kogarashi kernels/native.cu:113-117); row i = tid * grid + cta
+  cp_async_wait<0>();                            // a prefetch that was never used must not outlive the CTA
+
+  // ---- combine: x[i] += sum_s fma(p_s, down_s[i]) + sigmoid(sg) * shared[i]   (kogarashi kernels/native.cu:113-117);
+  //      row i = tid * grid + cta; the down rows arrive tagged ----
   const int row = tid * grid + cta;
-  if (row < a.H) {
+  if (ok && row < a.H) {
     const float xin = a.x[row];
-    const float ysh = a.has_shared ? __ldcg(a.y + row) : 0.f;
+    bool good = true;
+    float ysh[8] = {};
+    if (a.has_shared) good = poll_strided(a.ty + row, 0, 1, tag, ysh, a.status, abort_flag);
     float v = 0.f;
-    for (int s0 = 0; s0 < a.K; s0 += 8) {          // eight loads in flight at a time; the sum itself stays in slot order
-      float ys[8];
-#pragma unroll
-      for (int q = 0; q < 8; ++q) ys[q] = s0 + q < a.K ? __ldcg(a.y + size_t(s0 + q + a.has_shared) * a.H + row) : 0.f;
+    for (int s0 = 0; s0 < a.K && good; s0 += 8) {          // eight loads in flight at a time; the sum itself stays in slot order
+      float ys[8] = {};
+      const int nq = a.K - s0 < 8 ? a.K - s0 : 8;
+      good = poll_strided(a.ty + size_t(s0 + a.has_shared) * a.H + row, size_t(a.H), nq, tag, ys, a.status, abort_flag);
 #pragma unroll
       for (int q = 0; q < 8; ++q)
-        if (s0 + q < a.K) v = fmaf(sm_prob[s0 + q], ys[q], v);
+        if (q < nq) v = fmaf(sm_prob[s0 + q], ys[q], v);
     }
-    if (a.has_shared) v += sm_misc[0] * ysh;
-    a.x[row] = xin + v;
+    if (a.has_shared) v += sm_misc[0] * ysh[0];
+    if (good) a.x[row] = xin + v;
+  }
+  // ---- the call counter moves on (also after a failure: the next call must not take this call's words for its own) ----
+  if (cta == 0 && tid == 0) {
+    PollClock clk;
+    while (ld_acquire_u32(a.seen) < unsigned(grid) && !clk.expired(a.status, abort_flag)) {}
+    *a.seen = 0u;
+    *a.epoch = epoch_now + 1u;
   }
 }
 

@@ -53,19 +53,29 @@ static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 struct KogarashiWs {
   int* counters; unsigned* done; unsigned* status; unsigned* gbar; unsigned* tile_cnt; int* active; unsigned* ranges;
-  unsigned* assignments; int4* plan; float* sg; __half* xplanes; __half* xsum_planes; __half* hplanes; float* y; size_t bytes;
+  unsigned* assignments; int4* plan; float* sg; __half* xplanes; __half* xsum_planes; __half* hplanes; float* y;
+  unsigned* epoch; unsigned long long* tlog; unsigned long long* th; unsigned long long* ty;    // the one-token kernel's tagged words
+  size_t bytes;
 };
-constexpr int kFusedMaxRowTiles = 512;      // 16-row output tiles with a completion counter (hidden <= 8192)
+constexpr int kHeadKept = 256;              // bytes at the start of a workspace that only `kogarashi_moe_workspace_init` clears
+constexpr int kFusedMaxRowTiles = 512;
+constexpr int kFusedMaxCtas = 160;          // CTAs (SMs) the one-token kernel can run on
+constexpr int kFusedMaxLogits = 320;        // router rows it can route (shared gate row included)
+static int fused_logit_stride(int experts) { return ((experts + 1 < kFusedMaxLogits ? experts + 1 : kFusedMaxLogits) + 15) / 16 * 16; }      // 16-row output tiles with a completion counter (hidden <= 8192)
 static KogarashiWs carve(void* base, int hidden, int inter, int experts, int topk, int tokens) {
   KogarashiWs w;
   uint8_t* p = static_cast<uint8_t*>(base);
   size_t off = 0;
   auto take = [&](size_t bytes) { uint8_t* q = p ? p + off : nullptr; off = align_up(off + bytes, 256); return q; };
+  // first, at an offset that no shape moves: the call counter of the one-token kernel and the count of CTAs that have
+  // read it. The built-in workspace clears the rest of the head on every call but not these: the counter has to
+  // outlive a call, whatever shapes share the array, for a stale tagged word never to carry the current tag.
+  w.epoch = reinterpret_cast<unsigned*>(take(8));
   w.counters = reinterpret_cast<int*>(take(16));
   w.done = reinterpret_cast<unsigned*>(take(4));
   w.status = reinterpret_cast<unsigned*>(take(4));
-  w.gbar = reinterpret_cast<unsigned*>(take(16));                                   // three grid barrier counters
-  w.tile_cnt = reinterpret_cast<unsigned*>(take(size_t(kFusedMaxRowTiles) * 4));    // per-group maxima of the one-token kernel; ends at byte 3072: inside the zeroed head
+  w.gbar = reinterpret_cast<unsigned*>(take(16));                                   // unused (kept: the layout of the head is part of the status accessor)
+  w.tile_cnt = reinterpret_cast<unsigned*>(take(size_t(kFusedMaxRowTiles) * 4));    // unused; ends at byte 3072: inside the zeroed head
   w.active = reinterpret_cast<int*>(take(size_t(experts) * 4));
   w.ranges = reinterpret_cast<unsigned*>(take(size_t(experts) * 8));
   w.assignments = reinterpret_cast<unsigned*>(take(size_t(tokens) * topk * 4));
@@ -76,6 +86,10 @@ static KogarashiWs carve(void* base, int hidden, int inter, int experts, int top
   const size_t rows = size_t(tokens) * topk + tokens;
   w.hplanes = reinterpret_cast<__half*>(take(rows * 2 * inter * 2));
   w.y = reinterpret_cast<float*>(take(rows * hidden * 4));
+  // one-token kernel: {float, tag} words
+  w.tlog = reinterpret_cast<unsigned long long*>(take(size_t(kFusedMaxCtas) * fused_logit_stride(experts) * 8));   // one copy per CTA
+  w.th = reinterpret_cast<unsigned long long*>(take(size_t(topk + 1) * inter * 8));
+  w.ty = reinterpret_cast<unsigned long long*>(take(size_t(topk + 1) * hidden * 8));
   w.bytes = off;
   return w;
 }
@@ -103,10 +117,11 @@ static bool fused_plan(const KogarashiMoe* d, const KogarashiWs& w, FusedArgs* f
   if (d->down_ty != DARASK_GGML_Q4_K && d->down_ty != DARASK_GGML_Q6_K) return false;
   const bool shared = d->sh_gate_w != nullptr;
   const int grid = sm_count();
-  if (E + (shared ? 1 : 0) > 2 * grid || H > 8192 || H % (16 * kFusedPasses) || F % (8 * kFusedPasses)) return false;
+  if (E + (shared ? 1 : 0) > 2 * grid || E + (shared ? 1 : 0) > kFusedMaxLogits || grid > kFusedMaxCtas || H > 8192 || H % (16 * kFusedPasses) || F % (8 * kFusedPasses)) return false;
   FusedArgs a = {};
   a.H = H; a.F = F; a.E = E; a.K = K; a.has_shared = shared ? 1 : 0; a.G = K + a.has_shared;
   a.down_q6 = d->down_ty == DARASK_GGML_Q6_K;
+  a.ldlog = fused_logit_stride(E);
   a.nblk1 = H / 256; a.nblk2 = F / 256;
   a.row_bytes1 = row_bytes_of(DARASK_GGML_Q4_K, H);
   a.row_bytes2 = row_bytes_of(d->down_ty, F);
@@ -119,18 +134,20 @@ static bool fused_plan(const KogarashiMoe* d, const KogarashiWs& w, FusedArgs* f
   // shared memory: control words | barriers | partial sums | activation area | ring
   a.off_bars = 640;
   a.off_psum = (a.off_bars + (2 * kFusedMaxStages + 1 + 4) * 8 + 127) / 128 * 128;
-  a.off_act = (a.off_psum + kFusedSlots * kFusedQuad * 16 * kFusedPasses * 4 + 127) / 128 * 128;
-  // phase R / 1: the token's two byte planes (the second 32 bytes off the bank phase of the first), (sum, 1 / S) per 32
-  // columns, the router rows; phase 2: per expert group two byte planes, then all (sum, 1 / S) pairs
+  a.off_log = (a.off_psum + kFusedSlots * kFusedQuad * 16 * kFusedPasses * 4 + 127) / 128 * 128;
+  a.off_act = (a.off_log + (E + 1) * 4 + 127) / 128 * 128;
+  // the token's two byte planes (the second 32 bytes off the bank phase of the first), (sum, 1 / S) per 32 columns; then
+  // the router rows (phase R) and in the same place one area per quad (phase 2): the raw tagged products of one expert,
+  // their two byte planes, their (sum, 1 / S) pairs
   a.act_lo1 = H + 32;
   a.act_xs1 = (2 * a.act_lo1 + 15) / 16 * 16;
   a.act_rows = (a.act_xs1 + H / 32 * 8 + 127) / 128 * 128;
-  const int act1 = a.act_rows + 2 * H * 4;
   a.act_lo2 = F + 32;
-  a.act_grp2 = (2 * a.act_lo2 + 15) / 16 * 16;
-  a.act_xs2 = a.G * a.act_grp2;
-  const int act2 = a.act_xs2 + a.G * (F / 16) * 8;
-  a.off_ring = (a.off_act + (act1 > act2 ? act1 : act2) + 127) / 128 * 128;
+  a.act_xs2 = (2 * a.act_lo2 + 15) / 16 * 16;
+  a.act_q = a.act_rows;
+  a.act_qs = (8 * F + a.act_xs2 + F / 16 * 8 + 127) / 128 * 128;
+  const int rows_bytes = 2 * H * 4, quads_bytes = kFusedQuad * a.act_qs;
+  a.off_ring = (a.off_act + a.act_rows + (rows_bytes > quads_bytes ? rows_bytes : quads_bytes) + 127) / 128 * 128;
   a.nstage = (kSmemBudget - a.off_ring) / a.stage_bytes;
   if (a.nstage > kFusedMaxStages) a.nstage = kFusedMaxStages;
   if (a.nstage < 3) return false;
@@ -139,7 +156,7 @@ static bool fused_plan(const KogarashiMoe* d, const KogarashiWs& w, FusedArgs* f
   a.gate_w = static_cast<const uint8_t*>(d->gate_w); a.up_w = static_cast<const uint8_t*>(d->up_w); a.down_w = static_cast<const uint8_t*>(d->down_w);
   a.sh_gate = static_cast<const uint8_t*>(d->sh_gate_w); a.sh_up = static_cast<const uint8_t*>(d->sh_up_w); a.sh_down = static_cast<const uint8_t*>(d->sh_down_w);
   a.n = d->n; a.x = d->x; a.logits = d->logits; a.ids = d->ids; a.prob = d->prob;
-  a.gbar = w.gbar; a.status = w.status; a.hbuf = reinterpret_cast<float*>(w.hplanes); a.y = w.y; a.sg = w.sg;
+  a.status = w.status; a.epoch = w.epoch; a.seen = w.epoch + 1; a.tlog = w.tlog; a.th = w.th; a.ty = w.ty;
   *f = a;
   return true;
 }
@@ -179,7 +196,7 @@ extern "C" size_t kogarashi_moe_workspace_bytes(int hidden, int inter, int exper
 
 extern "C" int kogarashi_moe_workspace_init(void* workspace, size_t bytes, cudaStream_t st) {
   if (!workspace || !bytes) return cudaErrorInvalidValue;
-  return cudaMemsetAsync(workspace, 0, bytes < 4096 ? bytes : 4096, st);
+  return cudaMemsetAsync(workspace, 0, bytes, st);     // once per workspace: also the tagged words of the one-token kernel
 }
 
 extern "C" int kogarashi_moe_status(const void* workspace, unsigned* host_status, cudaStream_t st) {
@@ -347,7 +364,7 @@ extern "C" int kogarashi_moe_layer_static(const KogarashiMoe* d, cudaStream_t st
   void* scratch = static_scratch_address(&e);
   if (!scratch) return e;
   // The array keeps whatever the previous call left: the control words (counters, barrier words, status) start at zero.
-  e = cudaMemsetAsync(scratch, 0, 4096, st);
+  e = cudaMemsetAsync(static_cast<uint8_t*>(scratch) + kHeadKept, 0, 4096 - kHeadKept, st);
   if (e != cudaSuccess) return e;
   KogarashiMoe copy = *d;
   copy.workspace = scratch;

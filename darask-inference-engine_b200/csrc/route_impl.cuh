@@ -48,15 +48,17 @@ DEVI unsigned long long warp_max_u64(unsigned long long v) {
   return (static_cast<unsigned long long>(top) << 32) | low;
 }
 
+// A logit from global memory (through L2: another block may have written it) or from the caller's shared memory.
+DEVI float load_logit(const float* p) { return __isGlobal(p) ? __ldcg(p) : *p; }
 // One warp routes one token; lane l owns experts l, l + 32, ... (PER * 32 >= experts). `ids_out` / `w_out`
-// (k entries each) may point to global or shared memory.
+// (k entries each) may point to global or shared memory, and so may the logits.
 template <int MODE, int PER>
 DEVI void route_token(const RouteArgs& a, int token, int lane, int* ids_out, float* w_out) {
   const float* row = a.logits + size_t(token) * a.ld;
   const int E = a.experts, K = a.topk;
   float logit[PER];
 #pragma unroll
-  for (int i = 0; i < PER; ++i) logit[i] = lane + 32 * i < E ? __ldcg(row + lane + 32 * i) : -INFINITY;   // L2: another block may have written it
+  for (int i = 0; i < PER; ++i) logit[i] = lane + 32 * i < E ? load_logit(row + lane + 32 * i) : -INFINITY;
   unsigned long long cand[PER];
   float score[MODE == kRouteHayate ? PER : 1];
   float norm = 1.f;                          // Tsumuji: sum over all experts of exp(logit - max)
@@ -122,7 +124,7 @@ DEVI void route_token(const RouteArgs& a, int token, int lane, int* ids_out, flo
     if (lane < K) w_out[lane] = z / denom;
   } else if (MODE == kRouteTsumuji) {
     if (lane < K) w_out[lane] = keep / running;
-    if (lane == 0 && a.shared_gate) a.shared_gate[token] = 1.f / (1.f + expf(-__ldcg(row + E)));
+    if (lane == 0 && a.shared_gate) a.shared_gate[token] = 1.f / (1.f + expf(-load_logit(row + E)));
   } else {
     if (lane < K) w_out[lane] = keep / (running + 1.e-20f) * a.scale;
   }

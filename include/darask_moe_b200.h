@@ -116,12 +116,13 @@ typedef struct {
   int reserved;                                        /* must be 0 */
 } KogarashiMoe;
 size_t kogarashi_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens);
-/* zeroes the control words once after allocation */
+/* zeroes the whole workspace, once after allocation (the control words, and the tagged words through which the
+ * CTAs of the one-token launch hand values to each other: a workspace that was never cleared may hold a stale tag) */
 int kogarashi_moe_workspace_init(void* workspace, size_t bytes, darask_stream_t stream);
 int kogarashi_moe_layer(const KogarashiMoe* desc /* host */, darask_stream_t stream);
 /* One token with an F32 router and Q4_K gate/up runs as ONE persistent launch (router rows, top-k in every CTA,
- * gate/up, down and combine behind two bounded grid barriers, the weight stream running across them); other shapes
- * take four launches.  enabled = 0 makes the calling host thread take the four launches for one token as well
+ * gate/up, down and combine; the CTAs hand logits, products and rows to each other as tagged words with bounded
+ * polling, the weight stream running through); other shapes take four launches.  enabled = 0 makes the calling host thread take the four launches for one token as well
  * (no counterpart in the reference; used to compare the two paths). */
 int kogarashi_moe_set_single_launch(int enabled);
 /* copies the status word to *host_status and synchronizes the stream */
@@ -138,7 +139,7 @@ int kogarashi_moe_status(const void* workspace, unsigned* host_status /* host */
  * the array's device address (with that device current); make that first call before any stream
  * capture.  All calls on a device share the one array: calls whose kernels can overlap on the
  * GPU (different streams) race; serialize them.  Every call first clears the array's control
- * words, the status word among them: read the status of a call (kogarashi_moe_static_status,
+ * words (all but the call counter of the one-token launch), the status word among them: read the status of a call (kogarashi_moe_static_status,
  * which synchronizes the stream) before the next call if it matters.  A descriptor that fails
  * validation is refused before anything is enqueued. */
 size_t kogarashi_moe_static_scratch_bytes(void);
