@@ -774,6 +774,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
           q4k_rows(gate_rows + 8 * p * a.row_bytes1 + b * 144, up_rows + 8 * p * a.row_bytes1 + b * 144, j, fr, acc[p][0], acc[p][1]);
       }
     }
+    // the weights of the tile are not needed any more: the slots go back before the sums meet
+    __syncwarp();
+    if (lane == 0) {
+      mbar_arrive(empty + cg % NS);
+      mbar_arrive(empty + cu % NS);
+    }
     float rows = 0.f;
     if (!quad_reduce(lt % kFusedSlots, acc, rows)) { ok = false; break; }
     if (kq == 0) {
@@ -785,13 +791,6 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
         st_tagged(a.th + size_t(gi) * a.F + tile * (8 * kFusedPasses) + 8 * (lane >> 4) + (lane & 7), h, tag);
       }
       if (!(fabsf(h) <= 3.0e38f)) atomicOr(a.status, kStatusActRange);
-    }
-    // The chunks are handed back only now: the warp that sums a tile keeps the producer from running kFusedSlots tiles
-    // ahead, so a slot of partial sums is never reused while it is being read.
-    __syncwarp();
-    if (lane == 0) {
-      mbar_arrive(empty + cg % NS);
-      mbar_arrive(empty + cu % NS);
     }
   }
 
@@ -841,12 +840,12 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
         }
       }
     }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty + stage);
     float rows = 0.f;
     if (!quad_reduce(t2 % kFusedSlots, acc, rows)) { ok = false; break; }
     // the finished rows of this expert: lane l holds row 16 (l / 16) + (l % 16) of the tile
     if (kq == 0 && lane < 16 * kFusedPasses) st_tagged(a.ty + size_t(gi) * a.H + rt * (16 * kFusedPasses) + lane, rows, tag);
-    __syncwarp();
-    if (lane == 0) mbar_arrive(empty + stage);
   }
   if (!ok) *abort_flag = 1;
   cp_async_wait<0>();                            // a prefetch that was never used must not outlive the CTA

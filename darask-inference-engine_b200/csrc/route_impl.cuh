@@ -48,6 +48,30 @@ DEVI unsigned long long warp_max_u64(unsigned long long v) {
   return (static_cast<unsigned long long>(top) << 32) | low;
 }
 
+// Compare-exchange of two candidates, larger first.
+DEVI void order_pair(unsigned long long& x, unsigned long long& y) {
+  const unsigned long long hi = x > y ? x : y, lo = x > y ? y : x;
+  x = hi;
+  y = lo;
+}
+// This lane's candidates in descending order (sorting networks of 3 / 19 exchanges).
+template <int PER>
+DEVI void sort_candidates(unsigned long long (&c)[PER]) {
+  static_assert(PER == 4 || PER == 8, "networks for 4 and 8 candidates");
+  if (PER == 4) {
+    order_pair(c[0], c[1]); order_pair(c[2], c[3]);
+    order_pair(c[0], c[2]); order_pair(c[1], c[3]);
+    order_pair(c[1], c[2]);
+  } else {
+    order_pair(c[0], c[1]); order_pair(c[2], c[3]); order_pair(c[4 % PER], c[5 % PER]); order_pair(c[6 % PER], c[7 % PER]);
+    order_pair(c[0], c[2]); order_pair(c[1], c[3]); order_pair(c[4 % PER], c[6 % PER]); order_pair(c[5 % PER], c[7 % PER]);
+    order_pair(c[1], c[2]); order_pair(c[5 % PER], c[6 % PER]);
+    order_pair(c[0], c[4 % PER]); order_pair(c[1], c[5 % PER]); order_pair(c[2], c[6 % PER]); order_pair(c[3], c[7 % PER]);
+    order_pair(c[2], c[4 % PER]); order_pair(c[3], c[5 % PER]);
+    order_pair(c[1], c[2]); order_pair(c[3], c[4 % PER]); order_pair(c[5 % PER], c[6 % PER]);
+  }
+}
+
 // A logit from global memory (through L2: another block may have written it) or from the caller's shared memory.
 DEVI float load_logit(const float* p) { return __isGlobal(p) ? __ldcg(p) : *p; }
 // One warp routes one token; lane l owns experts l, l + 32, ... (PER * 32 >= experts). `ids_out` / `w_out`
@@ -87,22 +111,38 @@ DEVI void route_token(const RouteArgs& a, int token, int lane, int* ids_out, flo
       cand[i] = e < E ? pack_candidate(score[i] + a.bias[e], e) : 0ull;
     }
   }
+  // Few candidates per lane and no per-candidate side value: each lane sorts its own once, its best is then the
+  // first, and the lane that wins a round shifts its list. (Same words, same order of winners.)
+  constexpr bool SORTED = PER <= 8 && MODE != kRouteHayate;
+  if constexpr (SORTED) sort_candidates(cand);
   float keep = 0.f;       // lane t keeps the quantity slot t's weight is made from
   float running = 0.f;    // Tsumuji / Hayate: sum over the selected, in selection order
   float lead = 0.f;       // Kogarashi: the first (largest) selected logit
   for (int t = 0; t < K; ++t) {
     unsigned long long best = 0ull;
+    if (SORTED) {
+      best = cand[0];
+    } else {
 #pragma unroll
-    for (int i = 0; i < PER; ++i) best = cand[i] > best ? cand[i] : best;
+      for (int i = 0; i < PER; ++i) best = cand[i] > best ? cand[i] : best;
+    }
     best = warp_max_u64(best);
     const int winner = int(0xffffffffu - static_cast<uint32_t>(best));
     const float key = ordered_value(static_cast<uint32_t>(best >> 32));
     float won_score = 0.f;
+    if (SORTED) {
+      if ((winner & 31) == lane) {
 #pragma unroll
-    for (int i = 0; i < PER; ++i) {
-      const bool hit = (winner & 31) == lane && (winner >> 5) == i;
-      if (MODE == kRouteHayate && hit) won_score = score[i];
-      if (hit) cand[i] = 0ull;
+        for (int i = 0; i + 1 < PER; ++i) cand[i] = cand[i + 1];
+        cand[PER - 1] = 0ull;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < PER; ++i) {
+        const bool hit = (winner & 31) == lane && (winner >> 5) == i;
+        if (MODE == kRouteHayate && hit) won_score = score[i];
+        if (hit) cand[i] = 0ull;
+      }
     }
     if (lane == 0) ids_out[t] = winner;
     if (MODE == kRouteKogarashi) {
