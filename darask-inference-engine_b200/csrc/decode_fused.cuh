@@ -51,11 +51,35 @@
 
 namespace dmoe {
 
+// Build-time knobs of the one-token kernel (measured: inlining everything is fastest; the waits neither gain nor lose
+// from suspend hints or sleeps between probes).
+#ifndef DMOE_HOT
+#define DMOE_HOT DEVI
+#endif
+#ifndef DMOE_COLD
+#define DMOE_COLD DEVI
+#endif
+#ifndef DMOE_ROUTE
+#define DMOE_ROUTE DEVI
+#endif
+#ifndef DMOE_WAIT_HINT_NS
+#define DMOE_WAIT_HINT_NS 10000
+#endif
+#ifndef DMOE_WAIT_SLEEP_NS
+#define DMOE_WAIT_SLEEP_NS 64
+#endif
+#ifndef DMOE_FILL_SLEEP_NS
+#define DMOE_FILL_SLEEP_NS 32
+#endif
+
 constexpr float kFixedPointRange = 32000.f;     // the largest magnitude of a scale group maps to this integer
 constexpr unsigned kStatusActRange = 4u;   // an activation is not finite (the staged kernels: does not fit fp16 planes)
 
 constexpr int kFusedConsumers = 16;                          // consumer warps
-constexpr int kFusedProducers = 2;                           // warps that issue bulk copies (one thread each)
+#ifndef DMOE_FUSED_PRODUCERS
+#define DMOE_FUSED_PRODUCERS 2
+#endif
+constexpr int kFusedProducers = DMOE_FUSED_PRODUCERS;                           // warps that issue bulk copies (one thread each)
 constexpr int kFusedThreads = (kFusedConsumers + kFusedProducers) * 32;
 constexpr int kFusedSlots = 16;                              // partial-sum slots: a slot is reused 16 tiles later, further than the ring reaches
 constexpr int kFusedMaxStages = 14;
@@ -105,7 +129,7 @@ struct PollClock {
   uint64_t start;
   uint32_t spin;
   DEVI PollClock() : start(0), spin(0) {}
-  DEVI bool expired(unsigned* status, volatile int* abort_flag) {
+  DMOE_COLD bool expired(unsigned* status, volatile int* abort_flag) {
     if ((++spin & 15u) != 0) return false;
     if (*abort_flag) return true;
     const uint64_t now = global_timer_ns();
@@ -120,7 +144,7 @@ struct PollClock {
   }
 };
 // A warp collects entries lane, lane + 32, ... (< n <= 320) of a tagged array into `dst`. Uniform result.
-DEVI bool gather_tagged(const unsigned long long* src, int n, unsigned tag, float* dst, int lane, unsigned* status, volatile int* abort_flag) {
+DMOE_COLD bool gather_tagged(const unsigned long long* src, int n, unsigned tag, float* dst, int lane, unsigned* status, volatile int* abort_flag) {
   constexpr int MAXQ = 10;
   unsigned pend = 0;
 #pragma unroll
@@ -145,7 +169,7 @@ DEVI bool gather_tagged(const unsigned long long* src, int n, unsigned tag, floa
   }
 }
 // One thread: up to eight entries base[q * stride], q < n, all in flight together.
-DEVI bool poll_strided(const unsigned long long* base, size_t stride, int n, unsigned tag, float (&out)[8], unsigned* status, volatile int* abort_flag) {
+DMOE_COLD bool poll_strided(const unsigned long long* base, size_t stride, int n, unsigned tag, float (&out)[8], unsigned* status, volatile int* abort_flag) {
   unsigned pend = (1u << n) - 1u;
   PollClock clk;
   for (;;) {
@@ -164,7 +188,7 @@ DEVI bool poll_strided(const unsigned long long* base, size_t stride, int n, uns
   }
 }
 // One thread: four consecutive entries as (v, t, v, t) x 2.
-DEVI bool poll_four(const unsigned long long* p, unsigned tag, uint4& r0, uint4& r1, unsigned* status, volatile int* abort_flag) {
+DMOE_COLD bool poll_four(const unsigned long long* p, unsigned tag, uint4& r0, uint4& r1, unsigned* status, volatile int* abort_flag) {
   PollClock clk;
   for (;;) {
     r0 = ld_tagged2(p);
@@ -174,7 +198,7 @@ DEVI bool poll_four(const unsigned long long* p, unsigned tag, uint4& r0, uint4&
   }
 }
 // mbarrier wait that also leaves when another role gave up
-DEVI bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, unsigned* status, volatile int* abort_flag) {
+DMOE_HOT bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, unsigned* status, volatile int* abort_flag) {
   const uint32_t addr = smem_u32(bar);
   uint64_t start = 0;
   for (uint32_t spin = 0;; ++spin) {
@@ -184,11 +208,11 @@ DEVI bool mbar_wait_abortable(uint64_t* bar, uint32_t parity, unsigned* status, 
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(addr), "r"(parity), "r"(10000u)
+        : "r"(addr), "r"(parity), "r"(unsigned(DMOE_WAIT_HINT_NS))
         : "memory");
     if (ok) return true;
     if (*abort_flag) return false;
-    __nanosleep(64);                       // waiting warps leave the issue slots to the warps that have data
+    if (DMOE_WAIT_SLEEP_NS) __nanosleep(DMOE_WAIT_SLEEP_NS);     // waiting warps leave the issue slots to the warps that have data
     if ((spin & 15u) == 0) {
       const uint64_t now = global_timer_ns();
       if (spin == 0) start = now;
@@ -400,6 +424,31 @@ DEVI void sts32(uint32_t a, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;"
 DEVI void sts64(uint32_t a, uint2 v) { asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(a), "r"(v.x), "r"(v.y) : "memory"); }
 DEVI void sts32f(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory"); }
 
+// The selection of one token by one warp, as a function of its own: the kernel calls it twice (rehearsal and
+// selection) and both calls run the same instructions.
+DMOE_ROUTE void fused_route(const float* logits, int experts, int topk, int lane, int* ids, float* prob) {
+  RouteArgs r{logits, experts, experts, topk, 1, nullptr, 1.f, nullptr, nullptr, nullptr};
+  if (experts <= 128) route_token<kRouteKogarashi, 4>(r, 0, lane, ids, prob);
+  else if (experts <= 256) route_token<kRouteKogarashi, 8>(r, 0, lane, ids, prob);
+  else route_token<kRouteKogarashi, 16>(r, 0, lane, ids, prob);
+}
+// Waits until fill `use` of a ring slot has been requested (`fill` counts the requests) and has landed.
+DMOE_HOT bool wait_fill(volatile int* fill, uint64_t* full_bar, int use, unsigned* status, volatile int* abort_flag) {
+  if (use > 0 && *fill <= use) {
+    const uint64_t start = global_timer_ns();
+    while (*fill <= use) {
+      if (DMOE_FILL_SLEEP_NS) __nanosleep(DMOE_FILL_SLEEP_NS);
+      if (*abort_flag) return false;
+      if (global_timer_ns() - start > kWaitLimitNs) {
+        atomicOr(status, kStatusWaitTimeout);
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  return mbar_wait_abortable(full_bar, use & 1, status, abort_flag);
+}
+
 // ---- the kernel ----------------------------------------------------------------------------------------------
 template <int DOWN_Q6>
 __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(const FusedArgs a) {
@@ -493,8 +542,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
         // stream, where every instruction-cache line it touches for the first time is a miss. The time before the
         // dependency wait is idle, so the same code runs here once on stand-in values (a router row); what it writes
         // to shared memory is overwritten by the real selection.
-        RouteArgs r{a.router_w, a.E, a.E, a.K, 1, nullptr, 1.f, nullptr, nullptr, nullptr};
-        route_token_to<kRouteKogarashi>(r, 0, lane, sm_ids, sm_prob);
+        fused_route(a.router_w, a.E, a.K, lane, sm_ids, sm_prob);
         __syncwarp();
       }
       pdl_wait();
@@ -504,8 +552,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
       if (ok) ok = gather_tagged(a.tlog + size_t(cta) * a.ldlog, R, tag, sm_log, lane, a.status, abort_flag) ? 1 : 0;
       __syncwarp();
       if (ok) {
-        RouteArgs r{sm_log, a.E, a.E, a.K, 1, nullptr, 1.f, nullptr, nullptr, nullptr};
-        route_token_to<kRouteKogarashi>(r, 0, lane, sm_ids, sm_prob);
+        fused_route(sm_log, a.E, a.K, lane, sm_ids, sm_prob);
         if (lane == 0 && a.has_shared) sm_misc[0] = sigmoid_precise(sm_log[a.E]);
         __syncwarp();
         if (cta == 0 && lane < a.K) {
@@ -679,22 +726,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   // before it, and a quad does not see every fill of a slot (other quads consume some): so the producer publishes the
   // number of fills it has requested per slot, and a consumer first waits until its fill has been requested (the
   // barrier is then in that fill's phase or just past it) and only then for the parity.
-  auto wait_chunk = [&](int c) -> bool {
-    const int stage = c % NS, use = c / NS;
-    if (use > 0 && fill_id[stage] <= use) {
-      const uint64_t start = global_timer_ns();
-      while (fill_id[stage] <= use) {
-        __nanosleep(32);
-        if (*abort_flag) return false;
-        if (global_timer_ns() - start > kWaitLimitNs) {
-          atomicOr(a.status, kStatusWaitTimeout);
-          *abort_flag = 1;
-          return false;
-        }
-      }
-    }
-    return mbar_wait_abortable(full + stage, use & 1, a.status, abort_flag);
-  };
+  auto wait_chunk = [&](int c) -> bool { return wait_fill(fill_id + c % NS, full + c % NS, c / NS, a.status, abort_flag); };
 
   // ---- the product vector of one expert group for this quad's down tiles ----
   // Raw tagged words are copied asynchronously (every thread copies, and later reads, its own 32 bytes: four values)
