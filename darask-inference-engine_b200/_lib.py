@@ -97,6 +97,10 @@ _SIGNATURES = {
     "hayate_glm_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_void_p]),
     "hayate_glm_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_void_p]),
     "hayate_glm_copy": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
+    "hayate_glm_grouped_packed_set_config": (c_int, [c_uint]),
+    "hayate_glm_grouped_packed_gate_up": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_uint, c_void_p]),
+    "hayate_glm_grouped_packed_down": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_uint, c_uint, c_uint, c_void_p]),
+    "hayate_glm_grouped_packed_status": (c_int, [c_void_p, c_void_p]),
     "darask_fp8_ep_dispatch_scratch_bytes": (c_size_t, [c_int, c_int, c_int, c_int]),
     "darask_fp8_ep_dispatch": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_size_t, c_void_p]),

@@ -11,8 +11,7 @@
 //              the tensor pipe fed from shared memory) into one of two TMEM accumulator buffers of 256 columns and
 //              commits to the ring / accumulator barriers
 //   warps 4-11 epilogue, two warps per TMEM lane quarter with 128 columns each: tcgen05.ld the K block's partial
-//              tile (one TMEM lane = one row per thread) 32 columns at a time into two alternating register sets
-//              (a load is in flight while the previous set is consumed), multiply by the block scales and add
+//              tile (one TMEM lane = one row per thread) 16 columns at a time, multiply by the block scales and add
 //              into float32 registers ; after the last K block SwiGLU and one of three stores (float32, bf16, or e4m3 codes +
 //              scale per row and 128 columns), staged through shared memory so that rows leave in 64-byte pieces
 // The producer/MMA warpgroup gives registers to the two epilogue warpgroups (setmaxnreg).
@@ -85,32 +84,6 @@ DEVI void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr) : "memory");
 }
-// 32 columns of this warp's 32 TMEM lanes -> registers, asynchronously: the registers hold the values only after
-// tmem_ld_wait(). Two register sets alternate, so that one load is in flight while the other set is consumed.
-DEVI void tmem_ld32_async(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
-      "%25,%26,%27,%28,%29,%30,%31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-// Completes every tcgen05.ld of this thread. The register sets are passed through the statement so that the compiler
-// cannot move a use of them above the wait.
-DEVI void tmem_ld_wait(uint32_t (&x)[32], uint32_t (&y)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(x[0]), "+r"(x[1]), "+r"(x[2]), "+r"(x[3]), "+r"(x[4]), "+r"(x[5]), "+r"(x[6]), "+r"(x[7]), "+r"(x[8]), "+r"(x[9]),
-                 "+r"(x[10]), "+r"(x[11]), "+r"(x[12]), "+r"(x[13]), "+r"(x[14]), "+r"(x[15]), "+r"(x[16]), "+r"(x[17]), "+r"(x[18]),
-                 "+r"(x[19]), "+r"(x[20]), "+r"(x[21]), "+r"(x[22]), "+r"(x[23]), "+r"(x[24]), "+r"(x[25]), "+r"(x[26]), "+r"(x[27]),
-                 "+r"(x[28]), "+r"(x[29]), "+r"(x[30]), "+r"(x[31]), "+r"(y[0]), "+r"(y[1]), "+r"(y[2]), "+r"(y[3]), "+r"(y[4]), "+r"(y[5]),
-                 "+r"(y[6]), "+r"(y[7]), "+r"(y[8]), "+r"(y[9]), "+r"(y[10]), "+r"(y[11]), "+r"(y[12]), "+r"(y[13]), "+r"(y[14]),
-                 "+r"(y[15]), "+r"(y[16]), "+r"(y[17]), "+r"(y[18]), "+r"(y[19]), "+r"(y[20]), "+r"(y[21]), "+r"(y[22]), "+r"(y[23]),
-                 "+r"(y[24]), "+r"(y[25]), "+r"(y[26]), "+r"(y[27]), "+r"(y[28]), "+r"(y[29]), "+r"(y[30]), "+r"(y[31])
-               :: "memory");
-}
-
 struct G8Tile { int expert, m0, n0, rows, offset; };
 
 template <int MODE>
@@ -228,7 +201,7 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const int steps = my_tiles * kblocks;
     const uint32_t tlane = tmem_base + (uint32_t(quarter * 32) << 16);
     bool ok = true;
-    uint32_t vx[32], vy[32];          // two register sets for the TMEM loads
+    uint32_t va[16];
     auto await_step = [&](int step) {                   // the MMAs of this step have written their TMEM buffer
       const int buf = step & (kG8AccBufs - 1);
       // one lane watches the barrier (many threads probing one barrier word serialise in shared memory)
@@ -373,11 +346,11 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       if (half == 0 && valid) a.out_scales[size_t(grow0 + lane) * (a.n / 128) + t.n0 / 128] = scale;
       store_rows(a.out_codes, size_t(a.n), size_t(t.n0 + 64 * half), piece);
     };
-    auto fma32 = [&](const uint32_t (&v)[32], float f, int base) {      // acc[base .. base + 16) += v * f
+    auto fma16 = [&](float f, int base) {                // acc[base .. base + 8) += va * f
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {    // scalar fma: the packed f32x2 form measured slower here (operand pairing moves)
-        acc[base + i].x = fmaf(__uint_as_float(v[2 * i]), f, acc[base + i].x);
-        acc[base + i].y = fmaf(__uint_as_float(v[2 * i + 1]), f, acc[base + i].y);
+      for (int i = 0; i < 8; ++i) {     // scalar fma: the packed f32x2 form measured slower here (operand pairing moves)
+        acc[base + i].x = fmaf(__uint_as_float(va[2 * i]), f, acc[base + i].x);
+        acc[base + i].y = fmaf(__uint_as_float(va[2 * i + 1]), f, acc[base + i].y);
       }
     };
     if (steps > 0) {
@@ -386,7 +359,6 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
       fetch_sw(t);
       open_tile();
       await_step(0);
-      if (ok) tmem_ld32_async(tlane + colA, vx);
       for (int step = 0; step < steps && ok; ++step) {
         const uint32_t tbuf = tlane + (step & (kG8AccBufs - 1)) * 256;
         if ((kb & 3) == 0) {
@@ -402,27 +374,21 @@ grouped_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const float s_row = (valid && cols) ? pick(cur_r, kb & 3) : 0.f;
         const float wa = sw_staged ? my_sw[kb] : __ldg(sw_ptr(t, 0) + kb), wb = sw_staged ? my_sw[kG8MaxStagedK + kb] : __ldg(sw_ptr(t, 1) + kb);
         const float fA = s_row * wa, fB = s_row * wb;
-        // Four 32-column loads (columns colA, colA + 32, colB, colB + 32) through two alternating register sets: while
-        // one set is multiplied into the accumulators the next load is in flight. The first load of a step was issued
-        // at the end of the previous step (or before the loop), as soon as the step's MMAs had completed.
-        tmem_ld_wait(vx, vy);                                    // set x = columns colA .. +32
-        tmem_ld32_async(tbuf + colA + 32, vy);
-        fma32(vx, fA, 0);
-        tmem_ld_wait(vx, vy);                                    // set y = columns colA + 32 .. +32
-        tmem_ld32_async(tbuf + colB, vx);
-        fma32(vy, fA, 16);
-        tmem_ld_wait(vx, vy);                                    // set x = columns colB .. +32
-        tmem_ld32_async(tbuf + colB + 32, vy);
-        fma32(vx, fB, 32);
-        tmem_ld_wait(vx, vy);                                    // set y = columns colB + 32 .. +32: the buffer has been read
+        // eight 16-column loads (columns colA .. +64, colB .. +64); the partner warp of this scheduler partition
+        // covers a load's latency with its adds. (Measured: 32-column loads into two alternating register sets, one
+        // in flight while the other is consumed, made the kernel a fifth slower: 232 registers do not hold both sets
+        // and the 128 accumulators.)
+#pragma unroll
+        for (int j = 0; j < 7; ++j) {
+          tmem_ld16(tbuf + (j < 4 ? colA + 16 * j : colB + 16 * (j - 4)), va);
+          fma16(j < 4 ? fA : fB, 8 * j);
+        }
+        tmem_ld16(tbuf + colB + 48, va);
         tmem_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(tempty + (step & (kG8AccBufs - 1)));   // the values are in registers: the buffer may be overwritten
-        if (step + 1 < steps) {
-          await_step(step + 1);
-          if (ok) tmem_ld32_async(tlane + ((step + 1) & (kG8AccBufs - 1)) * 256 + colA, vx);
-        }
-        fma32(vy, fB, 48);
+        fma16(fB, 56);
+        if (step + 1 < steps) await_step(step + 1);
         if (++kb == kblocks) {
           close_tile();
           kb = 0;

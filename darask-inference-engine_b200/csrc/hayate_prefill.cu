@@ -6,6 +6,7 @@
 #include <cuda_fp8.h>
 #include "../../include/darask_moe_b200.h"
 #include "grouped_bf16.cuh"
+#include "grouped_nvfp4.cuh"
 #include "stream_launch.cuh"
 
 namespace dmoe {
@@ -114,9 +115,73 @@ static bool grouped_shape_ok(unsigned groups, unsigned n, unsigned k) {
   return groups && groups <= 1024 && n >= 128 && n % 128 == 0 && k >= unsigned(kGbTileK) && k % kGbTileK == 0;
 }
 
+// ---- packed NVFP4 images in place (grouped_nvfp4.cuh) ----------------------------------------------------------
+// The reference's launchers have no status argument: what the kernels find wrong with an image on the device (a format
+// other than NVFP4, a null pointer) goes to this word, which hayate_glm_grouped_packed_status reads and clears.
+__device__ unsigned g_packed_status;
+
+template <bool DOWN>
+static cudaError_t launch_grouped_packed(void* out, const void* x, const void* images, const void* formats, const void* ranges,
+                                         unsigned count, unsigned hidden, unsigned inter, cudaStream_t st) {
+  GnArgs g = {};
+  g.x = static_cast<const __nv_bfloat16*>(x);
+  g.images = static_cast<const void* const*>(images);
+  g.formats = static_cast<const HayateExpertFormat*>(formats);
+  g.ranges = static_cast<const unsigned*>(ranges);
+  g.count = int(count); g.hidden = int(hidden); g.inter = int(inter);
+  g.out = static_cast<__nv_bfloat16*>(out);
+  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&g.status), g_packed_status);
+  if (e != cudaSuccess) return e;
+  static_assert(kGnFixedSmem + 289 * sizeof(int) <= size_t(kSmemBudget), "stages and staging must fit one CTA");
+  const size_t smem = size_t(kGnFixedSmem) + size_t(count + 1) * sizeof(int);
+  static bool configured[64][2] = {};   // the opt-in is per device and per kernel
+  const int dev = current_device_slot();
+  if (dev < 0) return cudaErrorInvalidDevice;
+  if (!configured[dev][DOWN]) {
+    e = cudaFuncSetAttribute(grouped_nvfp4_kernel<DOWN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kGnFixedSmem + 289 * sizeof(int)));
+    if (e != cudaSuccess) return e;
+    configured[dev][DOWN] = true;
+  }
+  return launch_pdl(grouped_nvfp4_kernel<DOWN>, dim3(sm_count()), dim3(kGnThreads), smem, st, g);
+}
+// the argument checks of the reference (packed_grouped.cu:297-301)
+static bool packed_args_ok(const void* out, const void* x, const void* images, const void* formats, const void* ranges, unsigned count,
+                           unsigned hidden, unsigned inter) {
+  return out && x && out != x && images && formats && ranges && count && count <= 288 && hidden && hidden <= 4096 && hidden % 256 == 0 &&
+         inter && inter <= 4096 && inter % 256 == 0;
+}
+
 }  // namespace dmoe
 
 using namespace dmoe;
+
+extern "C" int hayate_glm_grouped_packed_gate_up(void* product, const void* x, const void* images, const void* formats, const void* ranges,
+                                                 unsigned count, unsigned hidden, unsigned intermediate, cudaStream_t st) {
+  if (!packed_args_ok(product, x, images, formats, ranges, count, hidden, intermediate)) return cudaErrorInvalidValue;
+  return launch_grouped_packed<false>(product, x, images, formats, ranges, count, hidden, intermediate, st);
+}
+
+extern "C" int hayate_glm_grouped_packed_down(void* out, const void* product, const void* images, const void* formats, const void* ranges,
+                                              unsigned count, unsigned hidden, unsigned intermediate, cudaStream_t st) {
+  if (!packed_args_ok(out, product, images, formats, ranges, count, hidden, intermediate)) return cudaErrorInvalidValue;
+  return launch_grouped_packed<true>(out, product, images, formats, ranges, count, hidden, intermediate, st);
+}
+
+// The reference picks one of four mma.sync tile shapes here; this library has one tcgen05 tile shape, so a valid id is
+// accepted and changes nothing.
+extern "C" int hayate_glm_grouped_packed_set_config(unsigned config) {
+  return config > 3 ? cudaErrorInvalidValue : cudaSuccess;
+}
+
+extern "C" int hayate_glm_grouped_packed_status(unsigned* host_status, cudaStream_t st) {
+  if (!host_status) return cudaErrorInvalidValue;
+  unsigned* dev = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&dev), g_packed_status);
+  if (e != cudaSuccess) return e;
+  e = cudaMemcpyAsync(host_status, dev, 4, cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaMemsetAsync(dev, 0, 4, st);
+  return e ? e : cudaStreamSynchronize(st);
+}
 
 extern "C" int hayate_glm_grouped(void* out, const void* x, const void* w, const void* ranges, unsigned groups, unsigned n, unsigned k,
                                   void* metadata, cudaStream_t st) {

@@ -262,6 +262,23 @@ int hayate_glm_gather(void* out, const void* x, const void* assignments, unsigne
 int hayate_glm_scatter(void* out, const void* x, const void* weights, const void* assignments, unsigned rows, unsigned hidden,
                        darask_stream_t stream);
 int hayate_glm_copy(void* out, const void* x, size_t bytes, darask_stream_t stream);
+/* Ragged grouped GEMM on the experts' packed NVFP4 images, read in place: the reference's names and signatures
+ * (engines/hayate/crates/kernels/src/glm53.rs:2843-2870, bodies cu/glm53/packed_grouped.cu:302-318).  images: device
+ * array of `count` image pointers ([gate | up | down] at the 256-byte-aligned stride of lowbit.cuh:9-13); formats:
+ * device array of `count` ExpertFormat (8 bytes: gate_up and down {format, grid, group, reserved}); ranges u32
+ * [count][2] = {rows, offset}.  gate_up: x [rows][hidden] bf16 -> product [rows][intermediate] bf16 =
+ * swiglu(bf16(x.gate * s_gate), bf16(x.up * s_up)); down: product -> out [rows][hidden] bf16 = bf16(product.down * s_down).
+ * count <= 288, hidden and intermediate multiples of 256 up to 4096, out != x (the reference's checks).  Only format 0
+ * (NVFP4) images are multiplied: the LOWBIT grids are outside this library, an expert with another format or a null
+ * image gets zero rows and bit 8 in the word hayate_glm_grouped_packed_status returns (and clears; synchronizes the
+ * stream; no counterpart in the reference, whose launchers have no status either).  set_config accepts the
+ * reference's ids 0-3 and changes nothing: there is one tcgen05 tile shape. */
+int hayate_glm_grouped_packed_set_config(unsigned config);
+int hayate_glm_grouped_packed_gate_up(void* product, const void* x, const void* images, const void* formats, const void* ranges,
+                                      unsigned count, unsigned hidden, unsigned intermediate, darask_stream_t stream);
+int hayate_glm_grouped_packed_down(void* out, const void* product, const void* images, const void* formats, const void* ranges,
+                                   unsigned count, unsigned hidden, unsigned intermediate, darask_stream_t stream);
+int hayate_glm_grouped_packed_status(unsigned* host_status /* host */, darask_stream_t stream);
 
 /* ---- FP8 prefill path -----------------------------------------------------------------------------------------
  * Ragged grouped GEMM on tcgen05 tensor cores over block-scaled e4m3 operands.  Replaces hayate_glm_grouped /
