@@ -22,7 +22,8 @@ class KogarashiMoe(ctypes.Structure):
         ("down_w", c_void_p), ("down_ty", c_int),
         ("sh_gate_w", c_void_p), ("sh_up_w", c_void_p), ("sh_down_w", c_void_p), ("sh_inp_w", c_void_p),
         ("n", c_void_p), ("x", c_void_p), ("logits", c_void_p), ("ids", c_void_p), ("prob", c_void_p),
-        ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("reserved", c_int),
+        ("workspace", c_void_p), ("workspace_bytes", c_size_t),
+        ("attn_out", c_void_p), ("norm_w", c_void_p), ("norm_eps", c_float), ("reserved", c_int),
     ]
 
 

@@ -91,6 +91,8 @@ struct FusedArgs {
   const uint8_t* gate_w; const uint8_t* up_w; const uint8_t* down_w;
   const uint8_t* sh_gate; const uint8_t* sh_up; const uint8_t* sh_down;
   const float* n; float* x; float* logits; int* ids; float* prob;
+  // optional layer entry: x += attn_out, n = x * rsqrt(mean(x^2) + norm_eps) * norm_w, written to n_out by CTA 0
+  const float* attn_out; const float* norm_w; float* n_out; float norm_eps;
   int H, F, E, K, G, has_shared, ldlog;
   int nblk1, row_bytes1, tps;                     // gate/up: 256-column blocks per row, bytes per row, tiles per group
   int nblk2, row_bytes2, rt2, down_q6;            // down: the same, row tiles of the output
@@ -461,6 +463,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   float* sm_prob = reinterpret_cast<float*>(smem + 128);             // [32]
   float* sm_misc = reinterpret_cast<float*>(smem + 256);             // [0] sigmoid of the shared gate logit
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + 272);
+  float* pss = reinterpret_cast<float*>(smem + 384);                 // [16] per-warp sums of squares (layer entry)
   float* part = reinterpret_cast<float*>(smem + 448);                // [16][2] router partial sums
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + a.off_bars);   // [nstage]
   uint64_t* empty = full + a.nstage;                                 // [nstage]
@@ -601,13 +604,29 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
     epoch_now = __ldcg(a.epoch);
     tag = make_tag(epoch_now);
     if (tid == 0) atomicAdd(a.seen, 1u);            // CTA 0 advances the counter only when every CTA has read it
-    const float* nsrc = a.n;
-    // the token's activations: this thread's chunks stay in registers for the planes below
+    // the token's activations: this thread's chunks stay in registers for the planes below. With the layer entry the
+    // kernel forms them itself: u = (x + attn_out) * norm_w here, times the norm's scale once the sum of squares of the
+    // whole vector is known (the logits are linear in that scale, so the router rows are multiplied with u meanwhile).
     float4 nv[MAXC];
+    float sumsq = 0.f;
 #pragma unroll
     for (int c = 0; c < MAXC; ++c) {
       const int i = tid + c * kFusedConsumers * 32;
-      nv[c] = i < chunks4 ? __ldcg(reinterpret_cast<const float4*>(nsrc) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      nv[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (i < chunks4) {
+        if (a.norm_w) {
+          float4 xv = __ldcg(reinterpret_cast<const float4*>(a.x) + i);
+          if (a.attn_out) {
+            const float4 o = __ldcg(reinterpret_cast<const float4*>(a.attn_out) + i);
+            xv = make_float4(xv.x + o.x, xv.y + o.y, xv.z + o.z, xv.w + o.w);
+          }
+          const float4 wv = __ldg(reinterpret_cast<const float4*>(a.norm_w) + i);
+          sumsq = fmaf(xv.x, xv.x, fmaf(xv.y, xv.y, fmaf(xv.z, xv.z, fmaf(xv.w, xv.w, sumsq))));
+          nv[c] = make_float4(xv.x * wv.x, xv.y * wv.y, xv.z * wv.z, xv.w * wv.w);
+        } else {
+          nv[c] = __ldcg(reinterpret_cast<const float4*>(a.n) + i);
+        }
+      }
     }
     cp_async_wait<0>();
     float dot[2] = {0.f, 0.f};
@@ -628,11 +647,26 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
       }
     dot[0] = warp_sum(dot[0]);
     dot[1] = warp_sum(dot[1]);
+    sumsq = warp_sum(sumsq);
     if (lane == 0) {
       part[warp * 2] = dot[0];
       part[warp * 2 + 1] = dot[1];
+      pss[warp] = sumsq;
     }
     named_barrier(1, kFusedConsumers * 32);
+    float nscale = 1.f;
+    if (a.norm_w) {
+      float total = 0.f;
+#pragma unroll
+      for (int w = 0; w < kFusedConsumers; ++w) total += pss[w];        // the same order in every thread and CTA
+      nscale = rsqrtf(total / float(a.H) + a.norm_eps);
+#pragma unroll
+      for (int c = 0; c < MAXC; ++c) {
+        nv[c] = make_float4(nv[c].x * nscale, nv[c].y * nscale, nv[c].z * nscale, nv[c].w * nscale);
+        const int i = tid + c * kFusedConsumers * 32;
+        if (cta == 0 && i < chunks4) reinterpret_cast<float4*>(a.n_out)[i] = nv[c];
+      }
+    }
     if (warp == 0) {
       // lanes 0-15 hold the partial sums of row 0, lanes 16-31 those of row 1; summed in a fixed tree
       float v = part[(lane & 15) * 2 + (lane >> 4)];
@@ -640,6 +674,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
       v += __shfl_xor_sync(0xffffffffu, v, 4);
       v += __shfl_xor_sync(0xffffffffu, v, 2);
       v += __shfl_xor_sync(0xffffffffu, v, 1);
+      v *= nscale;
       const int q = lane >> 4, row = cta + q * grid;
       if ((lane & 15) == 0 && q < my_rows && row < a.E) {
         if (a.router_bias) v += a.router_bias[row];
@@ -886,7 +921,7 @@ __global__ void __launch_bounds__(kFusedThreads, 1) kogarashi_decode1_kernel(con
   //      row i = tid * grid + cta; the down rows arrive tagged ----
   const int row = tid * grid + cta;
   if (ok && row < a.H) {
-    const float xin = a.x[row];
+    const float xin = a.x[row] + (a.attn_out ? a.attn_out[row] : 0.f);
     bool good = true;
     float ysh[8] = {};
     if (a.has_shared) good = poll_strided(a.ty + row, 0, 1, tag, ysh, a.status, abort_flag);

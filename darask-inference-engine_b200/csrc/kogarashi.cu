@@ -109,6 +109,34 @@ static cudaError_t launch_gemv_ggml(int ty, const GemvArgs& a, cudaStream_t st) 
   return cudaErrorInvalidValue;
 }
 
+// ---- layer entry for the staged launches: `residual` and `rms_native` of the reference as one launch --------------
+// One block of 256 threads per token, sums taken in the reference's order (native.cu:8-17, 89-96: thread t adds
+// elements t, t + 256, ... with fused multiply-adds, warps by xor shuffles 16 .. 1, then the eight warp sums the same
+// way), so that x and n come out bit for bit as from the reference's two kernels.
+__global__ void __launch_bounds__(256) kogarashi_entry_kernel(float* x, const float* attn_out, const float* w, float* n, int h, float eps) {
+  __shared__ float partial[8];
+  pdl_wait();
+  pdl_launch();
+  float* xr = x + size_t(blockIdx.x) * h;
+  float* nr = n + size_t(blockIdx.x) * h;
+  const float* ar = attn_out ? attn_out + size_t(blockIdx.x) * h : nullptr;
+  float v = 0.f;
+  for (int i = threadIdx.x; i < h; i += 256) {
+    float xv = xr[i];
+    if (ar) {
+      xv += ar[i];
+      xr[i] = xv;
+    }
+    v = fmaf(xv, xv, v);
+  }
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = v;
+  __syncthreads();
+  v = warp_sum((threadIdx.x & 31) < 8 ? partial[threadIdx.x & 31] : 0.f);      // every warp forms the same total, as warp 0 of the reference does
+  const float scale = rsqrtf(v / h + eps);
+  for (int i = threadIdx.x; i < h; i += 256) nr[i] = xr[i] * scale * w[i];
+}
+
 // ---- the one-token layer as one launch (decode_fused.cuh) ---------------------------------------------------
 // Fills `f` and returns true when the shape can take the single-launch path.
 static bool fused_plan(const KogarashiMoe* d, const KogarashiWs& w, FusedArgs* f, int* smem_bytes) {
@@ -155,7 +183,7 @@ static bool fused_plan(const KogarashiMoe* d, const KogarashiWs& w, FusedArgs* f
   a.router_w = static_cast<const float*>(d->router_w); a.router_bias = d->router_bias; a.sh_inp = static_cast<const float*>(d->sh_inp_w);
   a.gate_w = static_cast<const uint8_t*>(d->gate_w); a.up_w = static_cast<const uint8_t*>(d->up_w); a.down_w = static_cast<const uint8_t*>(d->down_w);
   a.sh_gate = static_cast<const uint8_t*>(d->sh_gate_w); a.sh_up = static_cast<const uint8_t*>(d->sh_up_w); a.sh_down = static_cast<const uint8_t*>(d->sh_down_w);
-  a.n = d->n; a.x = d->x; a.logits = d->logits; a.ids = d->ids; a.prob = d->prob;
+  a.n = d->n; a.n_out = d->norm_w ? d->n : nullptr; a.attn_out = d->attn_out; a.norm_w = d->norm_w; a.norm_eps = d->norm_eps; a.x = d->x; a.logits = d->logits; a.ids = d->ids; a.prob = d->prob;
   a.status = w.status; a.epoch = w.epoch; a.seen = w.epoch + 1; a.tlog = w.tlog; a.th = w.th; a.ty = w.ty;
   *f = a;
   return true;
@@ -229,6 +257,8 @@ static bool descriptor_ok(const KogarashiMoe* d) {
   if (d->router_ty != DARASK_GGML_F32 && d->router_ty != DARASK_GGML_BF16 && d->router_ty != DARASK_GGML_F16) return false;
   if (row_bytes_of(d->gate_ty, H) == 0 || row_bytes_of(d->down_ty, F) == 0) return false;
   if (d->sh_gate_w && (!d->sh_up_w || !d->sh_down_w || !d->sh_inp_w)) return false;
+  if (d->attn_out && !d->norm_w) return false;
+  if (d->norm_w && !(d->norm_eps >= 0.f)) return false;
   return true;
 }
 
@@ -246,6 +276,11 @@ extern "C" int kogarashi_moe_layer(const KogarashiMoe* d, cudaStream_t st) {
     if (!g_force_staged && fused_plan(d, w, &f, &smem_bytes)) return launch_fused(f, smem_bytes, st);
   }
 
+  // 0. layer entry (optional): x += attn_out, n = rms_norm(x) * norm_w
+  if (d->norm_w) {
+    const cudaError_t e0 = launch_pdl(kogarashi_entry_kernel, dim3(T), dim3(256), size_t(0), st, d->x, d->attn_out, d->norm_w, d->n, H, d->norm_eps);
+    if (e0) return e0;
+  }
   // 1. router projection, top-k, permutation
   RouterArgs r = {};
   r.w = d->router_w; r.extra = shared ? d->sh_inp_w : nullptr; r.x = d->n; r.row_bias = d->router_bias; r.logits = d->logits; r.extra_out = w.sg;

@@ -69,8 +69,11 @@ class KogarashiMoeLayer:
         w = self.weights.get(name)
         return (w.data.data_ptr(), w.ty) if w is not None else (None, 0)
 
-    def forward(self, x: torch.Tensor, n: torch.Tensor) -> torch.Tensor:
-        """x [T,H] float32 residual stream (updated in place), n [T,H] float32 normalised input."""
+    def forward(self, x: torch.Tensor, n: torch.Tensor, attn_out: torch.Tensor | None = None, norm_w: torch.Tensor | None = None,
+                eps: float = 1e-6) -> torch.Tensor:
+        """x [T,H] float32 residual stream (updated in place), n [T,H] float32 normalised input.
+        With `norm_w` (post_attention_norm.weight) the layer entry of engine.rs:507-526 is part of the call: x += attn_out
+        (when given), n = rms_norm(x) * norm_w is computed by the layer and written to `n`."""
         t = n.shape[0]
         if t > self.max_tokens or n.shape != x.shape or n.shape[1] != self.hidden:
             raise ValueError("token count / shape")
@@ -88,6 +91,13 @@ class KogarashiMoeLayer:
         d.sh_down_w = self._w("ffn_down_shexp.weight")[0]
         d.sh_inp_w = self._w("ffn_gate_inp_shexp.weight")[0]
         d.n, d.x = n.data_ptr(), x.data_ptr()
+        if norm_w is not None:
+            if norm_w.dtype != torch.float32 or norm_w.numel() != self.hidden or (attn_out is not None and (attn_out.shape != x.shape or attn_out.dtype != torch.float32)):
+                raise ValueError("norm_w / attn_out")
+            d.norm_w, d.norm_eps = norm_w.data_ptr(), eps
+            d.attn_out = attn_out.data_ptr() if attn_out is not None else None
+        elif attn_out is not None:
+            raise ValueError("attn_out needs norm_w")
         d.logits, d.ids, d.prob = self.logits.data_ptr(), self.ids.data_ptr(), self.prob.data_ptr()
         d.workspace, d.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
         _lib.check(_lib.lib().kogarashi_moe_layer(ctypes.byref(d), self._stream()), "kogarashi_moe_layer")

@@ -107,12 +107,19 @@ typedef struct {
   const void* sh_gate_w; const void* sh_up_w;          /* ffn_{gate,up}_shexp, same types; NULL: no shared expert */
   const void* sh_down_w;                               /* ffn_down_shexp                            */
   const void* sh_inp_w;                                /* ffn_gate_inp_shexp  [hidden], type router_ty */
-  const float* n;                                      /* [tokens][hidden] normalised input (buffer "n") */
+  float* n;                                            /* [tokens][hidden] normalised input (buffer "n"); written when norm_w is set */
   float* x;                                            /* [tokens][hidden] residual stream, updated in place ("x") */
   float* logits;                                       /* [tokens][experts]   ("router")            */
   int* ids;                                            /* [tokens][topk]      ("ids")               */
   float* prob;                                         /* [tokens][topk]      ("prob")              */
   void* workspace; size_t workspace_bytes;
+  /* Optional layer entry, the reference's `residual` and `rms_native` launches in front of the MoE block
+   * (engines/kogarashi/kernels/native.cu:89-96, engine.rs:507-526).  norm_w != NULL: first x += attn_out (skipped when
+   * attn_out is NULL), then n = x * rsqrt(mean(x^2) + norm_eps) * norm_w is formed by the layer itself and written to
+   * `n`, which is then an output buffer.  norm_w == NULL: `n` is an input and attn_out must be NULL. */
+  const float* attn_out;                               /* [tokens][hidden] ("out") */
+  const float* norm_w;                                 /* post_attention_norm.weight [hidden] */
+  float norm_eps;
   int reserved;                                        /* must be 0 */
 } KogarashiMoe;
 size_t kogarashi_moe_workspace_bytes(int hidden, int inter, int experts, int topk, int tokens);

@@ -48,6 +48,21 @@ def kogarashi_logits(layer: KogarashiLayer, n: np.ndarray) -> np.ndarray:
     return (layer.router.astype(np.float64) @ n.astype(np.float64).T).T.astype(np.float32)
 
 
+def kogarashi_entry(x: np.ndarray, attn_out, norm_w: np.ndarray, eps: float):
+    """The two launches in front of the MoE block: `residual` (x += out) and `rms_native`
+    (n = x * rsqrt(sum(x^2) / h + eps) * w), engines/kogarashi/kernels/native.cu:89-96, called at engine.rs:507-526.
+    float32 x and n as the kernels produce them, except that the sum of squares is taken in float64 here (the kernel adds
+    in float32 in a fixed thread order; the difference stays below 1e-6 relative)."""
+    x = np.asarray(x, np.float32)
+    if attn_out is not None:
+        x = (x + np.asarray(attn_out, np.float32)).astype(np.float32)
+    h = x.shape[-1]
+    mean = (x.astype(np.float64) ** 2).sum(-1, keepdims=True) / h
+    scale = (1.0 / np.sqrt(mean.astype(np.float32) + np.float32(eps))).astype(np.float32)
+    n = ((x * scale).astype(np.float32) * np.asarray(norm_w, np.float32)).astype(np.float32)
+    return x, n
+
+
 def kogarashi_forward(layer: KogarashiLayer, x: np.ndarray, n: np.ndarray, logits=None):
     """x float32 [T,H] residual stream, n float32 [T,H] normalised input.
     -> dict(logits, ids, prob, out) with out = x + sum_s p_s down_s + sigmoid(sg) shared
