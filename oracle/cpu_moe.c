@@ -122,6 +122,84 @@ static void decode_row(const Mat* m, int r, float* out) {
   }
 }
 
+/* ---- AVX2 + FMA row products for the two GGUF formats of the decode benchmark -------------------------------------
+ * The timed CPU baseline uses them when the host has AVX2 and FMA (the reference's CPU expert pool is AVX2 code on
+ * pinned threads: engines/hayate/crates/kernels/src/cpu_experts.rs:73-78); the parity checks keep the scalar loops
+ * above.  A row is multiplied while it is decoded: per 32-column sub-block sum(q x) and sum(x) in eight float lanes,
+ * then ds * sum(q x) - dmin m * sum(x) (Q4_K) or d sc * sum((q - 32) x) (Q6_K) in float32. */
+#include <immintrin.h>
+static int simd_enabled = 0;
+void cpu_set_simd(int on) { simd_enabled = on && __builtin_cpu_supports("avx2") && __builtin_cpu_supports("fma"); }
+int cpu_simd(void) { return simd_enabled; }
+
+__attribute__((target("avx2,fma"))) static inline float hsum8(__m256 v) {
+  __m128 lo = _mm256_castps256_ps128(v), hi = _mm256_extractf128_ps(v, 1);
+  lo = _mm_add_ps(lo, hi);
+  lo = _mm_add_ps(lo, _mm_movehl_ps(lo, lo));
+  lo = _mm_add_ss(lo, _mm_shuffle_ps(lo, lo, 1));
+  return _mm_cvtss_f32(lo);
+}
+__attribute__((target("avx2,fma"))) static float q4k_row_dot_avx2(const uint8_t* row, const float* x, int k) {
+  float total = 0.f;
+  const __m256i mask = _mm256_set1_epi32(15);
+  for (int b = 0; b < k / 256; ++b) {
+    const uint8_t* bl = row + b * 144; const uint8_t* sc = bl + 4;
+    uint16_t hd, hm; memcpy(&hd, bl, 2); memcpy(&hm, bl + 2, 2);
+    const float d = half_to_float(hd), dm = half_to_float(hm);
+    for (int p = 0; p < 4; ++p) {                       /* 32 bytes: low nibbles sub-block 2p, high nibbles 2p + 1 */
+      const uint8_t* q = bl + 16 + p * 32;
+      const float* x0 = x + b * 256 + p * 64; const float* x1 = x0 + 32;
+      __m256 q0 = _mm256_setzero_ps(), q1 = _mm256_setzero_ps(), s0 = _mm256_setzero_ps(), s1 = _mm256_setzero_ps();
+      for (int l = 0; l < 32; l += 8) {
+        const __m256i w = _mm256_cvtepu8_epi32(_mm_loadl_epi64((const __m128i*)(q + l)));
+        const __m256 lo = _mm256_cvtepi32_ps(_mm256_and_si256(w, mask)), hi = _mm256_cvtepi32_ps(_mm256_srli_epi32(w, 4));
+        const __m256 a = _mm256_loadu_ps(x0 + l), c = _mm256_loadu_ps(x1 + l);
+        q0 = _mm256_fmadd_ps(lo, a, q0); s0 = _mm256_add_ps(s0, a);
+        q1 = _mm256_fmadd_ps(hi, c, q1); s1 = _mm256_add_ps(s1, c);
+      }
+      for (int h = 0; h < 2; ++h) {
+        const int g = 2 * p + h;
+        const int scale = g < 4 ? (sc[g] & 63) : ((sc[g + 4] & 15) | ((sc[g - 4] >> 6) << 4));
+        const int mi = g < 4 ? (sc[g + 4] & 63) : ((sc[g + 4] >> 4) | ((sc[g] >> 6) << 4));
+        total += d * (float)scale * hsum8(h ? q1 : q0) - dm * (float)mi * hsum8(h ? s1 : s0);
+      }
+    }
+  }
+  return total;
+}
+__attribute__((target("avx2,fma"))) static float q6k_row_dot_avx2(const uint8_t* row, const float* x, int k) {
+  float total = 0.f;
+  const __m256i m4 = _mm256_set1_epi32(15), m2 = _mm256_set1_epi32(3), off = _mm256_set1_epi32(32);
+  for (int b = 0; b < k / 256; ++b) {
+    const uint8_t* bl = row + b * 210; const int8_t* sc = (const int8_t*)(bl + 192);
+    uint16_t hd; memcpy(&hd, bl + 208, 2); const float d = half_to_float(hd);
+    for (int n = 0; n < 2; ++n)
+      for (int g = 0; g < 4; ++g)
+        for (int half = 0; half < 2; ++half) {          /* 16 columns = one scale */
+          const uint8_t* ql = bl + n * 64 + (g & 1) * 32 + half * 16; const uint8_t* qh = bl + 128 + n * 32 + half * 16;
+          const float* xs = x + b * 256 + n * 128 + g * 32 + half * 16;
+          __m256 acc = _mm256_setzero_ps();
+          for (int l = 0; l < 16; l += 8) {
+            __m256i lo = _mm256_cvtepu8_epi32(_mm_loadl_epi64((const __m128i*)(ql + l)));
+            __m256i hi = _mm256_cvtepu8_epi32(_mm_loadl_epi64((const __m128i*)(qh + l)));
+            lo = _mm256_and_si256(_mm256_srli_epi32(lo, (g / 2) * 4), m4);
+            hi = _mm256_slli_epi32(_mm256_and_si256(_mm256_srli_epi32(hi, g * 2), m2), 4);
+            const __m256 qv = _mm256_cvtepi32_ps(_mm256_sub_epi32(_mm256_or_si256(lo, hi), off));
+            acc = _mm256_fmadd_ps(qv, _mm256_loadu_ps(xs + l), acc);
+          }
+          total += d * (float)sc[n * 8 + half + g * 2] * hsum8(acc);
+        }
+  }
+  return total;
+}
+/* one row of a quantized matrix times one activation row, through the AVX2 path when it is on and has the format */
+static int simd_row_dot(const Mat* m, int r, const float* x, float* out) {
+  if (!simd_enabled) return 0;
+  if (m->fmt == FMT_Q4K) { *out = q4k_row_dot_avx2(m->w + (size_t)r * (m->k / 256) * 144, x, m->k); return 1; }
+  if (m->fmt == FMT_Q6K) { *out = q6k_row_dot_avx2(m->w + (size_t)r * (m->k / 256) * 210, x, m->k); return 1; }
+  return 0;
+}
+
 /* dot of a decoded row with ntok activation rows; float partial sums in 16 lanes (vectorisable)
  * or double when f64 is set. */
 static void row_dots(const float* w, const float* x, int k, int ntok, int ldx, double* out, int f64) {
@@ -229,11 +307,15 @@ int cpu_kogarashi_layer(const KogarashiCpu* L, int threads) {
       const int is_sh = gi == nact; const int e = is_sh ? 0 : active[gi];
       Mat mg = {L->gate_ty, is_sh ? L->sh_gate : L->gate + (size_t)e * F * grow, NULL, 1.f, F, H, 0};
       Mat mu = {L->up_ty, is_sh ? L->sh_up : L->up + (size_t)e * F * urow, NULL, 1.f, F, H, 0};
-      decode_row(&mg, r, wg); decode_row(&mu, r, wu);
       const int cnt = is_sh ? T : count[e];
+      const int simd = simd_enabled && (mg.fmt == FMT_Q4K || mg.fmt == FMT_Q6K);
+      if (!simd) { decode_row(&mg, r, wg); decode_row(&mu, r, wu); }
       for (int i = 0; i < cnt; ++i) {
         const int a = is_sh ? -1 : assign[start[e] + i]; const int t = is_sh ? i : a / K, s = is_sh ? K : a % K;
-        double g, u; row_dots(wg, L->n + (size_t)t * H, H, 1, H, &g, 0); row_dots(wu, L->n + (size_t)t * H, H, 1, H, &u, 0);
+        double g, u;
+        float gs, us;
+        if (simd && simd_row_dot(&mg, r, L->n + (size_t)t * H, &gs) && simd_row_dot(&mu, r, L->n + (size_t)t * H, &us)) { g = gs; u = us; }
+        else { row_dots(wg, L->n + (size_t)t * H, H, 1, H, &g, 0); row_dots(wu, L->n + (size_t)t * H, H, 1, H, &u, 0); }
         const float gf = (float)g; ff[((size_t)t * slots + s) * F + r] = gf * (1.f / (1.f + expf(-gf))) * (float)u;
       }
     }
@@ -247,11 +329,15 @@ int cpu_kogarashi_layer(const KogarashiCpu* L, int threads) {
     for (int gi = 0; gi < groups; ++gi) for (int r = 0; r < H; ++r) {
       const int is_sh = gi == nact; const int e = is_sh ? 0 : active[gi];
       Mat md = {L->down_ty, is_sh ? L->sh_down : L->down + (size_t)e * H * drow, NULL, 1.f, H, F, 0};
-      decode_row(&md, r, wd);
       const int cnt = is_sh ? T : count[e];
+      const int simd = simd_enabled && (md.fmt == FMT_Q4K || md.fmt == FMT_Q6K);
+      if (!simd) decode_row(&md, r, wd);
       for (int i = 0; i < cnt; ++i) {
         const int a = is_sh ? -1 : assign[start[e] + i]; const int t = is_sh ? i : a / K, s = is_sh ? K : a % K;
-        double v; row_dots(wd, ff + ((size_t)t * slots + s) * F, F, 1, F, &v, 0);
+        double v;
+        float vs;
+        if (simd && simd_row_dot(&md, r, ff + ((size_t)t * slots + s) * F, &vs)) v = vs;
+        else row_dots(wd, ff + ((size_t)t * slots + s) * F, F, 1, F, &v, 0);
         dn[((size_t)t * slots + s) * H + r] = (float)v;
       }
     }
