@@ -110,6 +110,14 @@ _SIGNATURES = {
     "darask_fp8_ep_experts": (c_int, [c_void_p, c_void_p, ctypes.c_ulonglong, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                       c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "darask_fp8_ep_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "darask_fp8_ep_packed_row_bytes": (c_size_t, [c_int]),
+    "darask_fp8_ep_dispatch_packed": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                              c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "darask_fp8_ep_regroup_packed": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "darask_fp8_ep_reduce": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                     c_void_p, c_void_p, c_void_p, c_void_p]),
+    "darask_fp8_ep_sum": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "darask_fp8_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "darask_fp8_moe_layer": (c_int, [ctypes.POINTER(DaraskFp8Moe), c_void_p]),
     "darask_fp8_moe_status": (c_int, [c_void_p, ctypes.POINTER(c_uint), c_void_p]),

@@ -42,7 +42,8 @@ __global__ void __launch_bounds__(256) combine_rows_kernel(float* out, const flo
 // Rows received from `ranks` peers arrive grouped by source rank and, inside a source, by ascending local expert.
 // plan: per local expert the range {rows, offset} of the regrouped order (expert-major, then source rank, then
 // arrival order) and per (source, expert) segment its first received row and its first regrouped row.
-__global__ void __launch_bounds__(1024) ep_plan_kernel(const int* counts, int ranks, int local, unsigned* ranges, int* seg_src, int* seg_dst) {
+__global__ void __launch_bounds__(1024) ep_plan_kernel(const int* counts, int ranks, int local, unsigned* ranges, int* seg_src, int* seg_dst,
+                                                       int slab /* rows per source slab; 0: sources follow each other without gaps */) {
   __shared__ int expert_off[1025];
   __shared__ int rank_off[65];
   pdl_wait();
@@ -62,7 +63,7 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const int* counts, int ra
   if (tid == 32) {
     int run = 0;
     for (int r = 0; r < ranks; ++r) {
-      rank_off[r] = run;
+      rank_off[r] = slab ? r * slab : run;
       for (int e = 0; e < local; ++e) run += counts[r * local + e];
     }
   }
@@ -91,6 +92,109 @@ __global__ void __launch_bounds__(256) ep_regroup_rows_kernel(const uint8_t* in_
   for (int c = threadIdx.x; c < k / 16; c += 256)
     reinterpret_cast<uint4*>(codes + dst * k)[c] = __ldg(reinterpret_cast<const uint4*>(in_codes + src * k) + c);
   for (int c = threadIdx.x; c < k / 128; c += 256) scales[dst * (k / 128) + c] = __ldg(in_scales + src * (k / 128) + c);
+}
+
+// ---- expert-parallel exchange without split sizes on the host ---------------------------------------------------
+// Rows travel in slabs of fixed capacity, one per (source, destination) pair, as packed rows
+//   [hidden e4m3 codes | hidden/128 float32 scales | float32 routing weight | int32 token of the source rank | pad to 16]
+// so that both exchanges are equal-split all-to-alls and no device->host copy sits between the launches; the expert
+// rank adds each token's rows (weight * row, ascending local expert) before they return, so what comes back is one
+// float32 row per (token, expert rank), dense by token.
+DEVI int packed_row_bytes(int k) { return (k + 4 * (k / 128) + 8 + 15) / 16 * 16; }
+
+// dispatch row i (ascending expert order) -> slab of its expert's rank, at the row's index among that rank's rows
+__global__ void __launch_bounds__(256) gather_packed_kernel(const uint8_t* codes, const float* scales, const unsigned* assignments,
+                                                            const int* counters, const int* ids, const float* prob, const unsigned* ranges,
+                                                            int topk, int k, int local, int cap, uint8_t* send, unsigned* position) {
+  pdl_wait();
+  pdl_launch();
+  const int i = blockIdx.x;
+  if (i >= __ldcg(counters + 1)) return;
+  const unsigned asg = __ldcg(assignments + i);
+  const int tok = int(asg / topk), r = __ldcg(ids + asg) / local;
+  const int first = int(__ldcg(ranges + 2 * (r * local) + 1));            // first dispatch row that goes to rank r
+  uint8_t* row = send + (size_t(r) * cap + size_t(i - first)) * packed_row_bytes(k);
+  if (threadIdx.x == 0) {
+    position[asg] = i;
+    *reinterpret_cast<float*>(row + k + 4 * (k / 128)) = __ldg(prob + asg);
+    *reinterpret_cast<int*>(row + k + 4 * (k / 128) + 4) = tok;
+  }
+  for (int c = threadIdx.x; c < k / 16; c += 256) reinterpret_cast<uint4*>(row)[c] = __ldg(reinterpret_cast<const uint4*>(codes + size_t(tok) * k) + c);
+  for (int c = threadIdx.x; c < k / 128; c += 256) reinterpret_cast<float*>(row + k)[c] = __ldg(scales + size_t(tok) * (k / 128) + c);
+}
+// regrouped row <- packed row of its slab; also the row's source rank, token and routing weight
+__global__ void __launch_bounds__(256) ep_unpack_rows_kernel(const uint8_t* recv, const unsigned* row_map, const unsigned* ranges, int local,
+                                                             int k, int cap, uint8_t* codes, float* scales, int* meta_src, int* meta_tok,
+                                                             float* meta_prob) {
+  pdl_wait();
+  pdl_launch();
+  const unsigned total = __ldcg(ranges + 2 * (local - 1)) + __ldcg(ranges + 2 * (local - 1) + 1);
+  const size_t dst = blockIdx.x;
+  if (dst >= total) return;
+  const size_t src = __ldcg(row_map + dst);
+  const uint8_t* row = recv + src * packed_row_bytes(k);
+  for (int c = threadIdx.x; c < k / 16; c += 256) reinterpret_cast<uint4*>(codes + dst * k)[c] = __ldg(reinterpret_cast<const uint4*>(row) + c);
+  for (int c = threadIdx.x; c < k / 128; c += 256) scales[dst * (k / 128) + c] = __ldg(reinterpret_cast<const float*>(row + k) + c);
+  if (threadIdx.x == 0) {
+    meta_src[dst] = int(src / size_t(cap));
+    meta_prob[dst] = __ldg(reinterpret_cast<const float*>(row + k + 4 * (k / 128)));
+    meta_tok[dst] = __ldg(reinterpret_cast<const int*>(row + k + 4 * (k / 128) + 4));
+  }
+}
+// the rows of every (source rank, token): list[(s * tcap + t) * topk + j]; count[] must be zero on entry
+__global__ void __launch_bounds__(256) ep_index_kernel(const unsigned* ranges, int local, const int* meta_src, const int* meta_tok, int tcap,
+                                                       int topk, int* count, int* list, unsigned* status) {
+  pdl_wait();
+  pdl_launch();
+  const unsigned total = __ldcg(ranges + 2 * (local - 1)) + __ldcg(ranges + 2 * (local - 1) + 1);
+  const unsigned i = blockIdx.x * 256 + threadIdx.x;
+  if (i >= total) return;
+  const int t = meta_tok[i], slot_of = meta_src[i] * tcap + t;
+  if (t < 0 || t >= tcap) { atomicOr(status, kStatusBadRoute); return; }
+  const int j = atomicAdd(count + slot_of, 1);
+  if (j < topk) list[size_t(slot_of) * topk + j] = int(i);
+  else atomicOr(status, kStatusBadRoute);
+}
+// z[s][t] = sum over the rows of (s, t), ascending row (= ascending local expert), of weight * y[row]; zero without rows
+__global__ void __launch_bounds__(256) ep_reduce_kernel(const float* y, const float* meta_prob, const int* count, const int* list, int topk,
+                                                        int hidden, float* z) {
+  __shared__ int rows[32];
+  __shared__ float w[32];
+  pdl_wait();
+  pdl_launch();
+  const size_t slot_of = blockIdx.x;
+  const int n = min(__ldcg(count + slot_of), topk);
+  if (threadIdx.x == 0) {
+    for (int j = 0; j < n; ++j) {                       // insertion sort: the order in which the rows were indexed is arbitrary
+      const int v = __ldcg(list + slot_of * topk + j);
+      int q = j;
+      while (q > 0 && rows[q - 1] > v) { rows[q] = rows[q - 1]; --q; }
+      rows[q] = v;
+    }
+    for (int j = 0; j < n; ++j) w[j] = __ldg(meta_prob + rows[j]);
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < hidden / 4; c += 256) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < n; ++j) {
+      const float4 a = __ldcs(reinterpret_cast<const float4*>(y + size_t(rows[j]) * hidden) + c);
+      v.x = fmaf(w[j], a.x, v.x); v.y = fmaf(w[j], a.y, v.y); v.z = fmaf(w[j], a.z, v.z); v.w = fmaf(w[j], a.w, v.w);
+    }
+    reinterpret_cast<float4*>(z + slot_of * hidden)[c] = v;
+  }
+}
+// out[t] = sum over the expert ranks, ascending, of their partial rows
+__global__ void __launch_bounds__(256) ep_sum_kernel(float* out, const float* zr, int ranks, int tcap, int hidden) {
+  pdl_wait();
+  pdl_launch();
+  const int t = blockIdx.y, c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= hidden / 4) return;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int r = 0; r < ranks; ++r) {
+    const float4 a = __ldcs(reinterpret_cast<const float4*>(zr + (size_t(r) * tcap + t) * hidden) + c);
+    v.x += a.x; v.y += a.y; v.z += a.z; v.w += a.w;
+  }
+  reinterpret_cast<float4*>(out + size_t(t) * hidden)[c] = v;
 }
 
 typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -249,10 +353,11 @@ extern "C" size_t darask_fp8_ep_dispatch_scratch_bytes(int hidden, int experts, 
          align_up(size_t(tokens) * (hidden / 128) * 4, 1024);
 }
 
-extern "C" int darask_fp8_ep_dispatch(const void* x, const float* logits, int hidden, int experts, int topk, int tokens, int* ids,
-                                      float* prob, void* send_codes, float* send_scales, unsigned* ranges, unsigned* position,
-                                      void* scratch, size_t scratch_bytes, cudaStream_t st) {
-  if (!x || !logits || !ids || !prob || !send_codes || !send_scales || !ranges || !position || !scratch || hidden < 128 ||
+// ranks > 0: packed slabs of `cap` rows per destination rank into send_codes (send_scales unused)
+static int ep_dispatch(const void* x, const float* logits, int hidden, int experts, int topk, int tokens, int* ids, float* prob,
+                       void* send_codes, float* send_scales, unsigned* ranges, unsigned* position, void* scratch, size_t scratch_bytes,
+                       int ranks, int cap, cudaStream_t st) {
+  if (!x || !logits || !ids || !prob || !send_codes || (!send_scales && !ranks) || !ranges || !position || !scratch || hidden < 128 ||
       hidden % 128 || experts < topk || experts > 1024 || topk < 1 || topk > 32 || tokens < 1 ||
       scratch_bytes < darask_fp8_ep_dispatch_scratch_bytes(hidden, experts, topk, tokens))
     return cudaErrorInvalidValue;
@@ -275,9 +380,69 @@ extern "C" int darask_fp8_ep_dispatch(const void* x, const float* logits, int hi
     if ((e = launch_permute_large(perm, perm_scratch, st))) return e;
   } else if ((e = launch_pdl(permute_kernel<0>, dim3(1), dim3(1024), size_t(experts + 1) * 4, st, perm))) return e;
   if ((e = (cudaError_t)darask_quantize_fp8_act(xq, xs, x, 1, tokens, hidden, st))) return e;
+  if (ranks)
+    return launch_pdl(gather_packed_kernel, dim3(tokens * topk), dim3(256), 0, st, (const uint8_t*)xq, (const float*)xs,
+                      (const unsigned*)assignments, (const int*)counters, (const int*)ids, (const float*)prob, (const unsigned*)ranges, topk,
+                      hidden, experts / ranks, cap, static_cast<uint8_t*>(send_codes), position);
   return launch_pdl(gather_fp8_kernel, dim3(tokens * topk), dim3(256), 0, st, (const uint8_t*)xq, (const float*)xs,
                     (const unsigned*)assignments, (const int*)counters, topk, hidden, static_cast<uint8_t*>(send_codes), send_scales,
                     position);
+}
+
+extern "C" int darask_fp8_ep_dispatch(const void* x, const float* logits, int hidden, int experts, int topk, int tokens, int* ids,
+                                      float* prob, void* send_codes, float* send_scales, unsigned* ranges, unsigned* position,
+                                      void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  return ep_dispatch(x, logits, hidden, experts, topk, tokens, ids, prob, send_codes, send_scales, ranges, position, scratch, scratch_bytes,
+                     0, 0, st);
+}
+
+extern "C" size_t darask_fp8_ep_packed_row_bytes(int hidden) { return hidden >= 128 && hidden % 128 == 0 ? size_t((hidden + 4 * (hidden / 128) + 8 + 15) / 16 * 16) : 0; }
+
+extern "C" int darask_fp8_ep_dispatch_packed(const void* x, const float* logits, int hidden, int experts, int topk, int tokens, int ranks,
+                                             int cap, int* ids, float* prob, void* send, unsigned* ranges, unsigned* position,
+                                             void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  if (ranks < 1 || ranks > 64 || experts % ranks || cap < tokens * topk) return cudaErrorInvalidValue;   // a slab holds a rank's worst case
+  return ep_dispatch(x, logits, hidden, experts, topk, tokens, ids, prob, send, nullptr, ranges, position, scratch, scratch_bytes, ranks,
+                     cap, st);
+}
+
+extern "C" int darask_fp8_ep_regroup_packed(const int* recv_counts, int ranks, int local_experts, const void* recv, int cap, int hidden,
+                                            void* codes, float* scales, unsigned* ranges, unsigned* row_map, int* meta_src, int* meta_tok,
+                                            float* meta_prob, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  if (!recv_counts || !recv || !codes || !scales || !ranges || !row_map || !meta_src || !meta_tok || !meta_prob || !scratch || ranks < 1 ||
+      ranks > 64 || local_experts < 1 || local_experts > 1024 || hidden < 128 || hidden % 128 || cap < 1 ||
+      scratch_bytes < size_t(ranks) * local_experts * 8)
+    return cudaErrorInvalidValue;
+  int* seg_src = static_cast<int*>(scratch);
+  int* seg_dst = seg_src + size_t(ranks) * local_experts;
+  cudaError_t e;
+  if ((e = launch_pdl(ep_plan_kernel, dim3(1), dim3(1024), 0, st, recv_counts, ranks, local_experts, ranges, seg_src, seg_dst, cap))) return e;
+  if ((e = launch_pdl(ep_row_map_kernel, dim3(ranks * local_experts), dim3(128), 0, st, recv_counts, (const int*)seg_src,
+                      (const int*)seg_dst, row_map))) return e;
+  // the number of rows is known on the device only: one block per row a rank can receive, the surplus returns at once
+  return launch_pdl(ep_unpack_rows_kernel, dim3(unsigned(ranks) * unsigned(cap)), dim3(256), 0, st, static_cast<const uint8_t*>(recv),
+                    (const unsigned*)row_map, (const unsigned*)ranges, local_experts, hidden, cap, static_cast<uint8_t*>(codes), scales,
+                    meta_src, meta_tok, meta_prob);
+}
+
+extern "C" int darask_fp8_ep_reduce(const float* y, const unsigned* ranges, int local_experts, const int* meta_src, const int* meta_tok,
+                                    const float* meta_prob, int ranks, int cap, int tcap, int topk, int hidden, float* z, int* count,
+                                    int* list, unsigned* status, cudaStream_t st) {
+  if (!y || !ranges || !meta_src || !meta_tok || !meta_prob || !z || !count || !list || !status || ranks < 1 || cap < 1 || tcap < 1 ||
+      topk < 1 || topk > 32 || hidden < 4 || hidden % 4 || local_experts < 1)
+    return cudaErrorInvalidValue;
+  cudaError_t e;
+  if ((e = cudaMemsetAsync(count, 0, size_t(ranks) * tcap * 4, st))) return e;
+  const unsigned max_rows = unsigned(ranks) * unsigned(cap);
+  if ((e = launch_pdl(ep_index_kernel, dim3((max_rows + 255) / 256), dim3(256), 0, st, ranges, local_experts, meta_src, meta_tok, tcap, topk,
+                      count, list, status))) return e;
+  return launch_pdl(ep_reduce_kernel, dim3(unsigned(ranks) * unsigned(tcap)), dim3(256), 0, st, y, meta_prob, (const int*)count,
+                    (const int*)list, topk, hidden, z);
+}
+
+extern "C" int darask_fp8_ep_sum(float* out, const float* zr, int ranks, int tokens, int tcap, int hidden, cudaStream_t st) {
+  if (!out || !zr || ranks < 1 || tokens < 1 || tokens > tcap || hidden < 4 || hidden % 4) return cudaErrorInvalidValue;
+  return launch_pdl(ep_sum_kernel, dim3((hidden / 4 + 255) / 256, tokens), dim3(256), 0, st, out, zr, ranks, tcap, hidden);
 }
 
 extern "C" int darask_fp8_ep_regroup(const int* recv_counts, int ranks, int local_experts, const void* recv_codes,
@@ -290,7 +455,7 @@ extern "C" int darask_fp8_ep_regroup(const int* recv_counts, int ranks, int loca
   int* seg_src = static_cast<int*>(scratch);
   int* seg_dst = seg_src + size_t(ranks) * local_experts;
   cudaError_t e;
-  if ((e = launch_pdl(ep_plan_kernel, dim3(1), dim3(1024), 0, st, recv_counts, ranks, local_experts, ranges, seg_src, seg_dst))) return e;
+  if ((e = launch_pdl(ep_plan_kernel, dim3(1), dim3(1024), 0, st, recv_counts, ranks, local_experts, ranges, seg_src, seg_dst, 0))) return e;
   if (recv_rows == 0) return cudaSuccess;
   if ((e = launch_pdl(ep_row_map_kernel, dim3(ranks * local_experts), dim3(128), 0, st, recv_counts, (const int*)seg_src,
                       (const int*)seg_dst, row_map))) return e;

@@ -51,25 +51,98 @@ def all_to_all_rows(send: torch.Tensor, send_splits, recv_splits, group=None, pa
     return out
 
 
-def ep_forward(backend, *inputs, group=None):
+def ep_forward(backend, *inputs, group=None, marks=None):
     """One expert-parallel layer call on this rank's tokens; returns (out, info).
 
     backend.dispatch(*inputs) -> dict with `send` (list of row tensors in ascending expert order), `ranges` [E, 2];
     backend.run_experts(recv_counts, received list, n_recv) -> rows [n_recv, H] in received order;
     backend.combine(rows back in dispatch order, dispatch dict) -> out."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
+    mark = (lambda name: marks.append((name, _event()))) if marks is not None else (lambda name: None)
+    mark("start")
     d = backend.dispatch(*inputs)                                     # rows in ascending expert order
+    mark("dispatch")
     counts = d["ranges"][:, 0].to(torch.int32).reshape(world, -1)
     recv_counts, send_splits, recv_splits = exchange_counts(counts, group)
+    mark("counts")
     bufs = getattr(backend, "buffers", {})
     received = [all_to_all_rows(t, send_splits, recv_splits, group, pad_rows=backend.pad_rows, out=bufs.get(f"recv{i}"))
                 for i, t in enumerate(d["send"])]
+    mark("a2a_out")
     n_recv = sum(recv_splits)
     y_recv = backend.run_experts(recv_counts, received, n_recv)       # [n_recv, H] in received order
+    mark("experts")
     y_home = all_to_all_rows(y_recv, recv_splits, send_splits, group, out=bufs.get("y_home"))
+    mark("a2a_back")
     out = backend.combine(y_home, d)
+    mark("combine")
     return out, dict(ids=d["ids"], prob=d["prob"], send_rows=sum(send_splits), recv_rows=n_recv,
                      cross_rows=sum(send_splits) - send_splits[dist.get_rank(group) if world > 1 else 0])
+
+
+def all_to_all_equal(send: torch.Tensor, group=None, out=None) -> torch.Tensor:
+    """Equal-split all-to-all: `send` is [G, ...], slice r goes to rank r; returns [G, ...] with slice r from rank r."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return send
+    out = torch.empty_like(send) if out is None else out
+    dist.all_to_all_single(out, send.contiguous(), group=group)
+    return out
+
+
+def ep_forward_packed(backend, *inputs, group=None, marks=None):
+    """One expert-parallel layer call whose exchanges need no sizes on the host: fixed-capacity slabs of packed rows out,
+    rows pre-reduced per (token, expert rank) back, no device->host copy between the launches.
+
+    backend.dispatch_packed(*inputs) -> dict with `send` [G, cap, row bytes], `counts` int32 [G, E/G];
+    backend.run_experts_packed(recv_counts [G, E/G], recv [G, cap, row bytes]) -> z [G, tcap, H] (slice s: partial rows for
+    rank s's tokens); backend.sum_packed(zr [G, tcap, H], dispatch dict) -> out."""
+    mark = (lambda name: marks.append((name, _event()))) if marks is not None else (lambda name: None)
+    bufs = getattr(backend, "buffers", {})
+    mark("start")
+    d = backend.dispatch_packed(*inputs)
+    mark("dispatch")
+    recv_counts = all_to_all_equal(d["counts"], group, out=bufs.get("recv_counts"))
+    mark("counts")
+    recv = all_to_all_equal(d["send"], group, out=bufs.get("recv_slabs"))
+    mark("a2a_out")
+    z = backend.run_experts_packed(recv_counts, recv)
+    mark("experts")
+    zr = all_to_all_equal(z, group, out=bufs.get("zr"))
+    mark("a2a_back")
+    out = backend.sum_packed(zr, d)
+    mark("combine")
+    return out, dict(ids=d["ids"], prob=d["prob"], recv_counts=recv_counts, send_counts=d["counts"])
+
+
+def _event():
+    e = torch.cuda.Event(enable_timing=True)
+    e.record()
+    return e
+
+
+def stage_times(forward, group=None, calls: int = 5):
+    """Microseconds per stage of `ep_forward` on the device (CUDA events on the launching stream, mean over `calls`,
+    then the maximum over the ranks), plus the host wall time of a whole call. `forward(marks)` makes one layer call."""
+    import time
+    forward(None)
+    torch.cuda.synchronize()
+    acc, wall = {}, 0.0
+    for _ in range(calls):
+        marks = []
+        t0 = time.perf_counter()
+        forward(marks)
+        torch.cuda.synchronize()
+        wall += time.perf_counter() - t0
+        for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
+            acc[name] = acc.get(name, 0.0) + a.elapsed_time(b) * 1e3
+    names = list(acc)
+    vals = torch.tensor([acc[n] / calls for n in names] + [wall / calls * 1e6], dtype=torch.float64, device="cuda")
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(vals, op=dist.ReduceOp.MAX, group=group)
+    out = {n: round(float(v), 1) for n, v in zip(names, vals[:-1])}
+    out["host_wall"] = round(float(vals[-1]), 1)
+    return out
 
 
 class CudaFp8Backend:
@@ -100,6 +173,65 @@ class CudaFp8Backend:
         self.buffers = {}
         self._reserve(2 * max_tokens * topk)
         self.buffers["y_home"] = torch.empty(max_tokens * topk, hidden, dtype=torch.float32, device=self.device)
+        self.packed_ready = False
+
+    def _reserve_packed(self):
+        """Buffers of the exchange without host-side sizes: a slab holds a rank's worst case, max_tokens * topk rows."""
+        if self.packed_ready:
+            return
+        dev, g = self.device, self.world
+        self.cap = self.max_tokens * self.topk
+        self.row_bytes = _lib.lib().darask_fp8_ep_packed_row_bytes(self.hidden)
+        rows = g * self.cap
+        self._reserve(rows)
+        self.send_slabs = torch.zeros(g, self.cap, self.row_bytes, dtype=torch.uint8, device=dev)
+        self.buffers["recv_slabs"] = torch.zeros(g, self.cap, self.row_bytes, dtype=torch.uint8, device=dev)
+        self.buffers["recv_counts"] = torch.zeros(g, self.local, dtype=torch.int32, device=dev)
+        self.buffers["zr"] = torch.empty(g, self.max_tokens, self.hidden, dtype=torch.float32, device=dev)
+        self.z = torch.empty(g, self.max_tokens, self.hidden, dtype=torch.float32, device=dev)
+        self.meta_src = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self.meta_tok = torch.zeros(rows, dtype=torch.int32, device=dev)
+        self.meta_prob = torch.zeros(rows, dtype=torch.float32, device=dev)
+        self.count = torch.zeros(g * self.max_tokens, dtype=torch.int32, device=dev)
+        self.list = torch.zeros(g * self.max_tokens * self.topk, dtype=torch.int32, device=dev)
+        self.packed_ready = True
+
+    def dispatch_packed(self, x, logits):
+        t = x.shape[0]
+        if t > self.max_tokens or x.dtype != torch.bfloat16 or logits.dtype != torch.float32 or not x.is_contiguous() or not logits.is_contiguous():
+            raise ValueError("x must be contiguous bf16 [T<=max_tokens,H], logits contiguous float32 [T,E]")
+        self._reserve_packed()
+        _lib.check(_lib.lib().darask_fp8_ep_dispatch_packed(
+            x.data_ptr(), logits.data_ptr(), self.hidden, self.experts, self.topk, t, self.world, self.cap, self.ids.data_ptr(),
+            self.prob.data_ptr(), self.send_slabs.data_ptr(), self.ranges.data_ptr(), self.position.data_ptr(), self.scratch.data_ptr(),
+            self.scratch.numel(), self._stream()), "darask_fp8_ep_dispatch_packed")
+        counts = self.ranges[:, 0].reshape(self.world, self.local).contiguous()
+        return dict(send=self.send_slabs, counts=counts, ids=self.ids[:t], prob=self.prob[:t], tokens=t)
+
+    def run_experts_packed(self, recv_counts, recv):
+        lib = _lib.lib()
+        (gw, gs), (uw, us), (dw, ds) = self.w["gate"], self.w["up"], self.w["down"]
+        rows = self.world * self.cap
+        _lib.check(lib.darask_fp8_ep_regroup_packed(
+            recv_counts.data_ptr(), self.world, self.local, recv.data_ptr(), self.cap, self.hidden, self.codes.data_ptr(),
+            self.scales.data_ptr(), self.local_ranges.data_ptr(), self.row_map.data_ptr(), self.meta_src.data_ptr(), self.meta_tok.data_ptr(),
+            self.meta_prob.data_ptr(), self.seg.data_ptr(), self.seg.numel() * 4, self._stream()), "darask_fp8_ep_regroup_packed")
+        _lib.check(lib.darask_fp8_ep_experts(
+            self.codes.data_ptr(), self.scales.data_ptr(), rows + self.pad_rows, self.local_ranges.data_ptr(), self.local, self.hidden,
+            self.inter, gw.data_ptr(), uw.data_ptr(), dw.data_ptr(), gs.data_ptr(), us.data_ptr(), ds.data_ptr(), None, self.y.data_ptr(),
+            self.prod.data_ptr(), self.prod_s.data_ptr(), self.status.data_ptr(), self._stream()), "darask_fp8_ep_experts")
+        _lib.check(lib.darask_fp8_ep_reduce(
+            self.y.data_ptr(), self.local_ranges.data_ptr(), self.local, self.meta_src.data_ptr(), self.meta_tok.data_ptr(),
+            self.meta_prob.data_ptr(), self.world, self.cap, self.max_tokens, self.topk, self.hidden, self.z.data_ptr(), self.count.data_ptr(),
+            self.list.data_ptr(), self.status.data_ptr(), self._stream()), "darask_fp8_ep_reduce")
+        return self.z
+
+    def sum_packed(self, zr, d):
+        t = d["tokens"]
+        out = torch.empty(t, self.hidden, dtype=torch.float32, device=self.device)
+        _lib.check(_lib.lib().darask_fp8_ep_sum(out.data_ptr(), zr.data_ptr(), self.world, t, self.max_tokens, self.hidden, self._stream()),
+                   "darask_fp8_ep_sum")
+        return out
 
     def _reserve(self, rows):
         if rows <= self.capacity:
@@ -184,8 +316,13 @@ class CudaFp8Backend:
 class Fp8ExpertParallelMoe:
     """The call a user makes: `forward(x, logits)` on every rank with that rank's tokens."""
 
-    def __init__(self, hidden, inter, experts, topk, max_tokens, group=None, device="cuda"):
-        self.group = group
+    def __init__(self, hidden, inter, experts, topk, max_tokens, group=None, device="cuda", exchange="packed"):
+        """exchange = "packed": fixed-capacity slabs out, rows pre-reduced per (token, expert rank) back, no host
+        synchronisation inside a call (every rank passes the same max_tokens); "exact": all-to-all-v of exactly the
+        routed rows with the split sizes read on the host, float32 rows back, combined in slot order."""
+        if exchange not in ("packed", "exact"):
+            raise ValueError("exchange")
+        self.group, self.exchange = group, exchange
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.backend = CudaFp8Backend(hidden, inter, experts, topk, world, max_tokens, device)
@@ -194,9 +331,23 @@ class Fp8ExpertParallelMoe:
     def load(self, name, payload, scales):
         self.backend.load(name, payload, scales)
 
+    def _call(self, x, logits, marks=None):
+        fn = ep_forward_packed if self.exchange == "packed" else ep_forward
+        return fn(self.backend, x, logits, group=self.group, marks=marks)
+
     def forward(self, x, logits):
-        out, self.info = ep_forward(self.backend, x, logits, group=self.group)
+        out, self.info = self._call(x, logits)
         return out
+
+    def rows(self):
+        """(rows sent, rows received, rows sent to other ranks) of the last call; reads device counters (synchronizes)."""
+        if "send_rows" in self.info:
+            return self.info["send_rows"], self.info["recv_rows"], self.info["cross_rows"]
+        sent = self.info["send_counts"].sum(1).cpu()
+        return int(sent.sum()), int(self.info["recv_counts"].sum().item()), int(sent.sum() - sent[self.rank])
+
+    def stage_times(self, x, logits):
+        return stage_times(lambda marks: self._call(x, logits, marks), self.group)
 
 
 class CudaTsumujiBackend:

@@ -352,6 +352,32 @@ int darask_fp8_ep_experts(const void* codes, const float* scales, unsigned long 
                           unsigned* status, darask_stream_t stream);
 int darask_fp8_ep_combine(float* out, const float* y, const float* prob, const unsigned* position, int tokens, int hidden,
                           int topk, darask_stream_t stream);
+/* The same layer with exchanges whose sizes the host never needs ("packed"): rows travel in slabs of `cap` rows per
+ * (source, destination) pair (cap >= tokens*topk, a rank's worst case) as packed rows of darask_fp8_ep_packed_row_bytes
+ * bytes [codes | scales | routing weight | token], so both exchanges and the counts are equal-split all-to-alls and no
+ * device->host copy sits between the launches; the expert rank adds a token's rows (weight * row, ascending local expert)
+ * before they return, so one float32 row per (token, expert rank) comes back, dense by token, and the home rank adds the
+ * ranks' partial rows in ascending rank order (P2's pre-reduction; the summation order differs from the single-GPU slot
+ * order, inside the layer tolerance).
+ *   1. darask_fp8_ep_dispatch_packed  send [ranks][cap] packed rows; ranges [E][2] as above (counts = ranges[:,0])
+ *   2. all-to-all of counts [ranks][E/ranks] and of the slabs
+ *   3. darask_fp8_ep_regroup_packed   slabs -> codes / scales in local expert order, ranges [E/ranks][2], per row its
+ *                                     source rank, token and weight
+ *   4. darask_fp8_ep_experts          with row_map = NULL and rows_alloc = ranks*cap + 128: y in regrouped order
+ *   5. darask_fp8_ep_reduce           z [ranks][tcap][hidden] (count: ranks*tcap ints, list: ranks*tcap*topk ints)
+ *   6. all-to-all of z; darask_fp8_ep_sum  out[t] = sum_r zr[r][t] */
+size_t darask_fp8_ep_packed_row_bytes(int hidden);
+int darask_fp8_ep_dispatch_packed(const void* x, const float* logits, int hidden, int experts, int topk, int tokens, int ranks,
+                                  int cap, int* ids, float* prob, void* send, unsigned* ranges, unsigned* position, void* scratch,
+                                  size_t scratch_bytes, darask_stream_t stream);
+int darask_fp8_ep_regroup_packed(const int* recv_counts, int ranks, int local_experts, const void* recv, int cap, int hidden,
+                                 void* codes, float* scales, unsigned* ranges, unsigned* row_map, int* meta_src, int* meta_tok,
+                                 float* meta_prob, void* scratch /* ranks*local_experts*8 bytes */, size_t scratch_bytes,
+                                 darask_stream_t stream);
+int darask_fp8_ep_reduce(const float* y, const unsigned* ranges, int local_experts, const int* meta_src, const int* meta_tok,
+                         const float* meta_prob, int ranks, int cap, int tcap, int topk, int hidden, float* z, int* count, int* list,
+                         unsigned* status, darask_stream_t stream);
+int darask_fp8_ep_sum(float* out, const float* zr, int ranks, int tokens, int tcap, int hidden, darask_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -60,6 +60,48 @@ class OracleBackend:
                 row += c
         return torch.from_numpy(y)
 
+    # ---- the exchange without sizes on the host: slabs of fixed capacity out, rows pre-reduced per (token, rank) back ----
+    def dispatch_packed(self, x, logits):
+        d = self.dispatch(x, logits)
+        k, t = self.layer.topk, x.shape[0]
+        cap, h = t * k, self.layer.hidden
+        codes, scales = d["send"][0].numpy(), d["send"][1].numpy()
+        counts = d["ranges"][:, 0].numpy().reshape(self.world, self.local)
+        order = np.argsort(d["position"])                      # dispatch row -> assignment
+        slabs = np.zeros((self.world, cap, h + 4 * (h // 128) + 8), np.uint8)
+        row = 0
+        for r in range(self.world):
+            n = int(counts[r].sum())
+            for j in range(n):
+                a = int(order[row + j])
+                slabs[r, j, :h] = codes[row + j]
+                slabs[r, j, h:h + 4 * (h // 128)] = scales[row + j].view(np.uint8)
+                slabs[r, j, h + 4 * (h // 128):] = np.concatenate([np.array([d["prob"][a // k, a % k]], np.float32).view(np.uint8),
+                                                                    np.array([a // k], np.int32).view(np.uint8)])
+            row += n
+        return dict(send=torch.from_numpy(slabs), counts=torch.from_numpy(counts.astype(np.int32)), ids=d["ids"], prob=d["prob"], tokens=t)
+
+    def run_experts_packed(self, recv_counts, recv):
+        counts, slabs = recv_counts.numpy(), recv.numpy()
+        h, tcap = self.layer.hidden, slabs.shape[1] // self.layer.topk
+        z = np.zeros((self.world, tcap, h), np.float32)
+        for s in range(self.world):
+            n = int(counts[s].sum())
+            rows = slabs[s, :n]
+            codes = np.ascontiguousarray(rows[:, :h])
+            scales = np.ascontiguousarray(rows[:, h:h + 4 * (h // 128)]).view(np.float32)
+            meta = np.ascontiguousarray(rows[:, h + 4 * (h // 128):])
+            prob, tok = meta[:, :4].copy().view(np.float32)[:, 0], meta[:, 4:8].copy().view(np.int32)[:, 0]
+            y = self.run_experts(torch.from_numpy(np.stack([counts[s]] + [np.zeros_like(counts[s])] * (self.world - 1))), [torch.from_numpy(codes),
+                                 torch.from_numpy(scales)], n).numpy() if n else np.zeros((0, h), np.float32)
+            # run_experts walks (rank, expert) segments in order: with the other ranks' counts zero it is this slab alone
+            for j in range(n):
+                z[s, tok[j]] += prob[j] * y[j]
+        return torch.from_numpy(z)
+
+    def sum_packed(self, zr, d):
+        return torch.from_numpy(zr.numpy()[:, :d["tokens"]].sum(0).astype(np.float32))
+
     def combine(self, y_home, d):
         y, k = y_home.numpy(), self.layer.topk
         out = np.zeros((d["tokens"], self.layer.hidden), np.float32)
@@ -101,8 +143,8 @@ def main():
             f.write(f"{info['send_rows']} {info['recv_rows']} {info['cross_rows']}\n")
         dist.destroy_process_group()
         return
-    if mode == "cuda":
-        m = D.Fp8ExpertParallelMoe(HIDDEN, INTER, EXPERTS, TOPK, TOKENS_PER_RANK)
+    if mode in ("cuda", "cuda_exact"):
+        m = D.Fp8ExpertParallelMoe(HIDDEN, INTER, EXPERTS, TOPK, TOKENS_PER_RANK, exchange="exact" if mode == "cuda_exact" else "packed")
         local = EXPERTS // world
         for name in ("gate", "up", "down"):
             mats = getattr(layer, name)[rank * local:(rank + 1) * local]
@@ -110,17 +152,24 @@ def main():
         out = m.forward(torch.from_numpy(x).bfloat16().cuda(), torch.from_numpy(logits).cuda())
         torch.cuda.synchronize()
         assert m.backend.device_status() == 0
-        info, out = m.info, out.cpu().numpy()
-        ids = info["ids"].cpu().numpy()
+        out = out.cpu().numpy()
+        ids = m.info["ids"].cpu().numpy()
+        rows = m.rows()
+    elif mode == "cpu_packed":
+        out, info = D.ep.ep_forward_packed(OracleBackend(layer, rank, world), torch.from_numpy(x), torch.from_numpy(logits))
+        out, ids = out.numpy(), info["ids"]
+        sent = info["send_counts"].numpy().sum(1)
+        rows = (int(sent.sum()), int(info["recv_counts"].numpy().sum()), int(sent.sum() - sent[rank]))
     else:
         out, info = D.ep.ep_forward(OracleBackend(layer, rank, world), torch.from_numpy(x), torch.from_numpy(logits))
         out, ids = out.numpy(), info["ids"]
+        rows = (info["send_rows"], info["recv_rows"], info["cross_rows"])
     assert np.array_equal(ids, ref["ids"]), "routes differ"
     W.check_output(out, ref["out"])
-    assert info["send_rows"] == TOKENS_PER_RANK * TOPK
+    assert rows[0] == TOKENS_PER_RANK * TOPK
     dist.barrier()
     with open(os.path.join(out_dir, f"ok.{rank}"), "w") as f:
-        f.write(f"{info['send_rows']} {info['recv_rows']} {info['cross_rows']}\n")
+        f.write(f"{rows[0]} {rows[1]} {rows[2]}\n")
     dist.destroy_process_group()
 
 

@@ -21,15 +21,19 @@ def test_single_rank_matches_fused_layer():
     import darask_inference_engine_b200 as D
     layer, acts = W.fp8_layer(31, 512, 256, 16, 4, 200, zipf=1.1)
     x, logits = torch.from_numpy(acts["x"]).bfloat16().cuda(), torch.from_numpy(acts["logits"]).cuda()
-    ep = D.Fp8ExpertParallelMoe(512, 256, 16, 4, 200)
-    load_rank(ep, layer, 0, 16)
-    out = ep.forward(x, logits)
     fused = D.Fp8MoeLayer(512, 256, 16, 4, 200)
     load_rank(fused, layer, 0, 16)
     ref = fused.forward(x, logits)
-    torch.cuda.synchronize()
-    assert ep.backend.device_status() == 0 and torch.equal(out, ref)
-    W.check_output(out.cpu().numpy(), L.fp8_forward(layer, acts["x"], acts["logits"])["out"])
+    for exchange in ("exact", "packed"):
+        ep = D.Fp8ExpertParallelMoe(512, 256, 16, 4, 200, exchange=exchange)
+        load_rank(ep, layer, 0, 16)
+        out = ep.forward(x, logits)
+        torch.cuda.synchronize()
+        assert ep.backend.device_status() == 0
+        if exchange == "exact":          # same kernels, same slot-order sum: bit for bit
+            assert torch.equal(out, ref)
+        W.check_output(out.cpu().numpy(), L.fp8_forward(layer, acts["x"], acts["logits"])["out"])
+        assert ep.rows() == (800, 800, 0)
 
 
 @pytest.mark.parametrize("world,tokens", [(2, 96), (4, 33)])
@@ -134,8 +138,40 @@ def test_tsumuji_ep_forward_nccl(tmp_path):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_ep_forward_nccl(tmp_path):
+@pytest.mark.parametrize("mode", ["cuda", "cuda_exact"])          # packed slabs / exact all-to-all-v
+def test_ep_forward_nccl(mode, tmp_path):
     world = min(4, torch.cuda.device_count())
     world = 2 if world == 3 else world
-    rows = run_workers("cuda", world, tmp_path, 29631)
+    rows = run_workers(mode, world, tmp_path, 29631 + (1 if mode == "cuda_exact" else 0))
     assert sum(r[0] for r in rows) == sum(r[1] for r in rows) and any(r[2] > 0 for r in rows)
+
+
+@pytest.mark.parametrize("world,tokens", [(1, 50), (2, 96), (4, 33)])
+def test_packed_exchange_virtual_ranks_on_one_gpu(world, tokens):
+    """The exchange without sizes on the host: all ranks' kernels run on one GPU one after the other; the three equal-split
+    all-to-alls are done by slicing. Outputs against the oracle, routes bit-exact."""
+    import darask_inference_engine_b200 as D
+    hidden, inter, experts, topk = 256, 128, 8, 2
+    local = experts // world
+    layer, acts = W.fp8_layer(15 + world, hidden, inter, experts, topk, tokens * world, pool=experts, zipf=1.1)
+    backends, sent = [], []
+    for r in range(world):
+        b = D.ep.CudaFp8Backend(hidden, inter, experts, topk, world, tokens)
+        load_rank(b, layer, r, local)
+        x = torch.from_numpy(acts["x"][r * tokens:(r + 1) * tokens]).bfloat16().cuda()
+        lg = torch.from_numpy(acts["logits"][r * tokens:(r + 1) * tokens]).cuda()
+        d = b.dispatch_packed(x, lg)
+        backends.append(b)
+        sent.append(dict(d, send=d["send"].clone(), counts=d["counts"].clone(), ids=d["ids"].clone(), prob=d["prob"].clone()))
+    zs = []
+    for dst in range(world):
+        recv_counts = torch.stack([sent[src]["counts"][dst] for src in range(world)]).contiguous()
+        recv = torch.stack([sent[src]["send"][dst] for src in range(world)]).contiguous()
+        zs.append(backends[dst].run_experts_packed(recv_counts, recv).clone())
+        assert backends[dst].device_status() == 0
+    for r in range(world):
+        zr = torch.stack([zs[src][r] for src in range(world)]).contiguous()
+        out = backends[r].sum_packed(zr, sent[r]).cpu().numpy()
+        ref = L.fp8_forward(layer, acts["x"][r * tokens:(r + 1) * tokens], acts["logits"][r * tokens:(r + 1) * tokens])
+        assert np.array_equal(sent[r]["ids"].cpu().numpy(), ref["ids"])
+        W.check_output(out, ref["out"])

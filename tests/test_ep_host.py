@@ -17,9 +17,10 @@ def run_workers(mode, world, tmp_path, port):
     return [[int(v) for v in r] for r in rows]
 
 
+@pytest.mark.parametrize("mode", ["cpu", "cpu_packed"])
 @pytest.mark.parametrize("world", [2, 4])
-def test_ep_forward_gloo(world, tmp_path):
-    rows = run_workers("cpu", world, tmp_path, 29611 + world)
+def test_ep_forward_gloo(world, mode, tmp_path):
+    rows = run_workers(mode, world, tmp_path, 29611 + world + (10 if mode == "cpu_packed" else 0))
     # every routed row is received by exactly one rank
     assert sum(r[0] for r in rows) == sum(r[1] for r in rows)
     assert any(r[2] > 0 for r in rows)          # and some rows did cross ranks
