@@ -112,7 +112,7 @@ _SIGNATURES = {
     "darask_fp8_ep_combine": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "darask_fp8_ep_packed_row_bytes": (c_size_t, [c_int]),
     "darask_fp8_ep_dispatch_packed": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                              c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
+                                              c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "darask_fp8_ep_regroup_packed": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, c_void_p]),
     "darask_fp8_ep_reduce": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p,

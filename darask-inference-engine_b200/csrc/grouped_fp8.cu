@@ -100,12 +100,14 @@ __global__ void __launch_bounds__(256) ep_regroup_rows_kernel(const uint8_t* in_
 // so that both exchanges are equal-split all-to-alls and no device->host copy sits between the launches; the expert
 // rank adds each token's rows (weight * row, ascending local expert) before they return, so what comes back is one
 // float32 row per (token, expert rank), dense by token.
+constexpr unsigned kStatusEpOverflow = 16u;     // more rows for one destination rank than a slab holds: rows were dropped
 DEVI int packed_row_bytes(int k) { return (k + 4 * (k / 128) + 8 + 15) / 16 * 16; }
 
 // dispatch row i (ascending expert order) -> slab of its expert's rank, at the row's index among that rank's rows
 __global__ void __launch_bounds__(256) gather_packed_kernel(const uint8_t* codes, const float* scales, const unsigned* assignments,
                                                             const int* counters, const int* ids, const float* prob, const unsigned* ranges,
-                                                            int topk, int k, int local, int cap, uint8_t* send, unsigned* position) {
+                                                            int topk, int k, int local, int cap, uint8_t* send, unsigned* position,
+                                                            unsigned* overflow) {
   pdl_wait();
   pdl_launch();
   const int i = blockIdx.x;
@@ -113,6 +115,10 @@ __global__ void __launch_bounds__(256) gather_packed_kernel(const uint8_t* codes
   const unsigned asg = __ldcg(assignments + i);
   const int tok = int(asg / topk), r = __ldcg(ids + asg) / local;
   const int first = int(__ldcg(ranges + 2 * (r * local) + 1));            // first dispatch row that goes to rank r
+  if (i - first >= cap) {                                                 // the slab is full: the row is dropped and reported
+    if (threadIdx.x == 0) atomicOr(overflow, kStatusEpOverflow);
+    return;
+  }
   uint8_t* row = send + (size_t(r) * cap + size_t(i - first)) * packed_row_bytes(k);
   if (threadIdx.x == 0) {
     position[asg] = i;
@@ -121,6 +127,19 @@ __global__ void __launch_bounds__(256) gather_packed_kernel(const uint8_t* codes
   }
   for (int c = threadIdx.x; c < k / 16; c += 256) reinterpret_cast<uint4*>(row)[c] = __ldg(reinterpret_cast<const uint4*>(codes + size_t(tok) * k) + c);
   for (int c = threadIdx.x; c < k / 128; c += 256) reinterpret_cast<float*>(row + k)[c] = __ldg(scales + size_t(tok) * (k / 128) + c);
+}
+// counts[e] = rows of expert e that fit its rank's slab (all of them unless the slab overflowed)
+__global__ void __launch_bounds__(64) ep_slab_counts_kernel(const unsigned* ranges, int ranks, int local, int cap, int* counts) {
+  pdl_wait();
+  pdl_launch();
+  const int r = threadIdx.x;
+  if (r >= ranks) return;
+  int run = 0;
+  for (int e = r * local; e < (r + 1) * local; ++e) {
+    const int c = min(int(__ldcg(ranges + 2 * e)), cap - run);
+    counts[e] = c;
+    run += c;
+  }
 }
 // regrouped row <- packed row of its slab; also the row's source rank, token and routing weight
 __global__ void __launch_bounds__(256) ep_unpack_rows_kernel(const uint8_t* recv, const unsigned* row_map, const unsigned* ranges, int local,
@@ -356,7 +375,7 @@ extern "C" size_t darask_fp8_ep_dispatch_scratch_bytes(int hidden, int experts, 
 // ranks > 0: packed slabs of `cap` rows per destination rank into send_codes (send_scales unused)
 static int ep_dispatch(const void* x, const float* logits, int hidden, int experts, int topk, int tokens, int* ids, float* prob,
                        void* send_codes, float* send_scales, unsigned* ranges, unsigned* position, void* scratch, size_t scratch_bytes,
-                       int ranks, int cap, cudaStream_t st) {
+                       int ranks, int cap, int* counts, unsigned* overflow, cudaStream_t st) {
   if (!x || !logits || !ids || !prob || !send_codes || (!send_scales && !ranks) || !ranges || !position || !scratch || hidden < 128 ||
       hidden % 128 || experts < topk || experts > 1024 || topk < 1 || topk > 32 || tokens < 1 ||
       scratch_bytes < darask_fp8_ep_dispatch_scratch_bytes(hidden, experts, topk, tokens))
@@ -380,10 +399,12 @@ static int ep_dispatch(const void* x, const float* logits, int hidden, int exper
     if ((e = launch_permute_large(perm, perm_scratch, st))) return e;
   } else if ((e = launch_pdl(permute_kernel<0>, dim3(1), dim3(1024), size_t(experts + 1) * 4, st, perm))) return e;
   if ((e = (cudaError_t)darask_quantize_fp8_act(xq, xs, x, 1, tokens, hidden, st))) return e;
-  if (ranks)
-    return launch_pdl(gather_packed_kernel, dim3(tokens * topk), dim3(256), 0, st, (const uint8_t*)xq, (const float*)xs,
-                      (const unsigned*)assignments, (const int*)counters, (const int*)ids, (const float*)prob, (const unsigned*)ranges, topk,
-                      hidden, experts / ranks, cap, static_cast<uint8_t*>(send_codes), position);
+  if (ranks) {
+    if ((e = launch_pdl(gather_packed_kernel, dim3(tokens * topk), dim3(256), 0, st, (const uint8_t*)xq, (const float*)xs,
+                        (const unsigned*)assignments, (const int*)counters, (const int*)ids, (const float*)prob, (const unsigned*)ranges, topk,
+                        hidden, experts / ranks, cap, static_cast<uint8_t*>(send_codes), position, overflow))) return e;
+    return launch_pdl(ep_slab_counts_kernel, dim3(1), dim3(64), 0, st, (const unsigned*)ranges, ranks, experts / ranks, cap, counts);
+  }
   return launch_pdl(gather_fp8_kernel, dim3(tokens * topk), dim3(256), 0, st, (const uint8_t*)xq, (const float*)xs,
                     (const unsigned*)assignments, (const int*)counters, topk, hidden, static_cast<uint8_t*>(send_codes), send_scales,
                     position);
@@ -393,17 +414,17 @@ extern "C" int darask_fp8_ep_dispatch(const void* x, const float* logits, int hi
                                       float* prob, void* send_codes, float* send_scales, unsigned* ranges, unsigned* position,
                                       void* scratch, size_t scratch_bytes, cudaStream_t st) {
   return ep_dispatch(x, logits, hidden, experts, topk, tokens, ids, prob, send_codes, send_scales, ranges, position, scratch, scratch_bytes,
-                     0, 0, st);
+                     0, 0, nullptr, nullptr, st);
 }
 
 extern "C" size_t darask_fp8_ep_packed_row_bytes(int hidden) { return hidden >= 128 && hidden % 128 == 0 ? size_t((hidden + 4 * (hidden / 128) + 8 + 15) / 16 * 16) : 0; }
 
 extern "C" int darask_fp8_ep_dispatch_packed(const void* x, const float* logits, int hidden, int experts, int topk, int tokens, int ranks,
-                                             int cap, int* ids, float* prob, void* send, unsigned* ranges, unsigned* position,
-                                             void* scratch, size_t scratch_bytes, cudaStream_t st) {
-  if (ranks < 1 || ranks > 64 || experts % ranks || cap < tokens * topk) return cudaErrorInvalidValue;   // a slab holds a rank's worst case
+                                             int cap, int* ids, float* prob, void* send, int* counts, unsigned* ranges,
+                                             unsigned* position, unsigned* status, void* scratch, size_t scratch_bytes, cudaStream_t st) {
+  if (ranks < 1 || ranks > 64 || experts % ranks || cap < 1 || !counts || !status) return cudaErrorInvalidValue;
   return ep_dispatch(x, logits, hidden, experts, topk, tokens, ids, prob, send, nullptr, ranges, position, scratch, scratch_bytes, ranks,
-                     cap, st);
+                     cap, counts, status, st);
 }
 
 extern "C" int darask_fp8_ep_regroup_packed(const int* recv_counts, int ranks, int local_experts, const void* recv, int cap, int hidden,

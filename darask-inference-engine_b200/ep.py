@@ -149,10 +149,11 @@ class CudaFp8Backend:
     """Kernels of one rank: block-FP8 weights of its E/G experts resident on the GPU."""
     pad_rows = 128          # the grouped GEMM loads whole 128-row tiles
 
-    def __init__(self, hidden, inter, experts, topk, world, max_tokens, device="cuda"):
+    def __init__(self, hidden, inter, experts, topk, world, max_tokens, device="cuda", capacity_factor=None):
         if experts % world:
             raise ValueError("experts must divide evenly over the ranks")
         self.hidden, self.inter, self.experts, self.topk, self.world = hidden, inter, experts, topk, world
+        self.capacity_factor = capacity_factor
         self.local = experts // world
         self.max_tokens, self.device = max_tokens, torch.device(device)
         lib = _lib.lib()
@@ -180,11 +181,15 @@ class CudaFp8Backend:
         if self.packed_ready:
             return
         dev, g = self.device, self.world
-        self.cap = self.max_tokens * self.topk
+        # rows per (source, destination) slab: the worst case, or capacity_factor x the mean load (rows beyond it are
+        # dropped and reported in the status word)
+        worst = self.max_tokens * self.topk
+        self.cap = worst if self.capacity_factor is None else max(1, min(worst, int(-(-worst * self.capacity_factor // g))))
         self.row_bytes = _lib.lib().darask_fp8_ep_packed_row_bytes(self.hidden)
         rows = g * self.cap
         self._reserve(rows)
         self.send_slabs = torch.zeros(g, self.cap, self.row_bytes, dtype=torch.uint8, device=dev)
+        self.send_counts = torch.zeros(g, self.local, dtype=torch.int32, device=dev)
         self.buffers["recv_slabs"] = torch.zeros(g, self.cap, self.row_bytes, dtype=torch.uint8, device=dev)
         self.buffers["recv_counts"] = torch.zeros(g, self.local, dtype=torch.int32, device=dev)
         self.buffers["zr"] = torch.empty(g, self.max_tokens, self.hidden, dtype=torch.float32, device=dev)
@@ -203,10 +208,9 @@ class CudaFp8Backend:
         self._reserve_packed()
         _lib.check(_lib.lib().darask_fp8_ep_dispatch_packed(
             x.data_ptr(), logits.data_ptr(), self.hidden, self.experts, self.topk, t, self.world, self.cap, self.ids.data_ptr(),
-            self.prob.data_ptr(), self.send_slabs.data_ptr(), self.ranges.data_ptr(), self.position.data_ptr(), self.scratch.data_ptr(),
-            self.scratch.numel(), self._stream()), "darask_fp8_ep_dispatch_packed")
-        counts = self.ranges[:, 0].reshape(self.world, self.local).contiguous()
-        return dict(send=self.send_slabs, counts=counts, ids=self.ids[:t], prob=self.prob[:t], tokens=t)
+            self.prob.data_ptr(), self.send_slabs.data_ptr(), self.send_counts.data_ptr(), self.ranges.data_ptr(), self.position.data_ptr(),
+            self.status.data_ptr(), self.scratch.data_ptr(), self.scratch.numel(), self._stream()), "darask_fp8_ep_dispatch_packed")
+        return dict(send=self.send_slabs, counts=self.send_counts, ids=self.ids[:t], prob=self.prob[:t], tokens=t)
 
     def run_experts_packed(self, recv_counts, recv):
         lib = _lib.lib()
@@ -316,16 +320,18 @@ class CudaFp8Backend:
 class Fp8ExpertParallelMoe:
     """The call a user makes: `forward(x, logits)` on every rank with that rank's tokens."""
 
-    def __init__(self, hidden, inter, experts, topk, max_tokens, group=None, device="cuda", exchange="packed"):
+    def __init__(self, hidden, inter, experts, topk, max_tokens, group=None, device="cuda", exchange="packed", capacity_factor=None):
         """exchange = "packed": fixed-capacity slabs out, rows pre-reduced per (token, expert rank) back, no host
         synchronisation inside a call (every rank passes the same max_tokens); "exact": all-to-all-v of exactly the
-        routed rows with the split sizes read on the host, float32 rows back, combined in slot order."""
+        routed rows with the split sizes read on the host, float32 rows back, combined in slot order.
+        capacity_factor (packed): rows a (source, destination) slab holds, as a multiple of the mean load tokens*topk/G;
+        None = the worst case tokens*topk. Rows that do not fit are dropped and `backend.device_status()` has bit 16."""
         if exchange not in ("packed", "exact"):
             raise ValueError("exchange")
         self.group, self.exchange = group, exchange
         world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        self.backend = CudaFp8Backend(hidden, inter, experts, topk, world, max_tokens, device)
+        self.backend = CudaFp8Backend(hidden, inter, experts, topk, world, max_tokens, device, capacity_factor)
         self.first_expert = self.rank * self.backend.local
 
     def load(self, name, payload, scales):

@@ -26,6 +26,7 @@ enum { DARASK_ROUTE_KOGARASHI = 0, DARASK_ROUTE_TSUMUJI = 1, DARASK_ROUTE_HAYATE
 enum {
   DARASK_STATUS_WAIT_TIMEOUT = 1,  /* a bounded device-side wait ran out; re-initialise the workspace before the next call */
   DARASK_STATUS_BAD_ROUTE = 2,     /* an expert id out of range or repeated inside a token was dropped */
+  DARASK_STATUS_EP_OVERFLOW = 16,  /* expert-parallel slab capacity exceeded: rows were dropped, the layer's result is wrong */
   DARASK_STATUS_ACT_RANGE = 4      /* an activation or SwiGLU product exceeds 65504 in magnitude: the decode kernels hold
                                       activations as two fp16 planes (the reference reads float32), the result is not finite */
 };
@@ -353,13 +354,14 @@ int darask_fp8_ep_experts(const void* codes, const float* scales, unsigned long 
 int darask_fp8_ep_combine(float* out, const float* y, const float* prob, const unsigned* position, int tokens, int hidden,
                           int topk, darask_stream_t stream);
 /* The same layer with exchanges whose sizes the host never needs ("packed"): rows travel in slabs of `cap` rows per
- * (source, destination) pair (cap >= tokens*topk, a rank's worst case) as packed rows of darask_fp8_ep_packed_row_bytes
+ * (source, destination) pair (cap = tokens*topk is a rank's worst case; with a smaller cap the rows that do not fit are
+ * dropped, bit 16 is set in *status and the result is wrong: raise the capacity) as packed rows of darask_fp8_ep_packed_row_bytes
  * bytes [codes | scales | routing weight | token], so both exchanges and the counts are equal-split all-to-alls and no
  * device->host copy sits between the launches; the expert rank adds a token's rows (weight * row, ascending local expert)
  * before they return, so one float32 row per (token, expert rank) comes back, dense by token, and the home rank adds the
  * ranks' partial rows in ascending rank order (P2's pre-reduction; the summation order differs from the single-GPU slot
  * order, inside the layer tolerance).
- *   1. darask_fp8_ep_dispatch_packed  send [ranks][cap] packed rows; ranges [E][2] as above (counts = ranges[:,0])
+ *   1. darask_fp8_ep_dispatch_packed  send [ranks][cap] packed rows; counts [E] = rows per expert that are in the slabs
  *   2. all-to-all of counts [ranks][E/ranks] and of the slabs
  *   3. darask_fp8_ep_regroup_packed   slabs -> codes / scales in local expert order, ranges [E/ranks][2], per row its
  *                                     source rank, token and weight
@@ -368,8 +370,8 @@ int darask_fp8_ep_combine(float* out, const float* y, const float* prob, const u
  *   6. all-to-all of z; darask_fp8_ep_sum  out[t] = sum_r zr[r][t] */
 size_t darask_fp8_ep_packed_row_bytes(int hidden);
 int darask_fp8_ep_dispatch_packed(const void* x, const float* logits, int hidden, int experts, int topk, int tokens, int ranks,
-                                  int cap, int* ids, float* prob, void* send, unsigned* ranges, unsigned* position, void* scratch,
-                                  size_t scratch_bytes, darask_stream_t stream);
+                                  int cap, int* ids, float* prob, void* send, int* counts /* [experts] */, unsigned* ranges,
+                                  unsigned* position, unsigned* status, void* scratch, size_t scratch_bytes, darask_stream_t stream);
 int darask_fp8_ep_regroup_packed(const int* recv_counts, int ranks, int local_experts, const void* recv, int cap, int hidden,
                                  void* codes, float* scales, unsigned* ranges, unsigned* row_map, int* meta_src, int* meta_tok,
                                  float* meta_prob, void* scratch /* ranks*local_experts*8 bytes */, size_t scratch_bytes,

@@ -175,3 +175,14 @@ def test_packed_exchange_virtual_ranks_on_one_gpu(world, tokens):
         ref = L.fp8_forward(layer, acts["x"][r * tokens:(r + 1) * tokens], acts["logits"][r * tokens:(r + 1) * tokens])
         assert np.array_equal(sent[r]["ids"].cpu().numpy(), ref["ids"])
         W.check_output(out, ref["out"])
+
+
+def test_packed_exchange_reports_slab_overflow():
+    """A slab smaller than a destination's load: the rows that do not fit are dropped and bit 16 is set."""
+    import darask_inference_engine_b200 as D
+    layer, acts = W.fp8_layer(3, 256, 128, 8, 2, 64, pool=8, zipf=1.1)
+    b = D.ep.CudaFp8Backend(256, 128, 8, 2, 2, 64, capacity_factor=0.25)          # 16 rows per slab, 128 routed rows
+    b.dispatch_packed(torch.from_numpy(acts["x"]).bfloat16().cuda(), torch.from_numpy(acts["logits"]).cuda())
+    torch.cuda.synchronize()
+    assert b.device_status() & 16
+    assert int(b.send_counts.sum()) == 2 * b.cap and b.cap == 16
