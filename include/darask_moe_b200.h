@@ -213,7 +213,7 @@ int tsumuji_ep_combine(float* out, const float* y_home, const float* rw, const u
  * hayate_glm_grouped_packed_set_config, packed_grouped.cu:269,315-318).  The expert launchers need scratch for the
  * fp16 activation planes and the routing plan: register it once per host thread with hayate_glm_moe_set_workspace
  * (hayate_glm_moe_workspace_bytes(hidden, inter, experts, topk, 1) bytes); the router calls work without it.
- * Only NVFP4 images (nv != 0, DenseWeight format 3) are implemented; block-FP8 images return cudaErrorInvalidValue. */
+ * NVFP4 and block-FP8 images are implemented; the combinations are listed in front of hayate_glm_moe_gate_up. */
 typedef struct { const void* data; const void* scale; unsigned format; } HayateDenseWeight;
 int hayate_glm_moe_set_shape(unsigned hidden, unsigned inter, unsigned experts, unsigned topk, float scale);
 size_t hayate_glm_moe_workspace_bytes(unsigned hidden, unsigned inter, unsigned experts, unsigned topk, unsigned tokens);
