@@ -25,9 +25,15 @@
 // into a ring of chunk slots in a fixed order (shared expert first, then the routed experts, then the down tiles);
 // while the gate/up tiles are being multiplied the ring refills with down weights, which depend on the routing only.
 // A tile is multiplied by a quad of warps that take its 256-column blocks in turn (warp k: blocks k, k + 4, ...) and
-// add their partial sums through shared memory. The block loop is bound by shared-memory wavefronts and the
-// half-rate integer pipe, not by the tensor pipe: the activation fragments of a block are loaded once into
-// registers, and the zero halves of the block-diagonal operand never travel through shared memory.
+// add their partial sums through shared memory. Inside the block loop the half-rate integer pipe that unpacks the codes
+// is the busy one, not the tensor pipe: the activation fragments of a block are loaded once into registers, and the
+// zero halves of the block-diagonal operand never travel through shared memory. (Measured on the whole kernel the
+// block loop is a small part: with it compiled out the launch is 1.3 us shorter of 24; the time from the dependency
+// wait to the first routed weight byte, about 6 us, and the per-tile hand-offs inside a quad are the larger parts.)
+//
+// Optionally the layer entry of the reference (`residual` + `rms_native`, native.cu:89-96) is part of phase R: every
+// CTA forms u = (x + attn_out) * norm_w and the sum of squares of x + attn_out itself, multiplies the router rows with
+// u and applies the norm's scale to logits and activations afterwards; CTA 0 writes n back.
 //
 // Arithmetic per 256-column block, `mma.sync.m16n8k32` on 8-bit integers (u8 weight codes x s8 activations, s32
 // accumulate; the legacy tensor path issues one such instruction per 8 cycles and scheduler, twice the weights of the
