@@ -357,3 +357,113 @@ int cpu_kogarashi_layer(const KogarashiCpu* L, int threads) {
 }
 
 int cpu_max_threads(void) { return omp_get_max_threads(); }
+
+/* ---- FP8 prefill layer on the CPU (timed baseline of the prefill workload) -----------------------------------------
+ * Block-FP8 weights (e4m3 payload [E][n][k], float32 scale per 128 x 128 block), activations quantized to e4m3 per token
+ * and 128 channels, SwiGLU product rounded to bf16 and quantized the same way, float32 rows combined in slot order:
+ * the layer of oracle/layers.py `fp8_forward`, with float32 sums instead of float64.  A weight row is decoded once and
+ * multiplied with every row routed to its expert.  The reference's own CPU expert pool (hayate crates/kernels/src/cpu/
+ * glm53.rs, cpu_experts.rs:142-393) handles block-FP8 the same way: dequantize a row, fused multiply-adds in float32. */
+typedef struct {
+  int hidden, inter, experts, topk, tokens;
+  const uint8_t* gate; const uint8_t* up; const uint8_t* down;       /* [E][n][k] */
+  const float* gate_s; const float* up_s; const float* down_s;       /* [E][n/128][k/128] */
+  const float* x; const float* logits; float* out; int* ids; float* prob;
+} Fp8Cpu;
+
+/* round to nearest even onto the e4m3 grid (saturating at 448), as a table search over the 127 positive codes */
+static uint8_t e4m3_encode(float v) {
+  const float a = fabsf(v) > 448.f ? 448.f : fabsf(v);
+  int lo = 0, hi = 126;                                   /* fp8_table[0 .. 126] ascends from 0 to 448 */
+  while (lo < hi) { const int mid = (lo + hi + 1) / 2; if (fp8_table[mid] <= a) lo = mid; else hi = mid - 1; }
+  int code = lo;
+  if (lo < 126) {
+    const float below = a - fp8_table[lo], above = fp8_table[lo + 1] - a;
+    if (above < below || (above == below && (lo & 1))) code = lo + 1;
+  }
+  return (uint8_t)(code | (v < 0 || (v == 0 && signbit(v)) ? 128 : 0));
+}
+/* rows [n][k] float32 -> their e4m3 dequantization in place (what the GEMM multiplies with) */
+static void act_quantize_dequant(float* rows, int n, int k, int threads) {
+#pragma omp parallel for num_threads(threads) schedule(static)
+  for (int r = 0; r < n; ++r)
+    for (int b = 0; b < k / 128; ++b) {
+      float* g = rows + (size_t)r * k + b * 128;
+      float amax = 0.f;
+      for (int i = 0; i < 128; ++i) amax = fmaxf(amax, fabsf(g[i]));
+      const float scale = amax == 0.f ? 1.f : amax / 448.f, inv = 1.f / scale;
+      for (int i = 0; i < 128; ++i) g[i] = fp8_table[e4m3_encode(g[i] * inv)] * scale;
+    }
+}
+static void fp8_row(const uint8_t* p, const float* s, int k, float* out) {      /* one weight row: payload and its row of block scales */
+  for (int b = 0; b < k / 128; ++b) {
+    const float sc = s[b];
+    for (int i = 0; i < 128; ++i) out[b * 128 + i] = fp8_table[p[b * 128 + i]] * sc;
+  }
+}
+static float dot_f32(const float* a, const float* b, int k) {
+  float acc[16] = {0};
+  for (int i = 0; i < k; i += 16) for (int j = 0; j < 16; ++j) acc[j] += a[i + j] * b[i + j];
+  float v = 0; for (int j = 0; j < 16; ++j) v += acc[j];
+  return v;
+}
+
+int cpu_fp8_layer(const Fp8Cpu* L, int threads) {
+  init_tables();
+  const int H = L->hidden, F = L->inter, E = L->experts, K = L->topk, T = L->tokens;
+  cpu_route_softmax_topk(L->logits, T, E, K, L->ids, L->prob);
+  int* count = (int*)calloc((size_t)E + 1, sizeof(int));
+  for (int a = 0; a < T * K; ++a) ++count[L->ids[a]];
+  int* start = (int*)malloc(((size_t)E + 1) * sizeof(int)); start[0] = 0;
+  for (int e = 0; e < E; ++e) start[e + 1] = start[e] + count[e];
+  int* fill = (int*)calloc((size_t)E, sizeof(int));
+  int* assign = (int*)malloc((size_t)T * K * sizeof(int));
+  for (int a = 0; a < T * K; ++a) { const int e = L->ids[a]; assign[start[e] + fill[e]++] = a; }
+  float* xq = (float*)malloc((size_t)T * H * 4);
+  memcpy(xq, L->x, (size_t)T * H * 4);
+  act_quantize_dequant(xq, T, H, threads);
+  float* hh = (float*)malloc((size_t)T * K * F * 4);                 /* SwiGLU products, one row per assignment */
+  float* y = (float*)malloc((size_t)T * K * H * 4);                  /* down rows, one per assignment */
+#pragma omp parallel num_threads(threads)
+  {
+    float* wg = (float*)malloc((size_t)H * 4); float* wu = (float*)malloc((size_t)H * 4);
+#pragma omp for schedule(dynamic, 64) collapse(2)
+    for (int e = 0; e < E; ++e) for (int r = 0; r < F; ++r) {
+      if (!count[e]) continue;
+      fp8_row(L->gate + ((size_t)e * F + r) * H, L->gate_s + ((size_t)e * (F / 128) + r / 128) * (H / 128), H, wg);
+      fp8_row(L->up + ((size_t)e * F + r) * H, L->up_s + ((size_t)e * (F / 128) + r / 128) * (H / 128), H, wu);
+      for (int i = 0; i < count[e]; ++i) {
+        const int a = assign[start[e] + i];
+        const float* xt = xq + (size_t)(a / K) * H;
+        const float g = dot_f32(wg, xt, H), u = dot_f32(wu, xt, H);
+        hh[(size_t)a * F + r] = bf16_round(g / (1.f + expf(-g)) * u);
+      }
+    }
+    free(wg); free(wu);
+  }
+  act_quantize_dequant(hh, T * K, F, threads);
+#pragma omp parallel num_threads(threads)
+  {
+    float* wd = (float*)malloc((size_t)F * 4);
+#pragma omp for schedule(dynamic, 64) collapse(2)
+    for (int e = 0; e < E; ++e) for (int r = 0; r < H; ++r) {
+      if (!count[e]) continue;
+      fp8_row(L->down + ((size_t)e * H + r) * F, L->down_s + ((size_t)e * (H / 128) + r / 128) * (F / 128), F, wd);
+      for (int i = 0; i < count[e]; ++i) {
+        const int a = assign[start[e] + i];
+        y[(size_t)a * H + r] = dot_f32(wd, hh + (size_t)a * F, F);
+      }
+    }
+    free(wd);
+  }
+#pragma omp parallel for num_threads(threads) schedule(static)
+  for (int t = 0; t < T; ++t)
+    for (int i = 0; i < H; ++i) {
+      float v = 0.f;
+      for (int s2 = 0; s2 < K; ++s2) v = fmaf(L->prob[t * K + s2], y[((size_t)t * K + s2) * H + i], v);
+      L->out[(size_t)t * H + i] = v;
+    }
+  free(count); free(start); free(fill); free(assign); free(xq); free(hh); free(y);
+  return 0;
+}
+

@@ -33,3 +33,21 @@ def test_simd_row_products_match_scalar_loops():
         lib.cpu_set_simd(0)
         assert np.array_equal(outs[0][1], outs[1][1])
         W.check_output(outs[1][0], outs[0][0], rel=2e-5, max_abs=2e-5)
+
+
+def test_c_fp8_layer_matches_the_numpy_oracle():
+    """`cpu_fp8_layer` (the timed CPU baseline of the prefill workload) against `oracle.layers.fp8_forward`."""
+    import bench
+    from oracle import layers as L
+    lib = ctypes.CDLL(str(build_ref.build_cpu()))
+    layer, acts = W.fp8_layer(9, 256, 128, 8, 2, 24, pool=8, zipf=1.1)
+    ref = L.fp8_forward(layer, acts["x"], acts["logits"])
+    stack = lambda mats, j: np.ascontiguousarray(np.stack([m[j] for m in mats]))
+    keep = [stack(layer.gate, 0), stack(layer.up, 0), stack(layer.down, 0), stack(layer.gate, 1), stack(layer.up, 1), stack(layer.down, 1),
+            np.ascontiguousarray(acts["x"]), np.ascontiguousarray(acts["logits"]), np.zeros((24, 256), np.float32), np.zeros((24, 2), np.int32),
+            np.zeros((24, 2), np.float32)]
+    desc = bench.Fp8Cpu(256, 128, 8, 2, 24, *[a.ctypes.data for a in keep])
+    assert lib.cpu_fp8_layer(ctypes.byref(desc), 2) == 0
+    assert np.array_equal(keep[9], ref["ids"])
+    np.testing.assert_allclose(keep[10], ref["prob"], rtol=1e-5, atol=1e-7)
+    W.check_output(keep[8], ref["out"])
