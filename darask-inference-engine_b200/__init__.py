@@ -15,6 +15,7 @@ from .fp8 import Fp8MoeLayer  # noqa: F401
 from . import fp8  # noqa: F401
 from . import ep  # noqa: F401
 from . import gguf  # noqa: F401
+from . import tsumuji_loader  # noqa: F401
 from .ep import Fp8ExpertParallelMoe, TsumujiExpertParallelMoe  # noqa: F401
 
 __all__ = ["KogarashiMoeLayer", "ggml_tensor_bytes", "nvfp4_tiled_bytes"]
