@@ -103,6 +103,52 @@ class KogarashiMoeLayer:
         _lib.check(_lib.lib().kogarashi_moe_layer(ctypes.byref(d), self._stream()), "kogarashi_moe_layer")
         return x
 
+    def forward_host(self, x_host: torch.Tensor, n_host: torch.Tensor, out_host: torch.Tensor | None = None) -> torch.Tensor:
+        """The layer for activations that live in host memory: x [T,H] and n [T,H] float32 on the CPU in, the updated
+        x on the CPU out (a pinned buffer owned by the layer unless `out_host` is given).
+
+        The two host->device copies, the layer call and the device->host copy are recorded once per token count as one
+        CUDA graph over pinned staging buffers; a call copies the inputs into the staging buffers, replays the graph
+        and waits for it. (The copies and the launch then cost one graph launch instead of four asynchronous calls.)"""
+        t = n_host.shape[0]
+        if x_host.shape != n_host.shape or n_host.shape[1] != self.hidden or t > self.max_tokens:
+            raise ValueError("token count / shape")
+        if x_host.dtype != torch.float32 or n_host.dtype != torch.float32 or x_host.is_cuda or n_host.is_cuda:
+            raise ValueError("x_host and n_host must be float32 CPU tensors")
+        plan = self._host_plans.get(t) if hasattr(self, "_host_plans") else None
+        if plan is None:
+            if not hasattr(self, "_host_plans"):
+                self._host_plans = {}
+            pin = lambda: torch.empty((t, self.hidden), dtype=torch.float32).pin_memory()
+            plan = dict(pin_x=pin(), pin_n=pin(), pin_out=pin(), dx=torch.empty((t, self.hidden), device=self.device),
+                        dn=torch.empty((t, self.hidden), device=self.device), graph=torch.cuda.CUDAGraph())
+            plan["pin_x"].copy_(x_host)
+            plan["pin_n"].copy_(n_host)
+
+            def record():
+                plan["dn"].copy_(plan["pin_n"], non_blocking=True)
+                plan["dx"].copy_(plan["pin_x"], non_blocking=True)
+                self.forward(plan["dx"], plan["dn"])
+                plan["pin_out"].copy_(plan["dx"], non_blocking=True)
+
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                record()                                   # once outside the capture: function attributes, lazy state
+                side.synchronize()
+                with torch.cuda.graph(plan["graph"], stream=side):
+                    record()
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            self._host_plans[t] = plan
+        plan["pin_x"].copy_(x_host)
+        plan["pin_n"].copy_(n_host)
+        plan["graph"].replay()
+        torch.cuda.current_stream(self.device).synchronize()
+        if out_host is not None:
+            out_host.copy_(plan["pin_out"])
+            return out_host
+        return plan["pin_out"]
+
     def status(self) -> int:
         out = ctypes.c_uint(0)
         _lib.check(_lib.lib().kogarashi_moe_status(self.workspace.data_ptr(), ctypes.byref(out), self._stream()), "status")
