@@ -105,3 +105,24 @@ def test_fixed_point_rows_against_float64(ty, kind):
     err = np.linalg.norm(got - exact) / np.linalg.norm(exact)
     # a tenth of the layer tolerance (1e-3), whatever the shape of the activations
     assert err < 1e-4, err
+
+
+def test_nvfp4_code_times_scale_is_exact_in_fp16_and_bf16():
+    """The packed NVFP4 grouped GEMM multiplies e2m1 code by e4m3 block scale in fp16 and stores bf16 in front of the
+    tensor core (csrc/grouped_nvfp4.cuh `expand8`): every one of the 16 x 254 finite products must be exactly
+    representable in both, so that the tile holds the same weights the reference decodes (packed_grouped.cu:103-108)."""
+    codes = F.E2M1_TABLE.astype(np.float64)                                  # 16 signed values
+    scales = F.e4m3_decode(np.arange(256, dtype=np.uint8)).astype(np.float64)
+    scales = scales[np.isfinite(scales)]
+    prod = codes[:, None] * scales[None, :]
+    assert np.array_equal(prod.astype(np.float16).astype(np.float64), prod)
+    assert np.array_equal(F.bf16_round(prod.astype(np.float32)).astype(np.float64), prod)
+
+
+def test_tags_of_the_one_token_kernel():
+    """`make_tag` (csrc/decode_fused.cuh): the tag of a call is never zero (a cleared workspace) and never the bit pattern of
+    -0.0f, and consecutive calls differ."""
+    tag = lambda epoch: (0x80000001 + epoch % 0x7FFFFFFE) & 0xFFFFFFFF
+    for e in (0, 1, 2, 0x7FFFFFFD, 0x7FFFFFFE, 0x7FFFFFFF, 0xFFFFFFFE, 0xFFFFFFFF):
+        assert tag(e) not in (0, 0x80000000) and tag(e) >> 31 == 1
+        assert tag(e) != tag((e + 1) & 0xFFFFFFFF)
