@@ -219,9 +219,6 @@ __global__ void __launch_bounds__(kGnThreads, 1) grouped_nvfp4_kernel(const GnAr
       int ntile = tile, nkb = kb + 1;
       if (nkb == kblocks) { nkb = 0; ntile += gridDim.x; }
       const bool more = ntile < total;
-      const G8Tile t_now = t;
-      const int kb_now = kb;
-      (void)kb_now;
       if (more) {
         if (ntile != tile) { tile = ntile; kb = 0; open_tile(); } else { kb = nkb; }
         fetch(nxt);
@@ -232,7 +229,6 @@ __global__ void __launch_bounds__(kGnThreads, 1) grouped_nvfp4_kernel(const GnAr
       got = __shfl_sync(0xffffffffu, got, 0);
       if (!got || abort_flag) { abort_flag = 1; break; }
       const uint32_t wt = smem_u32(smem + s * kGbStageBytes) + 128 * 128;
-      (void)t_now;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int hidx = j * 128 + et, r = hidx >> 1, half = hidx & 1;
@@ -257,7 +253,6 @@ __global__ void __launch_bounds__(kGnThreads, 1) grouped_nvfp4_kernel(const GnAr
   } else {
     // ---- epilogue: thread = one row of the tile; warps 4-7 take the first half of the output columns, 8-11 the second ----
     const int quarter = warp & 3, half = (warp - 4) >> 2;
-    const int row_in_tile = quarter * 32 + lane;
     uint8_t* my_stage = store_stage + (warp - 4) * 32 * kGnPitch;
     const uint32_t tlane = tmem_base + (uint32_t(quarter * 32) << 16);
     int tile_it = 0;
@@ -312,7 +307,6 @@ __global__ void __launch_bounds__(kGnThreads, 1) grouped_nvfp4_kernel(const GnAr
         }
         __syncwarp();
       }
-      (void)row_in_tile;
       tmem_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty + buf);
