@@ -16,6 +16,7 @@ from . import fp8  # noqa: F401
 from . import ep  # noqa: F401
 from . import gguf  # noqa: F401
 from . import tsumuji_loader  # noqa: F401
+from . import hyt  # noqa: F401
 from .ep import Fp8ExpertParallelMoe, TsumujiExpertParallelMoe  # noqa: F401
 
 __all__ = ["KogarashiMoeLayer", "ggml_tensor_bytes", "nvfp4_tiled_bytes"]
