@@ -218,9 +218,10 @@ def expert_image(f: HytFile, expert: int) -> np.ndarray:
     return mlp_image(f, f"mlp.experts.{expert}")
 
 
-def layer_images(f: HytFile, experts: int) -> np.ndarray:
-    """uint8 [experts, image bytes]: what `HayateMoeLayer.load` takes as `images` (all experts resident)."""
-    images = [expert_image(f, e) for e in range(experts)]
+def layer_images(f: HytFile, experts: int, first: int = 0) -> np.ndarray:
+    """uint8 [experts, image bytes] of experts [first, first + experts): what `HayateMoeLayer.load` takes as `images`
+    (all experts resident), or one rank's block of an expert-parallel group."""
+    images = [expert_image(f, first + e) for e in range(experts)]
     if len({im.size for im in images}) != 1:
         raise ValueError("expert images of one layer differ in size")
     return np.stack(images)

@@ -81,8 +81,9 @@ def _check(a, name, dtype, shape):
     return a
 
 
-def pack_experts(tensors, prefix: str, experts: int, hidden: int, inter: int):
-    """Routed experts under `prefix` (`...layers.<l>.mlp.experts`) -> (uint8 [experts * stride], float32 [experts, 3])."""
+def pack_experts(tensors, prefix: str, experts: int, hidden: int, inter: int, first: int = 0):
+    """Routed experts [first, first + experts) under `prefix` (`...layers.<l>.mlp.experts`) ->
+    (uint8 [experts * stride], float32 [experts, 3]); a rank of an expert-parallel group packs its own block only."""
     f, h = inter, hidden
     fh = f * h
     stride = expert_stride(h, f)
@@ -93,7 +94,7 @@ def pack_experts(tensors, prefix: str, experts: int, hidden: int, inter: int):
     for e in range(experts):
         base = e * stride
         for pi, (proj, (rows, cols, co, so)) in enumerate(zip(PROJECTIONS, layout)):
-            p = f"{prefix}.{e}.{proj}"
+            p = f"{prefix}.{first + e}.{proj}"
             w = _get(tensors, f"{p}.weight_packed")
             packed = w is not None
             if not packed:

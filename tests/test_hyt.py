@@ -127,6 +127,7 @@ def test_layer_images_from_reference_written_file():
             assert np.isfinite(w).all() and 0.01 < np.abs(w).max() < 1.0          # weights were drawn with std 0.05
     with pytest.raises(KeyError):
         H.expert_image(f, 2)
+    assert np.array_equal(H.layer_images(f, 1, first=1), want["images"][1:])          # one rank's block of experts
     assert np.array_equal(H.mlp_image(f, "mlp.shared_experts"), want["shared"])
     router = H.plain_tensor(f, "mlp.gate.weight")
     assert router.shape == (2, 64) and router.dtype == np.float32 and 0 < np.abs(router).max() < 1

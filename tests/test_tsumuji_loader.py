@@ -48,6 +48,18 @@ def test_pack_experts_gives_the_oracle_block(style, csf):
         np.testing.assert_allclose(got, gs, rtol=2e-7)
 
 
+def test_pack_experts_of_one_rank_is_a_slice_of_the_whole():
+    """Expert parallelism: rank g packs experts [g*E/G, (g+1)*E/G); the blocks are the same bytes as in the whole buffer."""
+    import darask_inference_engine_b200 as D
+    tensors, blocks, gs = checkpoint(4, 256, 128, "modelopt", False)
+    stride = D.tsumuji_loader.expert_stride(256, 128)
+    for rank in range(2):
+        buf, got = D.tsumuji_loader.pack_experts(tensors, "model.layers.0.mlp.experts", 2, 256, 128, first=2 * rank)
+        assert np.array_equal(buf, blocks[2 * rank * stride:(2 * rank + 2) * stride]) and np.array_equal(got, gs[2 * rank:2 * rank + 2])
+    with pytest.raises(KeyError):
+        D.tsumuji_loader.pack_experts(tensors, "model.layers.0.mlp.experts", 2, 256, 128, first=3)
+
+
 def test_csf_scales_round_trip_with_exceptions_and_wrapping():
     import darask_inference_engine_b200 as D
     rng = np.random.default_rng(5)
