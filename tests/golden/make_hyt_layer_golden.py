@@ -4,8 +4,9 @@ hayate_tools/glm53_convert.py composes a file) and the NVFP4 / FP8 tensor bytes 
 The expected expert images are put together here tensor by tensor (gate, up, down, each at the next multiple of
 256 bytes) so that the test has them independently of the library's assembly.
 
-The reference's own golden file for the container (engines/hayate/python-tools/tests/golden.hyt, the one its Rust
-and Python tests share) is carried over unchanged as reference_golden.hyt.
+The header and tensor table of the reference's own golden file for the container (engines/hayate/python-tools/tests/
+golden.hyt, the one its Rust and Python tests share) are recorded as `golden_head`; everything else in that file is
+zero padding and the three tensors whose bytes the reference's Rust test states, so the test rebuilds the file.
 
 Run where a reference checkout exists:  python tests/golden/make_hyt_layer_golden.py [ref]
 """
@@ -73,11 +74,16 @@ for e in range(EXPERTS):
         img += raw + b"\0" * (-len(raw) % 256)
     images.append(np.frombuffer(img, np.uint8))
 shared = b"".join(weights[f"mlp.shared_experts.{stem}_proj.weight"].tobytes().ljust(1792, b"\0") for stem in ("gate", "up", "down"))
-np.savez_compressed(os.path.join(here, "hyt_layer_expected.npz"), images=np.stack(images), shared=np.frombuffer(shared, np.uint8),
+gold = open(os.path.join(ref, "engines/hayate/python-tools/tests/golden.hyt"), "rb").read()
+head_len = max(i for i in range(4096) if gold[i]) + 1
+data = {4096: bytes([0x00, 0x38, 0xB8, 0x7E, 0, 0, 0x80, 0x3F]), 8192: bytes([0x00, 0x38]), 12288: bytes([0, 0, 0x80, 0x3F])}
+rebuilt = bytearray(len(gold))
+rebuilt[:head_len] = gold[:head_len]
+for at, raw in data.items():
+    rebuilt[at:at + len(raw)] = raw
+assert bytes(rebuilt) == gold and len(gold) == 12292
+np.savez_compressed(os.path.join(here, "hyt_layer_expected.npz"), golden_head=np.frombuffer(gold[:head_len], np.uint8), images=np.stack(images), shared=np.frombuffer(shared, np.uint8),
                     names=np.array([e[0] for e in entries]), offsets=np.array([base + e[3] for e in entries]),
                     sizes=np.array([e[4] for e in entries]), tags=np.array([e[2] for e in entries]),
                     source_hash=np.frombuffer(digest[:16], np.uint8))
-with open(os.path.join(ref, "engines/hayate/python-tools/tests/golden.hyt"), "rb") as src, \
-        open(os.path.join(here, "reference_golden.hyt"), "wb") as dst:
-    dst.write(src.read())
 print(os.path.getsize(path), np.stack(images).shape)

@@ -1,6 +1,7 @@
 """`.hyt` container reader and the assembly of expert images (`darask_inference_engine_b200.hyt`).
 
-Pinned on two files: the reference's own golden (python-tools/tests/golden.hyt, with the values its Rust test
+Pinned on two files: the reference's own golden (python-tools/tests/golden.hyt, rebuilt from its recorded header and
+table; with the values its Rust test
 `shared_python_golden_loads_and_reads` asserts, common/core/src/hyt.rs:528-557, and the mutations of
 `file_rejects_...`, hyt.rs:660-676) and a small layer file written with the reference's Python tools
 (tests/golden/make_hyt_layer_golden.py). The image layout follows glm53/experts.rs `read_image`."""
@@ -20,9 +21,23 @@ def hyt():
     return D.hyt
 
 
-def test_reference_golden_file():
+def reference_golden() -> bytes:
+    """The reference's golden file: its header and table as recorded from the file, zero padding, and the three tensors
+    with the bytes its Rust test states (hyt.rs:546-551); 12292 bytes."""
+    head = np.load(os.path.join(GOLD, "hyt_layer_expected.npz"))["golden_head"].tobytes()
+    raw = bytearray(12292)
+    raw[:len(head)] = head
+    raw[4096:4104] = bytes([0x00, 0x38, 0xB8, 0x7E, 0, 0, 0x80, 0x3F])
+    raw[8192:8194] = bytes([0x00, 0x38])
+    raw[12288:12292] = struct.pack("<f", 1.0)
+    return bytes(raw)
+
+
+def test_reference_golden_file(tmp_path):
     H = hyt()
-    f = H.HytFile(os.path.join(GOLD, "reference_golden.hyt"), machine=0)
+    path = tmp_path / "golden.hyt"
+    path.write_bytes(reference_golden())
+    f = H.HytFile(path, machine=0)
     assert f.source_hash.hex() == "c5e8ba63157fbff9984d1f11bc7ac56a"
     got = [(e.name, e.quant, e.shape, e.offset - 4096, e.nbytes) for e in f.entries]
     assert got == [("重み", (H.TAG_PER_TENSOR, 3, 0), (2, 2), 0, 8), ("half", (H.TAG_PLAIN, 2, 0), (), 4096, 2),
@@ -31,7 +46,7 @@ def test_reference_golden_file():
     assert bytes(f.read("half")) == bytes([0x00, 0x38])
     assert bytes(f.read("float")) == struct.pack("<f", 1.0)
     with pytest.raises(ValueError):
-        H.HytFile(os.path.join(GOLD, "reference_golden.hyt"), machine=1)       # converted for the other machine
+        H.HytFile(path, machine=1)       # converted for the other machine
     whole = bytes(f.read("重み"))
     for a in range(9):
         for b in range(a, 9):
@@ -49,7 +64,7 @@ def test_reference_golden_file():
     (0, "<I", 0), (4, "<I", 1), (8, "<I", 2), (12, "<I", 2 ** 32 - 1), (16, "<Q", 4080), (24, "<Q", 16384),
     (106, "<Q", 12288), (106, "<Q", 2 ** 64 - 4096), (146, "<Q", 0), (114, "<Q", 9)])
 def test_reference_golden_mutations_are_rejected(tmp_path, at, fmt, value):
-    raw = bytearray(open(os.path.join(GOLD, "reference_golden.hyt"), "rb").read())
+    raw = bytearray(reference_golden())
     struct.pack_into(fmt, raw, at, value)
     p = tmp_path / "bad.hyt"
     p.write_bytes(raw)
@@ -58,7 +73,7 @@ def test_reference_golden_mutations_are_rejected(tmp_path, at, fmt, value):
 
 
 def test_truncated_files_are_rejected(tmp_path):
-    raw = open(os.path.join(GOLD, "reference_golden.hyt"), "rb").read()
+    raw = reference_golden()
     for n in (0, 63, 4095, len(raw) - 1):
         p = tmp_path / f"t{n}.hyt"
         p.write_bytes(raw[:n])
