@@ -23,6 +23,7 @@ def test_reference_arm_line(workload, steps):
     assert line["impl"] == "reference" and line["metric"] == "MoE layer tokens/s" and line["unit"] == "tokens/s"
     assert line["value"] > 0 and line["higher_is_better"] is True and line["n_gpus"] == 1 and line["vs_baseline"] is None
     assert line["config"]["workload"] == workload
+    assert line["steps"] == int(steps) and line["warmup"] == 1          # exactly the steps asked for are timed
     base = line["cpu_baseline"]
     assert base["kind"] == "port" and base["cores"] >= 1 and base["value"] == line["value"] and "oracle/cpu_moe.c" in base["sample"]
     assert {c["cores"] for c in base["thread_counts"]} <= {base["cores"], min(8, base["cores"]), *[c["cores"] for c in base["thread_counts"]]}
