@@ -467,3 +467,223 @@ int cpu_fp8_layer(const Fp8Cpu* L, int threads) {
   return 0;
 }
 
+
+/* ---- Hayate-shaped whole layer on NVFP4 images: the reference's CPU expert path --------------------------------------
+ * The one CPU implementation of this path that the reference has (hayate crates/kernels/src/cpu/glm53.rs:192-260 row
+ * products, :700-760 work on a range of rows, :760-967 the pool; crates/models/src/glm53/cpu_experts.rs:142-393 the two
+ * dispatches).  What it does, restated: activations bf16 -> float32 once, with a second copy in which every 16 columns
+ * are stored as their 8 even then their 8 odd columns (the low and the high nibbles of the 8 weight bytes); a weight row
+ * is never decoded to memory: per 16-column block the nibbles go through a 16-entry table of 2 * e2m1 to integers, then
+ * floats, the block's sum for every activation row (at most four share one pass over the weights) is multiplied by the
+ * block's e4m3 scale, and the row total by global * 0.5; gate and up rows of one expert are produced together and leave
+ * as swiglu(bf16(g), bf16(u)); rows are claimed 128 at a time by whichever thread is free.  Around it, for a whole
+ * layer: the router projection and selection (cu/glm53/decode.cu:18-31), the shared expert with bf16-rounded weights
+ * (decode.cu:44-45, 52) and the sum in ascending expert id with a bf16 rounding per add (decode.cu:55-59). */
+typedef struct {
+  int hidden, inter, experts, topk, tokens;
+  float scale;
+  const uint16_t* router;                    /* bf16 [E][H] */
+  const float* bias;                         /* [E], selection only */
+  const uint8_t* images;                     /* [E][3 * stride]: gate | up | down, NVFP4 with tiled scales */
+  size_t stride;
+  const uint8_t* shared;                     /* [3 * stride], nullable */
+  const uint16_t* x;                         /* bf16 [T][H] */
+  uint16_t* out;                             /* bf16 [T][H] */
+  float* logits; int* ids; float* weights;   /* [T][E], [T][k], [T][k] */
+} HayateCpu;
+
+static inline uint16_t bf16_bits(float x) { uint32_t u; x = bf16_round(x); memcpy(&u, &x, 4); return (uint16_t)(u >> 16); }
+
+/* every 16 columns: even columns, then odd columns */
+static void split_even_odd(const float* x, float* out, int k) {
+  for (int c = 0; c < k; c += 16)
+    for (int i = 0; i < 8; ++i) { out[c + i] = x[c + 2 * i]; out[c + 8 + i] = x[c + 2 * i + 1]; }
+}
+
+typedef struct { const uint8_t* codes; const uint8_t* scales; float global; int n, k, cols; } Nv4;   /* one tiled NVFP4 matrix */
+static Nv4 nv4_view(const uint8_t* image, int n, int k) {
+  Nv4 m; m.codes = image; m.n = n; m.k = k; m.cols = (k / 16 + 3) / 4 * 4;
+  m.scales = image + (size_t)n * k / 2;
+  memcpy(&m.global, m.scales + (size_t)((n + 127) / 128 * 128) * m.cols, 4);
+  return m;
+}
+static inline size_t nv4_scale_at(const Nv4* m, int r, int block) {
+  return ((size_t)(r / 128) * (m->cols / 4) + block / 4) * 512 + (r % 32) * 16 + (r % 128 / 32) * 4 + block % 4;
+}
+
+/* One weight row times `rows` (<= 4) activation rows given in even/odd order at stride k.  ROUNDED: every weight is
+ * rounded to bf16 after its two scales are applied (the shared expert), so the scale cannot be taken out of the sum. */
+__attribute__((target("avx2,fma"))) static void nv4_row_avx2(const Nv4* m, int r, const float* xs, int rows, int rounded, float* out) {
+  const __m128i table = _mm_setr_epi8(0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12);
+  const __m128i low = _mm_set1_epi8(15);
+  const uint8_t* codes = m->codes + (size_t)r * (m->k / 2);
+  __m256 acc[4] = {_mm256_setzero_ps(), _mm256_setzero_ps(), _mm256_setzero_ps(), _mm256_setzero_ps()};
+  for (int b = 0; b < m->k / 16; ++b) {
+    const __m128i bytes = _mm_loadl_epi64((const __m128i*)(codes + b * 8));
+    const __m128i even = _mm_shuffle_epi8(table, _mm_and_si128(bytes, low));
+    const __m128i odd = _mm_shuffle_epi8(table, _mm_and_si128(_mm_srli_epi16(bytes, 4), low));
+    __m256 we = _mm256_cvtepi32_ps(_mm256_cvtepi8_epi32(even)), wo = _mm256_cvtepi32_ps(_mm256_cvtepi8_epi32(odd));
+    const float s = fp8_table[m->scales[nv4_scale_at(m, r, b)]];
+    if (rounded) {
+      const __m256 mult = _mm256_set1_ps(s * m->global * 0.5f);
+      const __m256i half = _mm256_set1_epi32(0x7fff), one = _mm256_set1_epi32(1), keep = _mm256_set1_epi32((int)0xffff0000u);
+      __m256i ue = _mm256_castps_si256(_mm256_mul_ps(we, mult)), uo = _mm256_castps_si256(_mm256_mul_ps(wo, mult));
+      ue = _mm256_and_si256(_mm256_add_epi32(ue, _mm256_add_epi32(half, _mm256_and_si256(_mm256_srli_epi32(ue, 16), one))), keep);
+      uo = _mm256_and_si256(_mm256_add_epi32(uo, _mm256_add_epi32(half, _mm256_and_si256(_mm256_srli_epi32(uo, 16), one))), keep);
+      we = _mm256_castsi256_ps(ue); wo = _mm256_castsi256_ps(uo);
+      for (int t = 0; t < rows; ++t) {
+        const float* x = xs + (size_t)t * m->k + b * 16;
+        acc[t] = _mm256_fmadd_ps(we, _mm256_loadu_ps(x), acc[t]);
+        acc[t] = _mm256_fmadd_ps(wo, _mm256_loadu_ps(x + 8), acc[t]);
+      }
+    } else {
+      const __m256 sv = _mm256_set1_ps(s);
+      for (int t = 0; t < rows; ++t) {
+        const float* x = xs + (size_t)t * m->k + b * 16;
+        const __m256 block = _mm256_fmadd_ps(wo, _mm256_loadu_ps(x + 8), _mm256_mul_ps(we, _mm256_loadu_ps(x)));
+        acc[t] = _mm256_fmadd_ps(sv, block, acc[t]);
+      }
+    }
+  }
+  for (int t = 0; t < rows; ++t) out[t] = hsum8(acc[t]) * (rounded ? 1.f : m->global * 0.5f);
+}
+/* the same sums without vector instructions */
+static void nv4_row_scalar(const Nv4* m, int r, const float* xs, int rows, int rounded, float* out) {
+  static const int twice[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12};
+  const uint8_t* codes = m->codes + (size_t)r * (m->k / 2);
+  float total[4] = {0, 0, 0, 0};
+  for (int b = 0; b < m->k / 16; ++b) {
+    const float s = fp8_table[m->scales[nv4_scale_at(m, r, b)]];
+    for (int t = 0; t < rows; ++t) {
+      const float* x = xs + (size_t)t * m->k + b * 16;
+      float block = 0.f;
+      for (int i = 0; i < 8; ++i) {
+        float we = (float)twice[codes[b * 8 + i] & 15], wo = (float)twice[codes[b * 8 + i] >> 4];
+        if (rounded) { we = bf16_round(we * (s * m->global * 0.5f)); wo = bf16_round(wo * (s * m->global * 0.5f)); }
+        block += we * x[i] + wo * x[8 + i];
+      }
+      total[t] += rounded ? block : s * block;
+    }
+  }
+  for (int t = 0; t < rows; ++t) out[t] = total[t] * (rounded ? 1.f : m->global * 0.5f);
+}
+static inline void nv4_row(const Nv4* m, int r, const float* xs, int rows, int rounded, float* out) {
+  if (simd_enabled) nv4_row_avx2(m, r, xs, rows, rounded, out); else nv4_row_scalar(m, r, xs, rows, rounded, out);
+}
+
+static inline float hayate_swiglu(float gate, float up) {     /* math.cuh:31-34 on bf16 inputs */
+  gate = gate < 10.f ? gate : 10.f;
+  up = up < -10.f ? -10.f : up > 10.f ? 10.f : up;
+  return bf16_round(bf16_round(gate / (1.f + expf(-gate))) * up);
+}
+
+/* a group of at most four activation rows that meet the same expert image */
+typedef struct { const uint8_t* image; int rounded; int rows; int first; } HayateJob;   /* first: index of its rows in the row buffers */
+
+int cpu_hayate_layer(const HayateCpu* L, int threads) {
+  init_tables();
+  const int H = L->hidden, F = L->inter, E = L->experts, K = L->topk, T = L->tokens;
+  if (H % 16 || F % 16 || K > 32 || K > E || T < 1) return -1;
+  const int per_token = K + (L->shared ? 1 : 0);
+  /* activations: float32, and the even/odd copy */
+  float* xf = (float*)malloc((size_t)T * H * 4);
+  float* xs = (float*)malloc((size_t)T * H * 4);
+  for (size_t i = 0; i < (size_t)T * H; ++i) xf[i] = bf16_to_float(L->x[i]);
+  for (int t = 0; t < T; ++t) split_even_odd(xf + (size_t)t * H, xs + (size_t)t * H, H);
+  /* router projection and selection */
+#pragma omp parallel for num_threads(threads) schedule(static)
+  for (int e = 0; e < E; ++e)
+    for (int t = 0; t < T; ++t) {
+      float acc[16] = {0};
+      const uint16_t* w = L->router + (size_t)e * H; const float* x = xf + (size_t)t * H;
+      for (int i = 0; i < H; i += 16) for (int j = 0; j < 16; ++j) acc[j] += bf16_to_float(w[i + j]) * x[i + j];
+      float s = 0; for (int j = 0; j < 16; ++j) s += acc[j];
+      L->logits[(size_t)t * E + e] = s;
+    }
+  for (int t = 0; t < T; ++t) {
+    const float* lg = L->logits + (size_t)t * E;
+    int* ids = L->ids + (size_t)t * K; float* w = L->weights + (size_t)t * K;
+    float total = 0.f;
+    for (int s = 0; s < K; ++s) {
+      int best = -1; float key = 0.f, score = 0.f;
+      for (int e = 0; e < E; ++e) {
+        int taken = 0; for (int q = 0; q < s; ++q) taken |= ids[q] == e;
+        if (taken) continue;
+        const float sc = 1.f / (1.f + expf(-lg[e])), v = sc + L->bias[e];
+        if (best < 0 || v > key) { best = e; key = v; score = sc; }
+      }
+      ids[s] = best; w[s] = score; total += score;
+    }
+    for (int s = 0; s < K; ++s) w[s] = w[s] / (total + 1e-20f) * L->scale;
+  }
+  /* jobs: per expert the (token, slot) pairs that chose it, four at a time; the shared expert takes every token */
+  const int pairs = T * per_token;
+  int* pair_of_row = (int*)malloc((size_t)pairs * sizeof(int));        /* row buffer index -> token * per_token + slot */
+  HayateJob* jobs = (HayateJob*)malloc((size_t)pairs * sizeof(HayateJob));
+  int njobs = 0, nrows = 0;
+  for (int e = 0; e <= E; ++e) {
+    if (e == E && !L->shared) break;
+    int open = 0;
+    for (int t = 0; t < T; ++t)
+      for (int s = 0; s < per_token; ++s) {
+        const int hit = e == E ? s == K : (s < K && L->ids[(size_t)t * K + s] == e);
+        if (!hit) continue;
+        if (!open) { jobs[njobs].image = e == E ? L->shared : L->images + (size_t)e * 3 * L->stride; jobs[njobs].rounded = e == E;
+                     jobs[njobs].rows = 0; jobs[njobs].first = nrows; ++njobs; }
+        pair_of_row[nrows++] = t * per_token + s;
+        open = ++jobs[njobs - 1].rows < 4;
+      }
+  }
+  float* in = (float*)malloc((size_t)nrows * H * 4);        /* even/odd activations of every job row */
+  float* act = (float*)malloc((size_t)nrows * F * 4);
+  float* acts = (float*)malloc((size_t)nrows * F * 4);
+  float* y = (float*)malloc((size_t)nrows * H * 4);
+  for (int r = 0; r < nrows; ++r) memcpy(in + (size_t)r * H, xs + (size_t)(pair_of_row[r] / per_token) * H, (size_t)H * 4);
+  /* dispatch 1: gate and up rows together, 128 rows per claim */
+  const int chunks1 = (F + 127) / 128, chunks2 = (H + 127) / 128;
+#pragma omp parallel for num_threads(threads) schedule(dynamic, 1)
+  for (int item = 0; item < njobs * chunks1; ++item) {
+    const HayateJob* j = jobs + item / chunks1;
+    const Nv4 gate = nv4_view(j->image, F, H), up = nv4_view(j->image + L->stride, F, H);
+    const int r0 = item % chunks1 * 128, r1 = r0 + 128 < F ? r0 + 128 : F;
+    float g[4], u[4];
+    for (int r = r0; r < r1; ++r) {
+      nv4_row(&gate, r, in + (size_t)j->first * H, j->rows, j->rounded, g);
+      nv4_row(&up, r, in + (size_t)j->first * H, j->rows, j->rounded, u);
+      for (int m = 0; m < j->rows; ++m) act[(size_t)(j->first + m) * F + r] = hayate_swiglu(bf16_round(g[m]), bf16_round(u[m]));
+    }
+  }
+  for (int r = 0; r < nrows; ++r) split_even_odd(act + (size_t)r * F, acts + (size_t)r * F, F);
+  /* dispatch 2: down rows */
+#pragma omp parallel for num_threads(threads) schedule(dynamic, 1)
+  for (int item = 0; item < njobs * chunks2; ++item) {
+    const HayateJob* j = jobs + item / chunks2;
+    const Nv4 down = nv4_view(j->image + 2 * L->stride, H, F);
+    const int r0 = item % chunks2 * 128, r1 = r0 + 128 < H ? r0 + 128 : H;
+    float d[4];
+    for (int r = r0; r < r1; ++r) {
+      nv4_row(&down, r, acts + (size_t)j->first * F, j->rows, j->rounded, d);
+      for (int m = 0; m < j->rows; ++m) y[(size_t)(j->first + m) * H + r] = bf16_round(d[m]);
+    }
+  }
+  /* sum per token: routed experts in ascending expert id, a bf16 rounding after every add, the shared expert last */
+  int* row_of_pair = (int*)malloc((size_t)pairs * sizeof(int));
+  for (int r = 0; r < nrows; ++r) row_of_pair[pair_of_row[r]] = r;
+#pragma omp parallel for num_threads(threads) schedule(static)
+  for (int t = 0; t < T; ++t) {
+    int order[32];
+    const int* ids = L->ids + (size_t)t * K;
+    for (int i = 0; i < K; ++i) { int v = i, q = i; while (q && ids[order[q - 1]] > ids[v]) { order[q] = order[q - 1]; --q; } order[q] = v; }
+    for (int c = 0; c < H; ++c) {
+      float acc = 0.f;
+      for (int i = 0; i < K; ++i) {
+        const int s = order[i];
+        acc = bf16_round(acc + bf16_round(y[(size_t)row_of_pair[t * per_token + s] * H + c] * L->weights[(size_t)t * K + s]));
+      }
+      if (L->shared) acc = bf16_round(acc + y[(size_t)row_of_pair[t * per_token + K] * H + c]);
+      L->out[(size_t)t * H + c] = bf16_bits(acc);
+    }
+  }
+  free(row_of_pair); free(y); free(acts); free(act); free(in); free(jobs); free(pair_of_row); free(xs); free(xf);
+  return 0;
+}

@@ -51,3 +51,43 @@ def test_c_fp8_layer_matches_the_numpy_oracle():
     assert np.array_equal(keep[9], ref["ids"])
     np.testing.assert_allclose(keep[10], ref["prob"], rtol=1e-5, atol=1e-7)
     W.check_output(keep[8], ref["out"])
+
+
+def hayate_c_layer(lib, layer, x, threads=2):
+    import bench
+    t = x.shape[0]
+    keep = [bench.bf16_bits(layer.router), np.ascontiguousarray(layer.bias, np.float32), np.ascontiguousarray(layer.images),
+            np.ascontiguousarray(layer.shared), bench.bf16_bits(x), np.zeros((t, layer.hidden), np.uint16),
+            np.zeros((t, layer.experts), np.float32), np.zeros((t, layer.topk), np.int32), np.zeros((t, layer.topk), np.float32)]
+    d = bench.HayateCpu(layer.hidden, layer.inter, layer.experts, layer.topk, t, layer.scale)
+    d.router, d.bias, d.images, d.shared, d.x, d.out, d.logits, d.ids, d.weights = (a.ctypes.data for a in keep)
+    d.stride = layer.stride
+    assert lib.cpu_hayate_layer(ctypes.byref(d), threads) == 0
+    out = (keep[5].astype(np.uint32) << 16).view(np.float32)
+    return dict(out=out, logits=keep[6], ids=keep[7], weights=keep[8])
+
+
+def test_c_hayate_layer_matches_the_numpy_oracle():
+    """`cpu_hayate_layer` (the reference's CPU expert path restated in C: NVFP4 rows multiplied without decoding them to
+    memory, at most four activation rows per pass, 128-row claims, two dispatches) against `oracle.layers.hayate_forward`,
+    with vector instructions and without; 7 tokens over 8 experts so that experts meet more than four rows."""
+    from oracle import layers as L
+    lib = ctypes.CDLL(str(build_ref.build_cpu()))
+    layer, acts = W.hayate_layer(12, hidden=512, inter=384, experts=8, topk=3, tokens=7, scale=1.8, pool=8)
+    got = {}
+    for simd in (0, 1):
+        lib.cpu_set_simd(simd)
+        if simd and not lib.cpu_simd():
+            continue
+        got[simd] = hayate_c_layer(lib, layer, acts["x"])
+    lib.cpu_set_simd(0)
+    for simd, g in got.items():
+        assert np.allclose(g["logits"], L.hayate_logits(layer, acts["x"]), rtol=1e-4, atol=1e-5)
+        ref = L.hayate_forward(layer, acts["x"], logits=g["logits"], ids=g["ids"])
+        ids, _ = __import__("oracle.routing", fromlist=["x"]).route_hayate(g["logits"], layer.bias, layer.topk, layer.scale)
+        assert np.array_equal(g["ids"], ids)
+        np.testing.assert_allclose(g["weights"], ref["weights"], rtol=1e-5)
+        W.check_output(g["out"], ref["out"], rel=4e-3, max_abs=2.0 ** -7)        # bf16 roundings at float32 against float64 sums
+    if len(got) == 2:
+        assert np.array_equal(got[0]["ids"], got[1]["ids"])
+        W.check_output(got[1]["out"], got[0]["out"], rel=4e-3, max_abs=2.0 ** -7)
