@@ -500,15 +500,17 @@ static void split_even_odd(const float* x, float* out, int k) {
     for (int i = 0; i < 8; ++i) { out[c + i] = x[c + 2 * i]; out[c + 8 + i] = x[c + 2 * i + 1]; }
 }
 
-typedef struct { const uint8_t* codes; const uint8_t* scales; float global; int n, k, cols; } Nv4;   /* one tiled NVFP4 matrix */
+/* one NVFP4 matrix: scales in 128 x 4 tiles behind the codes (Hayate), or `linear`: e4m3 [n][k/16] given apart (Tsumuji) */
+typedef struct { const uint8_t* codes; const uint8_t* scales; float global; int n, k, cols, linear; } Nv4;
 static Nv4 nv4_view(const uint8_t* image, int n, int k) {
-  Nv4 m; m.codes = image; m.n = n; m.k = k; m.cols = (k / 16 + 3) / 4 * 4;
+  Nv4 m; m.codes = image; m.n = n; m.k = k; m.cols = (k / 16 + 3) / 4 * 4; m.linear = 0;
   m.scales = image + (size_t)n * k / 2;
   memcpy(&m.global, m.scales + (size_t)((n + 127) / 128 * 128) * m.cols, 4);
   return m;
 }
-static inline size_t nv4_scale_at(const Nv4* m, int r, int block) {
-  return ((size_t)(r / 128) * (m->cols / 4) + block / 4) * 512 + (r % 32) * 16 + (r % 128 / 32) * 4 + block % 4;
+static inline uint8_t nv4_scale(const Nv4* m, int r, int block) {
+  if (m->linear) return m->scales[(size_t)r * (m->k / 16) + block];
+  return m->scales[((size_t)(r / 128) * (m->cols / 4) + block / 4) * 512 + (r % 32) * 16 + (r % 128 / 32) * 4 + block % 4];
 }
 
 /* One weight row times `rows` (<= 4) activation rows given in even/odd order at stride k.  ROUNDED: every weight is
@@ -523,7 +525,7 @@ __attribute__((target("avx2,fma"))) static void nv4_row_avx2(const Nv4* m, int r
     const __m128i even = _mm_shuffle_epi8(table, _mm_and_si128(bytes, low));
     const __m128i odd = _mm_shuffle_epi8(table, _mm_and_si128(_mm_srli_epi16(bytes, 4), low));
     __m256 we = _mm256_cvtepi32_ps(_mm256_cvtepi8_epi32(even)), wo = _mm256_cvtepi32_ps(_mm256_cvtepi8_epi32(odd));
-    const float s = fp8_table[m->scales[nv4_scale_at(m, r, b)]];
+    const float s = fp8_table[nv4_scale(m, r, b)];
     if (rounded) {
       const __m256 mult = _mm256_set1_ps(s * m->global * 0.5f);
       const __m256i half = _mm256_set1_epi32(0x7fff), one = _mm256_set1_epi32(1), keep = _mm256_set1_epi32((int)0xffff0000u);
@@ -553,7 +555,7 @@ static void nv4_row_scalar(const Nv4* m, int r, const float* xs, int rows, int r
   const uint8_t* codes = m->codes + (size_t)r * (m->k / 2);
   float total[4] = {0, 0, 0, 0};
   for (int b = 0; b < m->k / 16; ++b) {
-    const float s = fp8_table[m->scales[nv4_scale_at(m, r, b)]];
+    const float s = fp8_table[nv4_scale(m, r, b)];
     for (int t = 0; t < rows; ++t) {
       const float* x = xs + (size_t)t * m->k + b * 16;
       float block = 0.f;
@@ -685,5 +687,137 @@ int cpu_hayate_layer(const HayateCpu* L, int threads) {
     }
   }
   free(row_of_pair); free(y); free(acts); free(act); free(in); free(jobs); free(pair_of_row); free(xs); free(xf);
+  return 0;
+}
+
+
+/* ---- Tsumuji-shaped whole layer: NVFP4 experts in the linear layout, float32 activations --------------------------
+ * The reference has no CPU code for this layout; the arithmetic is that of its kernels (tsumuji kernels/decode/
+ * gemv.cu:97-107, 149-157: block sums times the e4m3 scale, the row total times the matrix's global scale,
+ * silu(g) * u without clamps in float32; ops.cu:148-200 the router; ops.cu:217-223 the weighted sum plus the gated
+ * shared expert), run with the work split of the CPU expert path above. */
+typedef struct {
+  int hidden, inter, experts, topk, tokens;
+  const uint16_t* router;                    /* bf16 [E + 1][H]; row E = shared gate */
+  const uint8_t* blocks;                     /* [E][27/16 * F * H] */
+  const float* gs;                           /* [E][3] */
+  const uint16_t* shared_gu;                 /* bf16 [2F][H] */
+  const uint16_t* shared_down;               /* bf16 [H][F] */
+  const float* x;                            /* [T][H] */
+  float* out;                                /* [T][H] */
+  float* logits;                             /* [T][E + 1]; input when given_logits */
+  int given_logits;
+  int* ids; float* w; float* shared_gate;    /* [T][k], [T][k], [T] */
+} TsumujiCpu;
+
+static float bf16_row_dot(const uint16_t* w, const float* x, int k) {
+  float acc[16] = {0};
+  for (int i = 0; i < k; i += 16) for (int j = 0; j < 16; ++j) acc[j] += bf16_to_float(w[i + j]) * x[i + j];
+  float s = 0; for (int j = 0; j < 16; ++j) s += acc[j];
+  return s;
+}
+
+int cpu_tsumuji_layer(const TsumujiCpu* L, int threads) {
+  init_tables();
+  const int H = L->hidden, F = L->inter, E = L->experts, K = L->topk, T = L->tokens;
+  if (H % 16 || F % 16 || K > 32 || K > E || T < 1) return -1;
+  const size_t FH = (size_t)F * H, stride = FH * 27 / 16;
+  if (!L->given_logits) {
+#pragma omp parallel for num_threads(threads) schedule(static)
+    for (int e = 0; e <= E; ++e)
+      for (int t = 0; t < T; ++t) L->logits[(size_t)t * (E + 1) + e] = bf16_row_dot(L->router + (size_t)e * H, L->x + (size_t)t * H, H);
+  }
+#pragma omp parallel for num_threads(threads) schedule(static)
+  for (int t = 0; t < T; ++t) {
+    const float* lg = L->logits + (size_t)t * (E + 1);
+    int* ids = L->ids + (size_t)t * K; float* w = L->w + (size_t)t * K;
+    float top = lg[0]; for (int e = 1; e < E; ++e) top = lg[e] > top ? lg[e] : top;
+    double all = 0; for (int e = 0; e < E; ++e) all += (double)expf(lg[e] - top);
+    double chosen = 0;
+    for (int s = 0; s < K; ++s) {
+      int best = -1; float key = 0.f;
+      for (int e = 0; e < E; ++e) {
+        int taken = 0; for (int q = 0; q < s; ++q) taken |= ids[q] == e;
+        if (taken) continue;
+        const float v = expf(lg[e] - top);
+        if (best < 0 || v > key) { best = e; key = v; }
+      }
+      ids[s] = best; w[s] = key / (float)all; chosen += (double)w[s];
+    }
+    for (int s = 0; s < K; ++s) w[s] = w[s] / (float)chosen;
+    L->shared_gate[t] = 1.f / (1.f + expf(-lg[E]));
+  }
+  /* per expert the (token, slot) pairs that chose it, four rows per pass over the weights */
+  const int pairs = T * K;
+  int* pair_of_row = (int*)malloc((size_t)pairs * sizeof(int));
+  int* row_of_pair = (int*)malloc((size_t)pairs * sizeof(int));
+  HayateJob* jobs = (HayateJob*)malloc((size_t)pairs * sizeof(HayateJob));   /* image = the expert's block; rounded = expert id */
+  int njobs = 0, nrows = 0;
+  for (int e = 0; e < E; ++e) {
+    int open = 0;
+    for (int t = 0; t < T; ++t)
+      for (int s = 0; s < K; ++s) {
+        if (L->ids[(size_t)t * K + s] != e) continue;
+        if (!open) { jobs[njobs].image = L->blocks + (size_t)e * stride; jobs[njobs].rounded = e; jobs[njobs].rows = 0; jobs[njobs].first = nrows; ++njobs; }
+        row_of_pair[t * K + s] = nrows; pair_of_row[nrows++] = t * K + s;
+        open = ++jobs[njobs - 1].rows < 4;
+      }
+  }
+  float* in = (float*)malloc((size_t)(nrows + T) * H * 4);       /* even/odd activations: job rows, then one row per token */
+  float* act = (float*)malloc((size_t)(nrows + T) * F * 4);
+  float* acts = (float*)malloc((size_t)nrows * F * 4);
+  float* y = (float*)malloc((size_t)(nrows + T) * H * 4);
+  for (int r = 0; r < nrows; ++r) split_even_odd(L->x + (size_t)(pair_of_row[r] / K) * H, in + (size_t)r * H, H);
+  const int chunks1 = (F + 127) / 128, chunks2 = (H + 127) / 128;
+  /* dispatch 1: routed gate / up rows, and the shared expert's (dense bf16, natural column order) */
+#pragma omp parallel for num_threads(threads) schedule(dynamic, 1)
+  for (int item = 0; item < (njobs + T) * chunks1; ++item) {
+    const int r0 = item % chunks1 * 128, r1 = r0 + 128 < F ? r0 + 128 : F;
+    if (item / chunks1 >= njobs) {
+      const int t = item / chunks1 - njobs;
+      for (int r = r0; r < r1; ++r) {
+        const float g = bf16_row_dot(L->shared_gu + (size_t)r * H, L->x + (size_t)t * H, H);
+        const float u = bf16_row_dot(L->shared_gu + (size_t)(F + r) * H, L->x + (size_t)t * H, H);
+        act[(size_t)(nrows + t) * F + r] = g / (1.f + expf(-g)) * u;
+      }
+      continue;
+    }
+    const HayateJob* j = jobs + item / chunks1;
+    const float* gs = L->gs + (size_t)j->rounded * 3;
+    const Nv4 gate = {j->image, j->image + FH * 3 / 2, gs[0], F, H, 0, 1}, up = {j->image + FH / 2, j->image + FH * 3 / 2 + FH / 16, gs[1], F, H, 0, 1};
+    float g[4], u[4];
+    for (int r = r0; r < r1; ++r) {
+      nv4_row(&gate, r, in + (size_t)j->first * H, j->rows, 0, g);
+      nv4_row(&up, r, in + (size_t)j->first * H, j->rows, 0, u);
+      for (int m = 0; m < j->rows; ++m) act[(size_t)(j->first + m) * F + r] = g[m] / (1.f + expf(-g[m])) * u[m];
+    }
+  }
+  for (int r = 0; r < nrows; ++r) split_even_odd(act + (size_t)r * F, acts + (size_t)r * F, F);
+  /* dispatch 2: down rows */
+#pragma omp parallel for num_threads(threads) schedule(dynamic, 1)
+  for (int item = 0; item < (njobs + T) * chunks2; ++item) {
+    const int r0 = item % chunks2 * 128, r1 = r0 + 128 < H ? r0 + 128 : H;
+    if (item / chunks2 >= njobs) {
+      const int t = item / chunks2 - njobs;
+      for (int r = r0; r < r1; ++r) y[(size_t)(nrows + t) * H + r] = bf16_row_dot(L->shared_down + (size_t)r * F, act + (size_t)(nrows + t) * F, F);
+      continue;
+    }
+    const HayateJob* j = jobs + item / chunks2;
+    const Nv4 down = {j->image + FH, j->image + FH * 3 / 2 + FH / 8, L->gs[(size_t)j->rounded * 3 + 2], H, F, 0, 1};
+    float d[4];
+    for (int r = r0; r < r1; ++r) {
+      nv4_row(&down, r, acts + (size_t)j->first * F, j->rows, 0, d);
+      for (int m = 0; m < j->rows; ++m) y[(size_t)(j->first + m) * H + r] = d[m];
+    }
+  }
+  /* out = sum over slots (slot order) of w * y, plus gate * shared */
+#pragma omp parallel for num_threads(threads) schedule(static)
+  for (int t = 0; t < T; ++t)
+    for (int c = 0; c < H; ++c) {
+      float acc = 0.f;
+      for (int s = 0; s < K; ++s) acc = fmaf(L->w[(size_t)t * K + s], y[(size_t)row_of_pair[t * K + s] * H + c], acc);
+      L->out[(size_t)t * H + c] = fmaf(L->shared_gate[t], y[(size_t)(nrows + t) * H + c], acc);
+    }
+  free(y); free(acts); free(act); free(in); free(jobs); free(row_of_pair); free(pair_of_row);
   return 0;
 }

@@ -16,7 +16,7 @@ def run_bench(args, env=None):
     return res.stdout
 
 
-@pytest.mark.parametrize("workload,steps", [("qwen35moe_decode_t1", "4"), ("fp8_prefill", "1"), ("hayate_decode_t8", "3")])
+@pytest.mark.parametrize("workload,steps", [("qwen35moe_decode_t1", "4"), ("fp8_prefill", "1"), ("hayate_decode_t8", "3"), ("tsumuji_verify", "1")])
 def test_reference_arm_line(workload, steps):
     out = run_bench(["--impl", "reference", "--workload", workload, "--steps", steps, "--warmup", "1"])
     line = json.loads(out.strip().splitlines()[-1])

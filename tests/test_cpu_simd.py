@@ -91,3 +91,34 @@ def test_c_hayate_layer_matches_the_numpy_oracle():
     if len(got) == 2:
         assert np.array_equal(got[0]["ids"], got[1]["ids"])
         W.check_output(got[1]["out"], got[0]["out"], rel=4e-3, max_abs=2.0 ** -7)
+
+
+def test_c_tsumuji_layer_matches_the_numpy_oracle():
+    """`cpu_tsumuji_layer` (linear-layout NVFP4 experts, float32 activations, dense bf16 shared expert) against
+    `oracle.layers.tsumuji_forward`: router projection by the C code, and logits handed in."""
+    import bench
+    from oracle import layers as L
+    from oracle import routing as R
+    lib = ctypes.CDLL(str(build_ref.build_cpu()))
+    for given in (False, True):
+        layer, acts = W.tsumuji_layer(21, hidden=256, inter=128, experts=12, topk=3, tokens=9, pool=6, uniform_logits=given)
+        t, e, k = 9, layer.experts, layer.topk
+        logits = acts["logits"].copy() if given else np.zeros((t, e + 1), np.float32)
+        keep = [bench.bf16_bits(layer.router), np.ascontiguousarray(layer.blocks), np.ascontiguousarray(layer.gs, np.float32),
+                bench.bf16_bits(layer.shared_gu), bench.bf16_bits(layer.shared_down), np.ascontiguousarray(acts["x"], np.float32),
+                np.zeros((t, layer.hidden), np.float32), logits, np.zeros((t, k), np.int32), np.zeros((t, k), np.float32), np.zeros(t, np.float32)]
+        for simd in (0, 1):
+            lib.cpu_set_simd(simd)
+            d = bench.TsumujiCpu(layer.hidden, layer.inter, e, k, t)
+            d.router, d.blocks, d.gs, d.shared_gu, d.shared_down, d.x, d.out, d.logits, d.ids, d.w, d.shared_gate = (a.ctypes.data for a in keep)
+            d.given_logits = int(given)
+            assert lib.cpu_tsumuji_layer(ctypes.byref(d), 2) == 0
+            if not given:
+                assert np.allclose(logits, L.tsumuji_logits(layer, acts["x"]), rtol=1e-4, atol=1e-5)
+            ids, w, sgate = R.route_tsumuji(logits, e, k)
+            assert np.array_equal(keep[8], ids)
+            np.testing.assert_allclose(keep[9], w, rtol=1e-5)
+            np.testing.assert_allclose(keep[10], sgate, rtol=1e-6)
+            ref = L.tsumuji_forward(layer, acts["x"], logits=logits, ids=keep[8])
+            W.check_output(keep[6], ref["out"])
+    lib.cpu_set_simd(0)
